@@ -1,0 +1,421 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized projection path.
+
+Workload (N = 1): Q4_K decode GEMV, batch 1, Llama-3-8B MLP shapes — per layer gate and up
+(14336 x 4096) and down (4096 x 14336), 32 layers, activations bf16, outputs fp32.  A step is one
+pass over all 32 layers' projections: 96 weight matrices, 3.17 GB of packed blocks, so every step
+streams far more than the 126 MB L2.  Inputs are seeded synthetic tensors (N(0, 0.02) weights
+encoded to Q4_K, N(0, 1) activations); layers reuse one encoded gate/up/down set at distinct HBM
+addresses.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
+
+For N > 1 launch under torchrun; weights are split tensor-parallel (gate/up by rows, down by K
+superblocks with one all-reduce per down projection).  Rank 0 prints one JSON line.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+METRIC = "q4_k_decode_gemv_weight_bandwidth"
+UNIT = "GB/s"
+LAYERS = 32
+HIDDEN, INTER = 4096, 14336
+Q4_K = 12
+FALLBACK_HBM_GBS = 6650.0
+
+
+def peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            d = json.loads(p.read_text())
+            return float(d["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+def algorithmic_bytes(n, k, m=1, x_bytes=2, y_bytes=4):
+    return n * (k // 256) * 144 + m * k * x_bytes + m * n * y_bytes
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.samples = []
+        self._stop = threading.Event()
+        self._t = threading.Thread(target=self._run, daemon=True)
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(
+                    ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-i", str(self.index)],
+                    capture_output=True, text=True, timeout=5).stdout.strip()
+                if out:
+                    self.samples.append([c.strip() for c in out.splitlines()[0].split(",")])
+            except Exception:
+                pass
+            self._stop.wait(0.1)
+
+    def __enter__(self):
+        self._t.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        self._t.join(timeout=10)
+
+    def summary(self):
+        mhz, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for s in self.samples:
+            try:
+                mhz.append(float(s[0]))
+                mx.append(float(s[1]))
+            except Exception:
+                continue
+            for nme, v in zip(names, s[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(nme)
+        return {
+            "sm_mhz": float(np.median(mhz)) if mhz else None,
+            "sm_max_mhz": max(mx) if mx else None,
+            "reasons": sorted(reasons),
+            "samples": len(mhz),
+        }
+
+
+def dist_env():
+    return int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+
+
+# ------------------------------------------------------------------------------------------------
+# reference arm: the CPU path (integer block dots on re-quantized activations), all host threads
+# ------------------------------------------------------------------------------------------------
+
+def cpu_reference_pass(orc, mats, xs, reps):
+    """Times `reps` passes over the given (packed, n, k) matrices; returns seconds per pass."""
+    t0 = time.perf_counter()
+    for _ in range(reps):
+        for (p, n, k), x in zip(mats, xs):
+            orc.matmul_cpu(Q4_K, p, n, k, x)
+    return (time.perf_counter() - t0) / reps
+
+
+def make_host_layer(seed=0):
+    from magnitude_b200 import ggml_quant as gq
+
+    gate = gq.synth_weights(Q4_K, INTER, HIDDEN, seed)
+    up = gq.synth_weights(Q4_K, INTER, HIDDEN, seed + 1)
+    down = gq.synth_weights(Q4_K, HIDDEN, INTER, seed + 2)
+    return gate, up, down
+
+
+def run_reference(args):
+    rank, _, world = dist_env()
+    if rank != 0:
+        return
+    from oracle import oracle as orc  # the CPU restatement of the reference's path, timed here
+
+    orc.build()
+    from magnitude_b200 import ggml_quant as gq
+
+    gate, up, down = make_host_layer()
+    rng = np.random.default_rng(1)
+    xh = gq.f32_to_bf16_bits(rng.standard_normal((1, HIDDEN), dtype=np.float32)).astype(np.uint32) << 16
+    xi = gq.f32_to_bf16_bits(rng.standard_normal((1, INTER), dtype=np.float32)).astype(np.uint32) << 16
+    xh, xi = xh.view(np.float32), xi.view(np.float32)
+    # distinct copies per layer so the host caches do not hold the weights between layers
+    layers = min(LAYERS, 8)
+    mats, xs = [], []
+    for l in range(layers):
+        mats += [(gate.copy(), INTER, HIDDEN), (up.copy(), INTER, HIDDEN), (down.copy(), HIDDEN, INTER)]
+        xs += [xh, xh, xi]
+    bytes_pass = sum(algorithmic_bytes(n, k) for _, n, k in mats)
+    for _ in range(max(args.warmup, 1)):
+        cpu_reference_pass(orc, mats, xs, 1)
+    per = []
+    for _ in range(args.steps):
+        per.append(cpu_reference_pass(orc, mats, xs, 1))
+    sec = float(np.sum(per)) / len(per)
+    value = bytes_pass / sec / 1e9
+    cores = orc.num_threads()
+    sample = f"{layers} of {LAYERS} layers per step (gate, up, down each), all {cores} host threads"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3 * (LAYERS / layers),
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "u8/int32 block dots, fp32 accumulate",
+        "data": "synthetic", "config": workload_config(args.gpus),
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+def workload_config(n_gpus):
+    return {
+        "workload": "configs[1]: Q4_K decode GEMV, batch 1, Llama-3-8B MLP shapes, 32 layers per step",
+        "shapes": "gate/up 14336x4096, down 4096x14336, x bf16 1xK, y fp32",
+        "layers": LAYERS,
+        "weight_bytes_per_step": LAYERS * 3 * (INTER * HIDDEN // 256 * 144),
+        "l2": "inputs larger than L2 (3.17 GB of distinct weight buffers per step)",
+        "parallelism": f"tp{n_gpus}" if n_gpus > 1 else "single",
+    }
+
+
+# ------------------------------------------------------------------------------------------------
+# the CUDA arm
+# ------------------------------------------------------------------------------------------------
+
+def run_b200(args):
+    import torch
+
+    rank, local_rank, world = dist_env()
+    if world != args.gpus and world != 1:
+        raise SystemExit(f"--gpus {args.gpus} does not match WORLD_SIZE {world}")
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the projection path has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+
+        dist = dist_mod
+        dist.init_process_group("nccl", device_id=dev)
+
+    import magnitude_b200 as mb
+    from magnitude_b200 import ggml_quant as gq
+
+    be = mb.Backend(local_rank)
+    gate_h, up_h, down_h = make_host_layer()
+    if world > 1:
+        g0 = be.upload_shard(Q4_K, gate_h, INTER, HIDDEN, mb.SPLIT_COLUMN, rank, world, 256)
+        u0 = be.upload_shard(Q4_K, up_h, INTER, HIDDEN, mb.SPLIT_COLUMN, rank, world, 256)
+        d0 = be.upload_shard(Q4_K, down_h, HIDDEN, INTER, mb.SPLIT_ROW, rank, world)
+    else:
+        g0 = be.upload(Q4_K, gate_h, INTER, HIDDEN)
+        u0 = be.upload(Q4_K, up_h, INTER, HIDDEN)
+        d0 = be.upload(Q4_K, down_h, HIDDEN, INTER)
+    gates, ups, downs = [g0], [u0], [d0]
+    for _ in range(LAYERS - 1):
+        gates.append(g0.clone())
+        ups.append(u0.clone())
+        downs.append(d0.clone())
+    n_gu, k_d = g0.n, d0.k
+
+    rng = np.random.default_rng(1)
+    x_h = torch.from_numpy(rng.standard_normal((1, HIDDEN), dtype=np.float32)).to(torch.bfloat16)
+    x_i = torch.from_numpy(rng.standard_normal((1, INTER), dtype=np.float32)).to(torch.bfloat16)
+    x_hd = x_h.to(dev)
+    lo, hi = mb.shard_range(Q4_K, HIDDEN, INTER, mb.SPLIT_ROW, rank, world) if world > 1 else (0, INTER)
+    x_id = x_i[:, lo:hi].contiguous().to(dev)
+    y_g = torch.empty((1, n_gu), dtype=torch.float32, device=dev)
+    y_u = torch.empty((1, n_gu), dtype=torch.float32, device=dev)
+    y_d = torch.empty((1, HIDDEN), dtype=torch.float32, device=dev)
+
+    stream = torch.cuda.Stream(device=dev)
+
+    def step_device():
+        for l in range(LAYERS):
+            be.project_multi([gates[l], ups[l]], x_hd, outs=[y_g, y_u], stream=stream)
+            be.project(downs[l], x_id, out=y_d, stream=stream)
+            if world > 1:
+                with torch.cuda.stream(stream):
+                    dist.all_reduce(y_d)
+
+    launches_per_step = 2 * LAYERS
+
+    # capture one step in a CUDA graph (launch-bound inner loop); fall back to direct launches
+    graph = None
+    with torch.cuda.stream(stream):
+        step_device()
+    stream.synchronize()
+    be.sync(stream)
+    if not args.no_graph:
+        try:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream):
+                step_device()
+            graph = g
+        except Exception as exc:  # pragma: no cover - depends on driver behaviour
+            if rank == 0:
+                print(f"# graph capture unavailable ({type(exc).__name__}: {exc}); timing direct launches", file=sys.stderr)
+            graph = None
+            torch.cuda.synchronize()
+
+    def run_step():
+        if graph is not None:
+            with torch.cuda.stream(stream):
+                graph.replay()
+        else:
+            step_device()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        run_step()
+    barrier()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local_rank) as clocks:
+        barrier()
+        with torch.cuda.stream(stream):
+            ev0.record(stream)
+        for _ in range(args.steps):
+            run_step()
+        with torch.cuda.stream(stream):
+            ev1.record(stream)
+        barrier()
+        ms_total = ev0.elapsed_time(ev1)
+        # keep sampling clocks under the same load for a moment so short runs still get samples
+        t_end = time.time() + 0.6
+        while time.time() < t_end:
+            run_step()
+        torch.cuda.synchronize()
+    be.sync(stream)
+    if world > 1:
+        t = torch.tensor([ms_total], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total = float(t.item())
+    ms_step = ms_total / args.steps
+
+    # whole-job algorithmic bytes per step (all ranks): weights + activations + outputs
+    per_layer = 2 * algorithmic_bytes(INTER, HIDDEN) + algorithmic_bytes(HIDDEN, INTER)
+    bytes_step = LAYERS * per_layer
+    value = bytes_step / (ms_step * 1e-3) / 1e9
+
+    # ---- end to end through the host-buffer entry point (pinned host in, pinned host out) ----
+    xh_pin = x_h.clone().pin_memory()
+    xi_pin = x_i[:, lo:hi].contiguous().pin_memory()
+    yg_pin = torch.empty((1, n_gu), dtype=torch.float32).pin_memory()
+    yu_pin = torch.empty((1, n_gu), dtype=torch.float32).pin_memory()
+    yd_pin = torch.empty((1, HIDDEN), dtype=torch.float32).pin_memory()
+    yd_dev = torch.empty((1, HIDDEN), dtype=torch.float32, device=dev)
+
+    def step_e2e():
+        for l in range(LAYERS):
+            be.project_host_ptr([gates[l], ups[l]], xh_pin.data_ptr(), mb.TYPE_BF16, 1, HIDDEN,
+                                [yg_pin.data_ptr(), yu_pin.data_ptr()], mb.TYPE_F32, [n_gu, n_gu])
+            if world > 1:
+                # partial sums must meet before they are a result: device all-reduce, then one read back
+                xd = xi_pin.to(dev, non_blocking=True)
+                be.project(downs[l], xd, out=yd_dev)
+                dist.all_reduce(yd_dev)
+                yd_pin.copy_(yd_dev, non_blocking=True)
+                torch.cuda.current_stream().synchronize()
+            else:
+                be.project_host_ptr([downs[l]], xi_pin.data_ptr(), mb.TYPE_BF16, 1, k_d,
+                                    [yd_pin.data_ptr()], mb.TYPE_F32, [HIDDEN])
+
+    e2e_steps = max(3, min(args.steps, 10))
+    for _ in range(2):
+        step_e2e()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        step_e2e()
+    barrier()
+    e2e_s = (time.perf_counter() - t0) / e2e_steps
+    if world > 1:
+        t = torch.tensor([e2e_s], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+    e2e = {
+        "value": bytes_step / e2e_s / 1e9, "unit": UNIT,
+        "h2d_bytes_per_step": LAYERS * (HIDDEN * 2 + k_d * 2) * world,
+        "d2h_bytes_per_step": LAYERS * (2 * n_gu * 4 * world + HIDDEN * 4 * world),
+        "ms_per_step": e2e_s * 1e3,
+        "api": "b200q_matmul_multi_host per projection group (pinned host x -> device -> kernel -> pinned host y, synchronous)",
+    }
+
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+
+    peak, peak_src = peaks()
+    # dominant kernel: gemv_kernel<Q4_K, M=1>; two launch shapes per layer (gate+up fused, down),
+    # both Q4_K streaming launches — achieved = algorithmic bytes of this rank's launches / their time
+    rank_bytes = bytes_step / world
+    achieved = rank_bytes / (ms_step * 1e-3) / 1e9
+    roofline = {
+        "bound": "hbm", "kernel": "gemv_kernel<Q4_K,M=1,R=2>", "achieved": achieved, "peak": peak, "unit": "GB/s",
+        "frac": achieved / peak, "peak_source": f"of {peak_src}", "traffic": None,
+        "bytes_per_launch": rank_bytes / launches_per_step,
+        "us_per_launch": ms_step * 1e3 / launches_per_step,
+        "note": "per-rank algorithmic bytes per step / per-step device time (CUDA events on the launch stream)"
+                + ("; includes the all-reduce after each down projection" if world > 1 else ""),
+    }
+
+    cpu_baseline = None
+    if world == 1 and not args.no_cpu_baseline:
+        from oracle import oracle as orc  # CPU-baseline leg only
+
+        orc.build()
+        xh32 = x_h.float().numpy()
+        xi32 = x_i.float().numpy()
+        mats = [(gate_h, INTER, HIDDEN), (up_h, INTER, HIDDEN), (down_h, HIDDEN, INTER)]
+        xs = [xh32, xh32, xi32]
+        cpu_reference_pass(orc, mats, xs, 1)
+        reps, spent, t_start = 0, [], time.perf_counter()
+        while time.perf_counter() - t_start < 10.0 and reps < 400:
+            spent.append(cpu_reference_pass(orc, mats, xs, 1))
+            reps += 1
+        sec = float(np.median(spent))
+        cpu_baseline = {
+            "value": per_layer / sec / 1e9, "unit": UNIT, "cores": orc.num_threads(), "kind": "port",
+            "sample": f"one layer (gate, up, down) x {reps} passes, median; integer block-dot CPU path, OpenMP over rows",
+        }
+
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "u8 x s16 integer block dots (dp4a), fp32 accumulate", "data": "synthetic",
+        "config": workload_config(world), "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e,
+        "gpu_launches": launches_per_step * args.steps, "cuda_graph": graph is not None,
+        "clocks": clocks.summary(),
+    }
+    print(json.dumps(line))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", choices=["b200", "reference"], default="b200")
+    ap.add_argument("--no-graph", action="store_true", help="time direct launches instead of a CUDA graph replay")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_b200(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,203 @@
+/*
+ * b200q — GGUF block-quantized (Q8_0 / Q4_K / Q6_K) weight x activation product for
+ * NVIDIA B200 (sm_100a).  C ABI: plain pointers and sizes, no exceptions cross it.
+ *
+ * What this boundary replaces in the reference engine.  The reference (Rust) never sees
+ * a matmul: every attention QKV/O and MLP gate/up/down projection runs inside
+ *     context.decode(batch)            inference/crates/icn-engine/src/lib.rs:2264
+ * of its llama.cpp bindings, with weights placed on the device by
+ *     LlamaModel::load_from_file       inference/crates/icn-engine/src/lib.rs:972
+ * and multi-GPU placement declared by SplitMode / tensor_split
+ *     inference/crates/icn-contracts/src/lib.rs:122-124,200-205
+ *     inference/crates/icn-hardware/src/lib.rs:2568-2590.
+ * The entry points below are what an FFI crate for that path would bind: a context per
+ * device (one executor thread owns it, as design/inference/engine.md:49-50 requires of native
+ * state), weight handles that stay resident like a loaded model, and one projection call
+ * whose activation row count M is `batch.n_tokens()` (1 for decode, 1 + n_draft for
+ * speculative verify, up to n_ubatch = 512 and beyond for prefill).
+ *
+ * Conventions
+ *   - every function returns b200q_status (0 = OK); out-parameters come last;
+ *   - handles are opaque; the library owns device memory until *_destroy;
+ *   - `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream);
+ *   - a b200q_ctx is single-thread-affine; distinct contexts are independent;
+ *   - weights are W[N][K] in GGUF order: N output rows, each K/blk consecutive packed blocks;
+ *   - activations X[M][K] and outputs Y[M][N] are row-major with leading dimensions in elements.
+ *   - there is no CPU fallback: without a CUDA device every compute call fails with
+ *     B200Q_ERR_BACKEND.
+ */
+#ifndef B200Q_H
+#define B200Q_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef int32_t b200q_status;
+
+/* Error vocabulary mirrors InferenceError (inference/crates/icn-contracts/src/lib.rs:709-723)
+ * plus TIMEOUT for bounded device/host waits. */
+enum {
+    B200Q_OK = 0,
+    B200Q_ERR_INVALID_CONFIG = 1, /* bad type id, K not a block multiple, null pointer, bad shard */
+    B200Q_ERR_BACKEND = 2,        /* CUDA / NCCL failure; text in b200q_last_error */
+    B200Q_ERR_CANCELLED = 3,
+    B200Q_ERR_OVERLOADED = 4,     /* out of device memory */
+    B200Q_ERR_STOPPED = 5,        /* context already destroyed / poisoned by a device error */
+    B200Q_ERR_CALLBACK = 6,
+    B200Q_ERR_TIMEOUT = 7         /* a bounded wait ran out (host sync or device pipeline) */
+};
+
+/* ggml tensor type ids, the values GGUF files carry (gguf.rs:126 reads them as u32). */
+enum {
+    B200Q_TYPE_F32 = 0,
+    B200Q_TYPE_Q8_0 = 8,
+    B200Q_TYPE_Q4_K = 12,
+    B200Q_TYPE_Q6_K = 14,
+    B200Q_TYPE_BF16 = 30
+};
+
+/* How a weight is cut for tensor parallelism (the reference only names the modes:
+ * SplitMode::Row / SplitMode::Tensor, icn-contracts/src/lib.rs:200-205). */
+enum {
+    B200Q_SPLIT_COLUMN = 0, /* split output rows N: QKV, gate, up; no exchange */
+    B200Q_SPLIT_ROW = 1     /* split K at 256-weight superblocks: O, down; outputs are partial sums */
+};
+
+/* Which kernel family b200q_matmul picked (b200q_last_route). */
+enum {
+    B200Q_ROUTE_NONE = 0,
+    B200Q_ROUTE_GEMV = 1,   /* M <= 4: dp4a streaming kernel, HBM-bound */
+    B200Q_ROUTE_SKINNY = 2, /* M <= 16: int8 tensor-core streaming kernel, HBM-bound */
+    B200Q_ROUTE_GEMM = 3    /* larger M: tcgen05 / TMEM bf16 GEMM with in-kernel dequantization */
+};
+
+typedef struct b200q_ctx b200q_ctx;
+typedef struct b200q_weight b200q_weight;
+
+/* -- library ------------------------------------------------------------------------------ */
+
+/* "major.minor.patch" of this library; never NULL. */
+const char *b200q_version(void);
+
+/* Bytes of a GGUF tensor of `type` with `n_elements` weights, or -1 when the type is unknown or
+ * the count is not a block multiple.  Same rule as llama_cpp_2::gguf::tensor_storage_bytes used
+ * at inference/crates/icn-models/src/gguf.rs:129. */
+int64_t b200q_tensor_storage_bytes(int32_t type, int64_t n_elements);
+
+/* -- context -------------------------------------------------------------------------------- */
+
+/* One context per GPU / executor thread.  Replaces LlamaBackend::init + model.new_context
+ * (icn-engine/src/lib.rs:141, 990) for this path. */
+b200q_status b200q_ctx_create(int32_t device, b200q_ctx **out);
+void b200q_ctx_destroy(b200q_ctx *ctx);
+
+/* Copies the last error text of this context (NUL-terminated, truncated to n). */
+b200q_status b200q_last_error(const b200q_ctx *ctx, char *buf, size_t n);
+
+/* Waits for `stream` with a host-side deadline.  Replaces LlamaContext::synchronize
+ * (icn-engine/src/lib.rs:1601-1615 uses it after a failed decode).  Also reads the device
+ * status word: a kernel whose bounded pipeline wait ran out reports B200Q_ERR_TIMEOUT here. */
+b200q_status b200q_sync(b200q_ctx *ctx, void *stream, uint64_t timeout_ms);
+
+/* Kernel family chosen by the last b200q_matmul* call on this context (B200Q_ROUTE_*), and
+ * the number of kernels that call launched. */
+b200q_status b200q_last_route(const b200q_ctx *ctx, int32_t *route, int32_t *launches);
+
+/* -- weights -------------------------------------------------------------------------------- */
+
+/* Uploads a GGUF tensor (packed_host = N rows of K/blk blocks, `bytes` must equal
+ * b200q_tensor_storage_bytes(type, N*K)).  The device copy is re-laid-out for 16-byte aligned
+ * streaming (same byte count up to per-row padding).  Replaces the weight placement done inside
+ * LlamaModel::load_from_file (icn-engine/src/lib.rs:972). */
+b200q_status b200q_weight_upload(b200q_ctx *ctx, int32_t type, int64_t N, int64_t K,
+                                 const void *packed_host, size_t bytes, b200q_weight **out);
+
+/* Uploads only this rank's shard of the full tensor.  COLUMN: rows [N*rank/world, N*(rank+1)/world)
+ * rounded to `align_rows` (pass the head size in rows for QKV, 0 or 1 otherwise).  ROW: superblock
+ * columns [B*rank/world, B*(rank+1)/world) of every row, B = K/256 (remainders go to the low ranks,
+ * e.g. 100 superblocks over 8 ranks = 13,13,13,13,12,12,12,12).  Replaces with_split_mode /
+ * with_tensor_split (icn-hardware/src/lib.rs:2578-2589). */
+b200q_status b200q_weight_upload_shard(b200q_ctx *ctx, int32_t type, int64_t N, int64_t K,
+                                       const void *packed_host, size_t bytes, int32_t split,
+                                       int32_t rank, int32_t world, int64_t align_rows,
+                                       b200q_weight **out);
+
+/* The range a rank owns under the rule above: rows for COLUMN, weights (multiples of 256; of 32
+ * for Q8_0) for ROW.  Pure host arithmetic, usable without a device. */
+b200q_status b200q_shard_range(int32_t type, int64_t N, int64_t K, int32_t split, int32_t rank,
+                               int32_t world, int64_t align_rows, int64_t *begin, int64_t *end);
+
+/* Host-only helpers (no device needed): the size of, and the conversion to, the device
+ * ("streaming") layout of rows [0, N) of a GGUF tensor.  b200q_weight_upload applies the same
+ * conversion; callers that cache converted weights on disk can use these directly. */
+int64_t b200q_layout_row_bytes(int32_t type, int64_t K);
+b200q_status b200q_layout_pack(int32_t type, int64_t N, int64_t K, const void *packed_host,
+                               size_t bytes, void *out_host, size_t out_bytes);
+
+/* A second, independent device copy of a weight (distinct HBM addresses). */
+b200q_status b200q_weight_clone(b200q_ctx *ctx, const b200q_weight *w, b200q_weight **out);
+
+b200q_status b200q_weight_info(const b200q_weight *w, int32_t *type, int64_t *N, int64_t *K,
+                               size_t *gguf_bytes, size_t *device_bytes);
+void b200q_weight_destroy(b200q_weight *w);
+
+/* Writes the N*K fp32 values the blocks encode to out_dev (row-major, device memory).
+ * Bit-exact: fp16 scales widen exactly, each product/difference is one rounded fp32 operation,
+ * no fused multiply-add.  (Qualified upstream by the dependency's test-quantize-fns,
+ * inference/parity/upstream/targets.toml:38.) */
+b200q_status b200q_dequantize(b200q_ctx *ctx, const b200q_weight *w, float *out_dev, void *stream);
+
+/* -- the projection -------------------------------------------------------------------------- */
+
+/* Y[M][N] = X[M][K] . W[N][K]^T   (ggml MUL_MAT with quantized src0; the op named at
+ * inference/parity/cases/performance/backend-ops/native-perf-qualification.json:22).
+ * x_dtype in {B200Q_TYPE_BF16, B200Q_TYPE_F32}; y_dtype in {B200Q_TYPE_F32, B200Q_TYPE_BF16}.
+ * x_dev / y_dev are device pointers; ldx >= K, ldy >= N.  M == 0 is a no-op.
+ * The kernel family is chosen by M (see B200Q_ROUTE_*). */
+b200q_status b200q_matmul(b200q_ctx *ctx, const b200q_weight *w, const void *x_dev, int32_t x_dtype,
+                          int64_t M, int64_t ldx, void *y_dev, int32_t y_dtype, int64_t ldy,
+                          void *stream);
+
+/* Several weights of the same type and K applied to one activation in a single launch
+ * (gate+up, or Q+K sharing x): Y_i[M][N_i] = X . W_i^T.  n_weights <= 4.  Falls back to one
+ * launch per weight for M > 4. */
+b200q_status b200q_matmul_multi(b200q_ctx *ctx, const b200q_weight *const *w, int32_t n_weights,
+                                const void *x_dev, int32_t x_dtype, int64_t M, int64_t ldx,
+                                void *const *y_dev, int32_t y_dtype, const int64_t *ldy, void *stream);
+
+/* The same product with HOST activations and outputs: copies X to the device, runs the
+ * projection, copies Y back and waits — the shape of the reference's own boundary, where
+ * decode() takes host tokens and get_logits_ith returns host floats
+ * (icn-engine/src/lib.rs:2264, parity_probe.rs:701). */
+b200q_status b200q_matmul_host(b200q_ctx *ctx, const b200q_weight *w, const void *x_host,
+                               int32_t x_dtype, int64_t M, int64_t ldx, void *y_host,
+                               int32_t y_dtype, int64_t ldy);
+
+/* Host-buffer form of b200q_matmul_multi. */
+b200q_status b200q_matmul_multi_host(b200q_ctx *ctx, const b200q_weight *const *w, int32_t n_weights,
+                                     const void *x_host, int32_t x_dtype, int64_t M, int64_t ldx,
+                                     void *const *y_host, int32_t y_dtype, const int64_t *ldy);
+
+/* -- tensor parallel exchange ------------------------------------------------------------------ */
+
+/* 128-byte NCCL unique id for rank 0 to broadcast out of band. */
+b200q_status b200q_tp_unique_id(void *id_out_128);
+
+/* Joins a `world`-rank NCCL communicator on this context's device.  The reference has no
+ * collective of its own (its multi-GPU is llama.cpp's in-process split); this is the single
+ * all-reduce a row-parallel projection (O, down) needs. */
+b200q_status b200q_tp_init(b200q_ctx *ctx, int32_t rank, int32_t world, const void *id_128);
+
+/* In-place sum over ranks of y_dev[count] (dtype F32 or BF16) on `stream`. */
+b200q_status b200q_allreduce(b200q_ctx *ctx, void *y_dev, int64_t count, int32_t dtype, void *stream);
+
+b200q_status b200q_tp_finalize(b200q_ctx *ctx);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200Q_H */

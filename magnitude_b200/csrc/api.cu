@@ -1,0 +1,643 @@
+// C-ABI layer: contexts, weight handles, route selection, host-buffer path, NCCL exchange.
+// Everything behind `extern "C"` returns a status; no exception leaves this file.
+#include <dlfcn.h>
+#include <stdarg.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include <chrono>
+#include <new>
+#include <thread>
+#include <vector>
+
+#include "common.cuh"
+#include "kernels.h"
+
+using namespace b200q;
+
+// ---------------------------------------------------------------------------------------------
+// NCCL through dlopen: the library must load on machines without NCCL, and inside a Python
+// process it must share the NCCL that process already loaded.
+// ---------------------------------------------------------------------------------------------
+namespace {
+
+struct NcclUniqueId { char internal[128]; };
+typedef void *NcclComm;
+struct NcclApi {
+    void *handle = nullptr;
+    int (*GetUniqueId)(NcclUniqueId *) = nullptr;
+    int (*CommInitRank)(NcclComm *, int, NcclUniqueId, int) = nullptr;
+    int (*AllReduce)(const void *, void *, size_t, int, int, NcclComm, cudaStream_t) = nullptr;
+    int (*CommDestroy)(NcclComm) = nullptr;
+    int (*CommAbort)(NcclComm) = nullptr;
+    int (*CommGetAsyncError)(NcclComm, int *) = nullptr;
+    const char *(*GetErrorString)(int) = nullptr;
+};
+constexpr int kNcclFloat32 = 7, kNcclBfloat16 = 9, kNcclSum = 0;
+
+NcclApi *nccl_api() {
+    static NcclApi api;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        const char *names[] = {"libnccl.so.2", "libnccl.so"};
+        for (const char *n : names) {
+            api.handle = dlopen(n, RTLD_NOW | RTLD_GLOBAL);
+            if (api.handle) break;
+        }
+        if (api.handle) {
+            api.GetUniqueId = (decltype(api.GetUniqueId))dlsym(api.handle, "ncclGetUniqueId");
+            api.CommInitRank = (decltype(api.CommInitRank))dlsym(api.handle, "ncclCommInitRank");
+            api.AllReduce = (decltype(api.AllReduce))dlsym(api.handle, "ncclAllReduce");
+            api.CommDestroy = (decltype(api.CommDestroy))dlsym(api.handle, "ncclCommDestroy");
+            api.CommAbort = (decltype(api.CommAbort))dlsym(api.handle, "ncclCommAbort");
+            api.CommGetAsyncError = (decltype(api.CommGetAsyncError))dlsym(api.handle, "ncclCommGetAsyncError");
+            api.GetErrorString = (decltype(api.GetErrorString))dlsym(api.handle, "ncclGetErrorString");
+            if (!api.GetUniqueId || !api.CommInitRank || !api.AllReduce || !api.CommDestroy) {
+                dlclose(api.handle);
+                api.handle = nullptr;
+            }
+        }
+    }
+    return api.handle ? &api : nullptr;
+}
+
+int env_int(const char *name, int dflt) {
+    const char *v = getenv(name);
+    return (v && *v) ? atoi(v) : dflt;
+}
+
+}  // namespace
+
+struct b200q_ctx {
+    int device = 0;
+    int sm_count = 0;
+    size_t smem_optin = 0;
+    int *status_dev = nullptr;
+    char err[512] = {0};
+    int last_route = B200Q_ROUTE_NONE;
+    int last_launches = 0;
+    bool poisoned = false;
+    // host-buffer path
+    cudaStream_t hstream = nullptr;
+    void *hx_dev = nullptr;
+    size_t hx_bytes = 0;
+    void *hy_dev = nullptr;
+    size_t hy_bytes = 0;
+    // tunables (environment overrides for experiments)
+    int gemv_warps = 0, gemv_depth = 0, gemv_grid = 0;
+    // tensor parallel
+    NcclComm comm = nullptr;
+    int tp_rank = 0, tp_world = 1;
+};
+
+struct b200q_weight {
+    b200q_ctx *ctx = nullptr;
+    int type = 0;
+    int64_t N = 0, K = 0, Kpad = 0;
+    int64_t row_bytes = 0;
+    size_t gguf_bytes = 0, device_bytes = 0;
+    uint8_t *dev = nullptr;
+};
+
+namespace {
+
+b200q_status fail(b200q_ctx *ctx, b200q_status code, const char *fmt, ...) {
+    if (ctx) {
+        va_list ap;
+        va_start(ap, fmt);
+        vsnprintf(ctx->err, sizeof(ctx->err), fmt, ap);
+        va_end(ap);
+    }
+    return code;
+}
+
+b200q_status cuda_fail(b200q_ctx *ctx, cudaError_t e, const char *what) {
+    const b200q_status code = (e == cudaErrorMemoryAllocation) ? B200Q_ERR_OVERLOADED : B200Q_ERR_BACKEND;
+    return fail(ctx, code, "%s: %s", what, cudaGetErrorString(e));
+}
+
+#define CU_TRY(ctx, expr)                                          \
+    do {                                                           \
+        cudaError_t e__ = (expr);                                  \
+        if (e__ != cudaSuccess) return cuda_fail(ctx, e__, #expr); \
+    } while (0)
+
+bool known_type(int t) { return t == QT_Q8_0 || t == QT_Q4_K || t == QT_Q6_K; }
+bool act_type(int t) { return t == B200Q_TYPE_F32 || t == B200Q_TYPE_BF16; }
+size_t act_size(int t) { return t == B200Q_TYPE_BF16 ? 2 : 4; }
+
+void split_even(int64_t units, int rank, int world, int64_t *b, int64_t *e) {
+    const int64_t base = units / world, rem = units % world;
+    *b = rank * base + (rank < rem ? rank : rem);
+    *e = *b + base + (rank < rem ? 1 : 0);
+}
+
+b200q_status make_weight(b200q_ctx *ctx, int type, int64_t N, int64_t Kfull, const uint8_t *gguf,
+                         int64_t r0, int64_t r1, int64_t k0, int64_t k1, b200q_weight **out) {
+    const int64_t n = r1 - r0, k = k1 - k0;
+    const int64_t sb0 = k0 / SB, sb1 = (k1 + SB - 1) / SB;
+    b200q_weight *w = new (std::nothrow) b200q_weight();
+    if (!w) return fail(ctx, B200Q_ERR_OVERLOADED, "out of host memory");
+    w->ctx = ctx;
+    w->type = type;
+    w->N = n;
+    w->K = k;
+    w->Kpad = (sb1 - sb0) * SB;
+    w->row_bytes = row_bytes_for(type, sb1 - sb0);
+    w->gguf_bytes = (size_t)(n * (k / gguf_block_elems(type)) * gguf_block_bytes(type));
+    w->device_bytes = (size_t)(n * w->row_bytes);
+    if (n > 0 && k > 0) {
+        std::vector<uint8_t> staged;
+        try {
+            staged.resize(w->device_bytes);
+        } catch (...) {
+            const size_t need = w->device_bytes;
+            delete w;
+            return fail(ctx, B200Q_ERR_OVERLOADED, "out of host memory staging %zu bytes", need);
+        }
+        // rows are independent: re-lay them on a few threads
+        const int nt = (int)std::min<int64_t>(8, std::max<int64_t>(1, n / 256));
+        std::vector<std::thread> th;
+        for (int t = 0; t < nt; ++t) {
+            const int64_t a = r0 + n * t / nt, b = r0 + n * (t + 1) / nt;
+            uint8_t *dst = staged.data() + (a - r0) * w->row_bytes;
+            th.emplace_back([=] { repack_host(type, Kfull, gguf, a, b, sb0, sb1, dst); });
+        }
+        for (auto &t : th) t.join();
+        cudaError_t e = cudaMalloc(&w->dev, w->device_bytes + 256);
+        if (e == cudaSuccess) e = cudaMemcpy(w->dev, staged.data(), w->device_bytes, cudaMemcpyHostToDevice);
+        if (e == cudaSuccess) e = cudaMemset(w->dev + w->device_bytes, 0, 256);
+        if (e != cudaSuccess) {
+            if (w->dev) cudaFree(w->dev);
+            delete w;
+            return cuda_fail(ctx, e, "weight upload");
+        }
+    }
+    *out = w;
+    return B200Q_OK;
+}
+
+b200q_status check_ctx(b200q_ctx *ctx) {
+    if (!ctx) return B200Q_ERR_INVALID_CONFIG;
+    if (ctx->poisoned) return fail(ctx, B200Q_ERR_STOPPED, "context stopped after a device error");
+    cudaError_t e = cudaSetDevice(ctx->device);
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "cudaSetDevice");
+    return B200Q_OK;
+}
+
+b200q_status run_gemv(b200q_ctx *ctx, const b200q_weight *const *w, int nw, const void *x, int x_dtype,
+                      int M, int64_t ldx, void *const *y, int y_dtype, const int64_t *ldy,
+                      cudaStream_t st) {
+    GemvLaunch a{};
+    a.qt = w[0]->type;
+    a.nseg = nw;
+    for (int i = 0; i < nw; ++i) {
+        a.w[i] = w[i]->dev;
+        a.y[i] = y[i];
+        a.ldy[i] = ldy[i];
+        a.n[i] = (int)w[i]->N;
+    }
+    a.x = x;
+    a.ldx = ldx;
+    a.x_is_bf16 = x_dtype == B200Q_TYPE_BF16;
+    a.y_is_bf16 = y_dtype == B200Q_TYPE_BF16;
+    a.M = M;
+    a.K = (int)w[0]->K;
+    a.Kpad = (int)w[0]->Kpad;
+    a.row_bytes = w[0]->row_bytes;
+    a.status = ctx->status_dev;
+    a.sm_count = ctx->sm_count;
+    a.smem_limit = ctx->smem_optin;
+    a.warps = ctx->gemv_warps;
+    a.depth = ctx->gemv_depth;
+    a.grid = ctx->gemv_grid;
+    cudaError_t e = gemv_launch(a, st);
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "gemv launch");
+    return B200Q_OK;
+}
+
+b200q_status validate_mm(b200q_ctx *ctx, const b200q_weight *w, const void *x, int x_dtype, int64_t M,
+                         int64_t ldx, const void *y, int y_dtype, int64_t ldy) {
+    if (!w) return fail(ctx, B200Q_ERR_INVALID_CONFIG, "null weight");
+    if (w->ctx != ctx) return fail(ctx, B200Q_ERR_INVALID_CONFIG, "weight belongs to another context");
+    if (!act_type(x_dtype) || !act_type(y_dtype))
+        return fail(ctx, B200Q_ERR_INVALID_CONFIG, "activation/output dtype must be F32 (0) or BF16 (30)");
+    if (M < 0) return fail(ctx, B200Q_ERR_INVALID_CONFIG, "M < 0");
+    if (M > 0 && ((!x && w->K > 0) || (!y && w->N > 0)))
+        return fail(ctx, B200Q_ERR_INVALID_CONFIG, "null activation or output pointer");
+    if (ldx < w->K || ldy < w->N) return fail(ctx, B200Q_ERR_INVALID_CONFIG, "leading dimension smaller than the row");
+    return B200Q_OK;
+}
+
+// One weight set (1..4 weights sharing x), any M: picks the route and launches.
+b200q_status matmul_any(b200q_ctx *ctx, const b200q_weight *const *w, int nw, const void *x, int x_dtype,
+                        int64_t M, int64_t ldx, void *const *y, int y_dtype, const int64_t *ldy,
+                        cudaStream_t st) {
+    ctx->last_route = B200Q_ROUTE_NONE;
+    ctx->last_launches = 0;
+    if (M == 0) return B200Q_OK;
+    bool any_rows = false;
+    for (int i = 0; i < nw; ++i) any_rows |= w[i]->N > 0;
+    if (!any_rows) return B200Q_OK;
+    if (w[0]->K == 0) {   // empty contraction: the product is all zeros
+        for (int i = 0; i < nw; ++i)
+            for (int64_t m = 0; m < M; ++m)
+                CU_TRY(ctx, cudaMemsetAsync((char *)y[i] + m * ldy[i] * act_size(y_dtype), 0,
+                                            w[i]->N * act_size(y_dtype), st));
+        return B200Q_OK;
+    }
+    const int mt = gemv_max_m();
+    ctx->last_route = B200Q_ROUTE_GEMV;
+    for (int64_t m0 = 0; m0 < M; m0 += mt) {
+        const int mc = (int)std::min<int64_t>(mt, M - m0);
+        void *yy[4];
+        for (int i = 0; i < nw; ++i) yy[i] = (char *)y[i] + m0 * ldy[i] * act_size(y_dtype);
+        const void *xx = (const char *)x + m0 * ldx * act_size(x_dtype);
+        b200q_status s = run_gemv(ctx, w, nw, xx, x_dtype, mc, ldx, yy, y_dtype, ldy, st);
+        if (s != B200Q_OK) return s;
+        ctx->last_launches++;
+    }
+    return B200Q_OK;
+}
+
+b200q_status ensure_host_path(b200q_ctx *ctx, size_t xb, size_t yb) {
+    if (!ctx->hstream) CU_TRY(ctx, cudaStreamCreateWithFlags(&ctx->hstream, cudaStreamNonBlocking));
+    if (xb > ctx->hx_bytes) {
+        if (ctx->hx_dev) cudaFree(ctx->hx_dev);
+        ctx->hx_dev = nullptr;
+        ctx->hx_bytes = 0;
+        CU_TRY(ctx, cudaMalloc(&ctx->hx_dev, xb));
+        ctx->hx_bytes = xb;
+    }
+    if (yb > ctx->hy_bytes) {
+        if (ctx->hy_dev) cudaFree(ctx->hy_dev);
+        ctx->hy_dev = nullptr;
+        ctx->hy_bytes = 0;
+        CU_TRY(ctx, cudaMalloc(&ctx->hy_dev, yb));
+        ctx->hy_bytes = yb;
+    }
+    return B200Q_OK;
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------------------------------------
+extern "C" {
+
+const char *b200q_version(void) { return "0.1.0"; }
+
+int64_t b200q_tensor_storage_bytes(int32_t type, int64_t n_elements) {
+    if (n_elements < 0) return -1;
+    if (type == B200Q_TYPE_F32) return n_elements * 4;
+    if (type == B200Q_TYPE_BF16) return n_elements * 2;
+    if (!known_type(type)) return -1;
+    const int64_t be = gguf_block_elems(type);
+    if (n_elements % be) return -1;
+    return n_elements / be * gguf_block_bytes(type);
+}
+
+b200q_status b200q_ctx_create(int32_t device, b200q_ctx **out) {
+    if (!out) return B200Q_ERR_INVALID_CONFIG;
+    *out = nullptr;
+    int count = 0;
+    cudaError_t e = cudaGetDeviceCount(&count);
+    if (e != cudaSuccess || count == 0) {
+        cudaGetLastError();
+        return B200Q_ERR_BACKEND;   // no CUDA device: there is no CPU fallback
+    }
+    if (device < 0 || device >= count) return B200Q_ERR_INVALID_CONFIG;
+    b200q_ctx *ctx = new (std::nothrow) b200q_ctx();
+    if (!ctx) return B200Q_ERR_OVERLOADED;
+    ctx->device = device;
+    cudaDeviceProp prop;
+    if ((e = cudaSetDevice(device)) != cudaSuccess || (e = cudaGetDeviceProperties(&prop, device)) != cudaSuccess) {
+        delete ctx;
+        return B200Q_ERR_BACKEND;
+    }
+    if (prop.major != 10) {   // the kernels are sm_100a only
+        delete ctx;
+        return B200Q_ERR_BACKEND;
+    }
+    ctx->sm_count = prop.multiProcessorCount;
+    ctx->smem_optin = prop.sharedMemPerBlockOptin;
+    if ((e = cudaMalloc(&ctx->status_dev, 256)) != cudaSuccess || (e = cudaMemset(ctx->status_dev, 0, 256)) != cudaSuccess) {
+        delete ctx;
+        return e == cudaErrorMemoryAllocation ? B200Q_ERR_OVERLOADED : B200Q_ERR_BACKEND;
+    }
+    ctx->gemv_warps = env_int("B200Q_GEMV_WARPS", 0);
+    ctx->gemv_depth = env_int("B200Q_GEMV_DEPTH", 0);
+    ctx->gemv_grid = env_int("B200Q_GEMV_GRID", 0);
+    *out = ctx;
+    return B200Q_OK;
+}
+
+void b200q_ctx_destroy(b200q_ctx *ctx) {
+    if (!ctx) return;
+    cudaSetDevice(ctx->device);
+    if (ctx->comm) {
+        NcclApi *api = nccl_api();
+        if (api) api->CommDestroy(ctx->comm);
+    }
+    if (ctx->hstream) cudaStreamDestroy(ctx->hstream);
+    if (ctx->hx_dev) cudaFree(ctx->hx_dev);
+    if (ctx->hy_dev) cudaFree(ctx->hy_dev);
+    if (ctx->status_dev) cudaFree(ctx->status_dev);
+    delete ctx;
+}
+
+b200q_status b200q_last_error(const b200q_ctx *ctx, char *buf, size_t n) {
+    if (!ctx || !buf || n == 0) return B200Q_ERR_INVALID_CONFIG;
+    snprintf(buf, n, "%s", ctx->err);
+    return B200Q_OK;
+}
+
+b200q_status b200q_last_route(const b200q_ctx *ctx, int32_t *route, int32_t *launches) {
+    if (!ctx) return B200Q_ERR_INVALID_CONFIG;
+    if (route) *route = ctx->last_route;
+    if (launches) *launches = ctx->last_launches;
+    return B200Q_OK;
+}
+
+b200q_status b200q_sync(b200q_ctx *ctx, void *stream, uint64_t timeout_ms) {
+    b200q_status s = check_ctx(ctx);
+    if (s != B200Q_OK) return s;
+    cudaStream_t st = (cudaStream_t)stream;
+    const auto t0 = std::chrono::steady_clock::now();
+    for (;;) {
+        cudaError_t e = cudaStreamQuery(st);
+        if (e == cudaSuccess) break;
+        if (e != cudaErrorNotReady) {
+            ctx->poisoned = true;
+            return cuda_fail(ctx, e, "stream");
+        }
+        const auto ms = std::chrono::duration_cast<std::chrono::milliseconds>(std::chrono::steady_clock::now() - t0).count();
+        if (timeout_ms && (uint64_t)ms > timeout_ms)
+            return fail(ctx, B200Q_ERR_TIMEOUT, "stream not finished after %llu ms", (unsigned long long)timeout_ms);
+        std::this_thread::yield();
+    }
+    int status = 0;
+    CU_TRY(ctx, cudaMemcpy(&status, ctx->status_dev, sizeof(int), cudaMemcpyDeviceToHost));
+    if (status != DEV_OK) {
+        cudaMemset(ctx->status_dev, 0, sizeof(int));
+        return fail(ctx, B200Q_ERR_TIMEOUT, "a kernel gave up a bounded wait (device status %d); results are invalid", status);
+    }
+    return B200Q_OK;
+}
+
+// -- weights ----------------------------------------------------------------------------------
+
+b200q_status b200q_shard_range(int32_t type, int64_t N, int64_t K, int32_t split, int32_t rank,
+                               int32_t world, int64_t align_rows, int64_t *begin, int64_t *end) {
+    if (!begin || !end || !known_type(type) || N < 0 || K < 0 || world < 1 || rank < 0 || rank >= world)
+        return B200Q_ERR_INVALID_CONFIG;
+    if (K % gguf_block_elems(type)) return B200Q_ERR_INVALID_CONFIG;
+    if (split == B200Q_SPLIT_COLUMN) {
+        const int64_t al = align_rows > 1 ? align_rows : 1;
+        if (N % al) return B200Q_ERR_INVALID_CONFIG;
+        split_even(N / al, rank, world, begin, end);
+        *begin *= al;
+        *end *= al;
+    } else if (split == B200Q_SPLIT_ROW) {
+        split_even((K + SB - 1) / SB, rank, world, begin, end);
+        *begin = std::min<int64_t>(K, *begin * SB);
+        *end = std::min<int64_t>(K, *end * SB);
+    } else {
+        return B200Q_ERR_INVALID_CONFIG;
+    }
+    return B200Q_OK;
+}
+
+int64_t b200q_layout_row_bytes(int32_t type, int64_t K) {
+    if (!known_type(type) || K < 0 || K % gguf_block_elems(type)) return -1;
+    return row_bytes_for(type, (K + SB - 1) / SB);
+}
+
+b200q_status b200q_layout_pack(int32_t type, int64_t N, int64_t K, const void *packed_host,
+                               size_t bytes, void *out_host, size_t out_bytes) {
+    const int64_t rb = b200q_layout_row_bytes(type, K);
+    if (rb < 0 || N < 0) return B200Q_ERR_INVALID_CONFIG;
+    if ((int64_t)bytes != b200q_tensor_storage_bytes(type, N * K) || (int64_t)out_bytes != N * rb)
+        return B200Q_ERR_INVALID_CONFIG;
+    if (N * K == 0) return B200Q_OK;
+    if (!packed_host || !out_host) return B200Q_ERR_INVALID_CONFIG;
+    repack_host(type, K, (const uint8_t *)packed_host, 0, N, 0, (K + SB - 1) / SB, (uint8_t *)out_host);
+    return B200Q_OK;
+}
+
+b200q_status b200q_weight_upload_shard(b200q_ctx *ctx, int32_t type, int64_t N, int64_t K,
+                                       const void *packed_host, size_t bytes, int32_t split,
+                                       int32_t rank, int32_t world, int64_t align_rows,
+                                       b200q_weight **out) {
+    b200q_status s = check_ctx(ctx);
+    if (s != B200Q_OK) return s;
+    if (!out) return fail(ctx, B200Q_ERR_INVALID_CONFIG, "null out pointer");
+    *out = nullptr;
+    if (!known_type(type)) return fail(ctx, B200Q_ERR_INVALID_CONFIG, "unsupported ggml type id %d (8=Q8_0, 12=Q4_K, 14=Q6_K)", type);
+    if (N < 0 || K < 0) return fail(ctx, B200Q_ERR_INVALID_CONFIG, "negative shape");
+    if (K % gguf_block_elems(type))
+        return fail(ctx, B200Q_ERR_INVALID_CONFIG, "K=%lld is not a multiple of the %d-weight block", (long long)K, gguf_block_elems(type));
+    if (N > 0x7FFFFFF0ll || K > 0x3FFFFF00ll) return fail(ctx, B200Q_ERR_INVALID_CONFIG, "shape too large");
+    const int64_t want = b200q_tensor_storage_bytes(type, N * K);
+    if ((int64_t)bytes != want)
+        return fail(ctx, B200Q_ERR_INVALID_CONFIG, "byte count %zu does not match the tensor (%lld expected)", bytes, (long long)want);
+    if (want > 0 && !packed_host) return fail(ctx, B200Q_ERR_INVALID_CONFIG, "null weight pointer");
+    int64_t r0 = 0, r1 = N, k0 = 0, k1 = K;
+    if (world != 1 || rank != 0) {
+        int64_t b, e;
+        if (b200q_shard_range(type, N, K, split, rank, world, align_rows, &b, &e) != B200Q_OK)
+            return fail(ctx, B200Q_ERR_INVALID_CONFIG, "bad shard request (split %d rank %d world %d align %lld)", split, rank, world, (long long)align_rows);
+        if (split == B200Q_SPLIT_COLUMN) { r0 = b; r1 = e; } else { k0 = b; k1 = e; }
+    }
+    return make_weight(ctx, type, N, K, (const uint8_t *)packed_host, r0, r1, k0, k1, out);
+}
+
+b200q_status b200q_weight_upload(b200q_ctx *ctx, int32_t type, int64_t N, int64_t K,
+                                 const void *packed_host, size_t bytes, b200q_weight **out) {
+    return b200q_weight_upload_shard(ctx, type, N, K, packed_host, bytes, B200Q_SPLIT_COLUMN, 0, 1, 0, out);
+}
+
+b200q_status b200q_weight_clone(b200q_ctx *ctx, const b200q_weight *w, b200q_weight **out) {
+    b200q_status s = check_ctx(ctx);
+    if (s != B200Q_OK) return s;
+    if (!w || !out || w->ctx != ctx) return fail(ctx, B200Q_ERR_INVALID_CONFIG, "bad clone arguments");
+    b200q_weight *c = new (std::nothrow) b200q_weight(*w);
+    if (!c) return fail(ctx, B200Q_ERR_OVERLOADED, "out of host memory");
+    c->dev = nullptr;
+    if (w->dev) {
+        cudaError_t e = cudaMalloc(&c->dev, w->device_bytes + 256);
+        if (e == cudaSuccess) e = cudaMemcpy(c->dev, w->dev, w->device_bytes + 256, cudaMemcpyDeviceToDevice);
+        if (e != cudaSuccess) {
+            if (c->dev) cudaFree(c->dev);
+            delete c;
+            return cuda_fail(ctx, e, "weight clone");
+        }
+    }
+    *out = c;
+    return B200Q_OK;
+}
+
+b200q_status b200q_weight_info(const b200q_weight *w, int32_t *type, int64_t *N, int64_t *K,
+                               size_t *gguf_bytes, size_t *device_bytes) {
+    if (!w) return B200Q_ERR_INVALID_CONFIG;
+    if (type) *type = w->type;
+    if (N) *N = w->N;
+    if (K) *K = w->K;
+    if (gguf_bytes) *gguf_bytes = w->gguf_bytes;
+    if (device_bytes) *device_bytes = w->device_bytes;
+    return B200Q_OK;
+}
+
+void b200q_weight_destroy(b200q_weight *w) {
+    if (!w) return;
+    if (w->dev) {
+        if (w->ctx) cudaSetDevice(w->ctx->device);
+        cudaFree(w->dev);
+    }
+    delete w;
+}
+
+b200q_status b200q_dequantize(b200q_ctx *ctx, const b200q_weight *w, float *out_dev, void *stream) {
+    b200q_status s = check_ctx(ctx);
+    if (s != B200Q_OK) return s;
+    if (!w || w->ctx != ctx) return fail(ctx, B200Q_ERR_INVALID_CONFIG, "bad weight");
+    if (w->N == 0 || w->K == 0) return B200Q_OK;
+    if (!out_dev) return fail(ctx, B200Q_ERR_INVALID_CONFIG, "null output pointer");
+    cudaError_t e = dequant_launch(w->type, w->dev, w->N, w->K, w->Kpad, w->row_bytes, out_dev, (cudaStream_t)stream);
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "dequantize launch");
+    return B200Q_OK;
+}
+
+// -- projection -------------------------------------------------------------------------------
+
+b200q_status b200q_matmul(b200q_ctx *ctx, const b200q_weight *w, const void *x_dev, int32_t x_dtype,
+                          int64_t M, int64_t ldx, void *y_dev, int32_t y_dtype, int64_t ldy,
+                          void *stream) {
+    b200q_status s = check_ctx(ctx);
+    if (s != B200Q_OK) return s;
+    if ((s = validate_mm(ctx, w, x_dev, x_dtype, M, ldx, y_dev, y_dtype, ldy)) != B200Q_OK) return s;
+    return matmul_any(ctx, &w, 1, x_dev, x_dtype, M, ldx, &y_dev, y_dtype, &ldy, (cudaStream_t)stream);
+}
+
+b200q_status b200q_matmul_multi(b200q_ctx *ctx, const b200q_weight *const *w, int32_t n_weights,
+                                const void *x_dev, int32_t x_dtype, int64_t M, int64_t ldx,
+                                void *const *y_dev, int32_t y_dtype, const int64_t *ldy, void *stream) {
+    b200q_status s = check_ctx(ctx);
+    if (s != B200Q_OK) return s;
+    if (!w || !y_dev || !ldy || n_weights < 1 || n_weights > 4)
+        return fail(ctx, B200Q_ERR_INVALID_CONFIG, "matmul_multi takes 1..4 weights");
+    for (int i = 0; i < n_weights; ++i) {
+        if ((s = validate_mm(ctx, w[i], x_dev, x_dtype, M, ldx, y_dev[i], y_dtype, ldy[i])) != B200Q_OK) return s;
+        if (w[i]->type != w[0]->type || w[i]->K != w[0]->K)
+            return fail(ctx, B200Q_ERR_INVALID_CONFIG, "weights of one launch must share type and K");
+    }
+    return matmul_any(ctx, w, n_weights, x_dev, x_dtype, M, ldx, y_dev, y_dtype, ldy, (cudaStream_t)stream);
+}
+
+b200q_status b200q_matmul_multi_host(b200q_ctx *ctx, const b200q_weight *const *w, int32_t n_weights,
+                                     const void *x_host, int32_t x_dtype, int64_t M, int64_t ldx,
+                                     void *const *y_host, int32_t y_dtype, const int64_t *ldy) {
+    b200q_status s = check_ctx(ctx);
+    if (s != B200Q_OK) return s;
+    if (!w || !y_host || !ldy || n_weights < 1 || n_weights > 4)
+        return fail(ctx, B200Q_ERR_INVALID_CONFIG, "matmul_multi takes 1..4 weights");
+    for (int i = 0; i < n_weights; ++i) {
+        if ((s = validate_mm(ctx, w[i], x_host, x_dtype, M, ldx, y_host[i], y_dtype, ldy[i])) != B200Q_OK) return s;
+        if (w[i]->type != w[0]->type || w[i]->K != w[0]->K)
+            return fail(ctx, B200Q_ERR_INVALID_CONFIG, "weights of one launch must share type and K");
+    }
+    if (M == 0) return B200Q_OK;
+    const size_t xs = act_size(x_dtype), ys = act_size(y_dtype);
+    const size_t xb = (size_t)((M - 1) * ldx + w[0]->K) * xs;
+    size_t yoff[4], yb = 0;
+    for (int i = 0; i < n_weights; ++i) {
+        yoff[i] = yb;
+        yb += (((size_t)((M - 1) * ldy[i] + w[i]->N) * ys) + 255) & ~size_t(255);
+    }
+    if ((s = ensure_host_path(ctx, xb, yb)) != B200Q_OK) return s;
+    cudaStream_t st = ctx->hstream;
+    CU_TRY(ctx, cudaMemcpyAsync(ctx->hx_dev, x_host, xb, cudaMemcpyHostToDevice, st));
+    void *yd[4];
+    for (int i = 0; i < n_weights; ++i) yd[i] = (char *)ctx->hy_dev + yoff[i];
+    if ((s = matmul_any(ctx, w, n_weights, ctx->hx_dev, x_dtype, M, ldx, yd, y_dtype, ldy, st)) != B200Q_OK) return s;
+    for (int i = 0; i < n_weights; ++i)
+        if (w[i]->N > 0)
+            CU_TRY(ctx, cudaMemcpyAsync(y_host[i], yd[i], (size_t)((M - 1) * ldy[i] + w[i]->N) * ys, cudaMemcpyDeviceToHost, st));
+    cudaError_t e = cudaStreamSynchronize(st);
+    if (e != cudaSuccess) {
+        ctx->poisoned = true;
+        return cuda_fail(ctx, e, "host-path synchronize");
+    }
+    return B200Q_OK;
+}
+
+b200q_status b200q_matmul_host(b200q_ctx *ctx, const b200q_weight *w, const void *x_host,
+                               int32_t x_dtype, int64_t M, int64_t ldx, void *y_host,
+                               int32_t y_dtype, int64_t ldy) {
+    return b200q_matmul_multi_host(ctx, &w, 1, x_host, x_dtype, M, ldx, &y_host, y_dtype, &ldy);
+}
+
+// -- tensor parallel --------------------------------------------------------------------------
+
+b200q_status b200q_tp_unique_id(void *id_out_128) {
+    if (!id_out_128) return B200Q_ERR_INVALID_CONFIG;
+    NcclApi *api = nccl_api();
+    if (!api) return B200Q_ERR_BACKEND;
+    NcclUniqueId id;
+    if (api->GetUniqueId(&id) != 0) return B200Q_ERR_BACKEND;
+    memcpy(id_out_128, &id, sizeof(id));
+    return B200Q_OK;
+}
+
+b200q_status b200q_tp_init(b200q_ctx *ctx, int32_t rank, int32_t world, const void *id_128) {
+    b200q_status s = check_ctx(ctx);
+    if (s != B200Q_OK) return s;
+    if (world < 1 || rank < 0 || rank >= world || !id_128)
+        return fail(ctx, B200Q_ERR_INVALID_CONFIG, "bad rank/world (%d/%d) or null id", rank, world);
+    if (ctx->comm) return fail(ctx, B200Q_ERR_INVALID_CONFIG, "communicator already initialised");
+    NcclApi *api = nccl_api();
+    if (!api) return fail(ctx, B200Q_ERR_BACKEND, "libnccl.so.2 could not be loaded");
+    NcclUniqueId id;
+    memcpy(&id, id_128, sizeof(id));
+    int rc = api->CommInitRank(&ctx->comm, world, id, rank);
+    if (rc != 0) {
+        ctx->comm = nullptr;
+        return fail(ctx, B200Q_ERR_BACKEND, "ncclCommInitRank: %s", api->GetErrorString ? api->GetErrorString(rc) : "error");
+    }
+    ctx->tp_rank = rank;
+    ctx->tp_world = world;
+    return B200Q_OK;
+}
+
+b200q_status b200q_allreduce(b200q_ctx *ctx, void *y_dev, int64_t count, int32_t dtype, void *stream) {
+    b200q_status s = check_ctx(ctx);
+    if (s != B200Q_OK) return s;
+    if (!act_type(dtype) || count < 0 || (count > 0 && !y_dev))
+        return fail(ctx, B200Q_ERR_INVALID_CONFIG, "bad all-reduce arguments");
+    if (!ctx->comm) {
+        if (ctx->tp_world == 1) return B200Q_OK;   // single rank: the sum is the input
+        return fail(ctx, B200Q_ERR_INVALID_CONFIG, "b200q_tp_init has not been called");
+    }
+    if (count == 0) return B200Q_OK;
+    NcclApi *api = nccl_api();
+    int rc = api->AllReduce(y_dev, y_dev, (size_t)count, dtype == B200Q_TYPE_BF16 ? kNcclBfloat16 : kNcclFloat32,
+                            kNcclSum, ctx->comm, (cudaStream_t)stream);
+    if (rc != 0) return fail(ctx, B200Q_ERR_BACKEND, "ncclAllReduce: %s", api->GetErrorString ? api->GetErrorString(rc) : "error");
+    return B200Q_OK;
+}
+
+b200q_status b200q_tp_finalize(b200q_ctx *ctx) {
+    if (!ctx) return B200Q_ERR_INVALID_CONFIG;
+    if (ctx->comm) {
+        cudaSetDevice(ctx->device);
+        NcclApi *api = nccl_api();
+        if (api) api->CommDestroy(ctx->comm);
+        ctx->comm = nullptr;
+    }
+    ctx->tp_world = 1;
+    ctx->tp_rank = 0;
+    return B200Q_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,245 @@
+"""Host-side projection interface over the b200q C ABI.
+
+Mirrors the ownership rules of the reference executor (design/inference/engine.md:49-52 in the
+reference tree): a `Backend` is owned by one thread and one GPU, weights are loaded once and stay
+resident, a failed call raises and leaves the backend usable unless the device itself faulted.
+PyTorch is used only to hold device memory and streams; every product runs in libb200q.so.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import byref, c_int32, c_int64, c_size_t, c_void_p
+from typing import Sequence
+
+import numpy as np
+
+from . import _binding as B
+
+_TORCH_DTYPE = {}
+
+
+def _torch():
+    import torch
+
+    if not _TORCH_DTYPE:
+        _TORCH_DTYPE.update({torch.float32: B.TYPE_F32, torch.bfloat16: B.TYPE_BF16})
+    return torch
+
+
+def tensor_storage_bytes(qtype: int, n_elements: int) -> int:
+    """GGUF byte count of a tensor (the rule used at inference/crates/icn-models/src/gguf.rs:129)."""
+    return int(B.lib().b200q_tensor_storage_bytes(qtype, n_elements))
+
+
+def shard_range(qtype: int, n: int, k: int, split: int, rank: int, world: int, align_rows: int = 0) -> tuple[int, int]:
+    """Rows (column split) or weights along K (row split) that `rank` of `world` owns."""
+    b, e = c_int64(), c_int64()
+    st = B.lib().b200q_shard_range(qtype, n, k, split, rank, world, align_rows, byref(b), byref(e))
+    if st:
+        raise B.B200QError(st, f"shard_range(type={qtype}, N={n}, K={k}, split={split}, rank={rank}/{world})")
+    return b.value, e.value
+
+
+class ProjectionWeight:
+    """A quantized W[N][K] resident on one GPU (streaming layout)."""
+
+    def __init__(self, backend: "Backend", handle: int):
+        self.backend = backend
+        self._h = c_void_p(handle)
+        t, n, k, gb, db = c_int32(), c_int64(), c_int64(), c_size_t(), c_size_t()
+        backend._check(B.lib().b200q_weight_info(self._h, byref(t), byref(n), byref(k), byref(gb), byref(db)))
+        self.qtype, self.n, self.k = t.value, n.value, k.value
+        self.gguf_bytes, self.device_bytes = gb.value, db.value
+
+    def clone(self) -> "ProjectionWeight":
+        out = c_void_p()
+        self.backend._check(B.lib().b200q_weight_clone(self.backend._h, self._h, byref(out)))
+        return ProjectionWeight(self.backend, out.value)
+
+    def close(self) -> None:
+        if self._h:
+            B.lib().b200q_weight_destroy(self._h)
+            self._h = c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class Backend:
+    """One b200q context: one GPU, one owning thread."""
+
+    def __init__(self, device: int = 0):
+        h = c_void_p()
+        st = B.lib().b200q_ctx_create(device, byref(h))
+        if st:
+            raise B.B200QError(st, f"cannot create a context on CUDA device {device} (no CPU fallback exists)")
+        self._h = h
+        self.device = device
+
+    # -- errors ------------------------------------------------------------------------------
+    def last_error(self) -> str:
+        buf = ctypes.create_string_buffer(512)
+        B.lib().b200q_last_error(self._h, buf, 512)
+        return buf.value.decode(errors="replace")
+
+    def _check(self, status: int) -> None:
+        if status:
+            raise B.B200QError(status, self.last_error())
+
+    def close(self) -> None:
+        if self._h:
+            B.lib().b200q_ctx_destroy(self._h)
+            self._h = c_void_p()
+
+    def last_route(self) -> tuple[int, int]:
+        r, n = c_int32(), c_int32()
+        B.lib().b200q_last_route(self._h, byref(r), byref(n))
+        return r.value, n.value
+
+    def sync(self, stream=None, timeout_ms: int = 60000) -> None:
+        self._check(B.lib().b200q_sync(self._h, self._stream_ptr(stream), timeout_ms))
+
+    # -- weights -----------------------------------------------------------------------------
+    def upload(self, qtype: int, packed: np.ndarray, n: int, k: int) -> ProjectionWeight:
+        packed = np.ascontiguousarray(packed, dtype=np.uint8)
+        out = c_void_p()
+        self._check(B.lib().b200q_weight_upload(self._h, qtype, n, k, packed.ctypes.data, packed.size, byref(out)))
+        return ProjectionWeight(self, out.value)
+
+    def upload_shard(self, qtype: int, packed: np.ndarray, n: int, k: int, split: int, rank: int, world: int,
+                     align_rows: int = 0) -> ProjectionWeight:
+        packed = np.ascontiguousarray(packed, dtype=np.uint8)
+        out = c_void_p()
+        self._check(
+            B.lib().b200q_weight_upload_shard(
+                self._h, qtype, n, k, packed.ctypes.data, packed.size, split, rank, world, align_rows, byref(out)
+            )
+        )
+        return ProjectionWeight(self, out.value)
+
+    # -- device-pointer path (torch tensors hold the memory) ---------------------------------
+    @staticmethod
+    def _stream_ptr(stream) -> c_void_p:
+        if stream is None:
+            torch = _torch()
+            if torch.cuda.is_available() and torch.cuda.is_initialized():
+                return c_void_p(torch.cuda.current_stream().cuda_stream)
+            return c_void_p(0)
+        if isinstance(stream, int):
+            return c_void_p(stream)
+        return c_void_p(stream.cuda_stream)
+
+    def dequantize(self, w: ProjectionWeight, stream=None):
+        torch = _torch()
+        out = torch.empty((w.n, w.k), dtype=torch.float32, device=f"cuda:{self.device}")
+        self._check(B.lib().b200q_dequantize(self._h, w._h, c_void_p(out.data_ptr()), self._stream_ptr(stream)))
+        return out
+
+    def project(self, w: ProjectionWeight, x, out=None, out_dtype=None, stream=None):
+        """y[M, N] = x[M, K] @ W^T for a CUDA tensor x (bf16 or fp32); returns a CUDA tensor."""
+        torch = _torch()
+        if x.dim() == 1:
+            x = x.unsqueeze(0)
+        if x.stride(-1) != 1:
+            x = x.contiguous()
+        m = x.shape[0]
+        xd = _TORCH_DTYPE.get(x.dtype)
+        if xd is None:
+            raise B.B200QError(B.ERR_INVALID_CONFIG, f"activation dtype {x.dtype} is not bf16/fp32")
+        if out is None:
+            out = torch.empty((m, w.n), dtype=out_dtype or torch.float32, device=x.device)
+        yd = _TORCH_DTYPE.get(out.dtype)
+        if yd is None:
+            raise B.B200QError(B.ERR_INVALID_CONFIG, f"output dtype {out.dtype} is not bf16/fp32")
+        ldx = x.stride(0) if m > 1 else max(x.shape[1], 1)
+        ldy = out.stride(0) if m > 1 else max(out.shape[1], 1)
+        self._check(
+            B.lib().b200q_matmul(
+                self._h, w._h, c_void_p(x.data_ptr()), xd, m, ldx, c_void_p(out.data_ptr()), yd, ldy,
+                self._stream_ptr(stream),
+            )
+        )
+        return out
+
+    def project_multi(self, ws: Sequence[ProjectionWeight], x, outs=None, out_dtype=None, stream=None):
+        """Several weights (same type and K) applied to one activation in one launch: gate+up, Q+K."""
+        torch = _torch()
+        if x.dim() == 1:
+            x = x.unsqueeze(0)
+        if x.stride(-1) != 1:
+            x = x.contiguous()
+        m = x.shape[0]
+        xd = _TORCH_DTYPE.get(x.dtype)
+        if xd is None:
+            raise B.B200QError(B.ERR_INVALID_CONFIG, f"activation dtype {x.dtype} is not bf16/fp32")
+        if outs is None:
+            outs = [torch.empty((m, w.n), dtype=out_dtype or torch.float32, device=x.device) for w in ws]
+        yd = _TORCH_DTYPE[outs[0].dtype]
+        n = len(ws)
+        wh = (c_void_p * n)(*[w._h for w in ws])
+        yp = (c_void_p * n)(*[c_void_p(o.data_ptr()) for o in outs])
+        ldy = (c_int64 * n)(*[(o.stride(0) if m > 1 else max(o.shape[1], 1)) for o in outs])
+        ldx = x.stride(0) if m > 1 else max(x.shape[1], 1)
+        self._check(
+            B.lib().b200q_matmul_multi(
+                self._h, wh, n, c_void_p(x.data_ptr()), xd, m, ldx, yp, yd, ldy, self._stream_ptr(stream)
+            )
+        )
+        return outs
+
+    # -- host-buffer path (the reference's own boundary: host in, host out) ------------------
+    def project_host(self, w: ProjectionWeight, x: np.ndarray, x_dtype: int = B.TYPE_F32, out: np.ndarray | None = None,
+                     y_dtype: int = B.TYPE_F32) -> np.ndarray:
+        """x is a host array: float32, or uint16 holding bf16 bits when x_dtype is TYPE_BF16."""
+        x = np.ascontiguousarray(x)
+        if x.ndim == 1:
+            x = x[None, :]
+        m, k = x.shape
+        if out is None:
+            out = np.empty((m, w.n), dtype=np.float32 if y_dtype == B.TYPE_F32 else np.uint16)
+        self._check(
+            B.lib().b200q_matmul_host(
+                self._h, w._h, c_void_p(x.ctypes.data), x_dtype, m, k, c_void_p(out.ctypes.data), y_dtype, max(out.shape[1], 1)
+            )
+        )
+        return out
+
+    def project_host_ptr(self, ws: Sequence[ProjectionWeight], x_ptr: int, x_dtype: int, m: int, ldx: int,
+                         y_ptrs: Sequence[int], y_dtype: int, ldys: Sequence[int]) -> None:
+        """Raw-pointer form for pinned host buffers (one launch for 1..4 weights sharing x)."""
+        n = len(ws)
+        wh = (c_void_p * n)(*[w._h for w in ws])
+        yp = (c_void_p * n)(*[c_void_p(p) for p in y_ptrs])
+        ldy = (c_int64 * n)(*ldys)
+        self._check(B.lib().b200q_matmul_multi_host(self._h, wh, n, c_void_p(x_ptr), x_dtype, m, ldx, yp, y_dtype, ldy))
+
+    # -- tensor-parallel exchange --------------------------------------------------------------
+    def tp_init(self, rank: int, world: int, unique_id: bytes) -> None:
+        buf = ctypes.create_string_buffer(unique_id, 128)
+        self._check(B.lib().b200q_tp_init(self._h, rank, world, buf))
+
+    def allreduce(self, y, stream=None) -> None:
+        torch = _torch()
+        self._check(
+            B.lib().b200q_allreduce(self._h, c_void_p(y.data_ptr()), y.numel(), _TORCH_DTYPE[y.dtype], self._stream_ptr(stream))
+        )
+
+    def tp_finalize(self) -> None:
+        self._check(B.lib().b200q_tp_finalize(self._h))
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def tp_unique_id() -> bytes:
+    buf = ctypes.create_string_buffer(128)
+    st = B.lib().b200q_tp_unique_id(buf)
+    if st:
+        raise B.B200QError(st, "NCCL unique id (is libnccl.so.2 loadable?)")
+    return buf.raw

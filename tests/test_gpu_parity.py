@@ -1,0 +1,226 @@
+"""GPU parity: the CUDA path through the C ABI against the CPU oracle and the golden vectors.
+
+Tolerances (fixed by the task statement): dequantized weights bit-exact; fp32-accumulated
+outputs within max relative error 1e-3 for M <= 16 (fp32 output) and 5e-3 for bf16 output, where
+"relative" is |err| <= rel * max(|ref|, rms(ref)).
+"""
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+torch = pytest.importorskip("torch")
+import magnitude_b200 as mb  # noqa: E402
+from magnitude_b200 import ggml_quant as gq  # noqa: E402
+
+GOLD = Path(__file__).resolve().parent / "golden" / "ggml_blocks.npz"
+TYPES = [mb.TYPE_Q4_K, mb.TYPE_Q6_K, mb.TYPE_Q8_0]
+REL_DECODE = 1e-3
+REL_BF16 = 5e-3
+
+
+def _weights(orc, qt, n, k, seed, use_oracle_quantizer=True):
+    rng = np.random.default_rng(seed)
+    w = rng.standard_normal((n, k), dtype=np.float32) * np.float32(0.02)
+    return orc.quantize(qt, w) if use_oracle_quantizer else gq.quantize(qt, w)
+
+
+def _acts(m, k, seed, dtype):
+    rng = np.random.default_rng(seed)
+    x = torch.from_numpy(rng.standard_normal((m, k), dtype=np.float32)).cuda()
+    return x.to(dtype)
+
+
+@pytest.mark.parametrize("qt", TYPES)
+def test_dequantize_golden_bit_exact(backend, qt):
+    g = np.load(GOLD)
+    packed = g[f"packed_{qt}"]
+    n, k = packed.shape[0], 768
+    w = backend.upload(qt, packed, n, k)
+    got = backend.dequantize(w).cpu().numpy()
+    assert np.array_equal(got.view(np.uint32), g[f"dequant_{qt}"].view(np.uint32))
+
+
+@pytest.mark.parametrize("qt", TYPES)
+@pytest.mark.parametrize("n,k", [(1, 256), (3, 512), (37, 2304), (64, 5120)])
+def test_dequantize_matches_oracle(backend, orc, qt, n, k):
+    packed = _weights(orc, qt, n, k, seed=n + k)
+    w = backend.upload(qt, packed, n, k)
+    got = backend.dequantize(w).cpu().numpy()
+    ref = orc.dequantize(qt, packed, k)
+    assert np.array_equal(got.view(np.uint32), ref.view(np.uint32))
+
+
+def test_dequantize_q8_0_ragged_k(backend, orc):
+    # Q8_0 rows need only be a multiple of 32 weights; the device layout pads them to 256
+    for k in (32, 96, 288):
+        packed = _weights(orc, mb.TYPE_Q8_0, 5, k, seed=k)
+        w = backend.upload(mb.TYPE_Q8_0, packed, 5, k)
+        got = backend.dequantize(w).cpu().numpy()
+        assert np.array_equal(got.view(np.uint32), orc.dequantize(mb.TYPE_Q8_0, packed, k).view(np.uint32))
+
+
+@pytest.mark.parametrize("qt", TYPES)
+@pytest.mark.parametrize("m", [1, 2, 3, 4])
+@pytest.mark.parametrize("n,k", [(1, 256), (2, 512), (3, 768), (17, 4096), (301, 2304), (130, 5120)])
+def test_decode_small_shapes(backend, orc, qt, m, n, k):
+    packed = _weights(orc, qt, n, k, seed=7 * n + k + m)
+    w = backend.upload(qt, packed, n, k)
+    x = _acts(m, k, seed=m, dtype=torch.bfloat16)
+    y = backend.project(w, x)
+    backend.sync()
+    assert backend.last_route()[0] == mb.ROUTE_GEMV
+    ref = orc.matmul_exact(qt, packed, n, k, x.float().cpu().numpy())
+    ok, worst = orc.within_tolerance(y.cpu().numpy(), ref, REL_DECODE)
+    assert ok, f"worst error {worst:.3f} x tolerance"
+
+
+@pytest.mark.parametrize("qt", TYPES)
+def test_decode_fp32_activation_and_bf16_output(backend, orc, qt):
+    n, k = 96, 1024
+    packed = _weights(orc, qt, n, k, seed=3)
+    w = backend.upload(qt, packed, n, k)
+    x = _acts(2, k, seed=9, dtype=torch.float32)
+    ref = orc.matmul_exact(qt, packed, n, k, x.cpu().numpy())
+    y32 = backend.project(w, x)
+    y16 = backend.project(w, x, out_dtype=torch.bfloat16)
+    backend.sync()
+    assert orc.within_tolerance(y32.cpu().numpy(), ref, REL_DECODE)[0]
+    assert orc.within_tolerance(y16.float().cpu().numpy(), ref, REL_BF16)[0]
+
+
+def test_q8_0_ragged_k_product(backend, orc):
+    for k in (32, 160, 4128):
+        packed = _weights(orc, mb.TYPE_Q8_0, 9, k, seed=k)
+        w = backend.upload(mb.TYPE_Q8_0, packed, 9, k)
+        x = _acts(1, k, seed=k, dtype=torch.float32)
+        y = backend.project(w, x)
+        backend.sync()
+        ref = orc.matmul_exact(mb.TYPE_Q8_0, packed, 9, k, x.cpu().numpy())
+        assert orc.within_tolerance(y.cpu().numpy(), ref, REL_DECODE)[0]
+
+
+def test_config1_q8_0_reference_cpu_case(backend, orc):
+    # 4096 x 4096 Q8_0, fp32 activation, fp32 output
+    n = k = 4096
+    rng = np.random.default_rng(0)
+    packed = orc.quantize(mb.TYPE_Q8_0, rng.standard_normal((n, k), dtype=np.float32) * np.float32(0.02))
+    x = np.random.default_rng(1).standard_normal((1, k), dtype=np.float32)
+    w = backend.upload(mb.TYPE_Q8_0, packed, n, k)
+    y = backend.project(w, torch.from_numpy(x).cuda())
+    backend.sync()
+    ref = orc.matmul_exact(mb.TYPE_Q8_0, packed, n, k, x)
+    ok, worst = orc.within_tolerance(y.cpu().numpy(), ref, REL_DECODE)
+    assert ok, worst
+
+
+@pytest.mark.parametrize("n,k", [(14336, 4096), (4096, 14336)])
+def test_config2_q4_k_decode_full_size(backend, orc, n, k):
+    packed = gq.synth_weights(mb.TYPE_Q4_K, n, k, seed=0)
+    w = backend.upload(mb.TYPE_Q4_K, packed, n, k)
+    x = _acts(1, k, seed=1, dtype=torch.bfloat16)
+    y = backend.project(w, x)
+    backend.sync()
+    ref = orc.matmul_exact(mb.TYPE_Q4_K, packed, n, k, x.float().cpu().numpy())
+    ok, worst = orc.within_tolerance(y.cpu().numpy(), ref, REL_DECODE)
+    assert ok, worst
+    # dequantized weights of the full tensor, bit for bit
+    got = backend.dequantize(w).cpu().numpy()
+    assert np.array_equal(got.view(np.uint32), orc.dequantize(mb.TYPE_Q4_K, packed, k).view(np.uint32))
+
+
+def test_linearity_full_size(backend):
+    # size-independent property: W(a*x1 + x2) = a*W x1 + W x2 (up to the decode tolerance)
+    n, k = 4096, 14336
+    packed = gq.synth_weights(mb.TYPE_Q6_K, n, k, seed=6)
+    w = backend.upload(mb.TYPE_Q6_K, packed, n, k)
+    x1 = _acts(1, k, seed=11, dtype=torch.float32)
+    x2 = _acts(1, k, seed=12, dtype=torch.float32)
+    y1, y2 = backend.project(w, x1), backend.project(w, x2)
+    y3 = backend.project(w, 2.0 * x1 + x2)
+    backend.sync()
+    ref = (2.0 * y1 + y2).cpu().numpy()
+    err = np.abs(y3.cpu().numpy() - ref)
+    rms = np.sqrt(np.mean(ref ** 2))
+    assert np.all(err <= 2e-3 * np.maximum(np.abs(ref), rms))
+
+
+def test_multi_weight_launch_matches_single(backend, orc):
+    k = 2048
+    ps = [_weights(orc, mb.TYPE_Q4_K, n, k, seed=n) for n in (129, 64, 7)]
+    ws = [backend.upload(mb.TYPE_Q4_K, p, p.shape[0], k) for p in ps]
+    x = _acts(1, k, seed=5, dtype=torch.bfloat16)
+    outs = backend.project_multi(ws, x)
+    singles = [backend.project(w, x) for w in ws]
+    backend.sync()
+    for a, b in zip(outs, singles):
+        assert torch.equal(a, b)
+
+
+def test_host_buffer_path(backend, orc):
+    n, k = 200, 1536
+    packed = _weights(orc, mb.TYPE_Q6_K, n, k, seed=2)
+    w = backend.upload(mb.TYPE_Q6_K, packed, n, k)
+    x = np.random.default_rng(3).standard_normal((2, k), dtype=np.float32)
+    y = backend.project_host(w, x)
+    ref = orc.matmul_exact(mb.TYPE_Q6_K, packed, n, k, x)
+    assert orc.within_tolerance(y, ref, REL_DECODE)[0]
+    xb = gq.f32_to_bf16_bits(x)
+    yb = backend.project_host(w, xb, x_dtype=mb.TYPE_BF16)
+    refb = orc.matmul_exact(mb.TYPE_Q6_K, packed, n, k, orc.bf16_to_f32(xb))
+    assert orc.within_tolerance(yb, refb, REL_DECODE)[0]
+
+
+def test_edge_cases_and_errors(backend, orc):
+    k = 512
+    packed = _weights(orc, mb.TYPE_Q4_K, 8, k, seed=1)
+    w = backend.upload(mb.TYPE_Q4_K, packed, 8, k)
+    # M = 0 is a no-op
+    x0 = torch.empty((0, k), dtype=torch.bfloat16, device="cuda")
+    assert backend.project(w, x0).shape == (0, 8)
+    # N = 0
+    w0 = backend.upload(mb.TYPE_Q4_K, np.zeros((0,), np.uint8), 0, k)
+    assert backend.project(w0, _acts(1, k, 0, torch.bfloat16)).shape == (1, 0)
+    # all-zero activation -> exact zeros; non-finite activation -> non-finite output, no hang
+    z = backend.project(w, torch.zeros((1, k), dtype=torch.bfloat16, device="cuda"))
+    backend.sync()
+    assert torch.count_nonzero(z) == 0
+    bad = _acts(1, k, 4, torch.float32)
+    bad[0, 17] = float("inf")
+    yb = backend.project(w, bad)
+    backend.sync()
+    assert not torch.isfinite(yb).all()
+    # errors: bad type, K not a block multiple, wrong byte count, wrong dtype
+    with pytest.raises(mb.B200QError) as e:
+        backend.upload(2, packed, 8, k)
+    assert e.value.status == 1
+    with pytest.raises(mb.B200QError):
+        backend.upload(mb.TYPE_Q4_K, packed, 8, k + 32)
+    with pytest.raises(mb.B200QError):
+        backend.upload(mb.TYPE_Q4_K, packed[:, :-1], 8, k)
+    with pytest.raises(mb.B200QError):
+        backend.project(w, torch.zeros((1, k), dtype=torch.float16, device="cuda"))
+    # the context stays usable after errors
+    y = backend.project(w, _acts(1, k, 8, torch.bfloat16))
+    backend.sync()
+    assert torch.isfinite(y).all()
+
+
+def test_one_hot_sub_blocks(backend, orc):
+    # every sub-block index separately: an activation that is non-zero in one 16-weight slice
+    k = 512
+    for qt in TYPES:
+        packed = _weights(orc, qt, 4, k, seed=qt)
+        w = backend.upload(qt, packed, 4, k)
+        wf = orc.dequantize(qt, packed, k).astype(np.float64)
+        xs = np.zeros((k // 16, k), dtype=np.float32)
+        for j in range(k // 16):
+            xs[j, 16 * j:16 * j + 16] = 1.0 + 0.25 * (j % 3)
+        for j0 in range(0, k // 16, 4):
+            x = torch.from_numpy(xs[j0:j0 + 4]).cuda()
+            y = backend.project(w, x)
+            backend.sync()
+            ref = xs[j0:j0 + 4].astype(np.float64) @ wf.T
+            assert np.allclose(y.cpu().numpy(), ref, rtol=1e-3, atol=1e-6), (qt, j0)
