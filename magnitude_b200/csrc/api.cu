@@ -74,6 +74,7 @@ struct b200q_ctx {
     int device = 0;
     int sm_count = 0;
     size_t smem_optin = 0;
+    size_t smem_sm = 0;
     int *status_dev = nullptr;
     char err[512] = {0};
     int last_route = B200Q_ROUTE_NONE;
@@ -86,7 +87,7 @@ struct b200q_ctx {
     void *hy_dev = nullptr;
     size_t hy_bytes = 0;
     // tunables (environment overrides for experiments)
-    int gemv_warps = 0, gemv_depth = 0, gemv_grid = 0;
+    int gemv_warps = 0, gemv_depth = 0, gemv_grid = 0, gemv_smem = 0, gemv_rows = 0, gemv_debug = 0, gemv_pdl = 1;
     // tensor parallel
     NcclComm comm = nullptr;
     int tp_rank = 0, tp_world = 1;
@@ -209,10 +210,14 @@ b200q_status run_gemv(b200q_ctx *ctx, const b200q_weight *const *w, int nw, cons
     a.row_bytes = w[0]->row_bytes;
     a.status = ctx->status_dev;
     a.sm_count = ctx->sm_count;
-    a.smem_limit = ctx->smem_optin;
+    a.smem_limit = (ctx->gemv_smem > 0 && (size_t)ctx->gemv_smem < ctx->smem_optin) ? (size_t)ctx->gemv_smem : ctx->smem_optin;
     a.warps = ctx->gemv_warps;
     a.depth = ctx->gemv_depth;
     a.grid = ctx->gemv_grid;
+    a.rows_per_item = ctx->gemv_rows;
+    a.debug = ctx->gemv_debug;
+    a.pdl = ctx->gemv_pdl;
+    a.smem_sm = ctx->smem_sm;
     cudaError_t e = gemv_launch(a, st);
     if (e != cudaSuccess) return cuda_fail(ctx, e, "gemv launch");
     return B200Q_OK;
@@ -322,6 +327,7 @@ b200q_status b200q_ctx_create(int32_t device, b200q_ctx **out) {
     }
     ctx->sm_count = prop.multiProcessorCount;
     ctx->smem_optin = prop.sharedMemPerBlockOptin;
+    ctx->smem_sm = prop.sharedMemPerMultiprocessor;
     if ((e = cudaMalloc(&ctx->status_dev, 256)) != cudaSuccess || (e = cudaMemset(ctx->status_dev, 0, 256)) != cudaSuccess) {
         delete ctx;
         return e == cudaErrorMemoryAllocation ? B200Q_ERR_OVERLOADED : B200Q_ERR_BACKEND;
@@ -329,6 +335,10 @@ b200q_status b200q_ctx_create(int32_t device, b200q_ctx **out) {
     ctx->gemv_warps = env_int("B200Q_GEMV_WARPS", 0);
     ctx->gemv_depth = env_int("B200Q_GEMV_DEPTH", 0);
     ctx->gemv_grid = env_int("B200Q_GEMV_GRID", 0);
+    ctx->gemv_smem = env_int("B200Q_GEMV_SMEM", 0);
+    ctx->gemv_rows = env_int("B200Q_GEMV_ROWS", 0);
+    ctx->gemv_debug = env_int("B200Q_GEMV_DEBUG", 0);
+    ctx->gemv_pdl = env_int("B200Q_GEMV_PDL", 1);
     *out = ctx;
     return B200Q_OK;
 }

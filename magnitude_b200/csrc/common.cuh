@@ -138,6 +138,15 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t
         : "memory");
 }
 
+// Programmatic dependent launch: a kernel launched with the programmatic-serialization attribute
+// may start while its predecessor in the stream still runs; it must call pdl_wait() before it
+// reads anything the predecessor writes or writes anything the predecessor may still read.
+// Both are no-ops for an ordinary launch.
+__device__ __forceinline__ void pdl_launch_dependents() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // dp4a: d = c + sum_i a.b[i] * b.b[i] with per-operand signedness
 __device__ __forceinline__ int dp4a_us(uint32_t a_u8, uint32_t b_s8, int c) {
     int d;

@@ -3,19 +3,23 @@
 // Y[m][n] = sum_k X[m][k] * dequant(W)[n][k]   for the streaming layout of common.cuh.
 //
 // Design (one persistent CTA per SM, no CPU fallback, no cluster multicast):
-//   * every warp owns a private ring of shared-memory slots and streams its own rows into it
-//     with 1-D bulk copies (cp.async.bulk, completion counted on an mbarrier).  A work item is
-//     R rows x one K-chunk of KC superblock records; the ring keeps D items in flight per warp,
-//     so an SM holds CW * D * R * ~2.3 KB of HBM reads in flight without spending registers.
+//   * CW consumer warps and one producer warp.  Every consumer warp owns a private ring of
+//     shared-memory slots; lane w of the producer warp keeps consumer w's ring full with 1-D
+//     bulk copies (cp.async.bulk, completion counted on a "full" mbarrier) and learns that a slot
+//     was consumed from an "empty" mbarrier.  A work item is R rows x one chunk of 8 superblock
+//     records (2048 weights per row); the rings keep CW * D items in flight per SM, so HBM reads
+//     stay outstanding without spending registers on them.
 //   * the activation is converted once per CTA into a 16-bit fixed-point form in shared memory:
-//     per 32 weights one fp32 scale sx and per weight a signed high byte and an unsigned low
-//     byte (x ~= sx * (256*hi + lo), relative step 2^-15 of the block maximum).  The packed
-//     4/6/8-bit weights then multiply the two byte planes with dp4a, four weights per
-//     instruction, and block results are scaled and accumulated in fp32.
+//     per 32 weights one fp32 scale sx and per weight two signed bytes (x ~= sx * (256*hi + lo),
+//     lo in [-128, 127]; relative step 2^-15 of the block maximum).  The packed 4/6/8-bit weights
+//     multiply the two byte planes with dp4a, four weights per instruction, and block results are
+//     scaled and accumulated in fp32.
 //   * sub-block scales and mins are unpacked in registers; the min term of Q4_K and the -32
-//     offset of Q6_K use per-16-weight integer sums of the activation computed in the prologue.
-//   * a row's partial sums live in the lanes of one warp and are combined by warp shuffles.
-//   * every mbarrier wait is bounded; on expiry the warp raises the status word and leaves.
+//     offset of Q6_K use per-block integer sums of the activation computed in the prologue.
+//   * one lane handles one 64-weight unit of each of the item's R rows, so the activation bytes
+//     it loads are reused R times; a row's partial sums live in the lanes of one warp and are
+//     combined by warp shuffles.
+//   * every mbarrier wait is bounded; on expiry the waiter raises the status word and leaves.
 #include "common.cuh"
 #include "kernels.h"
 
@@ -24,26 +28,27 @@ namespace b200q {
 namespace {
 
 constexpr int kMaxSeg = 4;
-constexpr int kMaxWarps = 16;
+constexpr int kMaxWarps = 15;    // consumer warps (+1 producer = 512 threads, 128 registers each)
 constexpr int kMaxDepth = 8;
+constexpr int KC = 8;            // superblock records per chunk: 32 units of 64 weights, one per lane
 
 template <int QT> struct GemvCfg;
-template <> struct GemvCfg<QT_Q4_K> { static constexpr int KC = 16; static constexpr int CHUNK = 16 * 144; };
-template <> struct GemvCfg<QT_Q8_0> { static constexpr int KC = 8;  static constexpr int CHUNK = 8 * 272; };
-template <> struct GemvCfg<QT_Q6_K> { static constexpr int KC = 16; static constexpr int CHUNK = 2 * 1680; };
+template <> struct GemvCfg<QT_Q4_K> { static constexpr int CHUNK = KC * 144; };
+template <> struct GemvCfg<QT_Q8_0> { static constexpr int CHUNK = KC * 272; };
+template <> struct GemvCfg<QT_Q6_K> { static constexpr int CHUNK = 1680; };
 
 struct GemvSeg {
     const uint8_t *w;   // streaming-layout rows
     void *y;            // output base (row m at y + m*ldy elements)
     long long ldy;
     int n;              // rows
-    int unit_begin;     // first unit (R rows each) of this segment in the global unit list
+    int row_begin;      // first virtual row of this segment (segments are concatenated)
 };
 
 struct GemvParams {
     GemvSeg seg[kMaxSeg];
     int nseg;
-    int total_units;
+    int total_rows;
     const void *x;
     long long ldx;
     int x_is_bf16;
@@ -53,7 +58,10 @@ struct GemvParams {
     int K, Kpad, nsb;
     long long row_bytes;
     int nchunks;
+    unsigned bytes_full, bytes_tail;   // bytes of one row's chunk: all but the last / the last
+    int partial_bytes;  // shared-memory bytes of the per-(row, chunk) partial sums
     int depth;          // ring slots per warp
+    int debug;          // experiments only: 1 = stream without computing, 2 = compute without streaming
     int *status;
 };
 
@@ -72,16 +80,12 @@ template <int QT> __device__ __forceinline__ int xplane_off(int k, int units16) 
 
 struct XView {            // shared-memory views of one activation row in fixed-point form
     const uint8_t *xh;    // signed high bytes
-    const uint8_t *xl;    // unsigned low bytes
+    const uint8_t *xl;    // signed low bytes
     const float *sx;      // per 32 weights
-    const int *isum;      // per 16 weights: sum of the 16-bit integers
+    const int *isum;      // sum of the 16-bit integers: per 32 weights (Q4_K) or per 16 (Q6_K)
 };
 
-// ---------------------------------------------------------------------------------------------
-// per-type work on one 64-weight unit of one row, for MT activation rows
-// ---------------------------------------------------------------------------------------------
-
-struct XRegs {          // one 64-weight unit of one activation row: 4 groups of 16 weights
+struct XRegs {            // one 64-weight unit of one activation row: 4 groups of 16 weights
     uint4 h[4];
     uint4 l[4];
 };
@@ -94,12 +98,11 @@ __device__ __forceinline__ void load_x(XRegs &xr, const XView &xv, int unit, int
     }
 }
 
-// Weights of one 64-weight unit of one row, unpacked to bytes once and reused for every
-// activation row.
+// Weights of one 64-weight unit of one row, unpacked once and reused for every activation row.
 template <int QT> struct WRegs;
 
 template <> struct WRegs<QT_Q4_K> {
-    uint32_t lo[8], hi[8];   // low nibbles = weights 0..31 of the group, high nibbles = 32..63
+    uint32_t lo[8], hi[8];   // low nibbles = weights 0..31 of the group; hi keeps 16 * nibble
     int scA, mnA, scB, mnB;
     float d, dmin;
     // `rec` points at the 144-byte block, j = 64-weight group 0..3
@@ -111,12 +114,21 @@ template <> struct WRegs<QT_Q4_K> {
         for (int i = 0; i < 4; ++i) {
             const uint32_t a = word_of(qa, i), b = word_of(qb, i);
             lo[i] = a & 0x0F0F0F0Fu;
-            hi[i] = (a >> 4) & 0x0F0F0F0Fu;
+            hi[i] = a & 0xF0F0F0F0u;
             lo[4 + i] = b & 0x0F0F0F0Fu;
-            hi[4 + i] = (b >> 4) & 0x0F0F0F0Fu;
+            hi[4 + i] = b & 0xF0F0F0F0u;
         }
-        q4k_scale_min(hdr.y, hdr.z, hdr.w, 2 * j, scA, mnA);
-        q4k_scale_min(hdr.y, hdr.z, hdr.w, 2 * j + 1, scB, mnB);
+        // 6-bit scales / mins of sub-blocks 2j and 2j+1 (bytes 2(j&1), 2(j&1)+1 of each word)
+        const int sh = 16 * (j & 1);
+        const uint32_t y2 = (hdr.y >> sh) & 0xFFFFu, z2 = (hdr.z >> sh) & 0xFFFFu, w2 = (hdr.w >> sh) & 0xFFFFu;
+        const uint32_t sc_lo = y2 & 0x3F3Fu, mn_lo = z2 & 0x3F3Fu;
+        const uint32_t sc_hi = (w2 & 0x0F0Fu) | ((y2 >> 2) & 0x3030u);
+        const uint32_t mn_hi = ((w2 >> 4) & 0x0F0Fu) | ((z2 >> 2) & 0x3030u);
+        const uint32_t sc2 = (j >= 2) ? sc_hi : sc_lo, mn2 = (j >= 2) ? mn_hi : mn_lo;
+        scA = sc2 & 0xFF;
+        scB = sc2 >> 8;
+        mnA = mn2 & 0xFF;
+        mnB = mn2 >> 8;
         d = half_bits_to_float(hdr.x);
         dmin = half_bits_to_float(hdr.x >> 16);
     }
@@ -126,20 +138,20 @@ template <> struct WRegs<QT_Q4_K> {
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             hA = dp4a_us(lo[i], word_of(xr.h[0], i), hA);
-            lA = dp4a_uu(lo[i], word_of(xr.l[0], i), lA);
+            lA = dp4a_us(lo[i], word_of(xr.l[0], i), lA);
             hA = dp4a_us(lo[4 + i], word_of(xr.h[1], i), hA);
-            lA = dp4a_uu(lo[4 + i], word_of(xr.l[1], i), lA);
+            lA = dp4a_us(lo[4 + i], word_of(xr.l[1], i), lA);
             hB = dp4a_us(hi[i], word_of(xr.h[2], i), hB);
-            lB = dp4a_uu(hi[i], word_of(xr.l[2], i), lB);
+            lB = dp4a_us(hi[i], word_of(xr.l[2], i), lB);
             hB = dp4a_us(hi[4 + i], word_of(xr.h[3], i), hB);
-            lB = dp4a_uu(hi[4 + i], word_of(xr.l[3], i), lB);
+            lB = dp4a_us(hi[4 + i], word_of(xr.l[3], i), lB);
         }
         const float2 sx = *reinterpret_cast<const float2 *>(xv.sx + 2 * gu);
-        const int4 is = *reinterpret_cast<const int4 *>(xv.isum + 4 * gu);
+        const int2 is = *reinterpret_cast<const int2 *>(xv.isum + 2 * gu);
         const float fa = (float)((hA * 256 + lA) * scA);
-        const float fb = (float)((hB * 256 + lB) * scB);
-        const float ua = (float)(mnA * (is.x + is.y));
-        const float ub = (float)(mnB * (is.z + is.w));
+        const float fb = (float)(((hB * 256 + lB) >> 4) * scB);   // hi held 16 * nibble: exact shift
+        const float ua = (float)(mnA * is.x);
+        const float ub = (float)(mnB * is.y);
         return sx.x * (d * fa - dmin * ua) + sx.y * (d * fb - dmin * ub);
     }
 };
@@ -160,13 +172,13 @@ template <> struct WRegs<QT_Q8_0> {
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             hA = dp4a_ss(word_of(q[0], i), word_of(xr.h[0], i), hA);
-            lA = dp4a_su(word_of(q[0], i), word_of(xr.l[0], i), lA);
+            lA = dp4a_ss(word_of(q[0], i), word_of(xr.l[0], i), lA);
             hA = dp4a_ss(word_of(q[1], i), word_of(xr.h[1], i), hA);
-            lA = dp4a_su(word_of(q[1], i), word_of(xr.l[1], i), lA);
+            lA = dp4a_ss(word_of(q[1], i), word_of(xr.l[1], i), lA);
             hB = dp4a_ss(word_of(q[2], i), word_of(xr.h[2], i), hB);
-            lB = dp4a_su(word_of(q[2], i), word_of(xr.l[2], i), lB);
+            lB = dp4a_ss(word_of(q[2], i), word_of(xr.l[2], i), lB);
             hB = dp4a_ss(word_of(q[3], i), word_of(xr.h[3], i), hB);
-            lB = dp4a_su(word_of(q[3], i), word_of(xr.l[3], i), lB);
+            lB = dp4a_ss(word_of(q[3], i), word_of(xr.l[3], i), lB);
         }
         const float2 sx = *reinterpret_cast<const float2 *>(xv.sx + 2 * gu);
         return (dA * sx.x) * (float)(hA * 256 + lA) + (dB * sx.y) * (float)(hB * 256 + lB);
@@ -208,7 +220,7 @@ template <> struct WRegs<QT_Q6_K> {
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 ah[c] = dp4a_us(q[c][i], word_of(xr.h[c], i), ah[c]);
-                al[c] = dp4a_uu(q[c][i], word_of(xr.l[c], i), al[c]);
+                al[c] = dp4a_us(q[c][i], word_of(xr.l[c], i), al[c]);
             }
         }
         // 32-weight scale blocks 8*sb + 4h + c ; 16-weight sums 16*sb + 8h + 2c + ph
@@ -229,147 +241,265 @@ template <> struct WRegs<QT_Q6_K> {
 // prologue: activation row -> fixed-point planes in shared memory
 // ---------------------------------------------------------------------------------------------
 
-template <int QT>
-__device__ __forceinline__ void prep_row(const GemvParams &p, int m, uint8_t *xh, uint8_t *xl,
-                                         float *sx, int *isum, int units16) {
-    const int T = blockDim.x;
-    for (int k0 = threadIdx.x * 8; k0 < p.Kpad; k0 += T * 8) {
-        float v[8];
-        if (k0 < p.K) {
-            if (p.x_is_bf16) {
-                const __nv_bfloat16 *xr = reinterpret_cast<const __nv_bfloat16 *>(p.x) + (long long)m * p.ldx + k0;
-                if (p.x_vec_ok) {
-                    const uint4 raw = *reinterpret_cast<const uint4 *>(xr);
-                    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+constexpr float kXMax = 32512.f;   // 127 * 256: hi = (q + 128) >> 8 stays within a signed byte
+
+// loads 8 consecutive activation elements starting at k0 (zeros beyond K)
+__device__ __forceinline__ void load_x8(const GemvParams &p, int m, int k0, float (&v)[8]) {
+    if (k0 >= p.K) {
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        v[2 * i] = __uint_as_float(w[i] << 16);
-                        v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
-                    }
-                } else {
+        for (int i = 0; i < 8; ++i) v[i] = 0.f;
+        return;
+    }
+    if (p.x_is_bf16) {
+        const __nv_bfloat16 *xr = reinterpret_cast<const __nv_bfloat16 *>(p.x) + (long long)m * p.ldx + k0;
+        if (p.x_vec_ok) {
+            const uint4 raw = *reinterpret_cast<const uint4 *>(xr);
+            const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) v[i] = __bfloat162float(xr[i]);
-                }
-            } else {
-                const float *xr = reinterpret_cast<const float *>(p.x) + (long long)m * p.ldx + k0;
-                if (p.x_vec_ok) {
-                    const float4 a = *reinterpret_cast<const float4 *>(xr);
-                    const float4 b = *reinterpret_cast<const float4 *>(xr + 4);
-                    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
-                    v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) v[i] = xr[i];
-                }
+            for (int i = 0; i < 4; ++i) {
+                v[2 * i] = __uint_as_float(w[i] << 16);
+                v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
             }
         } else {
 #pragma unroll
-            for (int i = 0; i < 8; ++i) v[i] = 0.f;
+            for (int i = 0; i < 8; ++i) v[i] = __bfloat162float(xr[i]);
         }
-        float amax = 0.f;
-        bool bad = false;
+    } else {
+        const float *xr = reinterpret_cast<const float *>(p.x) + (long long)m * p.ldx + k0;
+        if (p.x_vec_ok) {
+            const float4 a = *reinterpret_cast<const float4 *>(xr);
+            const float4 b = *reinterpret_cast<const float4 *>(xr + 4);
+            v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+            v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+        } else {
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            amax = fmaxf(amax, fabsf(v[i]));
-            bad |= !(fabsf(v[i]) <= 3.0e38f);   // inf or nan
+            for (int i = 0; i < 8; ++i) v[i] = xr[i];
         }
-        // four consecutive lanes cover one 32-weight block
-        amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
-        amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 2));
-        unsigned badm = __ballot_sync(0xFFFFFFFFu, bad);
-        const unsigned grp = 0xFu << ((threadIdx.x & 31) & ~3);
-        const bool blk_bad = (badm & grp) != 0;
-        const float inv = (amax > 0.f && !blk_bad) ? 32767.f / amax : 0.f;
-        int q[8], sum = 0;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            q[i] = blk_bad ? 0 : __float2int_rn(v[i] * inv);
-            q[i] = max(-32767, min(32767, q[i]));
-            sum += q[i];
-        }
-        uint32_t h0 = 0, h1 = 0, l0 = 0, l1 = 0;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            h0 |= (uint32_t)((q[i] >> 8) & 0xFF) << (8 * i);
-            l0 |= (uint32_t)(q[i] & 0xFF) << (8 * i);
-            h1 |= (uint32_t)((q[4 + i] >> 8) & 0xFF) << (8 * i);
-            l1 |= (uint32_t)(q[4 + i] & 0xFF) << (8 * i);
-        }
-        const int off = xplane_off<QT>(k0, units16);
-        *reinterpret_cast<uint2 *>(xh + off) = make_uint2(h0, h1);
-        *reinterpret_cast<uint2 *>(xl + off) = make_uint2(l0, l1);
-        const int sum16 = sum + __shfl_xor_sync(0xFFFFFFFFu, sum, 1);
-        if ((threadIdx.x & 1) == 0) isum[k0 >> 4] = sum16;
-        if ((threadIdx.x & 3) == 0)
-            sx[k0 >> 5] = blk_bad ? __int_as_float(0x7FC00000) : amax * (1.0f / 32767.f);
     }
+}
+
+template <int QT>
+__device__ __forceinline__ void prep_store8(const float (&v)[8], int k0, uint8_t *xh, uint8_t *xl, float *sx,
+                                            int *isum, int units16) {
+    float amax = 0.f;
+    bool bad = false;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        amax = fmaxf(amax, fabsf(v[i]));
+        bad |= !(fabsf(v[i]) <= 3.0e38f);   // inf or nan
+    }
+    // four consecutive lanes cover one 32-weight block
+    amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 2));
+    const unsigned badm = __ballot_sync(0xFFFFFFFFu, bad);
+    const unsigned grp = 0xFu << ((threadIdx.x & 31) & ~3);
+    const bool blk_bad = (badm & grp) != 0;
+    const float inv = (amax > 0.f && !blk_bad) ? kXMax / amax : 0.f;
+    int q[8], sum = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        q[i] = blk_bad ? 0 : __float2int_rn(v[i] * inv);
+        q[i] = max(-32512, min(32512, q[i]));
+        sum += q[i];
+    }
+    uint32_t h0 = 0, h1 = 0, l0 = 0, l1 = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int ha = (q[i] + 128) >> 8, hb = (q[4 + i] + 128) >> 8;   // balanced digits
+        h0 |= (uint32_t)(ha & 0xFF) << (8 * i);
+        l0 |= (uint32_t)((q[i] - 256 * ha) & 0xFF) << (8 * i);
+        h1 |= (uint32_t)(hb & 0xFF) << (8 * i);
+        l1 |= (uint32_t)((q[4 + i] - 256 * hb) & 0xFF) << (8 * i);
+    }
+    const int off = xplane_off<QT>(k0, units16);
+    *reinterpret_cast<uint2 *>(xh + off) = make_uint2(h0, h1);
+    *reinterpret_cast<uint2 *>(xl + off) = make_uint2(l0, l1);
+    const int sum16 = sum + __shfl_xor_sync(0xFFFFFFFFu, sum, 1);
+    if (QT == QT_Q6_K) {
+        if ((threadIdx.x & 1) == 0) isum[k0 >> 4] = sum16;
+    } else {
+        const int sum32 = sum16 + __shfl_xor_sync(0xFFFFFFFFu, sum16, 2);
+        if ((threadIdx.x & 3) == 0) isum[k0 >> 5] = sum32;
+    }
+    if ((threadIdx.x & 3) == 0)
+        sx[k0 >> 5] = blk_bad ? __int_as_float(0x7FC00000) : amax * (1.0f / kXMax);
+}
+
+// Threads [0, T) convert activation row m.  Loads are issued four deep before any is used so a
+// long row costs one trip to L2, not one per 8 * T elements.
+template <int QT>
+__device__ __forceinline__ void prep_row(const GemvParams &p, int m, int T, uint8_t *xh, uint8_t *xl,
+                                         float *sx, int *isum, int units16) {
+    constexpr int PB = 4;
+    const int stride = T * 8;
+    for (int base = threadIdx.x * 8; base < p.Kpad; base += stride * PB) {
+        float v[PB][8];
+#pragma unroll
+        for (int b = 0; b < PB; ++b)
+            if (base + b * stride < p.Kpad) load_x8(p, m, base + b * stride, v[b]);
+#pragma unroll
+        for (int b = 0; b < PB; ++b)
+            if (base + b * stride < p.Kpad) prep_store8<QT>(v[b], base + b * stride, xh, xl, sx, isum, units16);
+    }
+}
+
+// Sum R per-lane values over the 32 lanes with a folding butterfly (6 shuffles for R = 4, 5 for
+// R = 2 instead of 5 per value).  The total of value r ends up in lane r * (32 / R).
+template <int R> __device__ __forceinline__ float fold_rows(const float (&a)[R], int lane) {
+    static_assert(R == 2 || R == 4, "R");
+    float y;
+    if (R == 4) {
+        const bool up = lane & 16;
+        float k0 = up ? a[2] : a[0], k1 = up ? a[3] : a[1];
+        const float s0 = up ? a[0] : a[2], s1 = up ? a[1] : a[3];
+        k0 += __shfl_xor_sync(0xFFFFFFFFu, s0, 16);
+        k1 += __shfl_xor_sync(0xFFFFFFFFu, s1, 16);
+        const bool up8 = lane & 8;
+        y = (up8 ? k1 : k0) + __shfl_xor_sync(0xFFFFFFFFu, up8 ? k0 : k1, 8);
+    } else {
+        const bool up = lane & 16;
+        y = (up ? a[1] : a[0]) + __shfl_xor_sync(0xFFFFFFFFu, up ? a[0] : a[1], 16);
+        y += __shfl_xor_sync(0xFFFFFFFFu, y, 8);
+    }
+    y += __shfl_xor_sync(0xFFFFFFFFu, y, 4);
+    y += __shfl_xor_sync(0xFFFFFFFFu, y, 2);
+    y += __shfl_xor_sync(0xFFFFFFFFu, y, 1);
+    return y;
 }
 
 // ---------------------------------------------------------------------------------------------
 // the kernel
 // ---------------------------------------------------------------------------------------------
 
+// (segment, row inside it) of virtual row vr; segments are concatenated in launch order
+__device__ __forceinline__ void locate_row(const GemvParams &p, int vr, int &s, int &row) {
+    s = 0;
+#pragma unroll
+    for (int i = 1; i < kMaxSeg; ++i)
+        if (i < p.nseg && vr >= p.seg[i].row_begin) s = i;
+    row = vr - p.seg[s].row_begin;
+}
+
+// M = 1 runs with 8 consumer warps + 1 producer and at most half an SM's registers and shared
+// memory, so two CTAs fit on an SM: under programmatic dependent launch the next projection's CTA
+// moves in beside this one and streams its weights while this one still computes.
+template <int MT> struct GemvShape {
+    static constexpr int kWarps = MT == 1 ? 8 : kMaxWarps;       // default consumer warps
+    static constexpr int kThreads = (kWarps + 1) * 32;
+    static constexpr int kBlocksPerSm = MT == 1 ? 2 : 1;
+};
+
 template <int QT, int MT, int R>
-__global__ void __launch_bounds__(kMaxWarps * 32, 1) gemv_kernel(const GemvParams p) {
+__global__ void __launch_bounds__(GemvShape<MT>::kThreads, GemvShape<MT>::kBlocksPerSm) gemv_kernel(const GemvParams p) {
     using Cfg = GemvCfg<QT>;
     extern __shared__ __align__(128) uint8_t smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int CW = blockDim.x >> 5;
+    const int CW = (blockDim.x >> 5) - 1;     // consumer warps; warp CW is the producer
     const int D = p.depth;
 
-    // shared-memory carve-up
-    uint64_t *bars = reinterpret_cast<uint64_t *>(smem);                 // [CW][kMaxDepth]
-    uint8_t *xbase = smem + kMaxWarps * kMaxDepth * 8;
-    const int units = p.Kpad >> 6, units16 = units * 16;
-    const int plane = p.Kpad;                                            // bytes per byte plane
-    const int per_m = 2 * plane + (p.Kpad >> 5) * 4 + (p.Kpad >> 4) * 4;  // xh, xl, sx, isum
-    uint8_t *ring = xbase + ((MT * per_m + 127) & ~127) + warp * (D * R * Cfg::CHUNK);
-    const uint32_t ring_s = smem_u32(ring);
-    const uint32_t bar_s = smem_u32(bars + warp * kMaxDepth);
+    // shared-memory carve-up: full[CW][D], empty[CW][D], activation planes, partial sums, rings
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem);
+    const uint32_t full0 = smem_u32(bars), empty0 = full0 + kMaxWarps * kMaxDepth * 8;
+    uint8_t *xbase = smem + 2 * kMaxWarps * kMaxDepth * 8;
+    const int units16 = (p.Kpad >> 6) * 16;
+    const int plane = p.Kpad;
+    const int n_isum = (QT == QT_Q6_K) ? (p.Kpad >> 4) : (p.Kpad >> 5);
+    const int per_m = 2 * plane + (p.Kpad >> 5) * 4 + n_isum * 4;        // xh, xl, sx, isum
+    float *partial = reinterpret_cast<float *>(xbase + ((MT * per_m + 127) & ~127));   // [row][chunk][MT]
+    uint8_t *rings = reinterpret_cast<uint8_t *>(partial) + p.partial_bytes;
+    const int ring_bytes = D * R * Cfg::CHUNK;
 
-    // this warp's contiguous range of units (R rows each); consecutive virtual warp ids sit on
-    // different SMs so a small N still spreads over the whole GPU
-    const int vw = warp * gridDim.x + blockIdx.x, TW = CW * gridDim.x;
-    const int u_begin = (int)((long long)p.total_units * vw / TW);
-    const int u_end = (int)((long long)p.total_units * (vw + 1) / TW);
-    const int n_items = (u_end - u_begin) * p.nchunks;
+    // this CTA's contiguous range of virtual rows, cut into groups of R rows; a work item is one
+    // group x one K-chunk, dealt round-robin to the consumer warps
+    const int vb = (int)((long long)p.total_rows * blockIdx.x / gridDim.x);
+    const int ve = (int)((long long)p.total_rows * (blockIdx.x + 1) / gridDim.x);
+    const int n_groups = (ve - vb + R - 1) / R;
+    const int n_items = n_groups * p.nchunks;
 
-    if (lane == 0) {
-        for (int i = 0; i < D; ++i) mbar_init(bar_s + 8 * i, 1);
+    if (threadIdx.x < CW) {
+        for (int i = 0; i < D; ++i) {
+            mbar_init(full0 + (threadIdx.x * kMaxDepth + i) * 8, 1);
+            mbar_init(empty0 + (threadIdx.x * kMaxDepth + i) * 8, 1);
+        }
         mbar_fence_init();
         fence_proxy_async();
     }
-    __syncwarp();
+    // let the next kernel in the stream start: it only prefetches its own weights until this
+    // grid has finished (see pdl_wait below)
+    pdl_launch_dependents();
+    __syncthreads();
 
-    // locate (segment, first row, row count) of unit u
-    auto unit_rows = [&](int u, int &s, int &r0, int &nr) {
-        s = 0;
+    // =========================================================================================
+    // producer warp: lane w feeds consumer warp w.  All lanes poll together (no lane blocks the
+    // others): a lane issues its next item as soon as its consumer has released the slot.
+    // =========================================================================================
+    if (warp == CW) {
+        const unsigned mask = __activemask();
+        const bool feeder = lane < CW;
+        const uint32_t ring_s = smem_u32(rings + lane * ring_bytes);
+        const uint32_t fbar = full0 + lane * kMaxDepth * 8, ebar = empty0 + lane * kMaxDepth * 8;
+        int item = (feeder && !(p.debug & 2)) ? lane : n_items;
+        int g = 0, c = lane;           // item = g * nchunks + c, kept without dividing
+        while (c >= p.nchunks) { c -= p.nchunks; ++g; }
+        int slot = 0, k = 0;
+        uint32_t phase = 0;            // parity of the release this slot's next reuse waits for
+        uint64_t t_first = 0;
+        bool timing = false;
+        int idle = 0;
+#pragma unroll 1
+        while (true) {
+            bool progressed = false;
+            if (item < n_items) {
+                const bool free_slot = (k < D) || mbar_try_wait(ebar + 8 * slot, phase ^ 1u);
+                if (free_slot) {
+                    const int vr0 = vb + g * R, nr = min(R, ve - vr0);
+                    const int sb0 = c * KC;
+                    const uint32_t bytes = (c == p.nchunks - 1) ? p.bytes_tail : p.bytes_full;
+                    const uint32_t bar = fbar + 8 * slot;
+                    const long long coff = rec_off(QT, sb0);
+                    fence_proxy_async();   // the consumer's reads of this slot precede the engine's writes
+                    mbar_expect_tx(bar, bytes * nr);
 #pragma unroll
-        for (int i = 1; i < kMaxSeg; ++i)
-            if (i < p.nseg && u >= p.seg[i].unit_begin) s = i;
-        r0 = (u - p.seg[s].unit_begin) * R;
-        nr = min(R, p.seg[s].n - r0);
-    };
-    auto issue = [&](int it) {   // lane 0 only
-        const int u = u_begin + it / p.nchunks, c = it % p.nchunks;
-        int s, r0, nr;
-        unit_rows(u, s, r0, nr);
-        const int sb0 = c * Cfg::KC, sb1 = min(p.nsb, sb0 + Cfg::KC);
-        const uint32_t bytes = (uint32_t)range_bytes(QT, sb0, sb1, p.nsb);
-        const int slot = it % D;
-        const uint32_t bar = bar_s + 8 * slot;
-        mbar_expect_tx(bar, bytes * nr);
-        const uint8_t *src = p.seg[s].w + (long long)r0 * p.row_bytes + rec_off(QT, sb0);
-        for (int r = 0; r < nr; ++r)
-            bulk_g2s(ring_s + (slot * R + r) * Cfg::CHUNK, src + (long long)r * p.row_bytes, bytes, bar);
-    };
+                    for (int r = 0; r < R; ++r) {
+                        if (r < nr) {
+                            int s, row;
+                            locate_row(p, vr0 + r, s, row);
+                            bulk_g2s(ring_s + (slot * R + r) * Cfg::CHUNK,
+                                     p.seg[s].w + (long long)row * p.row_bytes + coff, bytes, bar);
+                        }
+                    }
+                    item += CW;
+                    c += CW;
+                    while (c >= p.nchunks) { c -= p.nchunks; ++g; }
+                    ++k;
+                    if (++slot == D) { slot = 0; phase ^= 1u; }
+                    progressed = true;
+                }
+            }
+            if (__all_sync(mask, item >= n_items)) break;
+            if (__any_sync(mask, progressed)) {
+                idle = 0;
+                timing = false;
+            } else if (++idle >= 1024) {   // nobody moved for a while: look at the clock
+                idle = 0;
+                const uint64_t now = globaltimer_ns();
+                if (!timing) {
+                    timing = true;
+                    t_first = now;
+                } else if (now - t_first > kWaitLimitNs) {
+                    if (lane == 0) atomicMax(p.status, DEV_ERR_PIPE_TIMEOUT);
+                    break;
+                }
+            }
+        }
+        return;
+    }
 
-    // start streaming weights before touching the activation
-    const int pre = min(D, n_items);
-    if (lane == 0)
-        for (int it = 0; it < pre; ++it) issue(it);
-
-    // prologue: activation rows -> fixed point
+    // =========================================================================================
+    // consumer warps
+    // =========================================================================================
+    // everything below reads the activation or writes the output: the previous grid must be done
+    pdl_wait();
     XView xv[MT];
 #pragma unroll
     for (int m = 0; m < MT; ++m) {
@@ -378,99 +508,159 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) gemv_kernel(const GemvParam
         xv[m].xl = b + plane;
         xv[m].sx = reinterpret_cast<const float *>(b + 2 * plane);
         xv[m].isum = reinterpret_cast<const int *>(b + 2 * plane + (p.Kpad >> 5) * 4);
-        if (m < p.M)
-            prep_row<QT>(p, m, b, b + plane, reinterpret_cast<float *>(b + 2 * plane),
+        if (m < p.M && !(p.debug & 4))
+            prep_row<QT>(p, m, CW * 32, b, b + plane, reinterpret_cast<float *>(b + 2 * plane),
                          reinterpret_cast<int *>(b + 2 * plane + (p.Kpad >> 5) * 4), units16);
     }
-    __syncthreads();
+    // consumers only: the producer warp must not be held here, it is already feeding the rings
+    asm volatile("bar.sync 1, %0;" ::"r"(CW * 32) : "memory");
 
-    float acc[R][MT];
-#pragma unroll
-    for (int r = 0; r < R; ++r)
-#pragma unroll
-        for (int m = 0; m < MT; ++m) acc[r][m] = 0.f;
+    const uint8_t *ring = rings + warp * ring_bytes;
+    const uint32_t fbar = full0 + warp * kMaxDepth * 8, ebar = empty0 + warp * kMaxDepth * 8;
+    const int lsb = lane >> 2, j = lane & 3;   // this lane's record and 64-weight group in a chunk
 
+    int slot = 0;
+    uint32_t phase = 0;
     bool failed = false;
-    int it = 0;
-#pragma unroll 1
-    for (; it < n_items; ++it) {
-        const int slot = it % D;
-        const uint32_t parity = (uint32_t)(it / D) & 1u;
-        bool ok = mbar_wait_bounded(bar_s + 8 * slot, parity);
-        ok = __all_sync(0xFFFFFFFFu, ok);
-        if (!ok) { failed = true; break; }
+    int item = warp;
+    int g = 0, c = warp;               // item = g * nchunks + c, kept without dividing
+    while (c >= p.nchunks) { c -= p.nchunks; ++g; }
 
-        const int u = u_begin + it / p.nchunks, c = it % p.nchunks;
-        int s, r0, nr;
-        unit_rows(u, s, r0, nr);
-        const int sb0 = c * Cfg::KC;
-        const int nsb_c = min(p.nsb, sb0 + Cfg::KC) - sb0;
-        const uint8_t *sl = ring + (slot * R) * Cfg::CHUNK;
-
-#pragma unroll 1
-        for (int lu = lane; lu < nsb_c * 4; lu += 32) {
-            const int lsb = lu >> 2, j = lu & 3;
-            const int gsb = sb0 + lsb;
-            const int gu = gsb * 4 + j;
-            WRegs<QT> wr[R];
+    // The cross-lane sum of an item's results is taken one iteration late, after the next item's
+    // shared-memory loads have been issued, so its shuffle chain hides behind them.
+    float pend[R][MT];
+    int pend_cell = -1, pend_nr = 0;   // first partial-sum cell of the pending item
+    auto flush_pending = [&]() {
+        if (pend_cell < 0) return;
+        if constexpr (MT == 1) {
+            float a[R];
 #pragma unroll
-            for (int r = 0; r < R; ++r) {
-                if (r < nr) {
-                    const uint8_t *row = sl + r * Cfg::CHUNK;
-                    if constexpr (QT == QT_Q4_K) {
-                        wr[r].load(row + lsb * 144, j);
-                    } else if constexpr (QT == QT_Q8_0) {
-                        wr[r].load(row + lsb * 272, j);
-                    } else {
-                        const int doff = (int)(q6k_d_off(gsb, p.nsb) - rec_off(QT, sb0));
-                        const float d = half_bits_to_float(*reinterpret_cast<const uint16_t *>(row + doff));
-                        wr[r].load(row + (int)(rec_off(QT, gsb) - rec_off(QT, sb0)), j, d);
-                    }
-                }
-            }
-#pragma unroll
-            for (int m = 0; m < MT; ++m) {
-                XRegs xr;
-                load_x(xr, xv[m], gu, units16);
-#pragma unroll
-                for (int r = 0; r < R; ++r)
-                    if (r < nr) acc[r][m] += wr[r].dot(xr, xv[m], QT == QT_Q6_K ? gsb : gu);
-            }
-        }
-        __syncwarp();
-        if (lane == 0 && it + D < n_items) {
-            fence_proxy_async();   // order this warp's generic reads before the engine's writes
-            issue(it + D);
-        }
-
-        if (c == p.nchunks - 1) {   // unit finished: reduce over lanes and store
+            for (int r = 0; r < R; ++r) a[r] = pend[r][0];
+            const float v = fold_rows<R>(a, lane);
+            const int r = lane / (32 / R);
+            if ((lane & (32 / R - 1)) == 0 && r < pend_nr) partial[pend_cell + r * p.nchunks] = v;
+        } else {
 #pragma unroll
             for (int r = 0; r < R; ++r) {
 #pragma unroll
                 for (int m = 0; m < MT; ++m) {
-                    float v = acc[r][m];
+                    float v = pend[r][m];
 #pragma unroll
                     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
-                    acc[r][m] = 0.f;
-                    if (lane == 0 && r < nr && m < p.M) {
-                        const long long idx = (long long)m * p.seg[s].ldy + r0 + r;
-                        if (p.y_is_bf16)
-                            reinterpret_cast<__nv_bfloat16 *>(p.seg[s].y)[idx] = __float2bfloat16_rn(v);
-                        else
-                            reinterpret_cast<float *>(p.seg[s].y)[idx] = v;
-                    }
+                    if (lane == 0 && r < pend_nr) partial[(pend_cell + r * p.nchunks) * MT + m] = v;
                 }
             }
         }
+        pend_cell = -1;
+    };
+
+#pragma unroll 1
+    for (; item < n_items; item += CW) {
+        bool ok = (p.debug & 2) ? true : mbar_wait_bounded(fbar + 8 * slot, phase);
+        ok = __all_sync(0xFFFFFFFFu, ok);
+        if (!ok) { failed = true; break; }
+
+        const int nr = min(R, ve - vb - g * R);
+        const int sb0 = c * KC;
+        const int gsb = sb0 + lsb;
+        float acc[R][MT];
+#pragma unroll
+        for (int r = 0; r < R; ++r)
+#pragma unroll
+            for (int m = 0; m < MT; ++m) acc[r][m] = 0.f;
+
+        // the pending sum uses full-warp shuffles, so it may sit inside the branch below only when
+        // every lane takes that branch (a chunk of 8 whole records)
+        const bool whole = (sb0 + KC <= p.nsb) && !(p.debug & 1);
+        if (!whole) flush_pending();
+        if (gsb < p.nsb && !(p.debug & 1)) {
+            const int gu = gsb * 4 + j;
+            const uint8_t *sl = ring + (slot * R) * Cfg::CHUNK;
+            auto load_w = [&](WRegs<QT> &w, int r) {
+                const uint8_t *row = sl + r * Cfg::CHUNK;
+                if constexpr (QT == QT_Q4_K) {
+                    w.load(row + lsb * 144, j);
+                } else if constexpr (QT == QT_Q8_0) {
+                    w.load(row + lsb * 272, j);
+                } else {
+                    const int doff = (int)(q6k_d_off(gsb, p.nsb) - rec_off(QT, sb0));
+                    const float d = half_bits_to_float(*reinterpret_cast<const uint16_t *>(row + doff));
+                    w.load(row + lsb * 208, j, d);
+                }
+            };
+            if constexpr (MT == 1) {
+                // one activation row: keep its bytes in registers, stream the R weight rows past them
+                XRegs xr;
+                load_x(xr, xv[0], gu, units16);
+                if (whole) flush_pending();
+#pragma unroll
+                for (int r = 0; r < R; ++r) {
+                    if (r < nr) {
+                        WRegs<QT> w;
+                        load_w(w, r);
+                        acc[r][0] += w.dot(xr, xv[0], QT == QT_Q6_K ? gsb : gu);
+                    }
+                }
+            } else {
+                // several activation rows: unpack the weights once, stream the activations past them
+                WRegs<QT> wr[R];
+#pragma unroll
+                for (int r = 0; r < R; ++r)
+                    if (r < nr) load_w(wr[r], r);
+                if (whole) flush_pending();
+#pragma unroll
+                for (int m = 0; m < MT; ++m) {
+                    XRegs xr;
+                    load_x(xr, xv[m], gu, units16);
+#pragma unroll
+                    for (int r = 0; r < R; ++r)
+                        if (r < nr) acc[r][m] += wr[r].dot(xr, xv[m], QT == QT_Q6_K ? gsb : gu);
+                }
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(ebar + 8 * slot);   // slot may be refilled
+        if (++slot == D) { slot = 0; phase ^= 1u; }
+
+        // one shared-memory cell per (row, chunk, m): the final sum over chunks runs in a fixed
+        // order whatever warp produced which cell
+#pragma unroll
+        for (int r = 0; r < R; ++r)
+#pragma unroll
+            for (int m = 0; m < MT; ++m) pend[r][m] = acc[r][m];
+        pend_cell = (g * R) * p.nchunks + c;
+        pend_nr = nr;
+        c += CW;
+        while (c >= p.nchunks) { c -= p.nchunks; ++g; }
     }
+    flush_pending();
 
     if (failed) {
         if (lane == 0) atomicMax(p.status, DEV_ERR_PIPE_TIMEOUT);
-        // copies already issued must land before this CTA's shared memory is released:
-        // wait for each outstanding slot once more, again with a limit
-        const int last = min(n_items, it + D);
-        for (int j2 = it; j2 < last; ++j2)
-            (void)mbar_wait_bounded(bar_s + 8 * (j2 % D), (uint32_t)(j2 / D) & 1u);
+        // copies already issued for this warp must land before the CTA's shared memory is
+        // released: wait for each slot that can still be in flight once more, again with a limit
+        for (int i = 0; i < D && item < n_items; ++i, item += CW) {
+            (void)mbar_wait_bounded(fbar + 8 * slot, phase);
+            if (++slot == D) { slot = 0; phase ^= 1u; }
+        }
+    }
+    asm volatile("bar.sync 1, %0;" ::"r"(CW * 32) : "memory");
+
+    // final pass: sum the chunks of every row of this CTA in order and store
+    const int rows_here = (p.debug & 8) ? 0 : ve - vb;
+    for (int t = threadIdx.x; t < rows_here * MT; t += CW * 32) {
+        const int rl = t / MT, m = t - rl * MT;
+        float v = 0.f;
+        for (int c = 0; c < p.nchunks; ++c) v += partial[(rl * p.nchunks + c) * MT + m];
+        if (m < p.M) {
+            int s, row;
+            locate_row(p, vb + rl, s, row);
+            const long long idx = (long long)m * p.seg[s].ldy + row;
+            if (p.y_is_bf16)
+                reinterpret_cast<__nv_bfloat16 *>(p.seg[s].y)[idx] = __float2bfloat16_rn(v);
+            else
+                reinterpret_cast<float *>(p.seg[s].y)[idx] = v;
+        }
     }
 }
 
@@ -479,9 +669,31 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) gemv_kernel(const GemvParam
 // ---------------------------------------------------------------------------------------------
 
 template <int QT, int MT, int R>
-cudaError_t launch_t(const GemvParams &p, int grid, int warps, size_t smem, cudaStream_t st) {
+cudaError_t launch_t(const GemvLaunch &a, GemvParams &p, int grid, cudaStream_t st) {
+    using Shape = GemvShape<MT>;
+    constexpr int chunk = GemvCfg<QT>::CHUNK;
+    int warps = a.warps > 0 ? a.warps : Shape::kWarps;
+    if (warps > Shape::kWarps) warps = Shape::kWarps;
+    const size_t n_isum = QT == QT_Q6_K ? p.Kpad / 16 : p.Kpad / 32;
+    const size_t per_m = 2 * (size_t)p.Kpad + (p.Kpad / 32) * 4 + n_isum * 4;
+    const int rows_cta = (p.total_rows + grid - 1) / grid;
+    const int groups = (rows_cta + R - 1) / R;
+    p.partial_bytes = (int)((((size_t)groups * R * p.nchunks * MT * 4) + 127) & ~size_t(127));
+    const size_t fixed = 2 * kMaxWarps * kMaxDepth * 8 + ((MT * per_m + 127) & ~size_t(127)) + p.partial_bytes;
+    // two CTAs per SM when the shape allows it (each may use half of the SM's shared memory
+    // minus the per-block reservation), otherwise the whole SM
+    size_t budget = a.smem_limit;
+    const size_t half = (a.smem_sm - 2 * 1024) / 2;
+    if (Shape::kBlocksPerSm == 2 && half < budget && fixed + (size_t)warps * 2 * R * chunk <= half) budget = half;
+    if (fixed + (size_t)warps * 2 * R * chunk > budget) return cudaErrorInvalidValue;
+    int depth = (int)((budget - fixed) / ((size_t)warps * R * chunk));
+    if (depth > kMaxDepth) depth = kMaxDepth;
+    if (a.depth > 0 && a.depth < depth) depth = a.depth;
+    p.depth = depth;
+    const size_t smem = fixed + (size_t)warps * depth * R * chunk;
+
     auto kern = gemv_kernel<QT, MT, R>;
-    static size_t configured = 0;   // per instantiation; contexts on several devices re-set it
+    static size_t configured = 0;   // per instantiation; a context on another device re-sets it
     static int configured_dev = -1;
     int dev = 0;
     cudaGetDevice(&dev);
@@ -491,17 +703,34 @@ cudaError_t launch_t(const GemvParams &p, int grid, int warps, size_t smem, cuda
         configured = smem;
         configured_dev = dev;
     }
-    kern<<<grid, warps * 32, smem, st>>>(p);
-    return cudaGetLastError();
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3((unsigned)((warps + 1) * 32));
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = a.pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, p);
 }
 
-template <int QT>
-cudaError_t launch_q(const GemvParams &p, int mt, int grid, int warps, size_t smem, cudaStream_t st) {
-    switch (mt) {
-    case 1: return launch_t<QT, 1, 2>(p, grid, warps, smem, st);
-    case 2: return launch_t<QT, 2, 2>(p, grid, warps, smem, st);
-    case 3: return launch_t<QT, 3, 2>(p, grid, warps, smem, st);
-    default: return launch_t<QT, 4, 2>(p, grid, warps, smem, st);
+template <int QT, int R>
+cudaError_t launch_q(const GemvLaunch &a, GemvParams &p, int grid, cudaStream_t st) {
+    switch (a.M) {
+    case 1: return launch_t<QT, 1, R>(a, p, grid, st);
+    case 2: return launch_t<QT, 2, 2>(a, p, grid, st);
+    case 3: return launch_t<QT, 3, 2>(a, p, grid, st);
+    default: return launch_t<QT, 4, 2>(a, p, grid, st);
+    }
+}
+
+template <int R> cudaError_t launch_r(const GemvLaunch &a, GemvParams &p, int grid, cudaStream_t st) {
+    switch (a.qt) {
+    case QT_Q4_K: return launch_q<QT_Q4_K, R>(a, p, grid, st);
+    case QT_Q8_0: return launch_q<QT_Q8_0, R>(a, p, grid, st);
+    default: return launch_q<QT_Q6_K, R>(a, p, grid, st);
     }
 }
 
@@ -512,20 +741,20 @@ int gemv_max_m() { return 4; }
 // Returns cudaSuccess, or cudaErrorInvalidValue when the shape cannot be staged in shared memory
 // (caller then picks another route).
 cudaError_t gemv_launch(const GemvLaunch &a, cudaStream_t st) {
-    constexpr int R = 2;
     GemvParams p{};
     if (a.nseg < 1 || a.nseg > kMaxSeg || a.M < 1 || a.M > 4) return cudaErrorInvalidValue;
-    int units = 0;
+    if (a.qt != QT_Q4_K && a.qt != QT_Q8_0 && a.qt != QT_Q6_K) return cudaErrorInvalidValue;
+    int rows = 0;
     for (int i = 0; i < a.nseg; ++i) {
         p.seg[i].w = a.w[i];
         p.seg[i].y = a.y[i];
         p.seg[i].ldy = a.ldy[i];
         p.seg[i].n = a.n[i];
-        p.seg[i].unit_begin = units;
-        units += (a.n[i] + R - 1) / R;
+        p.seg[i].row_begin = rows;
+        rows += a.n[i];
     }
     p.nseg = a.nseg;
-    p.total_units = units;
+    p.total_rows = rows;
     p.x = a.x;
     p.ldx = a.ldx;
     p.x_is_bf16 = a.x_is_bf16;
@@ -538,33 +767,16 @@ cudaError_t gemv_launch(const GemvLaunch &a, cudaStream_t st) {
     p.nsb = a.Kpad / SB;
     p.row_bytes = a.row_bytes;
     p.status = a.status;
-
-    int kc, chunk;
-    switch (a.qt) {
-    case QT_Q4_K: kc = GemvCfg<QT_Q4_K>::KC; chunk = GemvCfg<QT_Q4_K>::CHUNK; break;
-    case QT_Q8_0: kc = GemvCfg<QT_Q8_0>::KC; chunk = GemvCfg<QT_Q8_0>::CHUNK; break;
-    case QT_Q6_K: kc = GemvCfg<QT_Q6_K>::KC; chunk = GemvCfg<QT_Q6_K>::CHUNK; break;
-    default: return cudaErrorInvalidValue;
-    }
-    p.nchunks = (p.nsb + kc - 1) / kc;
-
-    const int warps = a.warps > 0 ? (a.warps > kMaxWarps ? kMaxWarps : a.warps) : 8;
-    const size_t per_m = 2 * (size_t)p.Kpad + (p.Kpad / 32) * 4 + (p.Kpad / 16) * 4;
-    const size_t fixed = kMaxWarps * kMaxDepth * 8 + ((a.M * per_m + 127) & ~size_t(127));
-    const size_t budget = a.smem_limit;
-    if (fixed + (size_t)warps * 2 * R * chunk > budget) return cudaErrorInvalidValue;
-    int depth = (int)((budget - fixed) / ((size_t)warps * R * chunk));
-    if (depth > kMaxDepth) depth = kMaxDepth;
-    if (a.depth > 0 && a.depth < depth) depth = a.depth;
-    p.depth = depth;
-    const size_t smem = fixed + (size_t)warps * depth * R * chunk;
+    p.debug = a.debug;
+    p.nchunks = (p.nsb + KC - 1) / KC;
+    p.bytes_full = (unsigned)range_bytes(a.qt, 0, p.nsb < KC ? p.nsb : KC, p.nsb);
+    p.bytes_tail = (unsigned)range_bytes(a.qt, (p.nchunks - 1) * KC, p.nsb, p.nsb);
     const int grid = a.grid > 0 ? a.grid : a.sm_count;
-
-    switch (a.qt) {
-    case QT_Q4_K: return launch_q<QT_Q4_K>(p, a.M, grid, warps, smem, st);
-    case QT_Q8_0: return launch_q<QT_Q8_0>(p, a.M, grid, warps, smem, st);
-    default: return launch_q<QT_Q6_K>(p, a.M, grid, warps, smem, st);
-    }
+    // four rows per item when a CTA owns many rows (fewer, larger items) and M = 1; two otherwise
+    const int rows_cta = (rows + grid - 1) / grid;
+    const int rpi = a.rows_per_item > 0 ? a.rows_per_item : (rows_cta >= 64 ? 4 : 2);
+    if (rpi == 4 && a.M == 1) return launch_r<4>(a, p, grid, st);
+    return launch_r<2>(a, p, grid, st);
 }
 
 }  // namespace b200q

@@ -1,0 +1,321 @@
+// Device building blocks of the streaming projection kernel: the fixed-point activation form,
+// its prologue, and the per-type work on one 64-weight unit of one weight row.
+#pragma once
+
+#include "common.cuh"
+
+namespace b200q {
+
+// where an activation matrix lives (row m at x + m * ldx elements)
+struct XSrc {
+    const void *x;
+    long long ldx;
+    int x_is_bf16;
+    int x_vec_ok;       // rows are 16-byte aligned: vector loads allowed
+    int K, Kpad;
+};
+
+// byte offset, inside one byte plane of the fixed-point activation, of the 16-byte group that
+// holds element k.  Groups are stored [c][unit][16] so a lane's four 16-byte reads of one
+// 64-weight unit are contiguous across lanes (no bank conflicts).
+template <int QT> __device__ __forceinline__ int xplane_off(int k, int units16) {
+    if (QT == QT_Q6_K) {
+        // unit = (superblock, 128-half, 16-position half); c = 32-weight quadrant inside the half
+        const int unit = ((k >> 8) << 2) | (((k >> 7) & 1) << 1) | ((k >> 4) & 1);
+        const int c = (k >> 5) & 3;
+        return c * units16 + unit * 16 + (k & 15);
+    }
+    return ((k >> 4) & 3) * units16 + (k >> 6) * 16 + (k & 15);
+}
+
+struct XView {            // shared-memory views of one activation row in fixed-point form
+    const uint8_t *xh;    // signed high bytes
+    const uint8_t *xl;    // signed low bytes
+    const float *sx;      // per 32 weights
+    const int *isum;      // sum of the 16-bit integers: per 32 weights (Q4_K) or per 16 (Q6_K)
+};
+
+struct XRegs {            // one 64-weight unit of one activation row: 4 groups of 16 weights
+    uint4 h[4];
+    uint4 l[4];
+};
+
+__device__ __forceinline__ void load_x(XRegs &xr, const XView &xv, int unit, int units16) {
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        xr.h[c] = *reinterpret_cast<const uint4 *>(xv.xh + c * units16 + unit * 16);
+        xr.l[c] = *reinterpret_cast<const uint4 *>(xv.xl + c * units16 + unit * 16);
+    }
+}
+
+// Weights of one 64-weight unit of one row, unpacked once and reused for every activation row.
+template <int QT> struct WRegs;
+
+template <> struct WRegs<QT_Q4_K> {
+    uint32_t lo[8], hi[8];   // low nibbles = weights 0..31 of the group; hi keeps 16 * nibble
+    int scA, mnA, scB, mnB;
+    float d, dmin;
+    // `rec` points at the 144-byte block, j = 64-weight group 0..3
+    __device__ __forceinline__ void load(const uint8_t *rec, int j) {
+        const uint4 hdr = *reinterpret_cast<const uint4 *>(rec);
+        const uint4 qa = *reinterpret_cast<const uint4 *>(rec + 16 + 32 * j);
+        const uint4 qb = *reinterpret_cast<const uint4 *>(rec + 32 + 32 * j);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint32_t a = word_of(qa, i), b = word_of(qb, i);
+            lo[i] = a & 0x0F0F0F0Fu;
+            hi[i] = a & 0xF0F0F0F0u;
+            lo[4 + i] = b & 0x0F0F0F0Fu;
+            hi[4 + i] = b & 0xF0F0F0F0u;
+        }
+        // 6-bit scales / mins of sub-blocks 2j and 2j+1 (bytes 2(j&1), 2(j&1)+1 of each word)
+        const int sh = 16 * (j & 1);
+        const uint32_t y2 = (hdr.y >> sh) & 0xFFFFu, z2 = (hdr.z >> sh) & 0xFFFFu, w2 = (hdr.w >> sh) & 0xFFFFu;
+        const uint32_t sc_lo = y2 & 0x3F3Fu, mn_lo = z2 & 0x3F3Fu;
+        const uint32_t sc_hi = (w2 & 0x0F0Fu) | ((y2 >> 2) & 0x3030u);
+        const uint32_t mn_hi = ((w2 >> 4) & 0x0F0Fu) | ((z2 >> 2) & 0x3030u);
+        const uint32_t sc2 = (j >= 2) ? sc_hi : sc_lo, mn2 = (j >= 2) ? mn_hi : mn_lo;
+        scA = sc2 & 0xFF;
+        scB = sc2 >> 8;
+        mnA = mn2 & 0xFF;
+        mnB = mn2 >> 8;
+        d = half_bits_to_float(hdr.x);
+        dmin = half_bits_to_float(hdr.x >> 16);
+    }
+    // gu = global 64-weight unit index of the row
+    __device__ __forceinline__ float dot(const XRegs &xr, const XView &xv, int gu) const {
+        int hA = 0, lA = 0, hB = 0, lB = 0;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            hA = dp4a_us(lo[i], word_of(xr.h[0], i), hA);
+            lA = dp4a_us(lo[i], word_of(xr.l[0], i), lA);
+            hA = dp4a_us(lo[4 + i], word_of(xr.h[1], i), hA);
+            lA = dp4a_us(lo[4 + i], word_of(xr.l[1], i), lA);
+            hB = dp4a_us(hi[i], word_of(xr.h[2], i), hB);
+            lB = dp4a_us(hi[i], word_of(xr.l[2], i), lB);
+            hB = dp4a_us(hi[4 + i], word_of(xr.h[3], i), hB);
+            lB = dp4a_us(hi[4 + i], word_of(xr.l[3], i), lB);
+        }
+        const float2 sx = *reinterpret_cast<const float2 *>(xv.sx + 2 * gu);
+        const int2 is = *reinterpret_cast<const int2 *>(xv.isum + 2 * gu);
+        const float fa = (float)((hA * 256 + lA) * scA);
+        const float fb = (float)(((hB * 256 + lB) >> 4) * scB);   // hi held 16 * nibble: exact shift
+        const float ua = (float)(mnA * is.x);
+        const float ub = (float)(mnB * is.y);
+        return sx.x * (d * fa - dmin * ua) + sx.y * (d * fb - dmin * ub);
+    }
+};
+
+template <> struct WRegs<QT_Q8_0> {
+    uint4 q[4];
+    float dA, dB;
+    // `rec` points at the 272-byte record, j = 64-weight group 0..3 (native blocks 2j, 2j+1)
+    __device__ __forceinline__ void load(const uint8_t *rec, int j) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) q[c] = *reinterpret_cast<const uint4 *>(rec + 64 * j + 16 * c);
+        const uint32_t dd = *reinterpret_cast<const uint32_t *>(rec + 256 + 4 * j);
+        dA = half_bits_to_float(dd);
+        dB = half_bits_to_float(dd >> 16);
+    }
+    __device__ __forceinline__ float dot(const XRegs &xr, const XView &xv, int gu) const {
+        int hA = 0, lA = 0, hB = 0, lB = 0;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            hA = dp4a_ss(word_of(q[0], i), word_of(xr.h[0], i), hA);
+            lA = dp4a_ss(word_of(q[0], i), word_of(xr.l[0], i), lA);
+            hA = dp4a_ss(word_of(q[1], i), word_of(xr.h[1], i), hA);
+            lA = dp4a_ss(word_of(q[1], i), word_of(xr.l[1], i), lA);
+            hB = dp4a_ss(word_of(q[2], i), word_of(xr.h[2], i), hB);
+            lB = dp4a_ss(word_of(q[2], i), word_of(xr.l[2], i), lB);
+            hB = dp4a_ss(word_of(q[3], i), word_of(xr.h[3], i), hB);
+            lB = dp4a_ss(word_of(q[3], i), word_of(xr.l[3], i), lB);
+        }
+        const float2 sx = *reinterpret_cast<const float2 *>(xv.sx + 2 * gu);
+        return (dA * sx.x) * (float)(hA * 256 + lA) + (dB * sx.y) * (float)(hB * 256 + lB);
+    }
+};
+
+template <> struct WRegs<QT_Q6_K> {
+    uint32_t q[4][4];        // quadrant c (32-weight stride), word i: 6-bit values 0..63 as bytes
+    float f[4];              // d * sub-block scale of quadrant c
+    int h, ph;
+    // `rec` points at the 208-byte record, j = 2*half + position-half, d = superblock scale
+    __device__ __forceinline__ void load(const uint8_t *rec, int j, float d) {
+        h = j >> 1;
+        ph = j & 1;
+        const uint4 A = *reinterpret_cast<const uint4 *>(rec + 64 * h + 16 * ph);        // quadrants 0 | 2
+        const uint4 B = *reinterpret_cast<const uint4 *>(rec + 64 * h + 32 + 16 * ph);   // quadrants 1 | 3
+        const uint4 H = *reinterpret_cast<const uint4 *>(rec + 128 + 32 * h + 16 * ph);  // 2 bits x 4 quadrants
+        const uint2 s8 = *reinterpret_cast<const uint2 *>(rec + 192 + 8 * h);            // 8 int8 scales
+        // scales of sub-blocks 8h + 2c + ph, c = 0..3
+        const uint32_t sw0 = ph ? (s8.x >> 8) : s8.x, sw1 = ph ? (s8.y >> 8) : s8.y;
+        f[0] = d * (float)(int)(int8_t)(sw0 & 0xFF);
+        f[1] = d * (float)(int)(int8_t)((sw0 >> 16) & 0xFF);
+        f[2] = d * (float)(int)(int8_t)(sw1 & 0xFF);
+        f[3] = d * (float)(int)(int8_t)((sw1 >> 16) & 0xFF);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint32_t a = word_of(A, i), b = word_of(B, i), hh = word_of(H, i);
+            q[0][i] = (a & 0x0F0F0F0Fu) | ((hh << 4) & 0x30303030u);
+            q[1][i] = (b & 0x0F0F0F0Fu) | ((hh << 2) & 0x30303030u);
+            q[2][i] = ((a >> 4) & 0x0F0F0F0Fu) | (hh & 0x30303030u);
+            q[3][i] = ((b >> 4) & 0x0F0F0F0Fu) | ((hh >> 2) & 0x30303030u);
+        }
+    }
+    // sb = global superblock index of the row
+    __device__ __forceinline__ float dot(const XRegs &xr, const XView &xv, int sb) const {
+        int ah[4] = {0, 0, 0, 0}, al[4] = {0, 0, 0, 0};
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                ah[c] = dp4a_us(q[c][i], word_of(xr.h[c], i), ah[c]);
+                al[c] = dp4a_us(q[c][i], word_of(xr.l[c], i), al[c]);
+            }
+        }
+        // 32-weight scale blocks 8*sb + 4h + c ; 16-weight sums 16*sb + 8h + 2c + ph
+        const float4 sx = *reinterpret_cast<const float4 *>(xv.sx + 8 * sb + 4 * h);
+        const int4 i0 = *reinterpret_cast<const int4 *>(xv.isum + 16 * sb + 8 * h);
+        const int4 i1 = *reinterpret_cast<const int4 *>(xv.isum + 16 * sb + 8 * h + 4);
+        const int s0 = ph ? i0.y : i0.x, s1 = ph ? i0.w : i0.z;
+        const int s2 = ph ? i1.y : i1.x, s3 = ph ? i1.w : i1.z;
+        const float v0 = (float)(ah[0] * 256 + al[0] - 32 * s0);
+        const float v1 = (float)(ah[1] * 256 + al[1] - 32 * s1);
+        const float v2 = (float)(ah[2] * 256 + al[2] - 32 * s2);
+        const float v3 = (float)(ah[3] * 256 + al[3] - 32 * s3);
+        return (f[0] * sx.x) * v0 + (f[1] * sx.y) * v1 + (f[2] * sx.z) * v2 + (f[3] * sx.w) * v3;
+    }
+};
+
+// ---------------------------------------------------------------------------------------------
+// prologue: activation row -> fixed-point planes in shared memory
+// ---------------------------------------------------------------------------------------------
+
+constexpr float kXMax = 32512.f;   // 127 * 256: hi = (q + 128) >> 8 stays within a signed byte
+
+// loads 8 consecutive activation elements starting at k0 (zeros beyond K)
+__device__ __forceinline__ void load_x8(const XSrc &p, int m, int k0, float (&v)[8]) {
+    if (k0 >= p.K) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = 0.f;
+        return;
+    }
+    if (p.x_is_bf16) {
+        const __nv_bfloat16 *xr = reinterpret_cast<const __nv_bfloat16 *>(p.x) + (long long)m * p.ldx + k0;
+        if (p.x_vec_ok) {
+            const uint4 raw = *reinterpret_cast<const uint4 *>(xr);
+            const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                v[2 * i] = __uint_as_float(w[i] << 16);
+                v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] = __bfloat162float(xr[i]);
+        }
+    } else {
+        const float *xr = reinterpret_cast<const float *>(p.x) + (long long)m * p.ldx + k0;
+        if (p.x_vec_ok) {
+            const float4 a = *reinterpret_cast<const float4 *>(xr);
+            const float4 b = *reinterpret_cast<const float4 *>(xr + 4);
+            v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+            v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] = xr[i];
+        }
+    }
+}
+
+template <int QT>
+__device__ __forceinline__ void prep_store8(const float (&v)[8], int k0, uint8_t *xh, uint8_t *xl, float *sx,
+                                            int *isum, int units16) {
+    float amax = 0.f;
+    bool bad = false;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        amax = fmaxf(amax, fabsf(v[i]));
+        bad |= !(fabsf(v[i]) <= 3.0e38f);   // inf or nan
+    }
+    // four consecutive lanes cover one 32-weight block
+    amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 2));
+    const unsigned badm = __ballot_sync(0xFFFFFFFFu, bad);
+    const unsigned grp = 0xFu << ((threadIdx.x & 31) & ~3);
+    const bool blk_bad = (badm & grp) != 0;
+    const float inv = (amax > 0.f && !blk_bad) ? kXMax / amax : 0.f;
+    int q[8], sum = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        q[i] = blk_bad ? 0 : __float2int_rn(v[i] * inv);
+        q[i] = max(-32512, min(32512, q[i]));
+        sum += q[i];
+    }
+    uint32_t h0 = 0, h1 = 0, l0 = 0, l1 = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int ha = (q[i] + 128) >> 8, hb = (q[4 + i] + 128) >> 8;   // balanced digits
+        h0 |= (uint32_t)(ha & 0xFF) << (8 * i);
+        l0 |= (uint32_t)((q[i] - 256 * ha) & 0xFF) << (8 * i);
+        h1 |= (uint32_t)(hb & 0xFF) << (8 * i);
+        l1 |= (uint32_t)((q[4 + i] - 256 * hb) & 0xFF) << (8 * i);
+    }
+    const int off = xplane_off<QT>(k0, units16);
+    *reinterpret_cast<uint2 *>(xh + off) = make_uint2(h0, h1);
+    *reinterpret_cast<uint2 *>(xl + off) = make_uint2(l0, l1);
+    const int sum16 = sum + __shfl_xor_sync(0xFFFFFFFFu, sum, 1);
+    if (QT == QT_Q6_K) {
+        if ((threadIdx.x & 1) == 0) isum[k0 >> 4] = sum16;
+    } else {
+        const int sum32 = sum16 + __shfl_xor_sync(0xFFFFFFFFu, sum16, 2);
+        if ((threadIdx.x & 3) == 0) isum[k0 >> 5] = sum32;
+    }
+    if ((threadIdx.x & 3) == 0)
+        sx[k0 >> 5] = blk_bad ? __int_as_float(0x7FC00000) : amax * (1.0f / kXMax);
+}
+
+// Threads [0, T) convert activation row m.  Loads are issued four deep before any is used so a
+// long row costs one trip to L2, not one per 8 * T elements.
+template <int QT>
+__device__ __forceinline__ void prep_row(const XSrc &p, int m, int T, uint8_t *xh, uint8_t *xl,
+                                         float *sx, int *isum, int units16) {
+    constexpr int PB = 4;
+    const int stride = T * 8;
+    for (int base = threadIdx.x * 8; base < p.Kpad; base += stride * PB) {
+        float v[PB][8];
+#pragma unroll
+        for (int b = 0; b < PB; ++b)
+            if (base + b * stride < p.Kpad) load_x8(p, m, base + b * stride, v[b]);
+#pragma unroll
+        for (int b = 0; b < PB; ++b)
+            if (base + b * stride < p.Kpad) prep_store8<QT>(v[b], base + b * stride, xh, xl, sx, isum, units16);
+    }
+}
+
+// Sum R per-lane values over the 32 lanes with a folding butterfly (6 shuffles for R = 4, 5 for
+// R = 2 instead of 5 per value).  The total of value r ends up in lane r * (32 / R).
+template <int R> __device__ __forceinline__ float fold_rows(const float (&a)[R], int lane) {
+    static_assert(R == 2 || R == 4, "R");
+    float y;
+    if (R == 4) {
+        const bool up = lane & 16;
+        float k0 = up ? a[2] : a[0], k1 = up ? a[3] : a[1];
+        const float s0 = up ? a[0] : a[2], s1 = up ? a[1] : a[3];
+        k0 += __shfl_xor_sync(0xFFFFFFFFu, s0, 16);
+        k1 += __shfl_xor_sync(0xFFFFFFFFu, s1, 16);
+        const bool up8 = lane & 8;
+        y = (up8 ? k1 : k0) + __shfl_xor_sync(0xFFFFFFFFu, up8 ? k0 : k1, 8);
+    } else {
+        const bool up = lane & 16;
+        y = (up ? a[1] : a[0]) + __shfl_xor_sync(0xFFFFFFFFu, up ? a[0] : a[1], 16);
+        y += __shfl_xor_sync(0xFFFFFFFFu, y, 8);
+    }
+    y += __shfl_xor_sync(0xFFFFFFFFu, y, 4);
+    y += __shfl_xor_sync(0xFFFFFFFFu, y, 2);
+    y += __shfl_xor_sync(0xFFFFFFFFu, y, 1);
+    return y;
+}
+
+
+}  // namespace b200q

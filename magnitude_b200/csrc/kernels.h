@@ -33,7 +33,11 @@ struct GemvLaunch {
     int *status;              // device status word
     int sm_count;
     size_t smem_limit;        // opt-in shared memory per block
+    size_t smem_sm;           // shared memory per SM
+    int pdl;                  // launch with programmatic stream serialization
     int warps, depth, grid;   // 0 = default
+    int rows_per_item;        // 0 = choose, else 2 or 4
+    int debug;                // experiments only (see gemv.cu)
 };
 int gemv_max_m();
 cudaError_t gemv_launch(const GemvLaunch &a, cudaStream_t st);
