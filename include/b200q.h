@@ -182,6 +182,39 @@ b200q_status b200q_matmul_multi_host(b200q_ctx *ctx, const b200q_weight *const *
                                      const void *x_host, int32_t x_dtype, int64_t M, int64_t ldx,
                                      void *const *y_host, int32_t y_dtype, const int64_t *ldy);
 
+/* -- decode plans ------------------------------------------------------------------------------ */
+
+/* A plan is a fixed list of projections (M <= 4 activation rows, the same M for all) that one
+ * launch executes back to back on persistent CTAs: the weights of projection i+1 stream from HBM
+ * while projection i is still being reduced and stored, so a decode step is not broken up by
+ * launch gaps.  It plays the role of the per-token graph that context.decode(batch) runs for a
+ * batch of 1..4 tokens (inference/crates/icn-engine/src/lib.rs:2264).  Pointers are captured at
+ * creation: run the plan again after rewriting the activation buffers in place. */
+typedef struct b200q_plan b200q_plan;
+
+enum {
+    /* the job's activation is written by earlier jobs of the same plan (e.g. the down projection
+     * reading what gate/up produced): all CTAs finish those jobs before this one converts x */
+    B200Q_JOB_WAITS_FOR_EARLIER = 1
+};
+
+typedef struct b200q_job {
+    const b200q_weight *w[4]; /* 1..4 weights of one type and K sharing x */
+    int32_t n_weights;
+    int32_t x_dtype;          /* B200Q_TYPE_BF16 or B200Q_TYPE_F32 */
+    const void *x_dev;        /* X[M][K], device memory */
+    int64_t ldx;
+    void *y_dev[4];           /* Y_i[M][N_i], device memory */
+    int64_t ldy[4];
+    int32_t y_dtype;          /* B200Q_TYPE_F32 or B200Q_TYPE_BF16 */
+    int32_t flags;            /* B200Q_JOB_* */
+} b200q_job;
+
+b200q_status b200q_plan_create(b200q_ctx *ctx, const b200q_job *jobs, int32_t n_jobs, int64_t M,
+                               b200q_plan **out);
+b200q_status b200q_plan_run(b200q_ctx *ctx, b200q_plan *plan, void *stream);
+void b200q_plan_destroy(b200q_plan *plan);
+
 /* -- tensor parallel exchange ------------------------------------------------------------------ */
 
 /* 128-byte NCCL unique id for rank 0 to broadcast out of band. */

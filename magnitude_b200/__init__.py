@@ -19,7 +19,7 @@ from ._binding import (  # noqa: F401
     TYPE_Q6_K,
     TYPE_Q8_0,
 )
-from .projection import Backend, ProjectionWeight, shard_range, tensor_storage_bytes, tp_unique_id  # noqa: F401
+from .projection import Backend, Plan, ProjectionWeight, shard_range, tensor_storage_bytes, tp_unique_id  # noqa: F401
 
 _binding.lib()  # fail loudly at import time when the native library is absent
 

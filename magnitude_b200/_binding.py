@@ -29,6 +29,25 @@ TYPE_F32, TYPE_Q8_0, TYPE_Q4_K, TYPE_Q6_K, TYPE_BF16 = 0, 8, 12, 14, 30
 SPLIT_COLUMN, SPLIT_ROW = 0, 1
 ROUTE_NONE, ROUTE_GEMV, ROUTE_SKINNY, ROUTE_GEMM = 0, 1, 2, 3
 
+JOB_WAITS_FOR_EARLIER = 1
+
+
+class Job(ctypes.Structure):
+    """struct b200q_job of include/b200q.h."""
+
+    _fields_ = [
+        ("w", c_void_p * 4),
+        ("n_weights", c_int32),
+        ("x_dtype", c_int32),
+        ("x_dev", c_void_p),
+        ("ldx", c_int64),
+        ("y_dev", c_void_p * 4),
+        ("ldy", c_int64 * 4),
+        ("y_dtype", c_int32),
+        ("flags", c_int32),
+    ]
+
+
 # every symbol include/b200q.h declares: (restype, argtypes)
 SIGNATURES = {
     "b200q_version": (c_char_p, []),
@@ -74,6 +93,9 @@ SIGNATURES = {
         [c_void_p, POINTER(c_void_p), c_int32, c_void_p, c_int32, c_int64, c_int64, POINTER(c_void_p), c_int32,
          POINTER(c_int64)],
     ),
+    "b200q_plan_create": (c_int32, [c_void_p, POINTER(Job), c_int32, c_int64, POINTER(c_void_p)]),
+    "b200q_plan_run": (c_int32, [c_void_p, c_void_p, c_void_p]),
+    "b200q_plan_destroy": (None, [c_void_p]),
     "b200q_tp_unique_id": (c_int32, [c_void_p]),
     "b200q_tp_init": (c_int32, [c_void_p, c_int32, c_int32, c_void_p]),
     "b200q_allreduce": (c_int32, [c_void_p, c_void_p, c_int64, c_int32, c_void_p]),

@@ -93,6 +93,13 @@ struct b200q_ctx {
     int tp_rank = 0, tp_world = 1;
 };
 
+struct b200q_plan {
+    b200q_ctx *ctx = nullptr;
+    std::vector<StreamJob> jobs;
+    StreamJob *jobs_dev = nullptr;
+    int M = 0;
+};
+
 struct b200q_weight {
     b200q_ctx *ctx = nullptr;
     int type = 0;
@@ -152,7 +159,7 @@ b200q_status make_weight(b200q_ctx *ctx, int type, int64_t N, int64_t Kfull, con
     if (n > 0 && k > 0) {
         std::vector<uint8_t> staged;
         try {
-            staged.resize(w->device_bytes);
+            staged.assign(w->device_bytes, 0);
         } catch (...) {
             const size_t need = w->device_bytes;
             delete w;
@@ -162,9 +169,9 @@ b200q_status make_weight(b200q_ctx *ctx, int type, int64_t N, int64_t Kfull, con
         const int nt = (int)std::min<int64_t>(8, std::max<int64_t>(1, n / 256));
         std::vector<std::thread> th;
         for (int t = 0; t < nt; ++t) {
-            const int64_t a = r0 + n * t / nt, b = r0 + n * (t + 1) / nt;
-            uint8_t *dst = staged.data() + (a - r0) * w->row_bytes;
-            th.emplace_back([=] { repack_host(type, Kfull, gguf, a, b, sb0, sb1, dst); });
+            const int64_t a = n * t / nt, b = n * (t + 1) / nt;
+            uint8_t *dst = staged.data();
+            th.emplace_back([=] { repack_host(type, Kfull, gguf, r0, n, sb0, sb1, dst, a, b); });
         }
         for (auto &t : th) t.join();
         cudaError_t e = cudaMalloc(&w->dev, w->device_bytes + 256);
@@ -188,39 +195,57 @@ b200q_status check_ctx(b200q_ctx *ctx) {
     return B200Q_OK;
 }
 
-b200q_status run_gemv(b200q_ctx *ctx, const b200q_weight *const *w, int nw, const void *x, int x_dtype,
-                      int M, int64_t ldx, void *const *y, int y_dtype, const int64_t *ldy,
-                      cudaStream_t st) {
-    GemvLaunch a{};
-    a.qt = w[0]->type;
-    a.nseg = nw;
+void fill_job(StreamJob &J, const b200q_weight *const *w, int nw, const void *x, int x_dtype, int64_t ldx,
+              void *const *y, int y_dtype, const int64_t *ldy, int flags) {
+    J = StreamJob{};
+    J.nseg = nw;
     for (int i = 0; i < nw; ++i) {
-        a.w[i] = w[i]->dev;
-        a.y[i] = y[i];
-        a.ldy[i] = ldy[i];
-        a.n[i] = (int)w[i]->N;
+        J.seg[i].w = w[i]->dev;
+        J.seg[i].y = y[i];
+        J.seg[i].ldy = ldy[i];
+        J.seg[i].n = (int)w[i]->N;
     }
-    a.x = x;
-    a.ldx = ldx;
-    a.x_is_bf16 = x_dtype == B200Q_TYPE_BF16;
-    a.y_is_bf16 = y_dtype == B200Q_TYPE_BF16;
+    J.qt = w[0]->type;
+    J.K = (int)w[0]->K;
+    J.Kpad = (int)w[0]->Kpad;
+    J.row_bytes = w[0]->row_bytes;
+    J.x = x;
+    J.ldx = ldx;
+    J.x_is_bf16 = x_dtype == B200Q_TYPE_BF16;
+    const size_t xelt = act_size(x_dtype);
+    J.x_vec_ok = ((reinterpret_cast<uintptr_t>(x) & 15) == 0) && ((ldx * xelt) % 16 == 0);
+    J.y_is_bf16 = y_dtype == B200Q_TYPE_BF16;
+    J.flags = flags;
+    stream_job_finish(J);
+}
+
+b200q_status run_stream(b200q_ctx *ctx, const StreamJob *jobs_host, const StreamJob *jobs_dev, int njobs, int M,
+                        cudaStream_t st) {
+    StreamLaunch a{};
+    a.jobs_host = jobs_host;
+    a.jobs_dev = jobs_dev;
+    a.njobs = njobs;
     a.M = M;
-    a.K = (int)w[0]->K;
-    a.Kpad = (int)w[0]->Kpad;
-    a.row_bytes = w[0]->row_bytes;
     a.status = ctx->status_dev;
+    a.counter = reinterpret_cast<unsigned *>(ctx->status_dev) + 16;   // its own 64-byte line
     a.sm_count = ctx->sm_count;
     a.smem_limit = (ctx->gemv_smem > 0 && (size_t)ctx->gemv_smem < ctx->smem_optin) ? (size_t)ctx->gemv_smem : ctx->smem_optin;
     a.warps = ctx->gemv_warps;
     a.depth = ctx->gemv_depth;
     a.grid = ctx->gemv_grid;
-    a.rows_per_item = ctx->gemv_rows;
     a.debug = ctx->gemv_debug;
     a.pdl = ctx->gemv_pdl;
-    a.smem_sm = ctx->smem_sm;
-    cudaError_t e = gemv_launch(a, st);
-    if (e != cudaSuccess) return cuda_fail(ctx, e, "gemv launch");
+    cudaError_t e = stream_launch(a, st);
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "streaming kernel launch");
     return B200Q_OK;
+}
+
+b200q_status run_gemv(b200q_ctx *ctx, const b200q_weight *const *w, int nw, const void *x, int x_dtype,
+                      int M, int64_t ldx, void *const *y, int y_dtype, const int64_t *ldy,
+                      cudaStream_t st) {
+    StreamJob J;
+    fill_job(J, w, nw, x, x_dtype, ldx, y, y_dtype, ldy, 0);
+    return run_stream(ctx, &J, nullptr, 1, M, st);
 }
 
 b200q_status validate_mm(b200q_ctx *ctx, const b200q_weight *w, const void *x, int x_dtype, int64_t M,
@@ -432,7 +457,8 @@ b200q_status b200q_layout_pack(int32_t type, int64_t N, int64_t K, const void *p
         return B200Q_ERR_INVALID_CONFIG;
     if (N * K == 0) return B200Q_OK;
     if (!packed_host || !out_host) return B200Q_ERR_INVALID_CONFIG;
-    repack_host(type, K, (const uint8_t *)packed_host, 0, N, 0, (K + SB - 1) / SB, (uint8_t *)out_host);
+    memset(out_host, 0, out_bytes);
+    repack_host(type, K, (const uint8_t *)packed_host, 0, N, 0, (K + SB - 1) / SB, (uint8_t *)out_host, 0, N);
     return B200Q_OK;
 }
 
@@ -586,6 +612,84 @@ b200q_status b200q_matmul_host(b200q_ctx *ctx, const b200q_weight *w, const void
                                int32_t x_dtype, int64_t M, int64_t ldx, void *y_host,
                                int32_t y_dtype, int64_t ldy) {
     return b200q_matmul_multi_host(ctx, &w, 1, x_host, x_dtype, M, ldx, &y_host, y_dtype, &ldy);
+}
+
+// -- decode plans -------------------------------------------------------------------------------
+
+b200q_status b200q_plan_create(b200q_ctx *ctx, const b200q_job *jobs, int32_t n_jobs, int64_t M,
+                               b200q_plan **out) {
+    b200q_status s = check_ctx(ctx);
+    if (s != B200Q_OK) return s;
+    if (!out) return fail(ctx, B200Q_ERR_INVALID_CONFIG, "null out pointer");
+    *out = nullptr;
+    if (!jobs || n_jobs < 1) return fail(ctx, B200Q_ERR_INVALID_CONFIG, "a plan needs at least one job");
+    if (M < 1 || M > gemv_max_m()) return fail(ctx, B200Q_ERR_INVALID_CONFIG, "plans take 1..%d activation rows", gemv_max_m());
+    b200q_plan *pl = new (std::nothrow) b200q_plan();
+    if (!pl) return fail(ctx, B200Q_ERR_OVERLOADED, "out of host memory");
+    pl->ctx = ctx;
+    pl->M = (int)M;
+    for (int i = 0; i < n_jobs; ++i) {
+        const b200q_job &j = jobs[i];
+        if (j.n_weights < 1 || j.n_weights > 4) {
+            delete pl;
+            return fail(ctx, B200Q_ERR_INVALID_CONFIG, "job %d: 1..4 weights", i);
+        }
+        bool rows = false;
+        for (int k = 0; k < j.n_weights; ++k) {
+            s = validate_mm(ctx, j.w[k], j.x_dev, j.x_dtype, M, j.ldx, j.y_dev[k], j.y_dtype, j.ldy[k]);
+            if (s == B200Q_OK && (j.w[k]->type != j.w[0]->type || j.w[k]->K != j.w[0]->K))
+                s = fail(ctx, B200Q_ERR_INVALID_CONFIG, "job %d: weights of one job must share type and K", i);
+            if (s != B200Q_OK) {
+                delete pl;
+                return s;
+            }
+            rows |= j.w[k]->N > 0;
+        }
+        if (j.w[0]->K == 0) {
+            delete pl;
+            return fail(ctx, B200Q_ERR_INVALID_CONFIG, "job %d: K = 0 is not allowed in a plan", i);
+        }
+        if (!rows) continue;   // nothing to compute
+        StreamJob J;
+        fill_job(J, j.w, j.n_weights, j.x_dev, j.x_dtype, j.ldx, j.y_dev, j.y_dtype, j.ldy,
+                 (j.flags & B200Q_JOB_WAITS_FOR_EARLIER) && !pl->jobs.empty() ? STREAM_JOB_WAITS : 0);
+        pl->jobs.push_back(J);
+    }
+    if (!pl->jobs.empty()) {
+        const size_t bytes = pl->jobs.size() * sizeof(StreamJob);
+        cudaError_t e = cudaMalloc(&pl->jobs_dev, bytes);
+        if (e == cudaSuccess) e = cudaMemcpy(pl->jobs_dev, pl->jobs.data(), bytes, cudaMemcpyHostToDevice);
+        if (e != cudaSuccess) {
+            if (pl->jobs_dev) cudaFree(pl->jobs_dev);
+            delete pl;
+            return cuda_fail(ctx, e, "plan upload");
+        }
+    }
+    *out = pl;
+    return B200Q_OK;
+}
+
+b200q_status b200q_plan_run(b200q_ctx *ctx, b200q_plan *plan, void *stream) {
+    b200q_status s = check_ctx(ctx);
+    if (s != B200Q_OK) return s;
+    if (!plan || plan->ctx != ctx) return fail(ctx, B200Q_ERR_INVALID_CONFIG, "bad plan");
+    ctx->last_route = B200Q_ROUTE_NONE;
+    ctx->last_launches = 0;
+    if (plan->jobs.empty()) return B200Q_OK;
+    s = run_stream(ctx, plan->jobs.data(), plan->jobs_dev, (int)plan->jobs.size(), plan->M, (cudaStream_t)stream);
+    if (s != B200Q_OK) return s;
+    ctx->last_route = B200Q_ROUTE_GEMV;
+    ctx->last_launches = 1;
+    return B200Q_OK;
+}
+
+void b200q_plan_destroy(b200q_plan *plan) {
+    if (!plan) return;
+    if (plan->jobs_dev) {
+        if (plan->ctx) cudaSetDevice(plan->ctx->device);
+        cudaFree(plan->jobs_dev);
+    }
+    delete plan;
 }
 
 // -- tensor parallel --------------------------------------------------------------------------

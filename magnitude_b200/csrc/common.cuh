@@ -14,16 +14,21 @@ namespace b200q {
 // ---------------------------------------------------------------------------------------------
 // Streaming layout.
 //
-// A weight W[N][K] is stored row by row; a row is Kpad/256 "superblock records" of 256 weights
-// (Kpad = K rounded up to 256; only Q8_0 can need padding, its pad blocks are d = 0, q = 0).
-// Every record group a kernel copies in one piece starts on a 16-byte boundary and is a
-// multiple of 16 bytes long, which is what the bulk-copy engine requires.
+// A weight W[N][K] is cut into "superblock records" of 256 weights (Kpad = K rounded up to 256;
+// only Q8_0 can need padding, its pad blocks are d = 0, q = 0):
 //
 //   Q4_K : the native 144-byte block                    [d:2][dmin:2][scales:12][qs:128]
 //   Q8_0 : eight native 34-byte blocks regrouped as     [qs:8x32][d:8x2]            = 272 bytes
 //   Q6_K : the native 210-byte block without its d      [ql:128][qh:64][scales:16]  = 208 bytes,
 //          and after every eight records ("octet") one 16-byte group of their eight fp16 d
 //          (a trailing partial octet of r records is r*208 + 16 bytes).
+//
+// Records are stored tile by tile.  A tile is a group of kRowGroup = 4 consecutive rows x one
+// chunk of kChunkRecs = 8 consecutive records: inside a row group the chunks follow each other,
+// and inside a chunk the group's rows follow each other.  One tile (4 rows x 2048 weights, 4.5 KB
+// for Q4_K) is therefore one contiguous, 16-byte aligned byte range, which the streaming kernels
+// fetch with a single bulk copy.  The last row group of a tensor may hold fewer than 4 rows, the
+// last chunk of a row fewer than 8 records.
 //
 // The byte count equals GGUF's except for the Q8_0 K padding and at most 14 bytes per Q6_K row.
 // ---------------------------------------------------------------------------------------------
@@ -60,6 +65,36 @@ __host__ __device__ inline int64_t row_bytes_for(int qt, int64_t nsb) {
 __host__ __device__ inline int64_t range_bytes(int qt, int64_t sb0, int64_t sb1, int64_t nsb) {
     int64_t end = (sb1 >= nsb) ? row_bytes_for(qt, nsb) : rec_off(qt, sb1);
     return end - rec_off(qt, sb0);
+}
+
+constexpr int kRowGroup = 4;    // rows per tile
+constexpr int kChunkRecs = 8;   // records per tile row
+
+// bytes one row contributes to chunk c (records [8c, min(8c+8, nsb)))
+__host__ __device__ inline int64_t chunk_row_bytes(int qt, int64_t c, int64_t nsb) {
+    const int64_t sb1 = (c + 1) * kChunkRecs < nsb ? (c + 1) * kChunkRecs : nsb;
+    return range_bytes(qt, c * kChunkRecs, sb1, nsb);
+}
+// rows in row group g of an N-row tensor
+__host__ __device__ inline int group_rows(int64_t g, int64_t N) {
+    const int64_t left = N - g * kRowGroup;
+    return left < kRowGroup ? (int)left : kRowGroup;
+}
+// byte offset of tile (row group g, chunk c) from the start of the tensor
+__host__ __device__ inline int64_t tile_off(int qt, int64_t g, int64_t c, int64_t N, int64_t nsb) {
+    return g * kRowGroup * row_bytes_for(qt, nsb) + group_rows(g, N) * rec_off(qt, c * kChunkRecs);
+}
+// byte offset of record `sb` of row `row` (for Q6_K: of its 208-byte part)
+__host__ __device__ inline int64_t record_off(int qt, int64_t row, int64_t sb, int64_t N, int64_t nsb) {
+    const int64_t g = row / kRowGroup, c = sb / kChunkRecs;
+    return tile_off(qt, g, c, N, nsb) + (row - g * kRowGroup) * chunk_row_bytes(qt, c, nsb) +
+           (rec_off(qt, sb) - rec_off(qt, c * kChunkRecs));
+}
+// byte offset of the fp16 d of Q6_K record `sb` of row `row`
+__host__ __device__ inline int64_t q6k_d_record_off(int64_t row, int64_t sb, int64_t N, int64_t nsb) {
+    const int64_t g = row / kRowGroup, c = sb / kChunkRecs;
+    return tile_off(QT_Q6_K, g, c, N, nsb) + (row - g * kRowGroup) * chunk_row_bytes(QT_Q6_K, c, nsb) +
+           (q6k_d_off(sb, nsb) - rec_off(QT_Q6_K, c * kChunkRecs));
 }
 
 // Device status word values (atomicMax'ed, so larger = more severe).
@@ -104,6 +139,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+// non-blocking probe (try_wait may suspend the thread for a while; a polling loop that serves
+// several barriers must not)
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
         : "r"(bar), "r"(parity)

@@ -293,6 +293,46 @@ __device__ __forceinline__ void prep_row(const XSrc &p, int m, int T, uint8_t *x
     }
 }
 
+// The same conversion split in two, for a bf16 row of at most 4 * 8 * T elements: the global loads
+// are issued early (while the previous job is still being reduced and stored) and the values wait
+// in registers until the planes may be overwritten.
+constexpr int kPrepBatch = 4;
+struct XRaw {
+    uint4 r[kPrepBatch];
+};
+
+__device__ __forceinline__ bool prep_can_prefetch(const XSrc &p, int T) {
+    return p.x_is_bf16 && p.x_vec_ok && p.Kpad <= kPrepBatch * T * 8;
+}
+
+__device__ __forceinline__ void prep_prefetch(const XSrc &p, int T, XRaw &raw) {
+    const __nv_bfloat16 *x = reinterpret_cast<const __nv_bfloat16 *>(p.x);
+#pragma unroll
+    for (int b = 0; b < kPrepBatch; ++b) {
+        const int k0 = threadIdx.x * 8 + b * T * 8;
+        raw.r[b] = (k0 < p.K) ? *reinterpret_cast<const uint4 *>(x + k0) : make_uint4(0, 0, 0, 0);
+    }
+}
+
+template <int QT>
+__device__ __forceinline__ void prep_from_raw(const XSrc &p, int T, const XRaw &raw, uint8_t *xh, uint8_t *xl,
+                                              float *sx, int *isum, int units16) {
+#pragma unroll
+    for (int b = 0; b < kPrepBatch; ++b) {
+        const int k0 = threadIdx.x * 8 + b * T * 8;
+        if (k0 < p.Kpad) {   // warp-uniform: a warp covers 256 consecutive elements
+            const uint32_t w[4] = {raw.r[b].x, raw.r[b].y, raw.r[b].z, raw.r[b].w};
+            float v[8];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                v[2 * i] = __uint_as_float(w[i] << 16);
+                v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+            }
+            prep_store8<QT>(v, k0, xh, xl, sx, isum, units16);
+        }
+    }
+}
+
 // Sum R per-lane values over the 32 lanes with a folding butterfly (6 shuffles for R = 4, 5 for
 // R = 2 instead of 5 per value).  The total of value r ends up in lane r * (32 / R).
 template <int R> __device__ __forceinline__ float fold_rows(const float (&a)[R], int lane) {

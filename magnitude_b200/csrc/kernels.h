@@ -8,38 +8,59 @@
 namespace b200q {
 
 // ---- layout.cu ------------------------------------------------------------------------------
-// Host: re-lay GGUF rows [r0, r1) x superblocks [sb0, sb1) of a tensor into the streaming layout.
-// K is the full tensor's row length; dst receives (r1-r0) rows of row_bytes_for(qt, sb1-sb0).
-void repack_host(int qt, int64_t K, const uint8_t *gguf, int64_t r0, int64_t r1, int64_t sb0,
-                 int64_t sb1, uint8_t *dst);
+// Host: re-lay rows [r0, r0 + n) x superblocks [sb0, sb1) of a GGUF tensor (row length K) into the
+// streaming layout at dst (n * row_bytes_for(qt, sb1 - sb0) bytes).  Only shard rows [ra, rb) are
+// written, so several threads can share one call's work.
+void repack_host(int qt, int64_t K, const uint8_t *gguf, int64_t r0, int64_t n, int64_t sb0,
+                 int64_t sb1, uint8_t *dst, int64_t ra, int64_t rb);
 // Device: fp32 values of rows of a streaming-layout weight (bit-exact, no fused multiply-add).
 cudaError_t dequant_launch(int qt, const uint8_t *w, int64_t N, int64_t K, int64_t Kpad,
                            int64_t row_bytes, float *out, cudaStream_t st);
 
 // ---- gemv.cu --------------------------------------------------------------------------------
-struct GemvLaunch {
+// The streaming kernel runs a list of jobs in one launch.  A job is 1..4 weights of one type and
+// K applied to one activation (M <= 4 rows, the same M for every job of a launch).
+constexpr int kStreamMaxSeg = 4;
+enum : int { STREAM_JOB_WAITS = 1 };   // the job reads what earlier jobs of the launch wrote
+
+struct StreamSeg {
+    const uint8_t *w;   // streaming-layout rows
+    void *y;            // output base (row m at y + m*ldy elements)
+    long long ldy;
+    int n;              // rows
+    int group_begin;    // first virtual 4-row group of this segment (filled by stream_job_finish)
+};
+
+struct StreamJob {
+    StreamSeg seg[kStreamMaxSeg];
+    int nseg;
+    int total_groups;                  // filled by stream_job_finish: 4-row groups over all segments
     int qt;
-    int nseg;                 // 1..4 weights sharing x
-    const uint8_t *w[4];
-    void *y[4];
-    long long ldy[4];
-    int n[4];
+    int K, Kpad;
+    int nsb, nchunks;                  // filled by stream_job_finish
+    long long row_bytes;
+    unsigned bytes_full, bytes_tail;   // filled: bytes one row adds to a chunk, all but the last / the last
     const void *x;
     long long ldx;
-    int x_is_bf16, y_is_bf16;
-    int M;                    // 1..4
-    int K, Kpad;
-    long long row_bytes;
-    int *status;              // device status word
+    int x_is_bf16, x_vec_ok, y_is_bf16;
+    int flags;                         // STREAM_JOB_*
+};
+
+struct StreamLaunch {
+    const StreamJob *jobs_host;   // always: the descriptors, readable by the host
+    const StreamJob *jobs_dev;    // the same table in device memory, or nullptr for a single job
+    int njobs;
+    int M;                        // 1..4
+    int *status;                  // device status word
+    unsigned *counter;            // device word for grid-wide completion counting
     int sm_count;
-    size_t smem_limit;        // opt-in shared memory per block
-    size_t smem_sm;           // shared memory per SM
-    int pdl;                  // launch with programmatic stream serialization
-    int warps, depth, grid;   // 0 = default
-    int rows_per_item;        // 0 = choose, else 2 or 4
-    int debug;                // experiments only (see gemv.cu)
+    size_t smem_limit;            // opt-in shared memory per block
+    int warps, depth, grid;       // 0 = default
+    int debug;                    // experiments only (see gemv.cu)
+    int pdl;                      // launch with programmatic stream serialization
 };
 int gemv_max_m();
-cudaError_t gemv_launch(const GemvLaunch &a, cudaStream_t st);
+void stream_job_finish(StreamJob &job);
+cudaError_t stream_launch(const StreamLaunch &a, cudaStream_t st);
 
 }  // namespace b200q

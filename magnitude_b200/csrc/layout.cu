@@ -6,20 +6,18 @@
 
 namespace b200q {
 
-void repack_host(int qt, int64_t K, const uint8_t *gguf, int64_t r0, int64_t r1, int64_t sb0,
-                 int64_t sb1, uint8_t *dst) {
+void repack_host(int qt, int64_t K, const uint8_t *gguf, int64_t r0, int64_t n, int64_t sb0,
+                 int64_t sb1, uint8_t *dst, int64_t ra, int64_t rb) {
     const int64_t src_row = K / gguf_block_elems(qt) * gguf_block_bytes(qt);
     const int64_t nsb = sb1 - sb0;
-    const int64_t dst_row = row_bytes_for(qt, nsb);
-    for (int64_t r = r0; r < r1; ++r) {
-        const uint8_t *s = gguf + r * src_row;
-        uint8_t *d = dst + (r - r0) * dst_row;
-        if (qt == QT_Q4_K) {
-            memcpy(d, s + sb0 * 144, (size_t)nsb * 144);
-        } else if (qt == QT_Q8_0) {
-            const int64_t nblk = K / 32;
-            for (int64_t sb = 0; sb < nsb; ++sb) {
-                uint8_t *rec = d + sb * 272;
+    for (int64_t r = ra; r < rb; ++r) {   // r: row of the shard, r0 + r: row of the full tensor
+        const uint8_t *s = gguf + (r0 + r) * src_row;
+        for (int64_t sb = 0; sb < nsb; ++sb) {
+            uint8_t *rec = dst + record_off(qt, r, sb, n, nsb);
+            if (qt == QT_Q4_K) {
+                memcpy(rec, s + (sb0 + sb) * 144, 144);
+            } else if (qt == QT_Q8_0) {
+                const int64_t nblk = K / 32;
                 for (int b = 0; b < 8; ++b) {
                     const int64_t blk = (sb0 + sb) * 8 + b;
                     if (blk < nblk) {
@@ -30,13 +28,10 @@ void repack_host(int qt, int64_t K, const uint8_t *gguf, int64_t r0, int64_t r1,
                         memset(rec + 256 + 2 * b, 0, 2);
                     }
                 }
-            }
-        } else {
-            memset(d, 0, (size_t)dst_row);
-            for (int64_t sb = 0; sb < nsb; ++sb) {
+            } else {
                 const uint8_t *blk = s + (sb0 + sb) * 210;
-                memcpy(d + rec_off(qt, sb), blk, 208);
-                memcpy(d + q6k_d_off(sb, nsb), blk + 208, 2);
+                memcpy(rec, blk, 208);
+                memcpy(dst + q6k_d_record_off(r, sb, n, nsb), blk + 208, 2);
             }
         }
     }
@@ -46,18 +41,16 @@ namespace {
 
 // One CTA per (row, superblock record); thread t produces weight t of the record.
 template <int QT>
-__global__ void __launch_bounds__(256) dequant_kernel(const uint8_t *__restrict__ w, int64_t K,
-                                                      int nsb, int64_t row_bytes,
-                                                      float *__restrict__ out) {
+__global__ void __launch_bounds__(256) dequant_kernel(const uint8_t *__restrict__ w, int64_t N, int64_t K,
+                                                      int nsb, float *__restrict__ out) {
     const int sb = blockIdx.x % nsb;
     const int64_t row = blockIdx.x / nsb;
     const int t = threadIdx.x;
     const int64_t k = (int64_t)sb * 256 + t;
     if (k >= K) return;
-    const uint8_t *base = w + row * row_bytes;
     float v;
     if (QT == QT_Q4_K) {
-        const uint8_t *rec = base + (int64_t)sb * 144;
+        const uint8_t *rec = w + record_off(QT, row, sb, N, nsb);
         const uint32_t *hw = reinterpret_cast<const uint32_t *>(rec);
         const float d = half_bits_to_float(hw[0]), dmin = half_bits_to_float(hw[0] >> 16);
         int sc, mn;
@@ -68,13 +61,13 @@ __global__ void __launch_bounds__(256) dequant_kernel(const uint8_t *__restrict_
         const float m1 = __fmul_rn(dmin, (float)mn);
         v = __fsub_rn(__fmul_rn(d1, (float)q), m1);
     } else if (QT == QT_Q8_0) {
-        const uint8_t *rec = base + (int64_t)sb * 272;
+        const uint8_t *rec = w + record_off(QT, row, sb, N, nsb);
         const float d = half_bits_to_float(*reinterpret_cast<const uint16_t *>(rec + 256 + 2 * (t >> 5)));
         const int q = (int)(int8_t)rec[t];
         v = __fmul_rn(d, (float)q);
     } else {
-        const uint8_t *rec = base + rec_off(QT_Q6_K, sb);
-        const float d = half_bits_to_float(*reinterpret_cast<const uint16_t *>(base + q6k_d_off(sb, nsb)));
+        const uint8_t *rec = w + record_off(QT, row, sb, N, nsb);
+        const float d = half_bits_to_float(*reinterpret_cast<const uint16_t *>(w + q6k_d_record_off(row, sb, N, nsb)));
         const int h = t >> 7, l = t & 127, c = l >> 5, pos = l & 31;
         const uint8_t qlb = rec[64 * h + 32 * (c & 1) + pos];
         const uint8_t qhb = rec[128 + 32 * h + pos];
@@ -94,9 +87,9 @@ cudaError_t dequant_launch(int qt, const uint8_t *w, int64_t N, int64_t K, int64
     if (blocks == 0) return cudaSuccess;
     if (blocks > 0x7FFFFFFF) return cudaErrorInvalidValue;
     switch (qt) {
-    case QT_Q4_K: dequant_kernel<QT_Q4_K><<<(unsigned)blocks, 256, 0, st>>>(w, K, nsb, row_bytes, out); break;
-    case QT_Q8_0: dequant_kernel<QT_Q8_0><<<(unsigned)blocks, 256, 0, st>>>(w, K, nsb, row_bytes, out); break;
-    case QT_Q6_K: dequant_kernel<QT_Q6_K><<<(unsigned)blocks, 256, 0, st>>>(w, K, nsb, row_bytes, out); break;
+    case QT_Q4_K: dequant_kernel<QT_Q4_K><<<(unsigned)blocks, 256, 0, st>>>(w, N, K, nsb, out); break;
+    case QT_Q8_0: dequant_kernel<QT_Q8_0><<<(unsigned)blocks, 256, 0, st>>>(w, N, K, nsb, out); break;
+    case QT_Q6_K: dequant_kernel<QT_Q6_K><<<(unsigned)blocks, 256, 0, st>>>(w, N, K, nsb, out); break;
     default: return cudaErrorInvalidValue;
     }
     return cudaGetLastError();

@@ -68,6 +68,33 @@ class ProjectionWeight:
             pass
 
 
+class Plan:
+    """A fixed list of decode projections that one launch runs back to back (see b200q_plan_create).
+
+    The plan keeps references to the tensors it was built from; rewrite the activation tensors in
+    place and call run() again for the next token.
+    """
+
+    def __init__(self, backend: "Backend", handle: int, keep):
+        self.backend = backend
+        self._h = c_void_p(handle)
+        self._keep = keep
+
+    def run(self, stream=None) -> None:
+        self.backend._check(B.lib().b200q_plan_run(self.backend._h, self._h, self.backend._stream_ptr(stream)))
+
+    def close(self) -> None:
+        if self._h:
+            B.lib().b200q_plan_destroy(self._h)
+            self._h = c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
 class Backend:
     """One b200q context: one GPU, one owning thread."""
 
@@ -189,6 +216,44 @@ class Backend:
             )
         )
         return outs
+
+    def plan(self, jobs, waits: Sequence[bool] | None = None) -> Plan:
+        """jobs: sequence of (weights, x, outs) with weights/outs sequences of equal length (1..4),
+        x a CUDA tensor [M, K] (M <= 4, the same for every job).  waits[i] marks job i as reading
+        what earlier jobs of the plan write."""
+        torch = _torch()
+        n = len(jobs)
+        arr = (B.Job * n)()
+        keep = []
+        m = None
+        for i, (ws, x, outs) in enumerate(jobs):
+            if x.dim() == 1:
+                x = x.unsqueeze(0)
+            if x.stride(-1) != 1:
+                raise B.B200QError(B.ERR_INVALID_CONFIG, "plan activations must be contiguous along K")
+            if m is None:
+                m = x.shape[0]
+            elif m != x.shape[0]:
+                raise B.B200QError(B.ERR_INVALID_CONFIG, "every job of a plan takes the same number of rows")
+            if len(ws) != len(outs) or not 1 <= len(ws) <= 4:
+                raise B.B200QError(B.ERR_INVALID_CONFIG, "a job takes 1..4 weights and as many outputs")
+            j = arr[i]
+            j.n_weights = len(ws)
+            j.x_dtype = _TORCH_DTYPE[x.dtype]
+            j.x_dev = x.data_ptr()
+            j.ldx = x.stride(0) if m > 1 else max(x.shape[1], 1)
+            j.y_dtype = _TORCH_DTYPE[outs[0].dtype]
+            j.flags = B.JOB_WAITS_FOR_EARLIER if (waits and waits[i]) else 0
+            for k, (w, o) in enumerate(zip(ws, outs)):
+                if o.dim() == 1:
+                    o = o.unsqueeze(0)
+                j.w[k] = w._h.value
+                j.y_dev[k] = o.data_ptr()
+                j.ldy[k] = o.stride(0) if m > 1 else max(o.shape[1], 1)
+            keep.append((list(ws), x, list(outs)))
+        out = c_void_p()
+        self._check(B.lib().b200q_plan_create(self._h, arr, n, m or 1, byref(out)))
+        return Plan(self, out.value, keep)
 
     # -- host-buffer path (the reference's own boundary: host in, host out) ------------------
     def project_host(self, w: ProjectionWeight, x: np.ndarray, x_dtype: int = B.TYPE_F32, out: np.ndarray | None = None,

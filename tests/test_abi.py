@@ -68,37 +68,68 @@ def _pack(qt, packed, n, k):
     return out
 
 
+REC = {12: 144, 8: 272, 14: 208}
+
+
+def _rec_off(qt, sb):
+    return (sb >> 3) * 1680 + (sb & 7) * 208 if qt == 14 else sb * REC[qt]
+
+
+def _row_bytes(qt, nsb):
+    if qt == 14:
+        return (nsb >> 3) * 1680 + ((nsb & 7) * 208 + 16 if nsb & 7 else 0)
+    return nsb * REC[qt]
+
+
+def _record_off(qt, row, sb, n, nsb):
+    """Tile-major layout: groups of 4 rows, chunks of 8 records, rows of a group adjacent inside a chunk."""
+    g, c = row // 4, sb // 8
+    nr = min(4, n - 4 * g)
+    end = _row_bytes(qt, nsb) if (c + 1) * 8 >= nsb else _rec_off(qt, (c + 1) * 8)
+    chunk_row = end - _rec_off(qt, c * 8)
+    return 4 * g * _row_bytes(qt, nsb) + nr * _rec_off(qt, c * 8) + (row - 4 * g) * chunk_row + _rec_off(qt, sb) - _rec_off(qt, c * 8)
+
+
 def test_streaming_layout_is_a_permutation_of_the_gguf_bytes(orc):
     rng = np.random.default_rng(0)
-    # Q4_K: identical bytes
-    p = rng.integers(0, 256, size=(3, 5 * 144), dtype=np.uint8)
-    assert np.array_equal(_pack(12, p, 3, 5 * 256), p)
+    # Q4_K: native 144-byte blocks, tile order; 6 rows = one full row group + a group of 2
+    n, nsb = 6, 11
+    p = rng.integers(0, 256, size=(n, nsb * 144), dtype=np.uint8)
+    s = _pack(12, p, n, nsb * 256).reshape(-1)
+    assert s.size == p.size
+    for r in range(n):
+        for sb in range(nsb):
+            o = _record_off(12, r, sb, n, nsb)
+            assert np.array_equal(s[o:o + 144], p[r, sb * 144:(sb + 1) * 144])
+    # a tile (4 rows x 8 records) is one contiguous range
+    assert _record_off(12, 1, 0, n, nsb) - _record_off(12, 0, 0, n, nsb) == 8 * 144
+    assert _record_off(12, 0, 8, n, nsb) == 4 * 8 * 144
     # Q8_0: per 8 blocks [8 x 32 quants][8 x d]; ragged K padded with zero blocks
-    k = 11 * 32
-    p = rng.integers(0, 256, size=(2, 11 * 34), dtype=np.uint8)
-    s = _pack(8, p, 2, k)
-    assert s.shape[1] == 2 * 272
-    for r in range(2):
+    n, k = 5, 11 * 32
+    p = rng.integers(0, 256, size=(n, 11 * 34), dtype=np.uint8)
+    s = _pack(8, p, n, k).reshape(-1)
+    assert s.size == n * 2 * 272
+    for r in range(n):
         for b in range(16):
-            rec = s[r, (b // 8) * 272:(b // 8 + 1) * 272]
+            o = _record_off(8, r, b // 8, n, 2)
+            rec = s[o:o + 272]
             q, d = rec[32 * (b % 8):32 * (b % 8) + 32], rec[256 + 2 * (b % 8):258 + 2 * (b % 8)]
             if b < 11:
                 assert np.array_equal(q, p[r, 34 * b + 2:34 * b + 34]) and np.array_equal(d, p[r, 34 * b:34 * b + 2])
             else:
                 assert not q.any() and not d.any()
     # Q6_K: 208-byte records, the eight d of an octet after it; 11 superblocks = one octet + 3
-    nsb = 11
-    p = rng.integers(0, 256, size=(2, nsb * 210), dtype=np.uint8)
-    s = _pack(14, p, 2, nsb * 256)
-    assert s.shape[1] == 1680 + 3 * 208 + 16 and s.shape[1] % 16 == 0
-    for r in range(2):
+    n, nsb = 7, 11
+    p = rng.integers(0, 256, size=(n, nsb * 210), dtype=np.uint8)
+    s = _pack(14, p, n, nsb * 256).reshape(-1)
+    assert s.size == n * (1680 + 3 * 208 + 16) and s.size % 16 == 0
+    for r in range(n):
         for sb in range(nsb):
-            base = (sb // 8) * 1680
+            o = _record_off(14, r, sb, n, nsb)
             in_octet = min(8, nsb - (sb // 8) * 8)
-            rec = s[r, base + (sb % 8) * 208: base + (sb % 8) * 208 + 208]
-            d = s[r, base + in_octet * 208 + 2 * (sb % 8): base + in_octet * 208 + 2 * (sb % 8) + 2]
-            assert np.array_equal(rec, p[r, sb * 210: sb * 210 + 208])
-            assert np.array_equal(d, p[r, sb * 210 + 208: sb * 210 + 210])
+            od = _record_off(14, r, (sb // 8) * 8, n, nsb) + in_octet * 208 + 2 * (sb % 8)
+            assert np.array_equal(s[o:o + 208], p[r, sb * 210: sb * 210 + 208])
+            assert np.array_equal(s[od:od + 2], p[r, sb * 210 + 208: sb * 210 + 210])
 
 
 def test_layout_argument_checks():

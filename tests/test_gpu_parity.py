@@ -224,3 +224,68 @@ def test_one_hot_sub_blocks(backend, orc):
             backend.sync()
             ref = xs[j0:j0 + 4].astype(np.float64) @ wf.T
             assert np.allclose(y.cpu().numpy(), ref, rtol=1e-3, atol=1e-6), (qt, j0)
+
+
+def test_plan_matches_single_calls_mixed_types(backend, orc):
+    k = 2048
+    gate = backend.upload(mb.TYPE_Q4_K, _weights(orc, mb.TYPE_Q4_K, 300, k, 1), 300, k)
+    up = backend.upload(mb.TYPE_Q4_K, _weights(orc, mb.TYPE_Q4_K, 300, k, 2), 300, k)
+    v = backend.upload(mb.TYPE_Q6_K, _weights(orc, mb.TYPE_Q6_K, 65, k, 3), 65, k)
+    q8 = backend.upload(mb.TYPE_Q8_0, _weights(orc, mb.TYPE_Q8_0, 33, 1024, 4), 33, 1024)
+    x1 = _acts(1, k, 5, torch.bfloat16)
+    x2 = _acts(1, 1024, 6, torch.float32)
+    outs = [torch.zeros((1, n), device="cuda") for n in (300, 300, 65, 33)]
+    plan = backend.plan([([gate, up], x1, outs[0:2]), ([v], x1, outs[2:3]), ([q8], x2, outs[3:4])])
+    plan.run()
+    backend.sync()
+    assert backend.last_route() == (mb.ROUTE_GEMV, 1)
+    singles = [backend.project(gate, x1), backend.project(up, x1), backend.project(v, x1), backend.project(q8, x2)]
+    backend.sync()
+    for a, b in zip(outs, singles):
+        assert torch.equal(a, b)
+    # a second run after rewriting the activation in place
+    x1.copy_(_acts(1, k, 7, torch.bfloat16))
+    plan.run()
+    backend.sync()
+    ref = orc.matmul_exact(mb.TYPE_Q6_K, _weights(orc, mb.TYPE_Q6_K, 65, k, 3), 65, k, x1.float().cpu().numpy())
+    assert orc.within_tolerance(outs[2].cpu().numpy(), ref, REL_DECODE)[0]
+
+
+@pytest.mark.parametrize("m", [1, 2])
+def test_plan_with_dependent_job(backend, orc, m):
+    # job 1 reads what job 0 wrote: every CTA must have stored job 0's rows first
+    k0, n0, n1 = 1024, 4096, 512
+    p0 = _weights(orc, mb.TYPE_Q4_K, n0, k0, 11)
+    p1 = _weights(orc, mb.TYPE_Q4_K, n1, n0, 12)
+    w0 = backend.upload(mb.TYPE_Q4_K, p0, n0, k0)
+    w1 = backend.upload(mb.TYPE_Q4_K, p1, n1, n0)
+    x = _acts(m, k0, 13, torch.bfloat16)
+    mid = torch.zeros((m, n0), device="cuda")
+    out = torch.zeros((m, n1), device="cuda")
+    plan = backend.plan([([w0], x, [mid]), ([w1], mid, [out])], waits=[False, True])
+    for _ in range(3):
+        mid.zero_()
+        out.zero_()
+        plan.run()
+        backend.sync()
+        ref_mid = backend.project(w0, x)
+        ref_out = backend.project(w1, ref_mid)
+        backend.sync()
+        assert torch.equal(mid, ref_mid)
+        assert torch.equal(out, ref_out)
+    ref = orc.matmul_exact(mb.TYPE_Q4_K, p1, n1, n0, mid.cpu().numpy())
+    assert orc.within_tolerance(out.cpu().numpy(), ref, REL_DECODE)[0]
+
+
+def test_plan_argument_checks(backend, orc):
+    k = 512
+    w = backend.upload(mb.TYPE_Q4_K, _weights(orc, mb.TYPE_Q4_K, 8, k, 1), 8, k)
+    x = _acts(1, k, 2, torch.bfloat16)
+    y = torch.zeros((1, 8), device="cuda")
+    with pytest.raises(mb.B200QError):
+        backend.plan([([w], _acts(5, k, 2, torch.bfloat16), [torch.zeros((5, 8), device="cuda")])])   # M > 4
+    with pytest.raises(mb.B200QError):
+        backend.plan([([w], x, [y, y])])
+    w6 = backend.upload(mb.TYPE_Q6_K, _weights(orc, mb.TYPE_Q6_K, 8, k, 1), 8, k)
+    with pytest.raises(mb.B200QError):
+        backend.plan([([w, w6], x, [y, y.clone()])])   # mixed types inside one job
