@@ -86,58 +86,54 @@ __device__ __forceinline__ void locate_group(const StreamJob &J, int vg, int &s,
 __device__ __forceinline__ void consumer_sync(int T) { asm volatile("bar.sync 1, %0;" ::"r"(T) : "memory"); }
 
 // one item (a tile: up to 4 rows x one chunk) of one job for this lane's 64-weight unit;
-// `stride` is the byte distance between the tile's rows
+// `sl` = shared address of the tile, `stride` = byte distance between its rows
 template <int QT, int MT, typename Flush>
-__device__ __forceinline__ void item_dot(int nsb, const uint8_t *sl, int stride, int sb0, int lsb, int j, int nr,
+__device__ __forceinline__ void item_dot(int nsb, uint32_t sl, int stride, int sb0, int lsb, int j, int nr,
                                          const XView (&xv)[MT], int units16, bool whole, float (&acc)[R][MT],
                                          Flush &&flush_pending) {
     const int gsb = sb0 + lsb;
     const int gu = gsb * 4 + j;
+    const uint32_t rec0 = sl + lsb * rec_bytes(QT);
+    float d6[R];
+    if constexpr (QT == QT_Q6_K) {
+        const uint32_t doff = sl + (uint32_t)(q6k_d_off(gsb, nsb) - rec_off(QT, sb0));
+#pragma unroll
+        for (int r = 0; r < R; ++r) d6[r] = (r < nr) ? half_bits_to_float(lds16(doff + r * stride)) : 0.f;
+    }
     auto load_w = [&](WRegs<QT> &w, int r) {
-        const uint8_t *row = sl + r * stride;
-        if constexpr (QT == QT_Q4_K) {
-            w.load(row + lsb * 144, j);
-        } else if constexpr (QT == QT_Q8_0) {
-            w.load(row + lsb * 272, j);
-        } else {
-            const int doff = (int)(q6k_d_off(gsb, nsb) - rec_off(QT, sb0));
-            const float d = half_bits_to_float(*reinterpret_cast<const uint16_t *>(row + doff));
-            w.load(row + lsb * 208, j, d);
-        }
+        if constexpr (QT == QT_Q6_K) w.load(rec0 + r * stride, j, d6[r]);
+        else w.load(rec0 + r * stride, j);
     };
-    if constexpr (MT == 1) {
-        // one activation row: keep its bytes in registers, stream the weight rows past them
-        XRegs xr;
-        load_x(xr, xv[0], gu, units16);
+    if constexpr (MT <= 2) {
+        // one or two activation rows: keep their bytes in registers, stream the weight rows past them
+        XRegs<QT> xr[MT];
+#pragma unroll
+        for (int m = 0; m < MT; ++m) xr[m].load(xv[m], gu, gsb, j, units16);
         if (whole) flush_pending();
 #pragma unroll
         for (int r = 0; r < R; ++r) {
             if (r < nr) {
                 WRegs<QT> w;
                 load_w(w, r);
-                acc[r][0] += w.dot(xr, xv[0], QT == QT_Q6_K ? gsb : gu);
+#pragma unroll
+                for (int m = 0; m < MT; ++m) acc[r][m] += w.dot(xr[m]);
             }
         }
     } else {
-        // several activation rows: unpack two weight rows at a time, stream the activations past them
-        bool flushed = !whole;
-#pragma unroll
-        for (int rp = 0; rp < R; rp += 2) {
-            WRegs<QT> wr[2];
-#pragma unroll
-            for (int r = 0; r < 2; ++r)
-                if (rp + r < nr) load_w(wr[r], rp + r);
-            if (!flushed) {
-                flush_pending();
-                flushed = true;
-            }
+        // more activation rows than registers can hold: one weight row at a time, activations re-read
+        if (whole) flush_pending();
+#pragma unroll 1
+        for (int r = 0; r < nr; ++r) {
+            WRegs<QT> w;
+            load_w(w, r);
 #pragma unroll
             for (int m = 0; m < MT; ++m) {
-                XRegs xr;
-                load_x(xr, xv[m], gu, units16);
+                XRegs<QT> xr;
+                xr.load(xv[m], gu, gsb, j, units16);
+                const float v = w.dot(xr);
 #pragma unroll
-                for (int r = 0; r < 2; ++r)
-                    if (rp + r < nr) acc[rp + r][m] += wr[r].dot(xr, xv[m], QT == QT_Q6_K ? gsb : gu);
+                for (int rr = 0; rr < R; ++rr)
+                    if (rr == r) acc[rr][m] += v;
             }
         }
     }
@@ -268,7 +264,7 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1) stream_kernel(const S
     // consumer warps
     // =========================================================================================
     const int T = CW * 32;
-    const uint8_t *ring = rings + warp * ring_bytes;
+    const uint32_t ring_sa = smem_u32(rings + warp * ring_bytes);
     const uint32_t fbar = full0 + warp * kMaxDepth * 8, ebar = empty0 + warp * kMaxDepth * 8;
     const int lsb = lane >> 2, j = lane & 3;   // this lane's record and 64-weight group in a chunk
     volatile int *fail_flag = &head.fail;
@@ -328,10 +324,10 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1) stream_kernel(const S
                 uint8_t *b = xbase + m * per_m;
                 float *sxp = reinterpret_cast<float *>(b + 2 * plane);
                 int *isp = reinterpret_cast<int *>(b + 2 * plane + (J.Kpad >> 5) * 4);
-                xv[m].xh = b;
-                xv[m].xl = b + plane;
-                xv[m].sx = sxp;
-                xv[m].isum = isp;
+                xv[m].xh = smem_u32(b);
+                xv[m].xl = smem_u32(b + plane);
+                xv[m].sx = smem_u32(sxp);
+                xv[m].isum = smem_u32(isp);
                 if (m < p.M && !(p.debug & 4)) {
                     const bool q6 = (TYPES & TY_Q6K) && (TYPES == TY_Q6K || qt == QT_Q6_K);
                     if (MT == 1 && have_raw) {
@@ -375,8 +371,9 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1) stream_kernel(const S
             pend_cell = -1;
         };
 
-        int g = 0, c = warp;               // item = g * nchunks + c, kept without dividing
-        while (c >= nchunks) { c -= nchunks; ++g; }
+        // item = g * nchunks + c; stepping by CW items without dividing in the loop
+        const int step_g = CW / nchunks, step_c = CW - step_g * nchunks;
+        int g = warp / nchunks, c = warp - g * nchunks;
 #pragma unroll 1
         for (int item = (p.debug & 16) ? n_items : warp; item < n_items; item += CW) {
             bool ok = (p.debug & 2) ? true : mbar_wait_bounded(fbar + 8 * slot, phase);
@@ -404,7 +401,7 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1) stream_kernel(const S
             const bool whole = (sb0 + KC <= nsb) && !(p.debug & 1);
             if (!whole) flush_pending();
             if (sb0 + lsb < nsb && !(p.debug & 1)) {
-                const uint8_t *sl = ring + slot * slot_bytes;
+                const uint32_t sl = ring_sa + slot * slot_bytes;
                 if ((TYPES & TY_Q4K) && (TYPES == TY_Q4K || qt == QT_Q4_K))
                     item_dot<QT_Q4_K, MT>(nsb, sl, cb, sb0, lsb, j, nr, xv, units16, whole, acc, flush_pending);
                 else if ((TYPES & TY_Q6K) && (TYPES == TY_Q6K || qt == QT_Q6_K))
@@ -425,8 +422,10 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1) stream_kernel(const S
                 for (int m = 0; m < MT; ++m) pend[r][m] = acc[r][m];
             pend_cell = (p.debug & 32) ? -1 : (g * R) * nchunks + c;
             pend_nr = nr;
-            c += CW;
-            while (c >= nchunks) { c -= nchunks; ++g; }
+            if constexpr (MT > 1) flush_pending();   // several activation rows: registers are scarce, sum at once
+            g += step_g;
+            c += step_c;
+            if (c >= nchunks) { c -= nchunks; ++g; }
         }
         flush_pending();
         // start loading the next job's activation now: the loads fly while this job is summed and

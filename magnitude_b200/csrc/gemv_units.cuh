@@ -28,25 +28,71 @@ template <int QT> __device__ __forceinline__ int xplane_off(int k, int units16) 
     return ((k >> 4) & 3) * units16 + (k >> 6) * 16 + (k & 15);
 }
 
-struct XView {            // shared-memory views of one activation row in fixed-point form
-    const uint8_t *xh;    // signed high bytes
-    const uint8_t *xl;    // signed low bytes
-    const float *sx;      // per 32 weights
-    const int *isum;      // sum of the 16-bit integers: per 32 weights (Q4_K) or per 16 (Q6_K)
+// Shared-memory reads go through 32-bit shared-window addresses: the hot loop then spends no
+// instructions on 64-bit pointer arithmetic.  (volatile keeps them after the barrier waits.)
+__device__ __forceinline__ uint4 lds128(uint32_t a) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t a) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t a) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds16(uint32_t a) {
+    uint16_t v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(a));
+    return v;
+}
+
+struct XView {            // shared-window addresses of one activation row in fixed-point form
+    uint32_t xh;          // signed high bytes
+    uint32_t xl;          // signed low bytes
+    uint32_t sx;          // fp32 per 32 weights
+    uint32_t isum;        // int32 sum of the 16-bit integers: per 32 weights (Q4_K) or per 16 (Q6_K)
 };
 
-struct XRegs {            // one 64-weight unit of one activation row: 4 groups of 16 weights
+// One 64-weight unit of one activation row: 4 groups of 16 weights as byte planes, plus the
+// block scales and sums that go with the unit (loaded once per item, reused for its 4 rows).
+template <int QT> struct XRegs {
     uint4 h[4];
     uint4 l[4];
-};
+    float sx[4];          // Q4_K / Q8_0 use [0], [1]; Q6_K one per 32-weight quadrant
+    int is[4];            // Q4_K: [0], [1] 32-weight sums; Q6_K: the four 16-weight sums of this unit
 
-__device__ __forceinline__ void load_x(XRegs &xr, const XView &xv, int unit, int units16) {
+    // gu = global 64-weight unit of the row, gsb = its superblock, j = unit inside the superblock
+    __device__ __forceinline__ void load(const XView &xv, int gu, int gsb, int j, int units16) {
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
-        xr.h[c] = *reinterpret_cast<const uint4 *>(xv.xh + c * units16 + unit * 16);
-        xr.l[c] = *reinterpret_cast<const uint4 *>(xv.xl + c * units16 + unit * 16);
+        for (int c = 0; c < 4; ++c) {
+            h[c] = lds128(xv.xh + c * units16 + gu * 16);
+            l[c] = lds128(xv.xl + c * units16 + gu * 16);
+        }
+        if (QT == QT_Q6_K) {
+            // 32-weight scale blocks 8*sb + 4h + c ; 16-weight sums 16*sb + 8h + 2c + ph
+            const int hh = j >> 1, ph = j & 1;
+            const uint4 s = lds128(xv.sx + (8 * gsb + 4 * hh) * 4);
+            sx[0] = __uint_as_float(s.x); sx[1] = __uint_as_float(s.y);
+            sx[2] = __uint_as_float(s.z); sx[3] = __uint_as_float(s.w);
+            const uint4 i0 = lds128(xv.isum + (16 * gsb + 8 * hh) * 4);
+            const uint4 i1 = lds128(xv.isum + (16 * gsb + 8 * hh + 4) * 4);
+            is[0] = (int)(ph ? i0.y : i0.x); is[1] = (int)(ph ? i0.w : i0.z);
+            is[2] = (int)(ph ? i1.y : i1.x); is[3] = (int)(ph ? i1.w : i1.z);
+        } else {
+            const uint2 s = lds64(xv.sx + gu * 8);
+            sx[0] = __uint_as_float(s.x); sx[1] = __uint_as_float(s.y);
+            if (QT == QT_Q4_K) {
+                const uint2 i = lds64(xv.isum + gu * 8);
+                is[0] = (int)i.x; is[1] = (int)i.y;
+            }
+        }
     }
-}
+};
 
 // Weights of one 64-weight unit of one row, unpacked once and reused for every activation row.
 template <int QT> struct WRegs;
@@ -55,11 +101,11 @@ template <> struct WRegs<QT_Q4_K> {
     uint32_t lo[8], hi[8];   // low nibbles = weights 0..31 of the group; hi keeps 16 * nibble
     int scA, mnA, scB, mnB;
     float d, dmin;
-    // `rec` points at the 144-byte block, j = 64-weight group 0..3
-    __device__ __forceinline__ void load(const uint8_t *rec, int j) {
-        const uint4 hdr = *reinterpret_cast<const uint4 *>(rec);
-        const uint4 qa = *reinterpret_cast<const uint4 *>(rec + 16 + 32 * j);
-        const uint4 qb = *reinterpret_cast<const uint4 *>(rec + 32 + 32 * j);
+    // `rec` = shared address of the 144-byte block, j = 64-weight group 0..3
+    __device__ __forceinline__ void load(uint32_t rec, int j) {
+        const uint4 hdr = lds128(rec);
+        const uint4 qa = lds128(rec + 16 + 32 * j);
+        const uint4 qb = lds128(rec + 32 + 32 * j);
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const uint32_t a = word_of(qa, i), b = word_of(qb, i);
@@ -82,8 +128,7 @@ template <> struct WRegs<QT_Q4_K> {
         d = half_bits_to_float(hdr.x);
         dmin = half_bits_to_float(hdr.x >> 16);
     }
-    // gu = global 64-weight unit index of the row
-    __device__ __forceinline__ float dot(const XRegs &xr, const XView &xv, int gu) const {
+    __device__ __forceinline__ float dot(const XRegs<QT_Q4_K> &xr) const {
         int hA = 0, lA = 0, hB = 0, lB = 0;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -96,28 +141,26 @@ template <> struct WRegs<QT_Q4_K> {
             hB = dp4a_us(hi[4 + i], word_of(xr.h[3], i), hB);
             lB = dp4a_us(hi[4 + i], word_of(xr.l[3], i), lB);
         }
-        const float2 sx = *reinterpret_cast<const float2 *>(xv.sx + 2 * gu);
-        const int2 is = *reinterpret_cast<const int2 *>(xv.isum + 2 * gu);
         const float fa = (float)((hA * 256 + lA) * scA);
         const float fb = (float)(((hB * 256 + lB) >> 4) * scB);   // hi held 16 * nibble: exact shift
-        const float ua = (float)(mnA * is.x);
-        const float ub = (float)(mnB * is.y);
-        return sx.x * (d * fa - dmin * ua) + sx.y * (d * fb - dmin * ub);
+        const float ua = (float)(mnA * xr.is[0]);
+        const float ub = (float)(mnB * xr.is[1]);
+        return xr.sx[0] * (d * fa - dmin * ua) + xr.sx[1] * (d * fb - dmin * ub);
     }
 };
 
 template <> struct WRegs<QT_Q8_0> {
     uint4 q[4];
     float dA, dB;
-    // `rec` points at the 272-byte record, j = 64-weight group 0..3 (native blocks 2j, 2j+1)
-    __device__ __forceinline__ void load(const uint8_t *rec, int j) {
+    // `rec` = shared address of the 272-byte record, j = 64-weight group 0..3 (native blocks 2j, 2j+1)
+    __device__ __forceinline__ void load(uint32_t rec, int j) {
 #pragma unroll
-        for (int c = 0; c < 4; ++c) q[c] = *reinterpret_cast<const uint4 *>(rec + 64 * j + 16 * c);
-        const uint32_t dd = *reinterpret_cast<const uint32_t *>(rec + 256 + 4 * j);
+        for (int c = 0; c < 4; ++c) q[c] = lds128(rec + 64 * j + 16 * c);
+        const uint32_t dd = lds32(rec + 256 + 4 * j);
         dA = half_bits_to_float(dd);
         dB = half_bits_to_float(dd >> 16);
     }
-    __device__ __forceinline__ float dot(const XRegs &xr, const XView &xv, int gu) const {
+    __device__ __forceinline__ float dot(const XRegs<QT_Q8_0> &xr) const {
         int hA = 0, lA = 0, hB = 0, lB = 0;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -130,23 +173,20 @@ template <> struct WRegs<QT_Q8_0> {
             hB = dp4a_ss(word_of(q[3], i), word_of(xr.h[3], i), hB);
             lB = dp4a_ss(word_of(q[3], i), word_of(xr.l[3], i), lB);
         }
-        const float2 sx = *reinterpret_cast<const float2 *>(xv.sx + 2 * gu);
-        return (dA * sx.x) * (float)(hA * 256 + lA) + (dB * sx.y) * (float)(hB * 256 + lB);
+        return (dA * xr.sx[0]) * (float)(hA * 256 + lA) + (dB * xr.sx[1]) * (float)(hB * 256 + lB);
     }
 };
 
 template <> struct WRegs<QT_Q6_K> {
     uint32_t q[4][4];        // quadrant c (32-weight stride), word i: 6-bit values 0..63 as bytes
     float f[4];              // d * sub-block scale of quadrant c
-    int h, ph;
-    // `rec` points at the 208-byte record, j = 2*half + position-half, d = superblock scale
-    __device__ __forceinline__ void load(const uint8_t *rec, int j, float d) {
-        h = j >> 1;
-        ph = j & 1;
-        const uint4 A = *reinterpret_cast<const uint4 *>(rec + 64 * h + 16 * ph);        // quadrants 0 | 2
-        const uint4 B = *reinterpret_cast<const uint4 *>(rec + 64 * h + 32 + 16 * ph);   // quadrants 1 | 3
-        const uint4 H = *reinterpret_cast<const uint4 *>(rec + 128 + 32 * h + 16 * ph);  // 2 bits x 4 quadrants
-        const uint2 s8 = *reinterpret_cast<const uint2 *>(rec + 192 + 8 * h);            // 8 int8 scales
+    // `rec` = shared address of the 208-byte record, j = 2*half + position-half, d = superblock scale
+    __device__ __forceinline__ void load(uint32_t rec, int j, float d) {
+        const int h = j >> 1, ph = j & 1;
+        const uint4 A = lds128(rec + 64 * h + 16 * ph);         // quadrants 0 | 2
+        const uint4 B = lds128(rec + 64 * h + 32 + 16 * ph);    // quadrants 1 | 3
+        const uint4 H = lds128(rec + 128 + 32 * h + 16 * ph);   // 2 bits x 4 quadrants
+        const uint2 s8 = lds64(rec + 192 + 8 * h);              // 8 int8 scales
         // scales of sub-blocks 8h + 2c + ph, c = 0..3
         const uint32_t sw0 = ph ? (s8.x >> 8) : s8.x, sw1 = ph ? (s8.y >> 8) : s8.y;
         f[0] = d * (float)(int)(int8_t)(sw0 & 0xFF);
@@ -162,28 +202,19 @@ template <> struct WRegs<QT_Q6_K> {
             q[3][i] = ((b >> 4) & 0x0F0F0F0Fu) | ((hh >> 2) & 0x30303030u);
         }
     }
-    // sb = global superblock index of the row
-    __device__ __forceinline__ float dot(const XRegs &xr, const XView &xv, int sb) const {
-        int ah[4] = {0, 0, 0, 0}, al[4] = {0, 0, 0, 0};
+    __device__ __forceinline__ float dot(const XRegs<QT_Q6_K> &xr) const {
+        float r = 0.f;
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
+            int ah = 0, al = 0;
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-                ah[c] = dp4a_us(q[c][i], word_of(xr.h[c], i), ah[c]);
-                al[c] = dp4a_us(q[c][i], word_of(xr.l[c], i), al[c]);
+                ah = dp4a_us(q[c][i], word_of(xr.h[c], i), ah);
+                al = dp4a_us(q[c][i], word_of(xr.l[c], i), al);
             }
+            r += (f[c] * xr.sx[c]) * (float)(ah * 256 + al - 32 * xr.is[c]);
         }
-        // 32-weight scale blocks 8*sb + 4h + c ; 16-weight sums 16*sb + 8h + 2c + ph
-        const float4 sx = *reinterpret_cast<const float4 *>(xv.sx + 8 * sb + 4 * h);
-        const int4 i0 = *reinterpret_cast<const int4 *>(xv.isum + 16 * sb + 8 * h);
-        const int4 i1 = *reinterpret_cast<const int4 *>(xv.isum + 16 * sb + 8 * h + 4);
-        const int s0 = ph ? i0.y : i0.x, s1 = ph ? i0.w : i0.z;
-        const int s2 = ph ? i1.y : i1.x, s3 = ph ? i1.w : i1.z;
-        const float v0 = (float)(ah[0] * 256 + al[0] - 32 * s0);
-        const float v1 = (float)(ah[1] * 256 + al[1] - 32 * s1);
-        const float v2 = (float)(ah[2] * 256 + al[2] - 32 * s2);
-        const float v3 = (float)(ah[3] * 256 + al[3] - 32 * s3);
-        return (f[0] * sx.x) * v0 + (f[1] * sx.y) * v1 + (f[2] * sx.z) * v2 + (f[3] * sx.w) * v3;
+        return r;
     }
 };
 
