@@ -235,15 +235,37 @@ def run_b200(args):
 
     stream = torch.cuda.Stream(device=dev)
 
-    def step_device():
+    # One decode plan holds the whole step: 64 projection jobs run by one persistent launch, the
+    # weights of job i+1 streaming while job i is reduced and stored.  Under tensor parallelism the
+    # all-reduce after every down projection cuts the step into one two-job plan per layer.
+    if args.per_launch:
+        plans = None
+        launches_per_step = 2 * LAYERS
+    elif world == 1:
+        jobs = []
         for l in range(LAYERS):
-            be.project_multi([gates[l], ups[l]], x_hd, outs=[y_g, y_u], stream=stream)
-            be.project(downs[l], x_id, out=y_d, stream=stream)
-            if world > 1:
-                with torch.cuda.stream(stream):
-                    dist.all_reduce(y_d)
+            jobs.append(([gates[l], ups[l]], x_hd, [y_g, y_u]))
+            jobs.append(([downs[l]], x_id, [y_d]))
+        plans = [be.plan(jobs)]
+        launches_per_step = 1
+    else:
+        plans = [be.plan([([gates[l], ups[l]], x_hd, [y_g, y_u]), ([downs[l]], x_id, [y_d])]) for l in range(LAYERS)]
+        launches_per_step = LAYERS
 
-    launches_per_step = 2 * LAYERS
+    def step_device():
+        if plans is None:
+            for l in range(LAYERS):
+                be.project_multi([gates[l], ups[l]], x_hd, outs=[y_g, y_u], stream=stream)
+                be.project(downs[l], x_id, out=y_d, stream=stream)
+                if world > 1:
+                    with torch.cuda.stream(stream):
+                        dist.all_reduce(y_d)
+        else:
+            for pl in plans:
+                pl.run(stream=stream)
+                if world > 1:
+                    with torch.cuda.stream(stream):
+                        dist.all_reduce(y_d)
 
     # capture one step in a CUDA graph (launch-bound inner loop); fall back to direct launches
     graph = None
@@ -314,20 +336,36 @@ def run_b200(args):
     yd_pin = torch.empty((1, HIDDEN), dtype=torch.float32).pin_memory()
     yd_dev = torch.empty((1, HIDDEN), dtype=torch.float32, device=dev)
 
+    xhd_e2e = torch.empty_like(x_hd)
+    xid_e2e = torch.empty_like(x_id)
+    if plans is not None:
+        if world == 1:
+            e2e_plans = [be.plan([j for l in range(LAYERS) for j in (([gates[l], ups[l]], xhd_e2e, [y_g, y_u]), ([downs[l]], xid_e2e, [y_d]))])]
+        else:
+            e2e_plans = [be.plan([([gates[l], ups[l]], xhd_e2e, [y_g, y_u]), ([downs[l]], xid_e2e, [y_d])]) for l in range(LAYERS)]
+
     def step_e2e():
-        for l in range(LAYERS):
-            be.project_host_ptr([gates[l], ups[l]], xh_pin.data_ptr(), mb.TYPE_BF16, 1, HIDDEN,
-                                [yg_pin.data_ptr(), yu_pin.data_ptr()], mb.TYPE_F32, [n_gu, n_gu])
-            if world > 1:
-                # partial sums must meet before they are a result: device all-reduce, then one read back
-                xd = xi_pin.to(dev, non_blocking=True)
-                be.project(downs[l], xd, out=yd_dev)
-                dist.all_reduce(yd_dev)
-                yd_pin.copy_(yd_dev, non_blocking=True)
-                torch.cuda.current_stream().synchronize()
-            else:
+        if plans is None:
+            for l in range(LAYERS):
+                be.project_host_ptr([gates[l], ups[l]], xh_pin.data_ptr(), mb.TYPE_BF16, 1, HIDDEN,
+                                    [yg_pin.data_ptr(), yu_pin.data_ptr()], mb.TYPE_F32, [n_gu, n_gu])
                 be.project_host_ptr([downs[l]], xi_pin.data_ptr(), mb.TYPE_BF16, 1, k_d,
                                     [yd_pin.data_ptr()], mb.TYPE_F32, [HIDDEN])
+            return
+        # host activations in, one plan launch (per layer under TP), host results out
+        with torch.cuda.stream(stream):
+            xhd_e2e.copy_(xh_pin, non_blocking=True)
+            xid_e2e.copy_(xi_pin, non_blocking=True)
+        for pl in e2e_plans:
+            pl.run(stream=stream)
+            if world > 1:
+                with torch.cuda.stream(stream):
+                    dist.all_reduce(y_d)
+        with torch.cuda.stream(stream):
+            yg_pin.copy_(y_g, non_blocking=True)
+            yu_pin.copy_(y_u, non_blocking=True)
+            yd_pin.copy_(y_d, non_blocking=True)
+        stream.synchronize()
 
     e2e_steps = max(3, min(args.steps, 10))
     for _ in range(2):
@@ -344,10 +382,11 @@ def run_b200(args):
         e2e_s = float(t.item())
     e2e = {
         "value": bytes_step / e2e_s / 1e9, "unit": UNIT,
-        "h2d_bytes_per_step": LAYERS * (HIDDEN * 2 + k_d * 2) * world,
-        "d2h_bytes_per_step": LAYERS * (2 * n_gu * 4 * world + HIDDEN * 4 * world),
+        "h2d_bytes_per_step": (LAYERS if plans is None else 1) * (HIDDEN * 2 + k_d * 2) * world,
+        "d2h_bytes_per_step": (LAYERS if plans is None else 1) * (2 * n_gu * 4 + HIDDEN * 4) * world,
         "ms_per_step": e2e_s * 1e3,
-        "api": "b200q_matmul_multi_host per projection group (pinned host x -> device -> kernel -> pinned host y, synchronous)",
+        "api": ("b200q_matmul_multi_host per projection group" if plans is None else
+                "pinned host activations -> device, b200q_plan_run (whole step), results -> pinned host, synchronize"),
     }
 
     if rank != 0:
@@ -356,12 +395,12 @@ def run_b200(args):
         return
 
     peak, peak_src = peaks()
-    # dominant kernel: gemv_kernel<Q4_K, M=1>; two launch shapes per layer (gate+up fused, down),
-    # both Q4_K streaming launches — achieved = algorithmic bytes of this rank's launches / their time
+    # dominant (only) kernel: stream_kernel<M=1, Q4_K> running the step's 64 projection jobs;
+    # achieved = algorithmic bytes of this rank's launches / their device time
     rank_bytes = bytes_step / world
     achieved = rank_bytes / (ms_step * 1e-3) / 1e9
     roofline = {
-        "bound": "hbm", "kernel": "gemv_kernel<Q4_K,M=1,R=2>", "achieved": achieved, "peak": peak, "unit": "GB/s",
+        "bound": "hbm", "kernel": "stream_kernel<M=1,Q4_K>", "achieved": achieved, "peak": peak, "unit": "GB/s",
         "frac": achieved / peak, "peak_source": f"of {peak_src}", "traffic": None,
         "bytes_per_launch": rank_bytes / launches_per_step,
         "us_per_launch": ms_step * 1e3 / launches_per_step,
@@ -410,6 +449,7 @@ def main():
     ap.add_argument("--impl", choices=["b200", "reference"], default="b200")
     ap.add_argument("--no-graph", action="store_true", help="time direct launches instead of a CUDA graph replay")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--per-launch", action="store_true", help="one launch per projection group instead of a decode plan")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

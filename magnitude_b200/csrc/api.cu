@@ -86,6 +86,10 @@ struct b200q_ctx {
     size_t hx_bytes = 0;
     void *hy_dev = nullptr;
     size_t hy_bytes = 0;
+    // prefill path: bf16 copy of fp32 activations
+    void *gemm_scratch = nullptr;
+    size_t gemm_scratch_bytes = 0;
+    int gemm_bn = 0, gemm_wbf16 = 0;
     // tunables (environment overrides for experiments)
     int gemv_warps = 0, gemv_depth = 0, gemv_grid = 0, gemv_smem = 0, gemv_rows = 0, gemv_debug = 0, gemv_pdl = 1;
     // tensor parallel
@@ -248,6 +252,57 @@ b200q_status run_gemv(b200q_ctx *ctx, const b200q_weight *const *w, int nw, cons
     return run_stream(ctx, &J, nullptr, 1, M, st);
 }
 
+// prefill route: an activation conversion and one tensor-core launch per weight
+b200q_status run_gemm(b200q_ctx *ctx, const b200q_weight *w, const void *x, int x_dtype, int64_t M, int64_t ldx,
+                      void *y, int y_dtype, int64_t ldy, cudaStream_t st, int *launches) {
+    // Both tensor-core operands share one 16-bit format (fp16 by default): the activations are
+    // converted into context-owned scratch memory first, unless they already are bf16 and the
+    // bf16 mode is on.
+    const void *xb = x;
+    long long ldb = ldx;
+    const bool direct = ctx->gemm_wbf16 && x_dtype == B200Q_TYPE_BF16 &&
+                        !(reinterpret_cast<uintptr_t>(x) & 15) && (ldx * 2) % 16 == 0;
+    if (!direct) {
+        const size_t need = gemm_x_scratch_bytes((int)M, (int)w->K);
+        if (need > ctx->gemm_scratch_bytes) {
+            if (ctx->gemm_scratch) {
+                CU_TRY(ctx, cudaStreamSynchronize(st));   // earlier launches may still read the old buffer
+                cudaFree(ctx->gemm_scratch);
+                ctx->gemm_scratch = nullptr;
+                ctx->gemm_scratch_bytes = 0;
+            }
+            CU_TRY(ctx, cudaMalloc(&ctx->gemm_scratch, need));
+            ctx->gemm_scratch_bytes = need;
+        }
+        cudaError_t e = gemm_convert_x(x, x_dtype == B200Q_TYPE_BF16, ldx, ctx->gemm_scratch, (int)M, (int)w->K,
+                                       ctx->gemm_wbf16, st);
+        if (e != cudaSuccess) return cuda_fail(ctx, e, "activation conversion launch");
+        ++*launches;
+        xb = ctx->gemm_scratch;
+        ldb = (w->K + 7) & ~int64_t(7);
+    }
+    GemmLaunch a{};
+    a.qt = w->type;
+    a.w = w->dev;
+    a.N = (int)w->N;
+    a.K = (int)w->K;
+    a.Kpad = (int)w->Kpad;
+    a.x = xb;
+    a.ldx = ldb;
+    a.M = (int)M;
+    a.y = y;
+    a.ldy = ldy;
+    a.y_is_bf16 = y_dtype == B200Q_TYPE_BF16;
+    a.status = ctx->status_dev;
+    a.sm_count = ctx->sm_count;
+    a.bn_override = ctx->gemm_bn;
+    a.weights_bf16 = ctx->gemm_wbf16;
+    cudaError_t e = gemm_launch(a, st);
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "tensor-core GEMM launch");
+    ++*launches;
+    return B200Q_OK;
+}
+
 b200q_status validate_mm(b200q_ctx *ctx, const b200q_weight *w, const void *x, int x_dtype, int64_t M,
                          int64_t ldx, const void *y, int y_dtype, int64_t ldy) {
     if (!w) return fail(ctx, B200Q_ERR_INVALID_CONFIG, "null weight");
@@ -279,6 +334,15 @@ b200q_status matmul_any(b200q_ctx *ctx, const b200q_weight *const *w, int nw, co
         return B200Q_OK;
     }
     const int mt = gemv_max_m();
+    if (M > mt) {   // prefill / verify batches: tensor cores, one launch per weight
+        ctx->last_route = B200Q_ROUTE_GEMM;
+        for (int i = 0; i < nw; ++i) {
+            if (w[i]->N == 0) continue;
+            b200q_status s = run_gemm(ctx, w[i], x, x_dtype, M, ldx, y[i], y_dtype, ldy[i], st, &ctx->last_launches);
+            if (s != B200Q_OK) return s;
+        }
+        return B200Q_OK;
+    }
     ctx->last_route = B200Q_ROUTE_GEMV;
     for (int64_t m0 = 0; m0 < M; m0 += mt) {
         const int mc = (int)std::min<int64_t>(mt, M - m0);
@@ -364,6 +428,8 @@ b200q_status b200q_ctx_create(int32_t device, b200q_ctx **out) {
     ctx->gemv_rows = env_int("B200Q_GEMV_ROWS", 0);
     ctx->gemv_debug = env_int("B200Q_GEMV_DEBUG", 0);
     ctx->gemv_pdl = env_int("B200Q_GEMV_PDL", 1);
+    ctx->gemm_bn = env_int("B200Q_GEMM_BN", 0);
+    ctx->gemm_wbf16 = env_int("B200Q_GEMM_WBF16", 0);
     *out = ctx;
     return B200Q_OK;
 }
@@ -378,6 +444,7 @@ void b200q_ctx_destroy(b200q_ctx *ctx) {
     if (ctx->hstream) cudaStreamDestroy(ctx->hstream);
     if (ctx->hx_dev) cudaFree(ctx->hx_dev);
     if (ctx->hy_dev) cudaFree(ctx->hy_dev);
+    if (ctx->gemm_scratch) cudaFree(ctx->gemm_scratch);
     if (ctx->status_dev) cudaFree(ctx->status_dev);
     delete ctx;
 }

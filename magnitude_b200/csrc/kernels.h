@@ -63,4 +63,26 @@ int gemv_max_m();
 void stream_job_finish(StreamJob &job);
 cudaError_t stream_launch(const StreamLaunch &a, cudaStream_t st);
 
+// ---- gemm_tc.cu -----------------------------------------------------------------------------
+struct GemmLaunch {
+    int qt;
+    const uint8_t *w;        // streaming-layout weights
+    int N, K, Kpad;
+    const void *x;           // fp16 (bf16 if weights_bf16) activations [M][K], rows 16-byte aligned
+    long long ldx;
+    int M;
+    void *y;
+    long long ldy;
+    int y_is_bf16;
+    int *status;
+    int sm_count;
+    int bn_override;         // 0 = choose the token tile
+    int weights_bf16;        // 1 = both operands bf16 instead of fp16 (wider range, 8x the rounding error)
+};
+size_t gemm_x_scratch_bytes(int M, int K);
+// activations (bf16 or fp32) -> fp16 (or bf16) rows of ((K + 7) & ~7) elements in `scratch`
+cudaError_t gemm_convert_x(const void *x, int x_is_bf16, long long ldx, void *scratch, int M, int K, int to_bf16,
+                           cudaStream_t st);
+cudaError_t gemm_launch(const GemmLaunch &a, cudaStream_t st);
+
 }  // namespace b200q
