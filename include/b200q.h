@@ -133,7 +133,8 @@ b200q_status b200q_shard_range(int32_t type, int64_t N, int64_t K, int32_t split
 
 /* Host-only helpers (no device needed): the size of, and the conversion to, the device
  * ("streaming") layout of rows [0, N) of a GGUF tensor.  b200q_weight_upload applies the same
- * conversion; callers that cache converted weights on disk can use these directly. */
+ * conversion; callers that cache converted weights on disk can use these directly.  The layout
+ * pads N to a multiple of 4 rows: out_bytes = ((N + 3) / 4 * 4) * b200q_layout_row_bytes(type, K). */
 int64_t b200q_layout_row_bytes(int32_t type, int64_t K);
 b200q_status b200q_layout_pack(int32_t type, int64_t N, int64_t K, const void *packed_host,
                                size_t bytes, void *out_host, size_t out_bytes);

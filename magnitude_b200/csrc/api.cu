@@ -159,7 +159,7 @@ b200q_status make_weight(b200q_ctx *ctx, int type, int64_t N, int64_t Kfull, con
     w->Kpad = (sb1 - sb0) * SB;
     w->row_bytes = row_bytes_for(type, sb1 - sb0);
     w->gguf_bytes = (size_t)(n * (k / gguf_block_elems(type)) * gguf_block_bytes(type));
-    w->device_bytes = (size_t)(n * w->row_bytes);
+    w->device_bytes = (size_t)(padded_rows(n) * w->row_bytes);   // whole 4-row groups, zero padded
     if (n > 0 && k > 0) {
         std::vector<uint8_t> staged;
         try {
@@ -520,7 +520,7 @@ b200q_status b200q_layout_pack(int32_t type, int64_t N, int64_t K, const void *p
                                size_t bytes, void *out_host, size_t out_bytes) {
     const int64_t rb = b200q_layout_row_bytes(type, K);
     if (rb < 0 || N < 0) return B200Q_ERR_INVALID_CONFIG;
-    if ((int64_t)bytes != b200q_tensor_storage_bytes(type, N * K) || (int64_t)out_bytes != N * rb)
+    if ((int64_t)bytes != b200q_tensor_storage_bytes(type, N * K) || (int64_t)out_bytes != padded_rows(N) * rb)
         return B200Q_ERR_INVALID_CONFIG;
     if (N * K == 0) return B200Q_OK;
     if (!packed_host || !out_host) return B200Q_ERR_INVALID_CONFIG;

@@ -27,8 +27,9 @@ namespace b200q {
 // chunk of kChunkRecs = 8 consecutive records: inside a row group the chunks follow each other,
 // and inside a chunk the group's rows follow each other.  One tile (4 rows x 2048 weights, 4.5 KB
 // for Q4_K) is therefore one contiguous, 16-byte aligned byte range, which the streaming kernels
-// fetch with a single bulk copy.  The last row group of a tensor may hold fewer than 4 rows, the
-// last chunk of a row fewer than 8 records.
+// fetch with a single bulk copy.  The tensor is padded with zero rows to a multiple of 4 rows, so
+// every row group is whole and tiles sit at regular strides (which also lets a tiled TMA
+// descriptor address them); the last chunk of a row may hold fewer than 8 records.
 //
 // The byte count equals GGUF's except for the Q8_0 K padding and at most 14 bytes per Q6_K row.
 // ---------------------------------------------------------------------------------------------
@@ -75,14 +76,16 @@ __host__ __device__ inline int64_t chunk_row_bytes(int qt, int64_t c, int64_t ns
     const int64_t sb1 = (c + 1) * kChunkRecs < nsb ? (c + 1) * kChunkRecs : nsb;
     return range_bytes(qt, c * kChunkRecs, sb1, nsb);
 }
-// rows in row group g of an N-row tensor
+// rows of row group g that exist in an N-row tensor (the rest of the group is zero padding)
 __host__ __device__ inline int group_rows(int64_t g, int64_t N) {
     const int64_t left = N - g * kRowGroup;
     return left < kRowGroup ? (int)left : kRowGroup;
 }
+// rows a tensor of N rows occupies in device memory
+__host__ __device__ inline int64_t padded_rows(int64_t N) { return (N + kRowGroup - 1) / kRowGroup * kRowGroup; }
 // byte offset of tile (row group g, chunk c) from the start of the tensor
-__host__ __device__ inline int64_t tile_off(int qt, int64_t g, int64_t c, int64_t N, int64_t nsb) {
-    return g * kRowGroup * row_bytes_for(qt, nsb) + group_rows(g, N) * rec_off(qt, c * kChunkRecs);
+__host__ __device__ inline int64_t tile_off(int qt, int64_t g, int64_t c, int64_t, int64_t nsb) {
+    return g * kRowGroup * row_bytes_for(qt, nsb) + kRowGroup * rec_off(qt, c * kChunkRecs);
 }
 // byte offset of record `sb` of row `row` (for Q6_K: of its 208-byte part)
 __host__ __device__ inline int64_t record_off(int qt, int64_t row, int64_t sb, int64_t N, int64_t nsb) {
@@ -185,6 +188,29 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t
         "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
         "l"(src), "r"(bytes), "r"(bar)
         : "memory");
+}
+
+// Shared-memory reads go through 32-bit shared-window addresses: the hot loop then spends no
+// instructions on 64-bit pointer arithmetic.  (volatile keeps them after the barrier waits.)
+__device__ __forceinline__ uint4 lds128(uint32_t a) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t a) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t a) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds16(uint32_t a) {
+    uint16_t v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(a));
+    return v;
 }
 
 // Programmatic dependent launch: a kernel launched with the programmatic-serialization attribute

@@ -2,16 +2,17 @@
 //
 // One persistent CTA per SM walks output tiles of 128 weight rows x BN tokens (BN <= 256):
 //   * warp 0 (one lane) loads the activation tile X[m0 : m0+BN][k : k+64] with TMA (2-D tiled
-//     bulk tensor copy, 128-byte swizzle, no multicast) into a 4-stage shared-memory ring;
-//   * warps 2..9 read the packed weight records of the tile's 128 rows straight from global
-//     memory (L2 serves the repeats across token tiles), dequantize 64 weights per row and K-step
-//     to bf16 in registers and write them into the same ring in the K-major 128-byte-swizzled
-//     layout the tensor core reads (generic-proxy stores, then fence.proxy.async);
-//   * warp 1 (one lane) issues tcgen05.mma (kind::f16, bf16 x bf16 -> fp32) with the dequantized
+//     bulk tensor copy, 128-byte swizzle, no multicast) into a 3-stage shared-memory ring;
+//     the same lane fetches the packed weight records of the tile's 128 rows, one superblock
+//     record per row at a time (a 4-D tiled copy over the streaming layout), into a 2-deep ring;
+//   * warps 2..17 dequantize 16 weights per thread and K-step from that ring to fp16 in registers
+//     and write them into the stage ring in the K-major 128-byte-swizzled layout the tensor core
+//     reads (generic-proxy stores, then fence.proxy.async);
+//   * warp 1 (one lane) issues tcgen05.mma (kind::f16, fp16 x fp16 -> fp32) with the dequantized
 //     weights as the A operand (M = 128) and the activations as the B operand (N = BN), four
 //     K = 16 instructions per stage, accumulating in tensor memory; tcgen05.commit releases the
 //     stage to the producers and, after the last K-step, hands the accumulator to the epilogue;
-//   * warps 10..13 read the accumulator (tcgen05.ld, one 32-lane quadrant per warp), convert to
+//   * warps 18..21 read the accumulator (tcgen05.ld, one 32-lane quadrant per warp), convert to
 //     the output type and store Y; two accumulator buffers (2 x 256 TMEM columns) let the next
 //     tile's main loop run under the epilogue.
 // Every mbarrier wait is bounded; a wait that runs out raises the status word and an abort flag,
@@ -30,10 +31,13 @@ namespace {
 
 constexpr int BM = 128;          // weight rows per tile (MMA M)
 constexpr int BK = 64;           // weights per K-step (one 128-byte swizzle row of bf16)
-constexpr int kStages = 4;
-constexpr int kDequantWarps = 8;
+constexpr int kStages = 3;        // A/B stages
+constexpr int kWBufs = 2;         // packed-weight buffers (one superblock record per row each)
+constexpr int kWBufBytes = 35 * 1024;   // 128 rows x 272 bytes (largest record), rounded up to 1 KB
+constexpr int kDBufBytes = 2048;        // Q6_K: 128 rows x the 16-byte group of fp16 d of a chunk
+constexpr int kDequantWarps = 16;  // four threads per weight row, 16 weights each per K-step
 constexpr int kEpiWarps = 4;
-constexpr int kThreads = (2 + kDequantWarps + kEpiWarps) * 32;   // 448
+constexpr int kThreads = (2 + kDequantWarps + kEpiWarps) * 32;   // 704
 constexpr int kTmemCols = 512;   // two accumulator buffers of 256 columns
 constexpr int kStageABytes = BM * BK * 2;       // 16 KB
 constexpr int kStageBBytes = 256 * BK * 2;      // 32 KB (BN <= 256)
@@ -48,6 +52,7 @@ struct GemmParams {
     int M;
     int bn;                  // tokens per tile (multiple of 16, <= 256)
     int m_tiles, n_tiles;
+    int nchunks_full;        // chunks of 8 whole records per row; a shorter tail chunk may follow
     int *status;
 };
 
@@ -56,6 +61,8 @@ struct GemmSmem {
     uint64_t empty[kStages];
     uint64_t tmem_full[2];
     uint64_t tmem_empty[2];
+    uint64_t wfull[kWBufs];
+    uint64_t wempty[kWBufs];
     uint32_t tmem_base;
     int abort;
 };
@@ -108,6 +115,14 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map
         : "memory");
 }
 
+// 4-D tiled TMA load (packed weight records: [bytes/4][row in group][chunk][row group])
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap *map, int c0, int c1, int c2, int c3, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+        : "memory");
+}
+
 // shared-memory matrix descriptor: K-major, 128-byte swizzle, rows of 128 bytes, 8-row groups
 // 1024 bytes apart (see the tcgen05 matrix-descriptor format: start >> 4 in bits 0..13, leading
 // offset in 16..29, stride offset in 32..45, version 1 in 46..47, layout type 2 in 61..63)
@@ -130,11 +145,9 @@ template <bool F16> __device__ __forceinline__ uint32_t pack2(float lo, float hi
     return r;
 }
 
-__device__ __forceinline__ uint4 ldg128(const uint8_t *p) { return __ldg(reinterpret_cast<const uint4 *>(p)); }
-
 // ---- dequantization to the swizzled A tile ---------------------------------------------------
 //
-// A dequant thread owns one weight row of the tile and one half (32 weights) of the 64-weight
+// A dequant thread owns one weight row of the tile and one quarter (16 weights) of the 64-weight
 // K-step.  Small integers become fp32 without a conversion instruction: a byte v placed in the
 // mantissa of a float with a fixed exponent reads as (C + v), and one fused multiply-add
 // (C + v) * s - (C * s + m) gives the weight.  Eight bf16 values form one 16-byte chunk; chunk cc
@@ -154,87 +167,84 @@ template <int I> __device__ __forceinline__ float f32768_plus(uint32_t v) {
     return __uint_as_float(__byte_perm(v, 0x47000000u, 0x7404 | (I << 4)));
 }
 
+// `qd` = which quarter (16 weights, two 16-byte chunks) of the 64-weight K-step the thread makes.
 template <int QT> struct Packed;
 
 template <> struct Packed<QT_Q4_K> {
-    uint4 hdr, qa, qb;
-    // rec: the row's 144-byte record of this K-step's superblock; j: 64-weight unit inside it
-    __device__ __forceinline__ void load(const uint8_t *rec, const uint8_t *, int j, int) {
-        hdr = ldg128(rec);
-        qa = ldg128(rec + 16 + 32 * j);
-        qb = ldg128(rec + 32 + 32 * j);
+    uint4 hdr, q;
+    // rec: shared address of the row's 144-byte record of this K-step's superblock; j: 64-weight unit.
+    // Quarters 0, 1 are the low nibbles of bytes 0..15 / 16..31 of the unit, quarters 2, 3 the high.
+    __device__ __forceinline__ void load(uint32_t rec, uint32_t, int j, int qd) {
+        hdr = lds128(rec);
+        q = lds128(rec + 16 + 32 * j + 16 * (qd & 1));
     }
-    template <bool F16> __device__ __forceinline__ void emit(int j, int h, uint32_t row_saddr, int r7) const {
+    template <bool F16> __device__ __forceinline__ void emit(int j, int qd, uint32_t row_saddr, int r7) const {
         int sc, mn;
-        q4k_scale_min(hdr.y, hdr.z, hdr.w, 2 * j + h, sc, mn);
+        q4k_scale_min(hdr.y, hdr.z, hdr.w, 2 * j + (qd >> 1), sc, mn);
         const float ds = half_bits_to_float(hdr.x) * (float)sc;
         const float c0 = -(128.f * ds + half_bits_to_float(hdr.x >> 16) * (float)mn);
-        const uint32_t w[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
-        const int sh = 4 * h;   // low nibbles = weights 0..31 of the unit, high nibbles = 32..63
+        const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+        const int sh = 4 * (qd >> 1);
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < 2; ++c) {
             const uint32_t a = (w[2 * c] >> sh) & 0x0F0F0F0Fu, b = (w[2 * c + 1] >> sh) & 0x0F0F0F0Fu;
             const uint32_t p0 = pack2<F16>(fmaf(f128_plus<0>(a), ds, c0), fmaf(f128_plus<1>(a), ds, c0));
             const uint32_t p1 = pack2<F16>(fmaf(f128_plus<2>(a), ds, c0), fmaf(f128_plus<3>(a), ds, c0));
             const uint32_t p2 = pack2<F16>(fmaf(f128_plus<0>(b), ds, c0), fmaf(f128_plus<1>(b), ds, c0));
             const uint32_t p3 = pack2<F16>(fmaf(f128_plus<2>(b), ds, c0), fmaf(f128_plus<3>(b), ds, c0));
-            st_chunk(row_saddr, r7, 4 * h + c, p0, p1, p2, p3);
+            st_chunk(row_saddr, r7, 2 * qd + c, p0, p1, p2, p3);
         }
     }
 };
 
 template <> struct Packed<QT_Q8_0> {
-    uint4 q0, q1;
+    uint4 q;
     uint32_t d16;
-    // rec: the 272-byte record; unit j holds native blocks 2j, 2j+1; this thread takes block 2j + h
-    __device__ __forceinline__ void load(const uint8_t *rec, const uint8_t *, int j, int h) {
-        q0 = ldg128(rec + 64 * j + 32 * h);
-        q1 = ldg128(rec + 64 * j + 32 * h + 16);
-        d16 = __ldg(reinterpret_cast<const unsigned short *>(rec + 256 + 2 * (2 * j + h)));
+    // rec: shared address of the 272-byte record; unit j holds native blocks 2j, 2j+1; quarter qd is
+    // half of block 2j + qd/2
+    __device__ __forceinline__ void load(uint32_t rec, uint32_t, int j, int qd) {
+        q = lds128(rec + 64 * j + 16 * qd);
+        d16 = lds16(rec + 256 + 2 * (2 * j + (qd >> 1)));
     }
-    template <bool F16> __device__ __forceinline__ void emit(int, int h, uint32_t row_saddr, int r7) const {
+    template <bool F16> __device__ __forceinline__ void emit(int, int qd, uint32_t row_saddr, int r7) const {
         const float d = half_bits_to_float(d16);
         const float c0 = -32896.f * d;     // (32768 + 128): bytes are taken as unsigned after ^ 0x80
-        const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+        const uint32_t w[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < 2; ++c) {
             const uint32_t a = w[2 * c] ^ 0x80808080u, b = w[2 * c + 1] ^ 0x80808080u;
             const uint32_t p0 = pack2<F16>(fmaf(f32768_plus<0>(a), d, c0), fmaf(f32768_plus<1>(a), d, c0));
             const uint32_t p1 = pack2<F16>(fmaf(f32768_plus<2>(a), d, c0), fmaf(f32768_plus<3>(a), d, c0));
             const uint32_t p2 = pack2<F16>(fmaf(f32768_plus<0>(b), d, c0), fmaf(f32768_plus<1>(b), d, c0));
             const uint32_t p3 = pack2<F16>(fmaf(f32768_plus<2>(b), d, c0), fmaf(f32768_plus<3>(b), d, c0));
-            st_chunk(row_saddr, r7, 4 * h + c, p0, p1, p2, p3);
+            st_chunk(row_saddr, r7, 2 * qd + c, p0, p1, p2, p3);
         }
     }
 };
 
 template <> struct Packed<QT_Q6_K> {
-    uint4 l0, l1, h0, h1;
-    uint32_t sc16, d16;
-    // rec: the 208-byte record, dptr: its fp16 d.  The 64 weights of unit u are quadrants
-    // 2(u&1), 2(u&1)+1 of half u>>1; this thread takes quadrant c = 2(u&1) + h (32 weights).
-    __device__ __forceinline__ void load(const uint8_t *rec, const uint8_t *dptr, int u, int h) {
-        const int hh = u >> 1, c = 2 * (u & 1) + h;
-        const uint8_t *ql = rec + 64 * hh + 32 * (c & 1);
-        const uint8_t *qh = rec + 128 + 32 * hh;
-        l0 = ldg128(ql);
-        l1 = ldg128(ql + 16);
-        h0 = ldg128(qh);
-        h1 = ldg128(qh + 16);
-        sc16 = __ldg(reinterpret_cast<const unsigned short *>(rec + 192 + 8 * hh + 2 * c));
-        d16 = __ldg(reinterpret_cast<const unsigned short *>(dptr));
+    uint4 l, hq;
+    uint32_t sc8, d16;
+    // rec: shared address of the 208-byte record, dptr: of its fp16 d.  The 64 weights of unit u are quadrants
+    // 2(u&1), 2(u&1)+1 of half u>>1; quarter qd is positions 16(qd&1)..+15 of quadrant
+    // c = 2(u&1) + qd/2, which is exactly one 16-weight sub-block (one scale).
+    __device__ __forceinline__ void load(uint32_t rec, uint32_t dptr, int u, int qd) {
+        const int hh = u >> 1, c = 2 * (u & 1) + (qd >> 1), ph = qd & 1;
+        l = lds128(rec + 64 * hh + 32 * (c & 1) + 16 * ph);
+        hq = lds128(rec + 128 + 32 * hh + 16 * ph);
+        const uint32_t a = rec + 192 + 8 * hh + 2 * c + ph;
+        sc8 = (lds16(a & ~1u) >> (8 * (a & 1))) & 0xFF;
+        d16 = lds16(dptr);
     }
-    template <bool F16> __device__ __forceinline__ void emit(int u, int h, uint32_t row_saddr, int r7) const {
-        const int c = 2 * (u & 1) + h;
-        const float d = half_bits_to_float(d16);
-        const float s0 = d * (float)(int)(int8_t)(sc16 & 0xFF), s1 = d * (float)(int)(int8_t)(sc16 >> 8);
-        const float c00 = -32800.f * s0, c01 = -32800.f * s1;   // 32768 + 32
-        const uint32_t lw[8] = {l0.x, l0.y, l0.z, l0.w, l1.x, l1.y, l1.z, l1.w};
-        const uint32_t hw[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
+    template <bool F16> __device__ __forceinline__ void emit(int u, int qd, uint32_t row_saddr, int r7) const {
+        const int c = 2 * (u & 1) + (qd >> 1);
+        const float s = half_bits_to_float(d16) * (float)(int)(int8_t)sc8;
+        const float c0 = -32800.f * s;     // 32768 + 32
+        const uint32_t lw[4] = {l.x, l.y, l.z, l.w};
+        const uint32_t hw[4] = {hq.x, hq.y, hq.z, hq.w};
         const int lsh = 4 * (c >> 1), hsh = 2 * c;
 #pragma unroll
-        for (int cc = 0; cc < 4; ++cc) {
-            const float s = cc < 2 ? s0 : s1, c0 = cc < 2 ? c00 : c01;   // 16 weights per scale
+        for (int cc = 0; cc < 2; ++cc) {
             uint32_t v[2];
 #pragma unroll
             for (int i = 0; i < 2; ++i)
@@ -243,7 +253,7 @@ template <> struct Packed<QT_Q6_K> {
             const uint32_t p1 = pack2<F16>(fmaf(f32768_plus<2>(v[0]), s, c0), fmaf(f32768_plus<3>(v[0]), s, c0));
             const uint32_t p2 = pack2<F16>(fmaf(f32768_plus<0>(v[1]), s, c0), fmaf(f32768_plus<1>(v[1]), s, c0));
             const uint32_t p3 = pack2<F16>(fmaf(f32768_plus<2>(v[1]), s, c0), fmaf(f32768_plus<3>(v[1]), s, c0));
-            st_chunk(row_saddr, r7, 4 * h + cc, p0, p1, p2, p3);
+            st_chunk(row_saddr, r7, 2 * qd + cc, p0, p1, p2, p3);
         }
     }
 };
@@ -260,13 +270,18 @@ __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, Gem
 }
 
 template <int QT, bool F16>
-__global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap) {
+__global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap,
+                                                               const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap wtail,
+                                                               const __grid_constant__ CUtensorMap dmap, const __grid_constant__ CUtensorMap dtail) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     // stage buffers first (1024-byte aligned for the 128-byte swizzle), bookkeeping after them
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const uint32_t a_s = smem_u32(smem);
     const uint32_t b_s = a_s + kStages * kStageABytes;
-    GemmSmem *sm = reinterpret_cast<GemmSmem *>(smem + kStages * (kStageABytes + kStageBBytes));
+    const uint32_t w_s = b_s + kStages * kStageBBytes;            // packed-weight buffers
+    const uint32_t d_s = w_s + kWBufs * kWBufBytes;               // Q6_K d groups, one buffer per chunk parity
+    GemmSmem *sm = reinterpret_cast<GemmSmem *>(smem + kStages * (kStageABytes + kStageBBytes) + kWBufs * kWBufBytes + 2 * kDBufBytes);
+    const uint32_t wfull_s = smem_u32(sm->wfull), wempty_s = smem_u32(sm->wempty);
     const uint32_t full_s = smem_u32(sm->full), empty_s = smem_u32(sm->empty);
     const uint32_t tfull_s = smem_u32(sm->tmem_full), tempty_s = smem_u32(sm->tmem_empty);
 
@@ -283,6 +298,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const GemmParams p
             mbar_init(tfull_s + 8 * i, 1);
             mbar_init(tempty_s + 8 * i, kEpiWarps);
         }
+        for (int i = 0; i < kWBufs; ++i) {
+            mbar_init(wfull_s + 8 * i, 1);
+            mbar_init(wempty_s + 8 * i, kDequantWarps);
+        }
         sm->abort = 0;
         mbar_fence_init();
         fence_proxy_async();
@@ -297,21 +316,40 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const GemmParams p
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t *>(&sm->tmem_base);
 
     if (warp == 0) {
-        // ===== TMA producer: activation tiles ======================================================
+        // ===== TMA producer: activation tiles and packed weight records ============================
         if (lane == 0) {
             const uint32_t bytes = (uint32_t)p.bn * BK * 2;
-            int it = 0;
-            for (int tile = blockIdx.x; tile < n_tiles_total; tile += gridDim.x) {
-                const int tm = tile % p.m_tiles;
-                bool ok = true;
+            constexpr int REC = rec_bytes(QT);
+            int it = 0, rs = 0;     // K-steps and record-steps issued so far (rings run across tiles)
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < n_tiles_total && ok; tile += gridDim.x) {
+                const int tn = tile / p.m_tiles, tm = tile % p.m_tiles;
                 for (int ks = 0; ks < ksteps && ok; ++ks, ++it) {
+                    if ((ks & 3) == 0) {
+                        // one superblock record of each of the tile's 128 rows (four K-steps' worth)
+                        const int sb = ks >> 2, c = sb >> 3, s_in = sb & 7;
+                        const int wb = rs % kWBufs;
+                        ok = wait_or_abort(wempty_s + 8 * wb, ((rs / kWBufs) & 1) ^ 1, sm, p.status);
+                        if (!ok) break;
+                        const bool tail = c >= p.nchunks_full;
+                        uint32_t tx = BM * REC;
+                        if (QT == QT_Q6_K && s_in == 0) tx += BM * 16;
+                        mbar_expect_tx(wfull_s + 8 * wb, tx);
+                        tma_load_4d(w_s + wb * kWBufBytes, tail ? &wtail : &wmap, s_in * (REC / 4), 0, tail ? 0 : c,
+                                    tn * (BM / kRowGroup), wfull_s + 8 * wb);
+                        if (QT == QT_Q6_K && s_in == 0) {
+                            const int nrec = tail ? (p.nsb - c * kChunkRecs) : kChunkRecs;
+                            tma_load_4d(d_s + (c & 1) * kDBufBytes, tail ? &dtail : &dmap, nrec * (REC / 4), 0, tail ? 0 : c,
+                                        tn * (BM / kRowGroup), wfull_s + 8 * wb);
+                        }
+                        ++rs;
+                    }
                     const int stage = it % kStages;
                     ok = wait_or_abort(empty_s + 8 * stage, ((it / kStages) & 1) ^ 1, sm, p.status);
                     if (!ok) break;
                     mbar_expect_tx(full_s + 8 * stage, bytes);
                     tma_load_2d(b_s + stage * kStageBBytes, &xmap, ks * BK, tm * p.bn, full_s + 8 * stage);
                 }
-                if (!ok) break;
             }
         }
     } else if (warp == 1) {
@@ -345,48 +383,37 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const GemmParams p
     } else if (warp < 2 + kDequantWarps) {
         // ===== dequant producers: weight tiles =====================================================
         const int t = threadIdx.x - 64;
-        const int r = t & (BM - 1), h = t >> 7;
+        const int r = t & (BM - 1), qd = t >> 7;
         const int r7 = r & 7;
         const uint32_t row_off = (r >> 3) * 1024 + r7 * 128;
-        int it = 0;
+        constexpr int REC = rec_bytes(QT);
+        int it = 0, rs = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < n_tiles_total && ok; tile += gridDim.x) {
-            const int tn = tile / p.m_tiles;
-            const int row = tn * BM + r;
-            const bool live = row < p.N;
-            const int rowc = live ? row : p.N - 1;   // clamp: out-of-range rows read a valid row, store zeros
-            auto locate = [&](int ks, const uint8_t *&rec, const uint8_t *&dptr) {
-                const int sb = ks >> 2;
-                rec = p.w + record_off(QT, rowc, sb, p.N, p.nsb);
-                dptr = (QT == QT_Q6_K) ? p.w + q6k_d_record_off(rowc, sb, p.N, p.nsb) : rec;
-            };
-            Packed<QT> cur, nxt;
-            {
-                const uint8_t *rec, *dptr;
-                locate(0, rec, dptr);
-                cur.load(rec, dptr, 0, h);
-            }
+            int wb = 0;
             for (int ks = 0; ks < ksteps; ++ks, ++it) {
-                if (ks + 1 < ksteps) {   // next K-step's packed bytes fly while this one is converted
-                    const uint8_t *rec, *dptr;
-                    locate(ks + 1, rec, dptr);
-                    nxt.load(rec, dptr, (ks + 1) & 3, h);
+                const int j = ks & 3;
+                if (j == 0) {   // a new record: wait for its bytes
+                    wb = rs % kWBufs;
+                    if (lane == 0) ok = wait_or_abort(wfull_s + 8 * wb, (rs / kWBufs) & 1, sm, p.status);
+                    ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
+                    if (!ok) break;
                 }
+                const int sb = ks >> 2;
+                Packed<QT> cur;
+                cur.load(w_s + wb * kWBufBytes + r * REC, d_s + ((sb >> 3) & 1) * kDBufBytes + r * 16 + 2 * (sb & 7), j, qd);
                 const int stage = it % kStages;
-                ok = wait_or_abort(empty_s + 8 * stage, ((it / kStages) & 1) ^ 1, sm, p.status);
-                ok = __all_sync(0xFFFFFFFFu, ok);
+                if (lane == 0) ok = wait_or_abort(empty_s + 8 * stage, ((it / kStages) & 1) ^ 1, sm, p.status);
+                ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
                 if (!ok) break;
-                const uint32_t row_s = a_s + stage * kStageABytes + row_off;
-                if (live) {
-                    cur.template emit<F16>(ks & 3, h, row_s, r7);
-                } else {
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) st_chunk(row_s, r7, 4 * h + c, 0u, 0u, 0u, 0u);
-                }
+                cur.template emit<F16>(j, qd, a_s + stage * kStageABytes + row_off, r7);
                 fence_proxy_async();       // generic-proxy stores -> visible to the tensor core's reads
                 __syncwarp();
-                if (lane == 0) mbar_arrive(full_s + 8 * stage);
-                cur = nxt;
+                if (lane == 0) {
+                    mbar_arrive(full_s + 8 * stage);
+                    if (j == 3 || ks == ksteps - 1) mbar_arrive(wempty_s + 8 * wb);   // record consumed
+                }
+                if (j == 3 || ks == ksteps - 1) ++rs;
             }
         }
     } else {
@@ -477,10 +504,14 @@ EncodeTiledFn encode_fn() {
     return fn;
 }
 
+struct GemmMaps {
+    CUtensorMap x, w, wtail, d, dtail;
+};
+
 template <int QT, bool F16>
-cudaError_t launch_gemm(const GemmParams &p, const CUtensorMap &map, int grid, cudaStream_t st) {
+cudaError_t launch_gemm(const GemmParams &p, const GemmMaps &m, int grid, cudaStream_t st) {
     auto kern = gemm_tc_kernel<QT, F16>;
-    const size_t smem = kStages * (kStageABytes + kStageBBytes) + sizeof(GemmSmem) + 1024;
+    const size_t smem = kStages * (kStageABytes + kStageBBytes) + kWBufs * kWBufBytes + 2 * kDBufBytes + sizeof(GemmSmem) + 1024;
     static int configured_dev = -1;
     int dev = 0;
     cudaGetDevice(&dev);
@@ -489,8 +520,23 @@ cudaError_t launch_gemm(const GemmParams &p, const CUtensorMap &map, int grid, c
         if (e != cudaSuccess) return e;
         configured_dev = dev;
     }
-    kern<<<grid, kThreads, smem, st>>>(p, map);
+    kern<<<grid, kThreads, smem, st>>>(p, m.x, m.w, m.wtail, m.d, m.dtail);
     return cudaGetLastError();
+}
+
+// tensor map over the packed records of the chunks [c0, c0 + nc) of every row:
+// [bytes / 4 of a row-chunk][4 rows of a group][chunks][row groups], box = box0 x 4 x 1 x 32
+bool encode_weight_map(EncodeTiledFn enc, CUtensorMap *map, const uint8_t *w, int qt, int nsb, int64_t groups,
+                       int c0, int nc, int box0) {
+    const int64_t rb = row_bytes_for(qt, nsb);
+    const int64_t cb = chunk_row_bytes(qt, c0, nsb);
+    const cuuint64_t gdim[4] = {(cuuint64_t)(cb / 4), (cuuint64_t)kRowGroup, (cuuint64_t)nc, (cuuint64_t)groups};
+    const cuuint64_t gstride[3] = {(cuuint64_t)cb, (cuuint64_t)(kRowGroup * cb), (cuuint64_t)(kRowGroup * rb)};
+    const cuuint32_t box[4] = {(cuuint32_t)box0, (cuuint32_t)kRowGroup, 1, (cuuint32_t)(BM / kRowGroup)};
+    const cuuint32_t estride[4] = {1, 1, 1, 1};
+    void *base = const_cast<uint8_t *>(w) + kRowGroup * rec_off(qt, (int64_t)c0 * kChunkRecs);
+    return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, base, gdim, gstride, box, estride, CU_TENSOR_MAP_INTERLEAVE_NONE,
+               CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 }  // namespace
@@ -538,7 +584,8 @@ cudaError_t gemm_launch(const GemmLaunch &a, cudaStream_t st) {
     p.n_tiles = (a.N + BM - 1) / BM;
     p.status = a.status;
 
-    CUtensorMap map;
+    GemmMaps maps;
+    CUtensorMap &map = maps.x;
     const cuuint64_t gdim[2] = {(cuuint64_t)a.K, (cuuint64_t)a.M};
     const cuuint64_t gstride[1] = {(cuuint64_t)a.ldx * 2};
     const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)p.bn};
@@ -548,20 +595,33 @@ cudaError_t gemm_launch(const GemmLaunch &a, cudaStream_t st) {
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
 
+    // packed weights: whole chunks through one map, the shorter last chunk (if any) through another
+    const int64_t groups = padded_rows(a.N) / kRowGroup;
+    const int rec4 = rec_bytes(a.qt) / 4;
+    p.nchunks_full = p.nsb / kChunkRecs;
+    const int ntail = p.nsb % kChunkRecs;
+    const int c_main = p.nchunks_full > 0 ? 0 : p.nchunks_full, n_main = p.nchunks_full > 0 ? p.nchunks_full : 1;
+    const int c_tail = ntail > 0 ? p.nchunks_full : c_main;
+    bool okm = encode_weight_map(enc, &maps.w, a.w, a.qt, p.nsb, groups, c_main, n_main, rec4) &&
+               encode_weight_map(enc, &maps.wtail, a.w, a.qt, p.nsb, groups, c_tail, 1, rec4) &&
+               encode_weight_map(enc, &maps.d, a.w, a.qt, p.nsb, groups, c_main, n_main, 4) &&
+               encode_weight_map(enc, &maps.dtail, a.w, a.qt, p.nsb, groups, c_tail, 1, 4);
+    if (!okm) return cudaErrorInvalidValue;
+
     const int tiles = p.m_tiles * p.n_tiles;
     const int grid = std::min(tiles, a.sm_count);
     if (a.weights_bf16) {
         switch (a.qt) {
-        case QT_Q4_K: return launch_gemm<QT_Q4_K, false>(p, map, grid, st);
-        case QT_Q6_K: return launch_gemm<QT_Q6_K, false>(p, map, grid, st);
-        case QT_Q8_0: return launch_gemm<QT_Q8_0, false>(p, map, grid, st);
+        case QT_Q4_K: return launch_gemm<QT_Q4_K, false>(p, maps, grid, st);
+        case QT_Q6_K: return launch_gemm<QT_Q6_K, false>(p, maps, grid, st);
+        case QT_Q8_0: return launch_gemm<QT_Q8_0, false>(p, maps, grid, st);
         default: return cudaErrorInvalidValue;
         }
     }
     switch (a.qt) {
-    case QT_Q4_K: return launch_gemm<QT_Q4_K, true>(p, map, grid, st);
-    case QT_Q6_K: return launch_gemm<QT_Q6_K, true>(p, map, grid, st);
-    case QT_Q8_0: return launch_gemm<QT_Q8_0, true>(p, map, grid, st);
+    case QT_Q4_K: return launch_gemm<QT_Q4_K, true>(p, maps, grid, st);
+    case QT_Q6_K: return launch_gemm<QT_Q6_K, true>(p, maps, grid, st);
+    case QT_Q8_0: return launch_gemm<QT_Q8_0, true>(p, maps, grid, st);
     default: return cudaErrorInvalidValue;
     }
 }

@@ -216,7 +216,7 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1) stream_kernel(const S
                         int sg, lg;
                         locate_group(J, gb + g, sg, lg);
                         const int nr = group_rows(lg, J.seg[sg].n);
-                        const uint32_t bytes = nr * ((c == J.nchunks - 1) ? J.bytes_tail : J.bytes_full);
+                        const uint32_t bytes = R * ((c == J.nchunks - 1) ? J.bytes_tail : J.bytes_full);   // whole tile, padding rows included
                         const uint32_t bar = fbar + 8 * slot;
                         fence_proxy_async();   // the consumer's reads of this slot precede the engine's writes
                         mbar_expect_tx(bar, bytes);

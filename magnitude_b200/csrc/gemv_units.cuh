@@ -28,29 +28,6 @@ template <int QT> __device__ __forceinline__ int xplane_off(int k, int units16) 
     return ((k >> 4) & 3) * units16 + (k >> 6) * 16 + (k & 15);
 }
 
-// Shared-memory reads go through 32-bit shared-window addresses: the hot loop then spends no
-// instructions on 64-bit pointer arithmetic.  (volatile keeps them after the barrier waits.)
-__device__ __forceinline__ uint4 lds128(uint32_t a) {
-    uint4 v;
-    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
-    return v;
-}
-__device__ __forceinline__ uint2 lds64(uint32_t a) {
-    uint2 v;
-    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
-    return v;
-}
-__device__ __forceinline__ uint32_t lds32(uint32_t a) {
-    uint32_t v;
-    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
-    return v;
-}
-__device__ __forceinline__ uint32_t lds16(uint32_t a) {
-    uint16_t v;
-    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(a));
-    return v;
-}
-
 struct XView {            // shared-window addresses of one activation row in fixed-point form
     uint32_t xh;          // signed high bytes
     uint32_t xl;          // signed low bytes

@@ -62,7 +62,7 @@ def test_shard_ranges():
 
 def _pack(qt, packed, n, k):
     rb = B.lib().b200q_layout_row_bytes(qt, k)
-    out = np.zeros((n, rb), np.uint8)
+    out = np.zeros(((n + 3) // 4 * 4, rb), np.uint8)     # the layout pads to whole 4-row groups
     st = B.lib().b200q_layout_pack(qt, n, k, packed.ctypes.data, packed.size, out.ctypes.data, out.size)
     assert st == 0
     return out
@@ -84,7 +84,7 @@ def _row_bytes(qt, nsb):
 def _record_off(qt, row, sb, n, nsb):
     """Tile-major layout: groups of 4 rows, chunks of 8 records, rows of a group adjacent inside a chunk."""
     g, c = row // 4, sb // 8
-    nr = min(4, n - 4 * g)
+    nr = 4                                # groups are whole: missing rows are zero padding
     end = _row_bytes(qt, nsb) if (c + 1) * 8 >= nsb else _rec_off(qt, (c + 1) * 8)
     chunk_row = end - _rec_off(qt, c * 8)
     return 4 * g * _row_bytes(qt, nsb) + nr * _rec_off(qt, c * 8) + (row - 4 * g) * chunk_row + _rec_off(qt, sb) - _rec_off(qt, c * 8)
@@ -96,7 +96,7 @@ def test_streaming_layout_is_a_permutation_of_the_gguf_bytes(orc):
     n, nsb = 6, 11
     p = rng.integers(0, 256, size=(n, nsb * 144), dtype=np.uint8)
     s = _pack(12, p, n, nsb * 256).reshape(-1)
-    assert s.size == p.size
+    assert s.size == 8 * nsb * 144        # 6 rows padded to 8
     for r in range(n):
         for sb in range(nsb):
             o = _record_off(12, r, sb, n, nsb)
@@ -108,7 +108,7 @@ def test_streaming_layout_is_a_permutation_of_the_gguf_bytes(orc):
     n, k = 5, 11 * 32
     p = rng.integers(0, 256, size=(n, 11 * 34), dtype=np.uint8)
     s = _pack(8, p, n, k).reshape(-1)
-    assert s.size == n * 2 * 272
+    assert s.size == 8 * 2 * 272          # 5 rows padded to 8
     for r in range(n):
         for b in range(16):
             o = _record_off(8, r, b // 8, n, 2)
@@ -122,7 +122,7 @@ def test_streaming_layout_is_a_permutation_of_the_gguf_bytes(orc):
     n, nsb = 7, 11
     p = rng.integers(0, 256, size=(n, nsb * 210), dtype=np.uint8)
     s = _pack(14, p, n, nsb * 256).reshape(-1)
-    assert s.size == n * (1680 + 3 * 208 + 16) and s.size % 16 == 0
+    assert s.size == 8 * (1680 + 3 * 208 + 16) and s.size % 16 == 0
     for r in range(n):
         for sb in range(nsb):
             o = _record_off(14, r, sb, n, nsb)
@@ -141,10 +141,10 @@ def test_layout_argument_checks():
     assert L.b200q_layout_row_bytes(12, 100) == -1
     assert L.b200q_layout_row_bytes(3, 256) == -1
     buf = np.zeros(144, np.uint8)
-    out = np.zeros(144, np.uint8)
-    assert L.b200q_layout_pack(12, 1, 256, buf.ctypes.data, 143, out.ctypes.data, 144) == B.ERR_INVALID_CONFIG
+    out = np.zeros(4 * 144, np.uint8)
+    assert L.b200q_layout_pack(12, 1, 256, buf.ctypes.data, 143, out.ctypes.data, 576) == B.ERR_INVALID_CONFIG
     assert L.b200q_layout_pack(12, 1, 256, buf.ctypes.data, 144, out.ctypes.data, 100) == B.ERR_INVALID_CONFIG
-    assert L.b200q_layout_pack(12, 1, 256, None, 144, out.ctypes.data, 144) == B.ERR_INVALID_CONFIG
+    assert L.b200q_layout_pack(12, 1, 256, None, 144, out.ctypes.data, 576) == B.ERR_INVALID_CONFIG
     assert L.b200q_layout_pack(12, 0, 256, None, 0, None, 0) == B.OK
 
 

@@ -51,7 +51,7 @@ def test_prefill_fp32_activations_and_strided_output(backend, orc):
     out = big[:, :n]
     backend.project(w, x, out=out)
     backend.sync()
-    xb = x.to(torch.bfloat16).float().cpu().numpy()      # the route rounds fp32 activations to bf16
+    xb = x.half().float().cpu().numpy()                  # the route rounds fp32 activations to fp16
     ref = orc.matmul_exact(mb.TYPE_Q4_K, packed, n, k, xb)
     assert orc.within_tolerance(out.cpu().numpy(), ref, REL_PREFILL)[0]
     assert torch.all(big[:, n:] == 7.0)                  # nothing written past the row
