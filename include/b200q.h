@@ -183,6 +183,24 @@ b200q_status b200q_matmul_multi_host(b200q_ctx *ctx, const b200q_weight *const *
                                      const void *x_host, int32_t x_dtype, int64_t M, int64_t ldx,
                                      void *const *y_host, int32_t y_dtype, const int64_t *ldy);
 
+/* The prefill product for callers that must not allocate device memory.  No counterpart in the
+ * reference: there the engine sizes a model's whole GPU footprint before loading it and keeps the
+ * device to that plan, so a library that quietly grows a scratch buffer with cudaMalloc in the
+ * middle of serving can fail, or push the process past the budget it was admitted under; a host
+ * that has handed every free byte to its own pool has nothing left to give at all.  This entry
+ * point keeps the 16-bit copy of the activations in a fixed 8 MiB array inside the library image
+ * instead (each GPU that loads the library holds it until the process exits) and calls no
+ * allocator.  It always takes the tensor-core route.
+ *   - limit: M * round_up(K, 8) <= 4,194,304 elements; larger requests fail with
+ *     B200Q_ERR_INVALID_CONFIG and a message naming both numbers;
+ *   - the first call on a device looks up the array's device address; make that call before any
+ *     stream capture is begun;
+ *   - all calls on a device share the array: calls whose GPU work can overlap (different streams)
+ *     race on it, so keep them on one stream or order them yourself. */
+b200q_status b200q_matmul_prefill_noalloc(b200q_ctx *ctx, const b200q_weight *w, const void *x_dev,
+                                          int32_t x_dtype, int64_t M, int64_t ldx, void *y_dev,
+                                          int32_t y_dtype, int64_t ldy, void *stream);
+
 /* -- decode plans ------------------------------------------------------------------------------ */
 
 /* A plan is a fixed list of projections (M <= 4 activation rows, the same M for all) that one

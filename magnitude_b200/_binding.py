@@ -93,6 +93,10 @@ SIGNATURES = {
         [c_void_p, POINTER(c_void_p), c_int32, c_void_p, c_int32, c_int64, c_int64, POINTER(c_void_p), c_int32,
          POINTER(c_int64)],
     ),
+    "b200q_matmul_prefill_noalloc": (
+        c_int32,
+        [c_void_p, c_void_p, c_void_p, c_int32, c_int64, c_int64, c_void_p, c_int32, c_int64, c_void_p],
+    ),
     "b200q_plan_create": (c_int32, [c_void_p, POINTER(Job), c_int32, c_int64, POINTER(c_void_p)]),
     "b200q_plan_run": (c_int32, [c_void_p, c_void_p, c_void_p]),
     "b200q_plan_destroy": (None, [c_void_p]),

@@ -681,6 +681,42 @@ b200q_status b200q_matmul_host(b200q_ctx *ctx, const b200q_weight *w, const void
     return b200q_matmul_multi_host(ctx, &w, 1, x_host, x_dtype, M, ldx, &y_host, y_dtype, &ldy);
 }
 
+b200q_status b200q_matmul_prefill_noalloc(b200q_ctx *ctx, const b200q_weight *w, const void *x_dev,
+                                          int32_t x_dtype, int64_t M, int64_t ldx, void *y_dev, int32_t y_dtype,
+                                          int64_t ldy, void *stream) {
+    b200q_status s = check_ctx(ctx);
+    if (s != B200Q_OK) return s;
+    if ((s = validate_mm(ctx, w, x_dev, x_dtype, M, ldx, y_dev, y_dtype, ldy)) != B200Q_OK) return s;
+    if (M == 0 || w->N == 0) return B200Q_OK;
+    if (w->K == 0) return fail(ctx, B200Q_ERR_INVALID_CONFIG, "K = 0 is not supported by this entry point");
+    const size_t need = (size_t)M * (size_t)((w->K + 7) & ~int64_t(7));
+    if (need > gemm_static_scratch_elems())
+        return fail(ctx, B200Q_ERR_INVALID_CONFIG,
+                    "M x K = %lld x %lld needs %zu scratch elements, the built-in scratch holds %zu (8 MiB of 16-bit values)",
+                    (long long)M, (long long)w->K, need, gemm_static_scratch_elems());
+    GemmLaunch a{};
+    a.qt = w->type;
+    a.w = w->dev;
+    a.N = (int)w->N;
+    a.K = (int)w->K;
+    a.Kpad = (int)w->Kpad;
+    a.x = x_dev;
+    a.ldx = ldx;
+    a.M = (int)M;
+    a.y = y_dev;
+    a.ldy = ldy;
+    a.y_is_bf16 = y_dtype == B200Q_TYPE_BF16;
+    a.status = ctx->status_dev;
+    a.sm_count = ctx->sm_count;
+    a.bn_override = ctx->gemm_bn;
+    a.weights_bf16 = ctx->gemm_wbf16;
+    cudaError_t e = gemm_launch_static(a, x_dtype == B200Q_TYPE_BF16, (cudaStream_t)stream);
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "prefill launch (built-in scratch)");
+    ctx->last_route = B200Q_ROUTE_GEMM;
+    ctx->last_launches = 2;
+    return B200Q_OK;
+}
+
 // -- decode plans -------------------------------------------------------------------------------
 
 b200q_status b200q_plan_create(b200q_ctx *ctx, const b200q_job *jobs, int32_t n_jobs, int64_t M,

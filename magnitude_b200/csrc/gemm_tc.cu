@@ -626,4 +626,42 @@ cudaError_t gemm_launch(const GemmLaunch &a, cudaStream_t st) {
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Prefill without any allocation: the 16-bit copy of the activations lives in a fixed array that
+// is part of the library image (every GPU that loads the library holds these 8 MiB until the
+// process exits).  The array's name is only a host-side handle; the device address is asked for
+// once per device, with that device current, and that address is what the kernels receive.
+// Every call on a device shares the array and finds the previous call's contents in it; nothing
+// in it has to start at zero, because the conversion kernel overwrites every element the GEMM
+// then reads.  Calls that overlap on the GPU (two streams) race on it.
+// ---------------------------------------------------------------------------------------------
+constexpr size_t kStaticScratchBytes = size_t(8) << 20;
+static __device__ __align__(256) unsigned char g_static_x_scratch[kStaticScratchBytes];
+
+size_t gemm_static_scratch_elems() { return kStaticScratchBytes / 2; }
+
+// First use on a device resolves the array's device address (cudaGetSymbolAddress initialises the
+// module on that device, so that first call should happen outside any stream capture).
+cudaError_t gemm_launch_static(GemmLaunch a, int x_is_bf16, cudaStream_t st) {
+    constexpr int kMaxDevices = 64;
+    static void *dev_ptr[kMaxDevices] = {nullptr};
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+    if (!dev_ptr[dev]) {
+        void *ptr = nullptr;
+        e = cudaGetSymbolAddress(&ptr, g_static_x_scratch);
+        if (e != cudaSuccess) return e;
+        dev_ptr[dev] = ptr;
+    }
+    const long long ldd = (a.K + 7) & ~7;
+    if ((size_t)a.M * (size_t)ldd > gemm_static_scratch_elems()) return cudaErrorInvalidValue;
+    e = gemm_convert_x(a.x, x_is_bf16, a.ldx, dev_ptr[dev], a.M, a.K, a.weights_bf16, st);
+    if (e != cudaSuccess) return e;
+    a.x = dev_ptr[dev];
+    a.ldx = ldd;
+    return gemm_launch(a, st);
+}
+
 }  // namespace b200q

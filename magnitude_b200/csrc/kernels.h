@@ -84,5 +84,9 @@ size_t gemm_x_scratch_bytes(int M, int K);
 cudaError_t gemm_convert_x(const void *x, int x_is_bf16, long long ldx, void *scratch, int M, int K, int to_bf16,
                            cudaStream_t st);
 cudaError_t gemm_launch(const GemmLaunch &a, cudaStream_t st);
+// the same product with the activation copy in the library's built-in scratch array: a.x / a.ldx
+// describe the caller's activations (bf16 or fp32), nothing is allocated
+size_t gemm_static_scratch_elems();
+cudaError_t gemm_launch_static(GemmLaunch a, int x_is_bf16, cudaStream_t st);
 
 }  // namespace b200q
