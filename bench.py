@@ -35,6 +35,7 @@ LAYERS = 32
 HIDDEN, INTER = 4096, 14336
 Q4_K = 12
 FALLBACK_HBM_GBS = 6650.0
+FALLBACK_TFLOPS = 1400.0
 
 
 def peaks():
@@ -173,11 +174,12 @@ def run_reference(args):
 
 def workload_config(n_gpus):
     return {
-        "workload": "configs[1]: Q4_K decode GEMV, batch 1, Llama-3-8B MLP shapes, 32 layers per step",
+        "workload": f"configs[1]: Q4_K decode GEMV, batch 1, Llama-3-8B MLP shapes, {LAYERS} layers per step"
+                    + ("" if LAYERS == 32 else " (reduced profiling case, not the benchmark)"),
         "shapes": "gate/up 14336x4096, down 4096x14336, x bf16 1xK, y fp32",
         "layers": LAYERS,
         "weight_bytes_per_step": LAYERS * 3 * (INTER * HIDDEN // 256 * 144),
-        "l2": "inputs larger than L2 (3.17 GB of distinct weight buffers per step)",
+        "l2": f"inputs larger than L2 ({LAYERS * 3 * (INTER * HIDDEN // 256 * 144) / 1e9:.2f} GB of distinct weight buffers per step)",
         "parallelism": f"tp{n_gpus}" if n_gpus > 1 else "single",
     }
 
@@ -440,6 +442,142 @@ def run_b200(args):
     if dist is not None:
         dist.destroy_process_group()
 
+# ------------------------------------------------------------------------------------------------
+# secondary line: the prefill GEMM (configs[3]) — tcgen05 route, reported in TFLOP/s
+# ------------------------------------------------------------------------------------------------
+
+def run_prefill(args):
+    """M=2048 tokens x Q4_K 14336x4096, bf16 activations (1% of channels x20), bf16 output.
+
+    A step multiplies the same activations by `copies` distinct weight buffers (default 8, 264 MB,
+    larger than L2).  The reference arm of this line is the CPU path on a bounded token sample.
+    """
+    M, N, K = 2048, INTER, HIDDEN
+    copies = max(1, min(args.layers, 8)) if args.layers != 32 else 8
+    rank, local_rank, world = dist_env()
+    if world > 1:
+        if rank == 0:
+            print(json.dumps({"metric": "q4_k_prefill_gemm_tflops", "unavailable": "the prefill line is single-GPU"}))
+        return
+    from magnitude_b200 import ggml_quant as gq
+
+    w_h = gq.synth_weights(Q4_K, N, K, 0)
+    rng = np.random.default_rng(3)
+    x32 = rng.standard_normal((M, K), dtype=np.float32)
+    x32[:, rng.choice(K, K // 100, replace=False)] *= np.float32(20.0)
+    flops_one = 2.0 * M * N * K
+    cfg = {"workload": "configs[3]: Q4_K prefill GEMM, M=2048 K=4096 N=14336, bf16 activations with 1% outlier channels, bf16 output",
+           "weight_copies_per_step": copies, "l2": f"{copies} distinct weight buffers ({copies * N * K // 256 * 144 / 1e6:.0f} MB) per step",
+           "parallelism": "single"}
+
+    if args.impl == "reference":
+        from oracle import oracle as orc
+
+        orc.build()
+        rows = 8                                         # bounded sample: 8 of the 2048 token rows
+        xs = np.ascontiguousarray((gq.f32_to_bf16_bits(x32[:rows]).astype(np.uint32) << 16).view(np.float32))
+        for _ in range(max(args.warmup, 1)):
+            orc.matmul_cpu(Q4_K, w_h, N, K, xs)
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            orc.matmul_cpu(Q4_K, w_h, N, K, xs)
+        sec = (time.perf_counter() - t0) / args.steps
+        val = 2.0 * rows * N * K / sec / 1e12
+        cores = orc.num_threads()
+        print(json.dumps({"impl": "reference", "metric": "q4_k_prefill_gemm_tflops", "value": val, "unit": "TFLOP/s", "n_gpus": 1,
+                          "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3 * (M / rows) * copies,
+                          "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "u8/int32 block dots",
+                          "data": "synthetic", "config": cfg,
+                          "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+                                           "sample": f"{rows} of {M} token rows against one weight, all {cores} host threads"},
+                          "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
+        return
+
+    import torch
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the projection path has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    import magnitude_b200 as mb
+
+    be = mb.Backend(local_rank)
+    w0 = be.upload(Q4_K, w_h, N, K)
+    ws = [w0] + [w0.clone() for _ in range(copies - 1)]
+    x_host = torch.from_numpy(x32).to(torch.bfloat16)
+    x = x_host.to(dev)
+    y = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+    stream = torch.cuda.Stream(device=dev)
+
+    def step():
+        for w in ws:
+            be.project(w, x, out=y, stream=stream)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    if be.last_route()[0] != mb.ROUTE_GEMM:
+        raise SystemExit("prefill did not take the tcgen05 route")
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local_rank) as clocks:
+        torch.cuda.synchronize()
+        ev0.record(stream)
+        for _ in range(args.steps):
+            step()
+        ev1.record(stream)
+        torch.cuda.synchronize()
+        ms_step = ev0.elapsed_time(ev1) / args.steps
+        t_end = time.time() + 0.6
+        while time.time() < t_end:
+            step()
+        torch.cuda.synchronize()
+    be.sync(stream)
+    value = flops_one * copies / (ms_step * 1e-3) / 1e12
+
+    x_pin = x_host.clone().pin_memory()
+    y_pin = torch.empty((M, N), dtype=torch.bfloat16).pin_memory()
+    x_e = torch.empty_like(x)
+
+    def step_e2e():
+        with torch.cuda.stream(stream):
+            x_e.copy_(x_pin, non_blocking=True)
+        for w in ws:
+            be.project(w, x_e, out=y, stream=stream)
+        with torch.cuda.stream(stream):
+            y_pin.copy_(y, non_blocking=True)
+        stream.synchronize()
+
+    step_e2e()
+    t0 = time.perf_counter()
+    n_e2e = max(3, min(args.steps, 10))
+    for _ in range(n_e2e):
+        step_e2e()
+    e2e_s = (time.perf_counter() - t0) / n_e2e
+
+    peak, src = FALLBACK_TFLOPS, "fallback"
+    pk = ROOT / "MEASURED_PEAKS.json"
+    if pk.exists():
+        try:
+            peak, src = float(json.loads(pk.read_text())["bf16_tflops_sustained"]), "measured (sustained)"
+        except Exception:
+            pass
+    line = {
+        "metric": "q4_k_prefill_gemm_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "fp16 x fp16 tcgen05.mma, fp32 accumulate in TMEM (weights dequantized exactly to fp16, activations bf16 -> fp16)",
+        "data": "synthetic", "config": cfg,
+        "roofline": {"bound": "tensor", "kernel": "gemm_tc_kernel<Q4_K,fp16> (+ convert_x_kernel per product)", "achieved": value, "peak": peak,
+                     "unit": "TFLOP/s", "frac": value / peak, "peak_source": f"of {src}", "traffic": None,
+                     "us_per_launch": ms_step * 1e3 / copies,
+                     "note": "2*M*N*K per product / device time per product, activation conversion launch included"},
+        "cpu_baseline": None,
+        "e2e": {"value": flops_one * copies / e2e_s / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": M * K * 2,
+                "d2h_bytes_per_step": M * N * 2, "ms_per_step": e2e_s * 1e3,
+                "api": "pinned host activations -> device, b200q_matmul per weight, last result -> pinned host, synchronize"},
+        "gpu_launches": 2 * copies * args.steps, "clocks": clocks.summary(),
+    }
+    print(json.dumps(line))
+
 
 def main():
     ap = argparse.ArgumentParser()
@@ -450,8 +588,16 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="time direct launches instead of a CUDA graph replay")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--per-launch", action="store_true", help="one launch per projection group instead of a decode plan")
+    ap.add_argument("--layers", type=int, default=32,
+                    help="layers per step (default 32 = the benchmark; a smaller count is a profiling case, named as such in config)")
+    ap.add_argument("--workload", choices=["decode", "prefill"], default="decode",
+                    help="decode = the headline Q4_K GEMV step; prefill = the M=2048 Q4_K GEMM (secondary line, TFLOP/s)")
     args = ap.parse_args()
-    if args.impl == "reference":
+    global LAYERS
+    LAYERS = max(1, min(args.layers, 32))
+    if args.workload == "prefill":
+        run_prefill(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_b200(args)

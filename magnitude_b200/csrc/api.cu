@@ -89,7 +89,7 @@ struct b200q_ctx {
     // prefill path: bf16 copy of fp32 activations
     void *gemm_scratch = nullptr;
     size_t gemm_scratch_bytes = 0;
-    int gemm_bn = 0, gemm_wbf16 = 0;
+    int gemm_bn = 0, gemm_debug = 0;
     // tunables (environment overrides for experiments)
     int gemv_warps = 0, gemv_depth = 0, gemv_grid = 0, gemv_smem = 0, gemv_rows = 0, gemv_debug = 0, gemv_pdl = 1;
     // tensor parallel
@@ -252,17 +252,12 @@ b200q_status run_gemv(b200q_ctx *ctx, const b200q_weight *const *w, int nw, cons
     return run_stream(ctx, &J, nullptr, 1, M, st);
 }
 
-// prefill route: an activation conversion and one tensor-core launch per weight
+// prefill route: one activation conversion per weight set and one tensor-core launch per weight
 b200q_status run_gemm(b200q_ctx *ctx, const b200q_weight *w, const void *x, int x_dtype, int64_t M, int64_t ldx,
-                      void *y, int y_dtype, int64_t ldy, cudaStream_t st, int *launches) {
-    // Both tensor-core operands share one 16-bit format (fp16 by default): the activations are
-    // converted into context-owned scratch memory first, unless they already are bf16 and the
-    // bf16 mode is on.
-    const void *xb = x;
-    long long ldb = ldx;
-    const bool direct = ctx->gemm_wbf16 && x_dtype == B200Q_TYPE_BF16 &&
-                        !(reinterpret_cast<uintptr_t>(x) & 15) && (ldx * 2) % 16 == 0;
-    if (!direct) {
+                      void *y, int y_dtype, int64_t ldy, cudaStream_t st, int *launches, bool x_already_converted) {
+    // Both tensor-core operands are fp16: the activations are converted into context-owned scratch
+    // memory first (once for all the weights of a set, which share them).
+    if (!x_already_converted) {
         const size_t need = gemm_x_scratch_bytes((int)M, (int)w->K);
         if (need > ctx->gemm_scratch_bytes) {
             if (ctx->gemm_scratch) {
@@ -274,13 +269,12 @@ b200q_status run_gemm(b200q_ctx *ctx, const b200q_weight *w, const void *x, int 
             CU_TRY(ctx, cudaMalloc(&ctx->gemm_scratch, need));
             ctx->gemm_scratch_bytes = need;
         }
-        cudaError_t e = gemm_convert_x(x, x_dtype == B200Q_TYPE_BF16, ldx, ctx->gemm_scratch, (int)M, (int)w->K,
-                                       ctx->gemm_wbf16, st);
+        cudaError_t e = gemm_convert_x(x, x_dtype == B200Q_TYPE_BF16, ldx, ctx->gemm_scratch, (int)M, (int)w->K, st);
         if (e != cudaSuccess) return cuda_fail(ctx, e, "activation conversion launch");
         ++*launches;
-        xb = ctx->gemm_scratch;
-        ldb = (w->K + 7) & ~int64_t(7);
     }
+    const void *xb = ctx->gemm_scratch;
+    const long long ldb = (w->K + 7) & ~int64_t(7);
     GemmLaunch a{};
     a.qt = w->type;
     a.w = w->dev;
@@ -296,7 +290,7 @@ b200q_status run_gemm(b200q_ctx *ctx, const b200q_weight *w, const void *x, int 
     a.status = ctx->status_dev;
     a.sm_count = ctx->sm_count;
     a.bn_override = ctx->gemm_bn;
-    a.weights_bf16 = ctx->gemm_wbf16;
+    a.debug = ctx->gemm_debug;
     cudaError_t e = gemm_launch(a, st);
     if (e != cudaSuccess) return cuda_fail(ctx, e, "tensor-core GEMM launch");
     ++*launches;
@@ -336,10 +330,12 @@ b200q_status matmul_any(b200q_ctx *ctx, const b200q_weight *const *w, int nw, co
     const int mt = gemv_max_m();
     if (M > mt) {   // prefill / verify batches: tensor cores, one launch per weight
         ctx->last_route = B200Q_ROUTE_GEMM;
+        bool converted = false;
         for (int i = 0; i < nw; ++i) {
             if (w[i]->N == 0) continue;
-            b200q_status s = run_gemm(ctx, w[i], x, x_dtype, M, ldx, y[i], y_dtype, ldy[i], st, &ctx->last_launches);
+            b200q_status s = run_gemm(ctx, w[i], x, x_dtype, M, ldx, y[i], y_dtype, ldy[i], st, &ctx->last_launches, converted);
             if (s != B200Q_OK) return s;
+            converted = true;
         }
         return B200Q_OK;
     }
@@ -429,7 +425,7 @@ b200q_status b200q_ctx_create(int32_t device, b200q_ctx **out) {
     ctx->gemv_debug = env_int("B200Q_GEMV_DEBUG", 0);
     ctx->gemv_pdl = env_int("B200Q_GEMV_PDL", 1);
     ctx->gemm_bn = env_int("B200Q_GEMM_BN", 0);
-    ctx->gemm_wbf16 = env_int("B200Q_GEMM_WBF16", 0);
+    ctx->gemm_debug = env_int("B200Q_GEMM_DEBUG", 0);
     *out = ctx;
     return B200Q_OK;
 }
@@ -709,7 +705,7 @@ b200q_status b200q_matmul_prefill_noalloc(b200q_ctx *ctx, const b200q_weight *w,
     a.status = ctx->status_dev;
     a.sm_count = ctx->sm_count;
     a.bn_override = ctx->gemm_bn;
-    a.weights_bf16 = ctx->gemm_wbf16;
+    a.debug = ctx->gemm_debug;
     cudaError_t e = gemm_launch_static(a, x_dtype == B200Q_TYPE_BF16, (cudaStream_t)stream);
     if (e != cudaSuccess) return cuda_fail(ctx, e, "prefill launch (built-in scratch)");
     ctx->last_route = B200Q_ROUTE_GEMM;

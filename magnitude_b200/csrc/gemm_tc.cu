@@ -1,23 +1,27 @@
 // Prefill GEMM: Y[M][N] = X[M][K] . dequant(W)[N][K]^T on the 5th-generation tensor cores.
 //
 // One persistent CTA per SM walks output tiles of 128 weight rows x BN tokens (BN <= 256):
-//   * warp 0 (one lane) loads the activation tile X[m0 : m0+BN][k : k+64] with TMA (2-D tiled
-//     bulk tensor copy, 128-byte swizzle, no multicast) into a 3-stage shared-memory ring;
-//     the same lane fetches the packed weight records of the tile's 128 rows, one superblock
+//   * warp 0 (one lane) loads the activation tile X[m0 : m0+BN][k : k+64] (fp16) with TMA (2-D tiled
+//     bulk tensor copy, 128-byte swizzle, no multicast) into its own shared-memory ring;
+//   * warp 2 (one lane) fetches the packed weight records of the tile's 128 rows, one 256-weight
 //     record per row at a time (a 4-D tiled copy over the streaming layout), into a 2-deep ring;
-//   * warps 2..17 dequantize 16 weights per thread and K-step from that ring to fp16 in registers
-//     and write them into the stage ring in the K-major 128-byte-swizzled layout the tensor core
-//     reads (generic-proxy stores, then fence.proxy.async);
+//   * warps 3..18 dequantize: thread (row r, unit j) turns the j-th 64 weights of every record of
+//     row r into fp16 with packed half2 arithmetic and writes them into the weight-stage ring in the
+//     K-major 128-byte-swizzled layout the tensor core reads (generic-proxy stores, then
+//     fence.proxy.async).  The four units of a record are four consecutive K-steps, so the four
+//     groups of four warps work on four stages at once;
 //   * warp 1 (one lane) issues tcgen05.mma (kind::f16, fp16 x fp16 -> fp32) with the dequantized
 //     weights as the A operand (M = 128) and the activations as the B operand (N = BN), four
-//     K = 16 instructions per stage, accumulating in tensor memory; tcgen05.commit releases the
-//     stage to the producers and, after the last K-step, hands the accumulator to the epilogue;
-//   * warps 18..21 read the accumulator (tcgen05.ld, one 32-lane quadrant per warp), convert to
+//     K = 16 instructions per K-step, accumulating in tensor memory; tcgen05.commit releases the
+//     two stages to their producers and, after the last K-step, hands the accumulator to the epilogue;
+//   * warps 19..22 read the accumulator (tcgen05.ld, one 32-lane quadrant per warp), convert to
 //     the output type and store Y; two accumulator buffers (2 x 256 TMEM columns) let the next
 //     tile's main loop run under the epilogue.
 // Every mbarrier wait is bounded; a wait that runs out raises the status word and an abort flag,
 // all roles leave their loops, tensor memory is freed and the kernel returns.
 #include <cuda.h>
+#include <cuda_fp16.h>
+#include <stdio.h>
 #include <stdlib.h>
 
 #include <algorithm>
@@ -30,17 +34,28 @@ namespace b200q {
 namespace {
 
 constexpr int BM = 128;          // weight rows per tile (MMA M)
-constexpr int BK = 64;           // weights per K-step (one 128-byte swizzle row of bf16)
-constexpr int kStages = 3;        // A/B stages
-constexpr int kWBufs = 2;         // packed-weight buffers (one superblock record per row each)
-constexpr int kWBufBytes = 35 * 1024;   // 128 rows x 272 bytes (largest record), rounded up to 1 KB
+constexpr int BK = 64;           // weights per K-step (one 128-byte swizzle row of fp16)
+constexpr int kAStages = 4;       // dequantized-weight stages: one per unit group, so each group meets every phase of its stage
+constexpr int kWBufs = 2;         // packed-weight buffers (one 256-weight record per row each)
 constexpr int kDBufBytes = 2048;        // Q6_K: 128 rows x the 16-byte group of fp16 d of a chunk
-constexpr int kDequantWarps = 16;  // four threads per weight row, 16 weights each per K-step
+constexpr int kDequantWarps = 16;  // thread = (row, 64-weight unit of the record)
 constexpr int kEpiWarps = 4;
-constexpr int kThreads = (2 + kDequantWarps + kEpiWarps) * 32;   // 704
+constexpr int kFirstDequantWarp = 3, kFirstEpiWarp = kFirstDequantWarp + kDequantWarps;
+constexpr int kThreads = (kFirstEpiWarp + kEpiWarps) * 32;   // 736
+static_assert(kAStages * 4 == kDequantWarps, "one weight stage per group of four dequant warps");
 constexpr int kTmemCols = 512;   // two accumulator buffers of 256 columns
 constexpr int kStageABytes = BM * BK * 2;       // 16 KB
-constexpr int kStageBBytes = 256 * BK * 2;      // 32 KB (BN <= 256)
+constexpr int kMaxBStages = 4;
+
+// per-type shared-memory plan: the packed-record buffers differ in size, the activation ring takes
+// what is left of the 227 KB
+__host__ __device__ constexpr int wbuf_bytes(int qt) { return ((BM * rec_bytes(qt) + 1023) / 1024) * 1024; }
+__host__ __device__ constexpr int b_stages(int qt) { return qt == QT_Q4_K ? 4 : 3; }
+__host__ __device__ constexpr int bn_max(int qt) { return qt == QT_Q6_K ? 256 : 240; }     // widest token tile
+__host__ __device__ constexpr int b_stage_bytes(int qt) { return bn_max(qt) * BK * 2; }
+__host__ __device__ constexpr int smem_data_bytes(int qt) {
+    return kAStages * kStageABytes + b_stages(qt) * b_stage_bytes(qt) + kWBufs * wbuf_bytes(qt) + (qt == QT_Q6_K ? 2 * kDBufBytes : 0);
+}
 
 struct GemmParams {
     const uint8_t *w;        // streaming-layout weights
@@ -54,17 +69,23 @@ struct GemmParams {
     int m_tiles, n_tiles;
     int nchunks_full;        // chunks of 8 whole records per row; a shorter tail chunk may follow
     int *status;
+    int debug;               // timing experiments only (results invalid): 1 no activation loads, 2 no dequant math,
+                             // 4 no weight loads, 8 no MMA, 16 no epilogue body, 32 no proxy fence,
+                             // 64 plain arrives instead of commits, 256 print per-role clock counts from block 0
 };
 
 struct GemmSmem {
-    uint64_t full[kStages];
-    uint64_t empty[kStages];
+    uint64_t afull[kAStages];
+    uint64_t aempty[kAStages];
+    uint64_t bfull[kMaxBStages];
+    uint64_t bempty[kMaxBStages];
     uint64_t tmem_full[2];
     uint64_t tmem_empty[2];
     uint64_t wfull[kWBufs];
     uint64_t wempty[kWBufs];
     uint32_t tmem_base;
     int abort;
+    int wait_ns;
 };
 
 // ---- tcgen05 wrappers -----------------------------------------------------------------------
@@ -81,7 +102,7 @@ __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
@@ -136,163 +157,229 @@ __device__ __forceinline__ uint64_t make_desc_sw128(uint32_t saddr) {
     return d;
 }
 
-// two fp32 -> one packed pair of 16-bit floats (lo in the low half).  The weights enter the tensor
-// core as fp16 (11-bit significand: rounding error 2^-12, against 2^-9 for bf16) unless F16 is off.
-template <bool F16> __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
-    uint32_t r;
-    if (F16) asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
-    else asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
-    return r;
-}
-
 // ---- dequantization to the swizzled A tile ---------------------------------------------------
 //
-// A dequant thread owns one weight row of the tile and one quarter (16 weights) of the 64-weight
-// K-step.  Small integers become fp32 without a conversion instruction: a byte v placed in the
-// mantissa of a float with a fixed exponent reads as (C + v), and one fused multiply-add
-// (C + v) * s - (C * s + m) gives the weight.  Eight bf16 values form one 16-byte chunk; chunk cc
-// of row r is stored at chunk position cc ^ (r & 7) of the row (128-byte swizzle).
+// A dequant thread owns one weight row of the tile and one 64-weight unit (one K-step) of every
+// 256-weight record.  Small integers become fp16 without a conversion instruction: a byte v put
+// under the high byte 0x64 reads as the half 1024 + v (under 0x54, a byte with only its high
+// nibble set reads as 64 + v / 16).  One exact half2 subtraction removes the offset and one half2
+// fused multiply-add applies the block's scale and minimum, two weights per instruction.  Eight fp16 values
+// form one 16-byte chunk; chunk cc of row r is stored at chunk position cc ^ (r & 7) of the row
+// (128-byte swizzle).
 
 __device__ __forceinline__ void st_chunk(uint32_t row_saddr, int r7, int cc, uint32_t p0, uint32_t p1, uint32_t p2, uint32_t p3) {
     const uint32_t a = row_saddr + ((cc ^ r7) << 4);
     asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(a), "r"(p0), "r"(p1), "r"(p2), "r"(p3) : "memory");
 }
 
-// byte i of v -> float bits 0x43000000 | byte << 16   (value 128 + byte for byte < 128)
-template <int I> __device__ __forceinline__ float f128_plus(uint32_t v) {
-    return __uint_as_float(__byte_perm(v, 0x43000000u, 0x7044 | (I << 8)));
+__device__ __forceinline__ __half2 as_h2(uint32_t v) { return *reinterpret_cast<__half2 *>(&v); }
+__device__ __forceinline__ uint32_t as_u32(__half2 h) { return *reinterpret_cast<uint32_t *>(&h); }
+
+// bytes 0..3 of v -> ((b0, b1) - off) * s + c and ((b2, b3) - off) * s + c, MG the high byte given to each
+template <uint32_t MG>
+__device__ __forceinline__ void word_affine(uint32_t v, __half2 off, __half2 s, __half2 c, uint32_t &p0, uint32_t &p1) {
+    p0 = as_u32(__hfma2(__hsub2(as_h2(__byte_perm(v, MG, 0x4140)), off), s, c));
+    p1 = as_u32(__hfma2(__hsub2(as_h2(__byte_perm(v, MG, 0x4342)), off), s, c));
 }
-// byte i of v -> float bits 0x47000000 | byte << 8    (value 32768 + byte)
-template <int I> __device__ __forceinline__ float f32768_plus(uint32_t v) {
-    return __uint_as_float(__byte_perm(v, 0x47000000u, 0x7404 | (I << 4)));
+template <uint32_t MG>
+__device__ __forceinline__ void word_scale(uint32_t v, __half2 off, __half2 s, uint32_t &p0, uint32_t &p1) {
+    p0 = as_u32(__hmul2(__hsub2(as_h2(__byte_perm(v, MG, 0x4140)), off), s));
+    p1 = as_u32(__hmul2(__hsub2(as_h2(__byte_perm(v, MG, 0x4342)), off), s));
 }
 
-// `qd` = which quarter (16 weights, two 16-byte chunks) of the 64-weight K-step the thread makes.
-template <int QT> struct Packed;
+// Scale s and minimum m of a Q4_K sub-block (weight = s q - m) as half2 constants around the
+// integer q0 nearest m / s:  weight = s (q - q0) - (m - s q0).  Both terms are then of the weight's
+// own size, so rounding s and the small remainder to fp16 costs about one extra rounding of the
+// weight instead of a rounding of m, which is several times larger than the weights.
+// `base` is the offset the byte trick adds (1024 or 64); base + q0 stays an exact fp16 integer.
+__device__ __forceinline__ void centered(float s, float m, __half2 base, __half2 &off, __half2 &sh, __half2 &ch) {
+    float q0 = rintf(__fdividef(m, s));
+    q0 = (q0 >= 0.f && q0 <= 1023.f) ? q0 : (q0 > 1023.f ? 1023.f : 0.f);   // NaN (s == 0) -> 0
+    off = __hadd2(base, __float2half2_rn(q0));
+    sh = __float2half2_rn(s);
+    ch = __float2half2_rn(fmaf(s, q0, -m));
+}
 
-template <> struct Packed<QT_Q4_K> {
-    uint4 hdr, q;
-    // rec: shared address of the row's 144-byte record of this K-step's superblock; j: 64-weight unit.
-    // Quarters 0, 1 are the low nibbles of bytes 0..15 / 16..31 of the unit, quarters 2, 3 the high.
-    __device__ __forceinline__ void load(uint32_t rec, uint32_t, int j, int qd) {
+template <int QT> struct Unit;
+
+// the 64 converted weights of a thread (eight 16-byte chunks in K order) -> its row of the stage
+__device__ __forceinline__ void store_row(const uint32_t (&o)[32], uint32_t row_saddr, int r7) {
+#pragma unroll
+    for (int c = 0; c < 8; ++c) st_chunk(row_saddr, r7, c, o[4 * c], o[4 * c + 1], o[4 * c + 2], o[4 * c + 3]);
+}
+
+template <> struct Unit<QT_Q4_K> {
+    uint4 hdr, q0, q1;
+    // rec: shared address of the row's 144-byte record; unit j = bytes 32j..32j+31 of the nibbles:
+    // low nibbles are weights 0..31 of the K-step (sub-block 2j), high nibbles weights 32..63 (2j+1)
+    __device__ __forceinline__ void load(uint32_t rec, uint32_t, int j) {
         hdr = lds128(rec);
-        q = lds128(rec + 16 + 32 * j + 16 * (qd & 1));
+        q0 = lds128(rec + 16 + 32 * j);
+        q1 = lds128(rec + 32 + 32 * j);
     }
-    template <bool F16> __device__ __forceinline__ void emit(int j, int qd, uint32_t row_saddr, int r7) const {
-        int sc, mn;
-        q4k_scale_min(hdr.y, hdr.z, hdr.w, 2 * j + (qd >> 1), sc, mn);
-        const float ds = half_bits_to_float(hdr.x) * (float)sc;
-        const float c0 = -(128.f * ds + half_bits_to_float(hdr.x >> 16) * (float)mn);
-        const uint32_t w[4] = {q.x, q.y, q.z, q.w};
-        const int sh = 4 * (qd >> 1);
+    __device__ __forceinline__ void convert(int j, uint32_t (&o)[32]) const {
+        int sa, ma, sb, mb;
+        q4k_scale_min(hdr.y, hdr.z, hdr.w, 2 * j, sa, ma);
+        q4k_scale_min(hdr.y, hdr.z, hdr.w, 2 * j + 1, sb, mb);
+        const float d = half_bits_to_float(hdr.x), dmin = half_bits_to_float(hdr.x >> 16);
+        __half2 o_lo, s_lo, c_lo, o_hi, s_hi, c_hi;
+        centered(d * (float)sa, dmin * (float)ma, as_h2(0x64006400u), o_lo, s_lo, c_lo);
+        centered(d * (float)sb, dmin * (float)mb, as_h2(0x54005400u), o_hi, s_hi, c_hi);
+        const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
-            const uint32_t a = (w[2 * c] >> sh) & 0x0F0F0F0Fu, b = (w[2 * c + 1] >> sh) & 0x0F0F0F0Fu;
-            const uint32_t p0 = pack2<F16>(fmaf(f128_plus<0>(a), ds, c0), fmaf(f128_plus<1>(a), ds, c0));
-            const uint32_t p1 = pack2<F16>(fmaf(f128_plus<2>(a), ds, c0), fmaf(f128_plus<3>(a), ds, c0));
-            const uint32_t p2 = pack2<F16>(fmaf(f128_plus<0>(b), ds, c0), fmaf(f128_plus<1>(b), ds, c0));
-            const uint32_t p3 = pack2<F16>(fmaf(f128_plus<2>(b), ds, c0), fmaf(f128_plus<3>(b), ds, c0));
-            st_chunk(row_saddr, r7, 2 * qd + c, p0, p1, p2, p3);
+        for (int n = 0; n < 4; ++n) {     // chunk n = low nibbles of words 2n, 2n+1; chunk 4 + n = their high nibbles
+            word_affine<0x64>(w[2 * n] & 0x0F0F0F0Fu, o_lo, s_lo, c_lo, o[4 * n], o[4 * n + 1]);
+            word_affine<0x64>(w[2 * n + 1] & 0x0F0F0F0Fu, o_lo, s_lo, c_lo, o[4 * n + 2], o[4 * n + 3]);
+            word_affine<0x54>(w[2 * n] & 0xF0F0F0F0u, o_hi, s_hi, c_hi, o[16 + 4 * n], o[16 + 4 * n + 1]);
+            word_affine<0x54>(w[2 * n + 1] & 0xF0F0F0F0u, o_hi, s_hi, c_hi, o[16 + 4 * n + 2], o[16 + 4 * n + 3]);
         }
     }
 };
 
-template <> struct Packed<QT_Q8_0> {
-    uint4 q;
-    uint32_t d16;
-    // rec: shared address of the 272-byte record; unit j holds native blocks 2j, 2j+1; quarter qd is
-    // half of block 2j + qd/2
-    __device__ __forceinline__ void load(uint32_t rec, uint32_t, int j, int qd) {
-        q = lds128(rec + 64 * j + 16 * qd);
-        d16 = lds16(rec + 256 + 2 * (2 * j + (qd >> 1)));
-    }
-    template <bool F16> __device__ __forceinline__ void emit(int, int qd, uint32_t row_saddr, int r7) const {
-        const float d = half_bits_to_float(d16);
-        const float c0 = -32896.f * d;     // (32768 + 128): bytes are taken as unsigned after ^ 0x80
-        const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+template <> struct Unit<QT_Q8_0> {
+    uint4 q[4];
+    uint32_t dd;
+    // rec: shared address of the 272-byte record [8 x 32 int8][8 x fp16 d]; unit j = native blocks 2j, 2j+1
+    __device__ __forceinline__ void load(uint32_t rec, uint32_t, int j) {
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
-            const uint32_t a = w[2 * c] ^ 0x80808080u, b = w[2 * c + 1] ^ 0x80808080u;
-            const uint32_t p0 = pack2<F16>(fmaf(f32768_plus<0>(a), d, c0), fmaf(f32768_plus<1>(a), d, c0));
-            const uint32_t p1 = pack2<F16>(fmaf(f32768_plus<2>(a), d, c0), fmaf(f32768_plus<3>(a), d, c0));
-            const uint32_t p2 = pack2<F16>(fmaf(f32768_plus<0>(b), d, c0), fmaf(f32768_plus<1>(b), d, c0));
-            const uint32_t p3 = pack2<F16>(fmaf(f32768_plus<2>(b), d, c0), fmaf(f32768_plus<3>(b), d, c0));
-            st_chunk(row_saddr, r7, 2 * qd + c, p0, p1, p2, p3);
+        for (int i = 0; i < 4; ++i) q[i] = lds128(rec + 64 * j + 16 * i);
+        dd = lds32(rec + 256 + 4 * j);
+    }
+    __device__ __forceinline__ void convert(int, uint32_t (&o)[32]) const {
+        const __half2 d_lo = as_h2(__byte_perm(dd, 0, 0x1010)), d_hi = as_h2(__byte_perm(dd, 0, 0x3232));
+        const __half2 o1152 = as_h2(0x64806480u);      // bytes are taken as unsigned after ^ 0x80: 1024 + 128 + q
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const __half2 d = i < 2 ? d_lo : d_hi;
+            const uint32_t w[4] = {q[i].x, q[i].y, q[i].z, q[i].w};
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {     // chunk 2i + c
+                word_scale<0x64>(w[2 * c] ^ 0x80808080u, o1152, d, o[8 * i + 4 * c], o[8 * i + 4 * c + 1]);
+                word_scale<0x64>(w[2 * c + 1] ^ 0x80808080u, o1152, d, o[8 * i + 4 * c + 2], o[8 * i + 4 * c + 3]);
+            }
         }
     }
 };
 
-template <> struct Packed<QT_Q6_K> {
-    uint4 l, hq;
-    uint32_t sc8, d16;
-    // rec: shared address of the 208-byte record, dptr: of its fp16 d.  The 64 weights of unit u are quadrants
-    // 2(u&1), 2(u&1)+1 of half u>>1; quarter qd is positions 16(qd&1)..+15 of quadrant
-    // c = 2(u&1) + qd/2, which is exactly one 16-weight sub-block (one scale).
-    __device__ __forceinline__ void load(uint32_t rec, uint32_t dptr, int u, int qd) {
-        const int hh = u >> 1, c = 2 * (u & 1) + (qd >> 1), ph = qd & 1;
-        l = lds128(rec + 64 * hh + 32 * (c & 1) + 16 * ph);
-        hq = lds128(rec + 128 + 32 * hh + 16 * ph);
-        const uint32_t a = rec + 192 + 8 * hh + 2 * c + ph;
-        sc8 = (lds16(a & ~1u) >> (8 * (a & 1))) & 0xFF;
+template <> struct Unit<QT_Q6_K> {
+    uint4 l[4], hq[2];
+    uint32_t sc4, d16;
+    // rec: shared address of the 208-byte record [ql 128][qh 64][sc 16], dptr: of its fp16 d.  Unit u is
+    // quadrants 2(u&1), 2(u&1)+1 of half u>>1: 64 bytes of ql (low nibbles for even u, high for odd),
+    // 32 bytes of qh (bit pair 2(u&1) + quarter/2), four int8 scales (one per 16 weights).
+    __device__ __forceinline__ void load(uint32_t rec, uint32_t dptr, int u) {
+        const int hh = u >> 1;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) l[i] = lds128(rec + 64 * hh + 16 * i);
+        hq[0] = lds128(rec + 128 + 32 * hh);
+        hq[1] = lds128(rec + 144 + 32 * hh);
+        sc4 = lds32(rec + 192 + 8 * hh + 4 * (u & 1));
         d16 = lds16(dptr);
     }
-    template <bool F16> __device__ __forceinline__ void emit(int u, int qd, uint32_t row_saddr, int r7) const {
-        const int c = 2 * (u & 1) + (qd >> 1);
-        const float s = half_bits_to_float(d16) * (float)(int)(int8_t)sc8;
-        const float c0 = -32800.f * s;     // 32768 + 32
-        const uint32_t lw[4] = {l.x, l.y, l.z, l.w};
-        const uint32_t hw[4] = {hq.x, hq.y, hq.z, hq.w};
-        const int lsh = 4 * (c >> 1), hsh = 2 * c;
+    __device__ __forceinline__ void convert(int u, uint32_t (&o)[32]) const {
+        const float d = half_bits_to_float(d16);
+        const int lsh = 4 * (u & 1);
+        const __half2 o1056 = as_h2(0x64206420u);      // 1024 + 32
 #pragma unroll
-        for (int cc = 0; cc < 2; ++cc) {
-            uint32_t v[2];
+        for (int qd = 0; qd < 4; ++qd) {
+            const __half2 s = __float2half2_rn(d * (float)(int)(int8_t)(sc4 >> (8 * qd)));
+            const int hsh = lsh + 2 * (qd >> 1);
+            const uint32_t lw[4] = {l[qd].x, l[qd].y, l[qd].z, l[qd].w};
+            const uint32_t hw[4] = {hq[qd & 1].x, hq[qd & 1].y, hq[qd & 1].z, hq[qd & 1].w};
 #pragma unroll
-            for (int i = 0; i < 2; ++i)
-                v[i] = ((lw[2 * cc + i] >> lsh) & 0x0F0F0F0Fu) | (((hw[2 * cc + i] >> hsh) & 0x03030303u) << 4);
-            const uint32_t p0 = pack2<F16>(fmaf(f32768_plus<0>(v[0]), s, c0), fmaf(f32768_plus<1>(v[0]), s, c0));
-            const uint32_t p1 = pack2<F16>(fmaf(f32768_plus<2>(v[0]), s, c0), fmaf(f32768_plus<3>(v[0]), s, c0));
-            const uint32_t p2 = pack2<F16>(fmaf(f32768_plus<0>(v[1]), s, c0), fmaf(f32768_plus<1>(v[1]), s, c0));
-            const uint32_t p3 = pack2<F16>(fmaf(f32768_plus<2>(v[1]), s, c0), fmaf(f32768_plus<3>(v[1]), s, c0));
-            st_chunk(row_saddr, r7, 2 * qd + cc, p0, p1, p2, p3);
+            for (int cc = 0; cc < 2; ++cc) {     // chunk 2 qd + cc
+                uint32_t v[2];
+#pragma unroll
+                for (int i = 0; i < 2; ++i)
+                    v[i] = ((lw[2 * cc + i] >> lsh) & 0x0F0F0F0Fu) | (((hw[2 * cc + i] >> hsh) & 0x03030303u) << 4);
+                word_scale<0x64>(v[0], o1056, s, o[8 * qd + 4 * cc], o[8 * qd + 4 * cc + 1]);
+                word_scale<0x64>(v[1], o1056, s, o[8 * qd + 4 * cc + 2], o[8 * qd + 4 * cc + 3]);
+            }
         }
     }
 };
 
 // ---- the kernel -------------------------------------------------------------------------------
 
-__device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, GemmSmem *sm, int *status) {
-    volatile int *ab = &sm->abort;
-    if (*ab) return false;
-    if (mbar_wait_bounded(bar, parity)) return true;
-    *ab = 1;
-    atomicMax(status, DEV_ERR_PIPE_TIMEOUT);
-    return false;
+// try_wait with a cap on how long the hardware may keep the thread suspended: without the hint a
+// suspended waiter was seen to resume only about a microsecond after the phase completed (several
+// K-steps' worth of time), and a crowd of threads spinning on the non-suspending test_wait slowed
+// every barrier operation of the CTA down to a few hundred cycles.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity), "r"(ns)
+        : "memory");
+    return ok != 0;
 }
 
-template <int QT, bool F16>
+// Bounded wait.  FAST waits sit on the critical path (tensor-core issue, dequant hand-over, TMA
+// issue) and re-check every few dozen nanoseconds; the others (the epilogue's, long by design)
+// let the hardware suspend them for as long as it likes.  After the limit the waiter raises the
+// status word and the abort flag, which every other waiter polls.
+template <bool FAST>
+__device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, GemmSmem *sm, int *status) {
+    if (FAST) {
+#pragma unroll 1
+        for (int i = 0; i < (1 << 14); ++i)
+            if (mbar_try_wait_hint(bar, parity, (uint32_t)sm->wait_ns)) return true;
+    } else if (mbar_try_wait(bar, parity)) {
+        return true;
+    }
+    volatile int *ab = &sm->abort;
+    const uint64_t t0 = globaltimer_ns();
+#pragma unroll 1
+    while (true) {
+#pragma unroll 1
+        for (int i = 0; i < 64; ++i)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (*ab) return false;
+        if (globaltimer_ns() - t0 > kWaitLimitNs) {
+            *ab = 1;
+            atomicMax(status, DEV_ERR_PIPE_TIMEOUT);
+            return false;
+        }
+    }
+}
+
+template <int QT>
 __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap,
                                                                const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap wtail,
                                                                const __grid_constant__ CUtensorMap dmap, const __grid_constant__ CUtensorMap dtail) {
+    constexpr int SB_ = b_stages(QT);
+    constexpr int WBUF = wbuf_bytes(QT);
+    constexpr int REC = rec_bytes(QT);
+    constexpr int kStageBBytes = b_stage_bytes(QT);
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     // stage buffers first (1024-byte aligned for the 128-byte swizzle), bookkeeping after them
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const uint32_t a_s = smem_u32(smem);
-    const uint32_t b_s = a_s + kStages * kStageABytes;
-    const uint32_t w_s = b_s + kStages * kStageBBytes;            // packed-weight buffers
-    const uint32_t d_s = w_s + kWBufs * kWBufBytes;               // Q6_K d groups, one buffer per chunk parity
-    GemmSmem *sm = reinterpret_cast<GemmSmem *>(smem + kStages * (kStageABytes + kStageBBytes) + kWBufs * kWBufBytes + 2 * kDBufBytes);
+    const uint32_t b_s = a_s + kAStages * kStageABytes;
+    const uint32_t w_s = b_s + SB_ * kStageBBytes;                // packed-weight buffers
+    const uint32_t d_s = w_s + kWBufs * WBUF;                     // Q6_K d groups, one buffer per chunk parity
+    GemmSmem *sm = reinterpret_cast<GemmSmem *>(smem + smem_data_bytes(QT));
     const uint32_t wfull_s = smem_u32(sm->wfull), wempty_s = smem_u32(sm->wempty);
-    const uint32_t full_s = smem_u32(sm->full), empty_s = smem_u32(sm->empty);
+    const uint32_t afull_s = smem_u32(sm->afull), aempty_s = smem_u32(sm->aempty);
+    const uint32_t bfull_s = smem_u32(sm->bfull), bempty_s = smem_u32(sm->bempty);
     const uint32_t tfull_s = smem_u32(sm->tmem_full), tempty_s = smem_u32(sm->tmem_empty);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n_tiles_total = p.m_tiles * p.n_tiles;
-    const int ksteps = p.Kpad / BK;
+    const int ksteps = p.nsb * 4;                 // K-steps per tile: four per 256-weight record
+    const int chunks_per_tile = (p.nsb + kChunkRecs - 1) / kChunkRecs;
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < kStages; ++i) {
-            mbar_init(full_s + 8 * i, kDequantWarps + 1);
-            mbar_init(empty_s + 8 * i, 1);
+        for (int i = 0; i < kAStages; ++i) {
+            mbar_init(afull_s + 8 * i, kDequantWarps / 4);     // the four warps of one unit group
+            mbar_init(aempty_s + 8 * i, 1);
+        }
+        for (int i = 0; i < SB_; ++i) {
+            mbar_init(bfull_s + 8 * i, 1);
+            mbar_init(bempty_s + 8 * i, 1);
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(tfull_s + 8 * i, 1);
@@ -303,6 +390,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const GemmParams p
             mbar_init(wempty_s + 8 * i, kDequantWarps);
         }
         sm->abort = 0;
+        sm->wait_ns = (p.debug >> 12) ? (p.debug >> 12) : 40;
         mbar_fence_init();
         fence_proxy_async();
     }
@@ -316,106 +404,172 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const GemmParams p
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t *>(&sm->tmem_base);
 
     if (warp == 0) {
-        // ===== TMA producer: activation tiles and packed weight records ============================
+        // ===== TMA producer: activation tiles ======================================================
         if (lane == 0) {
             const uint32_t bytes = (uint32_t)p.bn * BK * 2;
-            constexpr int REC = rec_bytes(QT);
-            int it = 0, rs = 0;     // K-steps and record-steps issued so far (rings run across tiles)
+            int it = 0;             // K-steps issued so far (the ring runs across tiles)
             bool ok = true;
             for (int tile = blockIdx.x; tile < n_tiles_total && ok; tile += gridDim.x) {
-                const int tn = tile / p.m_tiles, tm = tile % p.m_tiles;
-                for (int ks = 0; ks < ksteps && ok; ++ks, ++it) {
-                    if ((ks & 3) == 0) {
-                        // one superblock record of each of the tile's 128 rows (four K-steps' worth)
-                        const int sb = ks >> 2, c = sb >> 3, s_in = sb & 7;
-                        const int wb = rs % kWBufs;
-                        ok = wait_or_abort(wempty_s + 8 * wb, ((rs / kWBufs) & 1) ^ 1, sm, p.status);
-                        if (!ok) break;
-                        const bool tail = c >= p.nchunks_full;
-                        uint32_t tx = BM * REC;
-                        if (QT == QT_Q6_K && s_in == 0) tx += BM * 16;
-                        mbar_expect_tx(wfull_s + 8 * wb, tx);
-                        tma_load_4d(w_s + wb * kWBufBytes, tail ? &wtail : &wmap, s_in * (REC / 4), 0, tail ? 0 : c,
-                                    tn * (BM / kRowGroup), wfull_s + 8 * wb);
-                        if (QT == QT_Q6_K && s_in == 0) {
-                            const int nrec = tail ? (p.nsb - c * kChunkRecs) : kChunkRecs;
-                            tma_load_4d(d_s + (c & 1) * kDBufBytes, tail ? &dtail : &dmap, nrec * (REC / 4), 0, tail ? 0 : c,
-                                        tn * (BM / kRowGroup), wfull_s + 8 * wb);
-                        }
-                        ++rs;
-                    }
-                    const int stage = it % kStages;
-                    ok = wait_or_abort(empty_s + 8 * stage, ((it / kStages) & 1) ^ 1, sm, p.status);
+                const int tm = tile % p.m_tiles;
+                for (int ks = 0; ks < ksteps; ++ks, ++it) {
+                    const int stage = it % SB_;
+                    if (p.debug & 2048) continue;
+                    ok = wait_or_abort<true>(bempty_s + 8 * stage, ((it / SB_) & 1) ^ 1, sm, p.status);
                     if (!ok) break;
-                    mbar_expect_tx(full_s + 8 * stage, bytes);
-                    tma_load_2d(b_s + stage * kStageBBytes, &xmap, ks * BK, tm * p.bn, full_s + 8 * stage);
+                    if (p.debug & 1) {
+                        mbar_arrive(bfull_s + 8 * stage);
+                        continue;
+                    }
+                    mbar_expect_tx(bfull_s + 8 * stage, bytes);
+                    tma_load_2d(b_s + stage * kStageBBytes, &xmap, ks * BK, tm * p.bn, bfull_s + 8 * stage);
+                }
+            }
+        }
+    } else if (warp == 2) {
+        // ===== TMA producer: packed weight records =================================================
+        if (lane == 0) {
+            int rs = 0, tcount = 0;   // records issued so far, tiles started
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < n_tiles_total && ok; tile += gridDim.x, ++tcount) {
+                const int tn = tile / p.m_tiles;
+                for (int sb = 0; sb < p.nsb; ++sb, ++rs) {
+                    // one record of each of the tile's 128 rows (four K-steps' worth)
+                    const int c = sb >> 3, s_in = sb & 7;
+                    const int wb = rs % kWBufs;
+                    ok = wait_or_abort<true>(wempty_s + 8 * wb, ((rs / kWBufs) & 1) ^ 1, sm, p.status);
+                    if (!ok) break;
+                    if (p.debug & 4) {
+                        mbar_arrive(wfull_s + 8 * wb);
+                        continue;
+                    }
+                    const bool tail = c >= p.nchunks_full;
+                    uint32_t tx = BM * REC;
+                    if (QT == QT_Q6_K && s_in == 0) tx += BM * 16;
+                    mbar_expect_tx(wfull_s + 8 * wb, tx);
+                    tma_load_4d(w_s + wb * WBUF, tail ? &wtail : &wmap, s_in * (REC / 4), 0, tail ? 0 : c,
+                                tn * (BM / kRowGroup), wfull_s + 8 * wb);
+                    if (QT == QT_Q6_K && s_in == 0) {
+                        // the chunk's fp16 d values: the buffer of the chunk before last is free once the
+                        // record two back has been read, which the wait above has established
+                        const int nrec = tail ? (p.nsb - c * kChunkRecs) : kChunkRecs;
+                        const int cs = tcount * chunks_per_tile + c;
+                        tma_load_4d(d_s + (cs & 1) * kDBufBytes, tail ? &dtail : &dmap, nrec * (REC / 4), 0, tail ? 0 : c,
+                                    tn * (BM / kRowGroup), wfull_s + 8 * wb);
+                    }
                 }
             }
         }
     } else if (warp == 1) {
         // ===== MMA issuer ==========================================================================
         if (lane == 0) {
-            const uint32_t idesc = (1u << 4) | ((F16 ? 0u : 1u) << 7) | ((F16 ? 0u : 1u) << 10) |   // C fp32; A and B both fp16 or both bf16
+            const uint32_t idesc = (1u << 4) |                                   // C fp32; A and B fp16 (format 0)
                                     ((uint32_t)(p.bn >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
             int it = 0, tcount = 0;
+            long long tw_b = 0, tw_a = 0, t_iss = 0, tw_t = 0, t_com = 0;
+            bool rdy_a = false, rdy_b = false;
+            const bool prof = (p.debug & 256) != 0;
+            const long long t_begin = clock64();
             for (int tile = blockIdx.x; tile < n_tiles_total; tile += gridDim.x, ++tcount) {
                 const int buf = tcount & 1;
-                bool ok = wait_or_abort(tempty_s + 8 * buf, ((tcount >> 1) & 1) ^ 1, sm, p.status);
+                long long c0 = prof ? clock64() : 0;
+                bool ok = wait_or_abort<true>(tempty_s + 8 * buf, ((tcount >> 1) & 1) ^ 1, sm, p.status);
+                if (prof) tw_t += clock64() - c0;
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + buf * 256;
                 for (int ks = 0; ks < ksteps; ++ks, ++it) {
-                    const int stage = it % kStages;
-                    ok = wait_or_abort(full_s + 8 * stage, (it / kStages) & 1, sm, p.status);
+                    const int sa = it % kAStages, sb = it % SB_;
+                    if (prof) c0 = clock64();
+                    // the probes for this K-step were issued before the previous one's MMAs
+                    ok = rdy_b || (p.debug & 2048) || wait_or_abort<true>(bfull_s + 8 * sb, (it / SB_) & 1, sm, p.status);
+                    long long c1 = prof ? clock64() : 0;
+                    ok = ok && (rdy_a || (p.debug & 1024) || wait_or_abort<true>(afull_s + 8 * sa, (it / kAStages) & 1, sm, p.status));
+                    long long c2 = prof ? clock64() : 0;
+                    if (prof) tw_b += c1 - c0, tw_a += c2 - c1;
                     if (!ok) break;
-                    tc_fence_after();
-                    const uint64_t adesc = make_desc_sw128(a_s + stage * kStageABytes);
-                    const uint64_t bdesc = make_desc_sw128(b_s + stage * kStageBBytes);
+                    if (p.debug & 512) tc_fence_after();
+                    {   // probe the next K-step's barriers now; the answers arrive while the MMAs issue
+                        const int nx = it + 1;
+                        rdy_b = mbar_test_wait(bfull_s + 8 * (nx % SB_), (nx / SB_) & 1);
+                        rdy_a = mbar_test_wait(afull_s + 8 * (nx % kAStages), (nx / kAStages) & 1);
+                    }
+                    const uint64_t adesc = make_desc_sw128(a_s + sa * kStageABytes);
+                    const uint64_t bdesc = make_desc_sw128(b_s + sb * kStageBBytes);
+                    if (!(p.debug & 8))
 #pragma unroll
-                    for (int kk = 0; kk < BK / 16; ++kk)   // 16 bf16 = 32 bytes = +2 in the address field
-                        umma_bf16(d_tmem, adesc + 2 * kk, bdesc + 2 * kk, idesc, (ks | kk) != 0);
-                    umma_commit(empty_s + 8 * stage);      // the stage may be refilled once these finish
+                    for (int kk = 0; kk < BK / 16; ++kk)   // 16 fp16 = 32 bytes = +2 in the address field
+                        umma_f16(d_tmem, adesc + 2 * kk, bdesc + 2 * kk, idesc, (ks | kk) != 0);
+                    if (p.debug & 64) {
+                        mbar_arrive(aempty_s + 8 * sa);
+                        mbar_arrive(bempty_s + 8 * sb);
+                        continue;
+                    }
+                    long long c3 = prof ? clock64() : 0;
+                    if (!(p.debug & 1024)) umma_commit(aempty_s + 8 * sa);        // both stages may be refilled once these finish
+                    if (!(p.debug & 2048)) umma_commit(bempty_s + 8 * sb);
+                    if (prof) t_iss += c3 - c2, t_com += clock64() - c3;
                 }
                 if (!ok) break;
                 umma_commit(tfull_s + 8 * buf);            // accumulator complete
             }
+            if (prof && blockIdx.x == 0 && it > 0)
+                printf("mma thread: %d k-steps, total %lld clk/k-step; wait B %lld, wait A %lld, probes+mma issue %lld, commits %lld, wait tmem %lld per tile\n",
+                       it, (clock64() - t_begin) / it, tw_b / it, tw_a / it, t_iss / it, t_com / it, tw_t / (tcount ? tcount : 1));
         }
-    } else if (warp < 2 + kDequantWarps) {
+    } else if (warp < kFirstEpiWarp) {
         // ===== dequant producers: weight tiles =====================================================
-        const int t = threadIdx.x - 64;
-        const int r = t & (BM - 1), qd = t >> 7;
+        const int t = threadIdx.x - kFirstDequantWarp * 32;
+        const int r = t & (BM - 1), j = t >> 7;      // weight row of the tile; 64-weight unit of each record
         const int r7 = r & 7;
         const uint32_t row_off = (r >> 3) * 1024 + r7 * 128;
-        constexpr int REC = rec_bytes(QT);
-        int it = 0, rs = 0;
+        // Records are taken one ahead: the bytes of record rs + 1 move into registers before record rs
+        // is dequantized, so its buffer goes back to the TMA producer a whole record (four K-steps)
+        // before the ring would otherwise allow, and the refill latency stays off the critical path.
+        const int my_tiles = blockIdx.x < n_tiles_total ? (n_tiles_total - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+        const int total = my_tiles * p.nsb;
         bool ok = true;
-        for (int tile = blockIdx.x; tile < n_tiles_total && ok; tile += gridDim.x) {
-            int wb = 0;
-            for (int ks = 0; ks < ksteps; ++ks, ++it) {
-                const int j = ks & 3;
-                if (j == 0) {   // a new record: wait for its bytes
-                    wb = rs % kWBufs;
-                    if (lane == 0) ok = wait_or_abort(wfull_s + 8 * wb, (rs / kWBufs) & 1, sm, p.status);
-                    ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
-                    if (!ok) break;
-                }
-                const int sb = ks >> 2;
-                Packed<QT> cur;
-                cur.load(w_s + wb * kWBufBytes + r * REC, d_s + ((sb >> 3) & 1) * kDBufBytes + r * 16 + 2 * (sb & 7), j, qd);
-                const int stage = it % kStages;
-                if (lane == 0) ok = wait_or_abort(empty_s + 8 * stage, ((it / kStages) & 1) ^ 1, sm, p.status);
-                ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
+        auto fetch = [&](int rs, Unit<QT> &u) {
+            const int wb = rs % kWBufs;
+            if (lane == 0) ok = wait_or_abort<true>(wfull_s + 8 * wb, (rs / kWBufs) & 1, sm, p.status);
+            ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
+            if (!ok) return;
+            const int tcount = rs / p.nsb, sb = rs - tcount * p.nsb;
+            const int cs = tcount * chunks_per_tile + (sb >> 3);
+            u.load(w_s + wb * WBUF + r * REC, d_s + (cs & 1) * kDBufBytes + r * 16 + 2 * (sb & 7), j);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(wempty_s + 8 * wb);     // the record is in registers
+        };
+        Unit<QT> cur, nxt;
+        const bool prof = (p.debug & 256) != 0;
+        long long t_fetch = 0, t_wait = 0, t_emit = 0;
+        const long long t_begin = clock64();
+        if (total > 0) fetch(0, cur);
+        for (int rs = 0; rs < total && ok; ++rs) {
+            long long c0 = prof ? clock64() : 0;
+            if (rs + 1 < total) {
+                fetch(rs + 1, nxt);
                 if (!ok) break;
-                cur.template emit<F16>(j, qd, a_s + stage * kStageABytes + row_off, r7);
-                fence_proxy_async();       // generic-proxy stores -> visible to the tensor core's reads
-                __syncwarp();
-                if (lane == 0) {
-                    mbar_arrive(full_s + 8 * stage);
-                    if (j == 3 || ks == ksteps - 1) mbar_arrive(wempty_s + 8 * wb);   // record consumed
-                }
-                if (j == 3 || ks == ksteps - 1) ++rs;
             }
+            // the arithmetic happens while the tensor core still reads the stage's previous contents:
+            // once the stage is free only the eight stores remain before it can be handed over
+            uint32_t o[32];
+            if (!(p.debug & 2)) cur.convert(j, o);
+            long long c1 = prof ? clock64() : 0;
+            const int stage = j;       // K-step 4 rs + j: kAStages == 4, so the group owns this stage
+            if (lane == 0 && !(p.debug & 1024)) ok = wait_or_abort<true>(aempty_s + 8 * stage, (rs & 1) ^ 1, sm, p.status);
+            ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
+            if (!ok) break;
+            long long c2 = prof ? clock64() : 0;
+            if (!(p.debug & 2)) store_row(o, a_s + stage * kStageABytes + row_off, r7);
+            if (!(p.debug & 32)) fence_proxy_async();       // generic-proxy stores -> visible to the tensor core's reads
+            __syncwarp();
+            if (lane == 0 && !(p.debug & 1024)) mbar_arrive(afull_s + 8 * stage);
+            cur = nxt;
+            if (prof) t_fetch += c1 - c0, t_wait += c2 - c1, t_emit += clock64() - c2;
         }
+        if (prof && blockIdx.x == 0 && (t & 127) == 0 && total > 0)
+            printf("dequant group %d: %d records, total %lld clk/record; fetch+convert %lld, wait stage %lld, store+fence+arrive %lld\n", j, total,
+                   (clock64() - t_begin) / total, t_fetch / total, t_wait / total, t_emit / total);
     } else {
         // ===== epilogue ============================================================================
         const int q = warp & 3;            // TMEM lane quadrant this warp may read
@@ -423,13 +577,13 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const GemmParams p
         for (int tile = blockIdx.x; tile < n_tiles_total; tile += gridDim.x, ++tcount) {
             const int tn = tile / p.m_tiles, tm = tile % p.m_tiles;
             const int buf = tcount & 1;
-            bool ok = wait_or_abort(tfull_s + 8 * buf, (tcount >> 1) & 1, sm, p.status);
+            bool ok = wait_or_abort<false>(tfull_s + 8 * buf, (tcount >> 1) & 1, sm, p.status);
             ok = __all_sync(0xFFFFFFFFu, ok);
             if (!ok) break;
             tc_fence_after();
             const int n = tn * BM + q * 32 + lane;
             const int m0 = tm * p.bn;
-            for (int c0 = 0; c0 < p.bn; c0 += 32) {
+            for (int c0 = 0; c0 < ((p.debug & 16) ? 0 : p.bn); c0 += 32) {
                 uint32_t v[32];
                 tmem_ld32(tmem_base + buf * 256 + ((uint32_t)(q * 32) << 16) + c0, v);
                 tmem_ld_wait();
@@ -463,10 +617,18 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const GemmParams p
     }
 }
 
-// Activations -> the 16-bit float type the weights are dequantized to (both tensor-core operands
-// must share one format).  fp16 is the default: bf16 activations convert exactly unless they
-// exceed fp16's range, where they saturate to +-65504; fp32 activations round to nearest even.
-template <bool F16, bool SRC_BF16>
+// Activations -> fp16, the format the weights are dequantized to (both tensor-core operands must
+// share one format).  bf16 activations convert exactly unless they exceed fp16's range, where they
+// saturate to +-65504; fp32 activations round to nearest even.
+__device__ __forceinline__ uint32_t to_h2_sat(float lo, float hi) {
+    lo = fminf(fmaxf(lo, -65504.f), 65504.f);   // NaN passes through both
+    hi = fminf(fmaxf(hi, -65504.f), 65504.f);
+    uint32_t r;
+    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+
+template <bool SRC_BF16>
 __global__ void convert_x_kernel(const void *__restrict__ src, long long lds, uint16_t *__restrict__ dst,
                                  long long ldd, int M, int K) {
     const long long total = (long long)M * K;
@@ -475,14 +637,37 @@ __global__ void convert_x_kernel(const void *__restrict__ src, long long lds, ui
         float v;
         if (SRC_BF16) v = __bfloat162float(reinterpret_cast<const __nv_bfloat16 *>(src)[m * lds + k]);
         else v = reinterpret_cast<const float *>(src)[m * lds + k];
-        uint16_t o;
-        if (F16) {
-            v = fminf(fmaxf(v, -65504.f), 65504.f);   // NaN passes through both
-            o = __half_as_ushort(__float2half_rn(v));
+        dst[m * ldd + k] = (uint16_t)to_h2_sat(v, 0.f);
+    }
+}
+
+// eight elements per thread with 16-byte accesses: K a multiple of 8, source rows 16-byte aligned
+template <bool SRC_BF16>
+__global__ void convert_x_vec8_kernel(const void *__restrict__ src, long long lds, uint16_t *__restrict__ dst,
+                                      long long ldd, int M, int K8) {
+    const unsigned total = (unsigned)M * (unsigned)K8;
+    for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+        const unsigned m = i / (unsigned)K8, c = i - m * (unsigned)K8;
+        float f[8];
+        if (SRC_BF16) {
+            const uint4 v = *reinterpret_cast<const uint4 *>(reinterpret_cast<const uint16_t *>(src) + (long long)m * lds + 8 * c);
+            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                f[2 * e] = __uint_as_float(w[e] << 16);
+                f[2 * e + 1] = __uint_as_float(w[e] & 0xFFFF0000u);
+            }
         } else {
-            o = __bfloat16_as_ushort(__float2bfloat16_rn(v));
+            const float4 a = *reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(src) + (long long)m * lds + 8 * c);
+            const float4 b = *reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(src) + (long long)m * lds + 8 * c + 4);
+            f[0] = a.x, f[1] = a.y, f[2] = a.z, f[3] = a.w, f[4] = b.x, f[5] = b.y, f[6] = b.z, f[7] = b.w;
         }
-        dst[m * ldd + k] = o;
+        uint4 o;
+        o.x = to_h2_sat(f[0], f[1]);
+        o.y = to_h2_sat(f[2], f[3]);
+        o.z = to_h2_sat(f[4], f[5]);
+        o.w = to_h2_sat(f[6], f[7]);
+        *reinterpret_cast<uint4 *>(dst + (long long)m * ldd + 8 * c) = o;
     }
 }
 
@@ -508,10 +693,11 @@ struct GemmMaps {
     CUtensorMap x, w, wtail, d, dtail;
 };
 
-template <int QT, bool F16>
+template <int QT>
 cudaError_t launch_gemm(const GemmParams &p, const GemmMaps &m, int grid, cudaStream_t st) {
-    auto kern = gemm_tc_kernel<QT, F16>;
-    const size_t smem = kStages * (kStageABytes + kStageBBytes) + kWBufs * kWBufBytes + 2 * kDBufBytes + sizeof(GemmSmem) + 1024;
+    auto kern = gemm_tc_kernel<QT>;
+    constexpr size_t smem = smem_data_bytes(QT) + sizeof(GemmSmem) + 1024;
+    static_assert(smem <= 232448, "shared-memory plan exceeds the 227 KB a block may use");
     static int configured_dev = -1;
     int dev = 0;
     cudaGetDevice(&dev);
@@ -522,6 +708,23 @@ cudaError_t launch_gemm(const GemmParams &p, const GemmMaps &m, int grid, cudaSt
     }
     kern<<<grid, kThreads, smem, st>>>(p, m.x, m.w, m.wtail, m.d, m.dtail);
     return cudaGetLastError();
+}
+
+// Token-tile width: with more tiles than SMs the last wave is partly idle, so a slightly narrower
+// tile that fills the waves evenly can finish sooner.  Cost model: waves x (width + 90), the
+// constant standing for the part of a K-step's time that does not shrink with the tile (measured:
+// 0.46 us per K-step at 128 tokens, 0.69 us at 240); ties go to the wider tile.
+int pick_bn(int M, int n_tiles, int sms, int widest) {
+    if (M <= widest) return ((M + 15) / 16) * 16;
+    int best = widest;
+    long long best_cost = -1;
+    for (int bn = widest; bn >= 128; bn -= 16) {
+        const long long tiles = (long long)((M + bn - 1) / bn) * n_tiles;
+        const long long waves = (tiles + sms - 1) / sms;
+        const long long cost = waves * (bn + 90);
+        if (best_cost < 0 || cost < best_cost) best_cost = cost, best = bn;
+    }
+    return best;
 }
 
 // tensor map over the packed records of the chunks [c0, c0 + nc) of every row:
@@ -543,23 +746,27 @@ bool encode_weight_map(EncodeTiledFn enc, CUtensorMap *map, const uint8_t *w, in
 
 size_t gemm_x_scratch_bytes(int M, int K) { return ((size_t)M * ((K + 7) & ~7) * 2 + 255) & ~size_t(255); }
 
-cudaError_t gemm_convert_x(const void *x, int x_is_bf16, long long ldx, void *scratch, int M, int K, int to_bf16,
-                           cudaStream_t st) {
+cudaError_t gemm_convert_x(const void *x, int x_is_bf16, long long ldx, void *scratch, int M, int K, cudaStream_t st) {
     const long long ldd = (K + 7) & ~7;
-    const long long total = (long long)M * K;
-    const int blocks = (int)std::min<long long>((total + 255) / 256, 148 * 16);
     uint16_t *dst = reinterpret_cast<uint16_t *>(scratch);
-    if (to_bf16) {
-        if (x_is_bf16) convert_x_kernel<false, true><<<blocks, 256, 0, st>>>(x, ldx, dst, ldd, M, K);
-        else convert_x_kernel<false, false><<<blocks, 256, 0, st>>>(x, ldx, dst, ldd, M, K);
+    const int esz = x_is_bf16 ? 2 : 4;
+    const bool vec = K % 8 == 0 && !(reinterpret_cast<uintptr_t>(x) & 15) && (ldx * esz) % 16 == 0 &&
+                     (long long)M * (K / 8) < (1ll << 31);
+    if (vec) {
+        const long long total = (long long)M * (K / 8);
+        const int blocks = (int)std::min<long long>((total + 255) / 256, 148 * 8);
+        if (x_is_bf16) convert_x_vec8_kernel<true><<<blocks, 256, 0, st>>>(x, ldx, dst, ldd, M, K / 8);
+        else convert_x_vec8_kernel<false><<<blocks, 256, 0, st>>>(x, ldx, dst, ldd, M, K / 8);
     } else {
-        if (x_is_bf16) convert_x_kernel<true, true><<<blocks, 256, 0, st>>>(x, ldx, dst, ldd, M, K);
-        else convert_x_kernel<true, false><<<blocks, 256, 0, st>>>(x, ldx, dst, ldd, M, K);
+        const long long total = (long long)M * K;
+        const int blocks = (int)std::min<long long>((total + 255) / 256, 148 * 16);
+        if (x_is_bf16) convert_x_kernel<true><<<blocks, 256, 0, st>>>(x, ldx, dst, ldd, M, K);
+        else convert_x_kernel<false><<<blocks, 256, 0, st>>>(x, ldx, dst, ldd, M, K);
     }
     return cudaGetLastError();
 }
 
-// x: 16-bit float activations [M][K] (fp16, or bf16 when a.weights_bf16) with leading dimension ldx
+// x: fp16 activations [M][K] with leading dimension ldx
 // (elements); 16-byte aligned rows.
 cudaError_t gemm_launch(const GemmLaunch &a, cudaStream_t st) {
     if (a.M < 1 || a.N < 1 || a.K < 1) return cudaErrorInvalidValue;
@@ -578,11 +785,13 @@ cudaError_t gemm_launch(const GemmLaunch &a, cudaStream_t st) {
     p.ldy = a.ldy;
     p.y_is_bf16 = a.y_is_bf16;
     p.M = a.M;
-    p.bn = a.M >= 256 ? 256 : ((a.M + 15) / 16) * 16;
-    if (a.bn_override >= 16 && a.bn_override <= 256 && a.bn_override % 16 == 0) p.bn = a.bn_override;
-    p.m_tiles = (a.M + p.bn - 1) / p.bn;
     p.n_tiles = (a.N + BM - 1) / BM;
+    const int widest = bn_max(a.qt);
+    p.bn = pick_bn(a.M, p.n_tiles, a.sm_count, widest);
+    if (a.bn_override >= 16 && a.bn_override <= widest && a.bn_override % 16 == 0) p.bn = a.bn_override;
+    p.m_tiles = (a.M + p.bn - 1) / p.bn;
     p.status = a.status;
+    p.debug = a.debug;
 
     GemmMaps maps;
     CUtensorMap &map = maps.x;
@@ -590,7 +799,7 @@ cudaError_t gemm_launch(const GemmLaunch &a, cudaStream_t st) {
     const cuuint64_t gstride[1] = {(cuuint64_t)a.ldx * 2};
     const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)p.bn};
     const cuuint32_t estride[2] = {1, 1};
-    CUresult r = enc(&map, a.weights_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(a.x), gdim, gstride, box, estride,
+    CUresult r = enc(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(a.x), gdim, gstride, box, estride,
                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
@@ -610,18 +819,10 @@ cudaError_t gemm_launch(const GemmLaunch &a, cudaStream_t st) {
 
     const int tiles = p.m_tiles * p.n_tiles;
     const int grid = std::min(tiles, a.sm_count);
-    if (a.weights_bf16) {
-        switch (a.qt) {
-        case QT_Q4_K: return launch_gemm<QT_Q4_K, false>(p, maps, grid, st);
-        case QT_Q6_K: return launch_gemm<QT_Q6_K, false>(p, maps, grid, st);
-        case QT_Q8_0: return launch_gemm<QT_Q8_0, false>(p, maps, grid, st);
-        default: return cudaErrorInvalidValue;
-        }
-    }
     switch (a.qt) {
-    case QT_Q4_K: return launch_gemm<QT_Q4_K, true>(p, maps, grid, st);
-    case QT_Q6_K: return launch_gemm<QT_Q6_K, true>(p, maps, grid, st);
-    case QT_Q8_0: return launch_gemm<QT_Q8_0, true>(p, maps, grid, st);
+    case QT_Q4_K: return launch_gemm<QT_Q4_K>(p, maps, grid, st);
+    case QT_Q6_K: return launch_gemm<QT_Q6_K>(p, maps, grid, st);
+    case QT_Q8_0: return launch_gemm<QT_Q8_0>(p, maps, grid, st);
     default: return cudaErrorInvalidValue;
     }
 }
@@ -657,7 +858,7 @@ cudaError_t gemm_launch_static(GemmLaunch a, int x_is_bf16, cudaStream_t st) {
     }
     const long long ldd = (a.K + 7) & ~7;
     if ((size_t)a.M * (size_t)ldd > gemm_static_scratch_elems()) return cudaErrorInvalidValue;
-    e = gemm_convert_x(a.x, x_is_bf16, a.ldx, dev_ptr[dev], a.M, a.K, a.weights_bf16, st);
+    e = gemm_convert_x(a.x, x_is_bf16, a.ldx, dev_ptr[dev], a.M, a.K, st);
     if (e != cudaSuccess) return e;
     a.x = dev_ptr[dev];
     a.ldx = ldd;

@@ -68,7 +68,7 @@ struct GemmLaunch {
     int qt;
     const uint8_t *w;        // streaming-layout weights
     int N, K, Kpad;
-    const void *x;           // fp16 (bf16 if weights_bf16) activations [M][K], rows 16-byte aligned
+    const void *x;           // fp16 activations [M][K], rows 16-byte aligned
     long long ldx;
     int M;
     void *y;
@@ -77,12 +77,11 @@ struct GemmLaunch {
     int *status;
     int sm_count;
     int bn_override;         // 0 = choose the token tile
-    int weights_bf16;        // 1 = both operands bf16 instead of fp16 (wider range, 8x the rounding error)
+    int debug;               // timing experiments (see GemmParams::debug); 0 in production
 };
 size_t gemm_x_scratch_bytes(int M, int K);
-// activations (bf16 or fp32) -> fp16 (or bf16) rows of ((K + 7) & ~7) elements in `scratch`
-cudaError_t gemm_convert_x(const void *x, int x_is_bf16, long long ldx, void *scratch, int M, int K, int to_bf16,
-                           cudaStream_t st);
+// activations (bf16 or fp32) -> fp16 rows of ((K + 7) & ~7) elements in `scratch`
+cudaError_t gemm_convert_x(const void *x, int x_is_bf16, long long ldx, void *scratch, int M, int K, cudaStream_t st);
 cudaError_t gemm_launch(const GemmLaunch &a, cudaStream_t st);
 // the same product with the activation copy in the library's built-in scratch array: a.x / a.ldx
 // describe the caller's activations (bf16 or fp32), nothing is allocated
