@@ -135,6 +135,8 @@ def run_reference(args):
     rank, _, world = dist_env()
     if rank != 0:
         return
+    # torchrun pins OMP_NUM_THREADS to 1 for its workers; this arm is the CPU path on all host cores
+    os.environ["OMP_NUM_THREADS"] = str(os.cpu_count() or 1)
     from oracle import oracle as orc  # the CPU restatement of the reference's path, timed here
 
     orc.build()
@@ -391,10 +393,17 @@ def run_b200(args):
                 "pinned host activations -> device, b200q_plan_run (whole step), results -> pinned host, synchronize"),
     }
 
+    # Teardown: the captured graph holds NCCL kernels, so it goes before anything of the process
+    # group does; ranks leave together, and they leave through os._exit so that no destructor can
+    # wait on a peer that has already gone.
+    used_graph = graph is not None
+    graph = None
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
     if rank != 0:
-        if dist is not None:
-            dist.destroy_process_group()
-        return
+        sys.stdout.flush()
+        os._exit(0)
 
     peak, peak_src = peaks()
     # dominant (only) kernel: stream_kernel<M=1, Q4_K> running the step's 64 projection jobs;
@@ -435,12 +444,14 @@ def run_b200(args):
         "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "u8 x s16 integer block dots (dp4a), fp32 accumulate", "data": "synthetic",
         "config": workload_config(world), "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e,
-        "gpu_launches": launches_per_step * args.steps, "cuda_graph": graph is not None,
+        "gpu_launches": launches_per_step * args.steps, "cuda_graph": used_graph,
         "clocks": clocks.summary(),
     }
     print(json.dumps(line))
+    sys.stdout.flush()
     if dist is not None:
-        dist.destroy_process_group()
+        os._exit(0)
+
 
 # ------------------------------------------------------------------------------------------------
 # secondary line: the prefill GEMM (configs[3]) — tcgen05 route, reported in TFLOP/s
@@ -471,6 +482,7 @@ def run_prefill(args):
            "parallelism": "single"}
 
     if args.impl == "reference":
+        os.environ["OMP_NUM_THREADS"] = str(os.cpu_count() or 1)
         from oracle import oracle as orc
 
         orc.build()
@@ -593,6 +605,10 @@ def main():
     ap.add_argument("--workload", choices=["decode", "prefill"], default="decode",
                     help="decode = the headline Q4_K GEMV step; prefill = the M=2048 Q4_K GEMM (secondary line, TFLOP/s)")
     args = ap.parse_args()
+    # last resort against a stuck collective or teardown: never hold a GPU box for more than 20 minutes
+    wd = threading.Timer(1200.0, lambda: os._exit(3))
+    wd.daemon = True
+    wd.start()
     global LAYERS
     LAYERS = max(1, min(args.layers, 32))
     if args.workload == "prefill":
