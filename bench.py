@@ -36,6 +36,12 @@ HIDDEN, INTER = 4096, 14336
 Q4_K = 12
 FALLBACK_HBM_GBS = 6650.0
 FALLBACK_TFLOPS = 1400.0
+# DRAM traffic of the dominant kernels from one ncu capture each (dram__bytes_read.sum +
+# dram__bytes_write.sum per launch; summaries under profiles/).  The decode figure was captured on a
+# 4-layer launch and is proportional to the layers a launch streams, so it is kept as a ratio to
+# the algorithmic bytes; a prefill launch is one whole product whatever the number of copies.
+NCU_DECODE_TRAFFIC_PER_ALGORITHMIC_BYTE = 1.009
+NCU_PREFILL_TRAFFIC_BYTES_PER_LAUNCH = 74.4e6
 
 
 def peaks():
@@ -186,6 +192,12 @@ def workload_config(n_gpus):
     }
 
 
+def mark_diagnostic(line, args):
+    if getattr(args, "no_exchange", False) and line.get("n_gpus", 1) > 1:
+        line["invalid"] = "diagnostic run without the all-reduce: partial sums only"
+    return line
+
+
 # ------------------------------------------------------------------------------------------------
 # the CUDA arm
 # ------------------------------------------------------------------------------------------------
@@ -211,6 +223,11 @@ def run_b200(args):
     from magnitude_b200 import ggml_quant as gq
 
     be = mb.Backend(local_rank)
+    # row-parallel sums: the library's one-kernel peer-memory all-reduce (NVLink stores and loads);
+    # --nccl times torch.distributed's NCCL all-reduce in its place
+    use_peer = world > 1 and not args.nccl
+    if use_peer:
+        be.peer_setup(dist)
     gate_h, up_h, down_h = make_host_layer()
     if world > 1:
         g0 = be.upload_shard(Q4_K, gate_h, INTER, HIDDEN, mb.SPLIT_COLUMN, rank, world, 256)
@@ -242,19 +259,30 @@ def run_b200(args):
     # One decode plan holds the whole step: 64 projection jobs run by one persistent launch, the
     # weights of job i+1 streaming while job i is reduced and stored.  Under tensor parallelism the
     # all-reduce after every down projection cuts the step into one two-job plan per layer.
+    fused = use_peer and not args.unfused and not args.per_launch and not args.no_exchange
     if args.per_launch:
         plans = None
         launches_per_step = 2 * LAYERS
-    elif world == 1:
+    elif world == 1 or fused:
         jobs = []
         for l in range(LAYERS):
             jobs.append(([gates[l], ups[l]], x_hd, [y_g, y_u]))
             jobs.append(([downs[l]], x_id, [y_d]))
-        plans = [be.plan(jobs)]
+        # tensor parallel: the down projections' partial sums are added up over the ranks inside the launch
+        plans = [be.plan(jobs, sum_ranks=[fused and (i % 2 == 1) for i in range(len(jobs))])]
         launches_per_step = 1
     else:
         plans = [be.plan([([gates[l], ups[l]], x_hd, [y_g, y_u]), ([downs[l]], x_id, [y_d])]) for l in range(LAYERS)]
         launches_per_step = LAYERS
+
+    def sum_ranks():
+        if args.no_exchange or fused:
+            return
+        if use_peer:
+            be.allreduce(y_d, stream=stream)
+        else:
+            with torch.cuda.stream(stream):
+                dist.all_reduce(y_d)
 
     def step_device():
         if plans is None:
@@ -262,14 +290,12 @@ def run_b200(args):
                 be.project_multi([gates[l], ups[l]], x_hd, outs=[y_g, y_u], stream=stream)
                 be.project(downs[l], x_id, out=y_d, stream=stream)
                 if world > 1:
-                    with torch.cuda.stream(stream):
-                        dist.all_reduce(y_d)
+                    sum_ranks()
         else:
             for pl in plans:
                 pl.run(stream=stream)
                 if world > 1:
-                    with torch.cuda.stream(stream):
-                        dist.all_reduce(y_d)
+                    sum_ranks()
 
     # capture one step in a CUDA graph (launch-bound inner loop); fall back to direct launches
     graph = None
@@ -343,8 +369,9 @@ def run_b200(args):
     xhd_e2e = torch.empty_like(x_hd)
     xid_e2e = torch.empty_like(x_id)
     if plans is not None:
-        if world == 1:
-            e2e_plans = [be.plan([j for l in range(LAYERS) for j in (([gates[l], ups[l]], xhd_e2e, [y_g, y_u]), ([downs[l]], xid_e2e, [y_d]))])]
+        if world == 1 or fused:
+            e2e_plans = [be.plan([j for l in range(LAYERS) for j in (([gates[l], ups[l]], xhd_e2e, [y_g, y_u]), ([downs[l]], xid_e2e, [y_d]))],
+                                 sum_ranks=[fused and (i % 2 == 1) for i in range(2 * LAYERS)])]
         else:
             e2e_plans = [be.plan([([gates[l], ups[l]], xhd_e2e, [y_g, y_u]), ([downs[l]], xid_e2e, [y_d])]) for l in range(LAYERS)]
 
@@ -363,8 +390,7 @@ def run_b200(args):
         for pl in e2e_plans:
             pl.run(stream=stream)
             if world > 1:
-                with torch.cuda.stream(stream):
-                    dist.all_reduce(y_d)
+                sum_ranks()
         with torch.cuda.stream(stream):
             yg_pin.copy_(y_g, non_blocking=True)
             yu_pin.copy_(y_u, non_blocking=True)
@@ -412,11 +438,15 @@ def run_b200(args):
     achieved = rank_bytes / (ms_step * 1e-3) / 1e9
     roofline = {
         "bound": "hbm", "kernel": "stream_kernel<M=1,Q4_K>", "achieved": achieved, "peak": peak, "unit": "GB/s",
-        "frac": achieved / peak, "peak_source": f"of {peak_src}", "traffic": None,
+        "frac": achieved / peak, "peak_source": f"of {peak_src}",
+        "traffic": NCU_DECODE_TRAFFIC_PER_ALGORITHMIC_BYTE * rank_bytes / launches_per_step,
+        "traffic_source": "ncu capture of a 4-layer launch, scaled by the bytes a launch streams",
         "bytes_per_launch": rank_bytes / launches_per_step,
         "us_per_launch": ms_step * 1e3 / launches_per_step,
         "note": "per-rank algorithmic bytes per step / per-step device time (CUDA events on the launch stream)"
-                + ("; includes the all-reduce after each down projection" if world > 1 else ""),
+                + (("; includes the sum over ranks of each down projection ("
+                    + ("peer-memory stores and loads inside the launch" if fused else "peer-memory kernel" if use_peer else "NCCL") + ")")
+                   if world > 1 else ""),
     }
 
     cpu_baseline = None
@@ -444,10 +474,10 @@ def run_b200(args):
         "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "u8 x s16 integer block dots (dp4a), fp32 accumulate", "data": "synthetic",
         "config": workload_config(world), "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e,
-        "gpu_launches": launches_per_step * args.steps, "cuda_graph": used_graph,
+        "gpu_launches": launches_per_step * (2 if (use_peer and not fused) else 1) * args.steps, "cuda_graph": used_graph,
         "clocks": clocks.summary(),
     }
-    print(json.dumps(line))
+    print(json.dumps(mark_diagnostic(line, args)))
     sys.stdout.flush()
     if dist is not None:
         os._exit(0)
@@ -579,7 +609,7 @@ def run_prefill(args):
         "dtype": "fp16 x fp16 tcgen05.mma, fp32 accumulate in TMEM (weights dequantized exactly to fp16, activations bf16 -> fp16)",
         "data": "synthetic", "config": cfg,
         "roofline": {"bound": "tensor", "kernel": "gemm_tc_kernel<Q4_K,fp16> (+ convert_x_kernel per product)", "achieved": value, "peak": peak,
-                     "unit": "TFLOP/s", "frac": value / peak, "peak_source": f"of {src}", "traffic": None,
+                     "unit": "TFLOP/s", "frac": value / peak, "peak_source": f"of {src}", "traffic": NCU_PREFILL_TRAFFIC_BYTES_PER_LAUNCH,
                      "us_per_launch": ms_step * 1e3 / copies,
                      "note": "2*M*N*K per product / device time per product, activation conversion launch included"},
         "cpu_baseline": None,
@@ -600,6 +630,11 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="time direct launches instead of a CUDA graph replay")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--per-launch", action="store_true", help="one launch per projection group instead of a decode plan")
+    ap.add_argument("--nccl", action="store_true", help="N > 1: NCCL all-reduce instead of the peer-memory kernel")
+    ap.add_argument("--unfused", action="store_true",
+                    help="N > 1: one plan per layer followed by the peer-memory all-reduce kernel, instead of sums inside one launch")
+    ap.add_argument("--no-exchange", action="store_true",
+                    help="N > 1 diagnostic: skip the all-reduce (partial sums only; the line is marked invalid)")
     ap.add_argument("--layers", type=int, default=32,
                     help="layers per step (default 32 = the benchmark; a smaller count is a profiling case, named as such in config)")
     ap.add_argument("--workload", choices=["decode", "prefill"], default="decode",

@@ -214,7 +214,13 @@ typedef struct b200q_plan b200q_plan;
 enum {
     /* the job's activation is written by earlier jobs of the same plan (e.g. the down projection
      * reading what gate/up produced): all CTAs finish those jobs before this one converts x */
-    B200Q_JOB_WAITS_FOR_EARLIER = 1
+    B200Q_JOB_WAITS_FOR_EARLIER = 1,
+    /* row-parallel projection under tensor parallelism: the job's outputs are partial sums, and the
+     * launch itself adds them up over the ranks attached with b200q_peer_attach (peer-memory stores
+     * and loads from inside the kernel, no separate all-reduce).  One weight, fp32 output, M x N at
+     * most B200Q_PEER_MAX_COUNT; every rank must run the same plan.  Without attached peers the
+     * flag does nothing (the sum over one rank is the output itself). */
+    B200Q_JOB_SUM_RANKS = 2
 };
 
 typedef struct b200q_job {
@@ -248,6 +254,20 @@ b200q_status b200q_tp_init(b200q_ctx *ctx, int32_t rank, int32_t world, const vo
 b200q_status b200q_allreduce(b200q_ctx *ctx, void *y_dev, int64_t count, int32_t dtype, void *stream);
 
 b200q_status b200q_tp_finalize(b200q_ctx *ctx);
+
+/* Low-latency exchange for decode-sized vectors: ranks that are processes on one NVLink-connected
+ * node map each other's exchange buffer (CUDA IPC) and b200q_allreduce then sums fp32 vectors of up
+ * to B200Q_PEER_MAX_COUNT elements with one kernel of peer stores and loads instead of NCCL.
+ *   1. every rank: b200q_peer_export -> a 64-byte handle of its own buffer;
+ *   2. the caller gathers the handles of all ranks (rank order) out of band;
+ *   3. every rank: b200q_peer_attach(rank, world <= 8, handles).
+ * All ranks must then issue the same sequence of b200q_allreduce calls.  No reference counterpart
+ * (see b200q_tp_init). */
+#define B200Q_PEER_HANDLE_BYTES 64
+#define B200Q_PEER_MAX_COUNT 16384
+b200q_status b200q_peer_export(b200q_ctx *ctx, void *handle_out_64);
+b200q_status b200q_peer_attach(b200q_ctx *ctx, int32_t rank, int32_t world, const void *handles);
+b200q_status b200q_peer_detach(b200q_ctx *ctx);
 
 #ifdef __cplusplus
 }

@@ -30,6 +30,7 @@ SPLIT_COLUMN, SPLIT_ROW = 0, 1
 ROUTE_NONE, ROUTE_GEMV, ROUTE_SKINNY, ROUTE_GEMM = 0, 1, 2, 3
 
 JOB_WAITS_FOR_EARLIER = 1
+JOB_SUM_RANKS = 2
 
 
 class Job(ctypes.Structure):
@@ -104,6 +105,9 @@ SIGNATURES = {
     "b200q_tp_init": (c_int32, [c_void_p, c_int32, c_int32, c_void_p]),
     "b200q_allreduce": (c_int32, [c_void_p, c_void_p, c_int64, c_int32, c_void_p]),
     "b200q_tp_finalize": (c_int32, [c_void_p]),
+    "b200q_peer_export": (c_int32, [c_void_p, c_void_p]),
+    "b200q_peer_attach": (c_int32, [c_void_p, c_int32, c_int32, c_void_p]),
+    "b200q_peer_detach": (c_int32, [c_void_p]),
 }
 
 

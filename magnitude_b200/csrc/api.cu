@@ -95,6 +95,10 @@ struct b200q_ctx {
     // tensor parallel
     NcclComm comm = nullptr;
     int tp_rank = 0, tp_world = 1;
+    // peer exchange (CUDA IPC): own buffer, every rank's buffer as mapped here
+    uint8_t *peer_local = nullptr;
+    uint8_t *peer_base[kPeerMaxWorld] = {nullptr};
+    int peer_rank = -1, peer_world = 0;
 };
 
 struct b200q_plan {
@@ -239,6 +243,9 @@ b200q_status run_stream(b200q_ctx *ctx, const StreamJob *jobs_host, const Stream
     a.grid = ctx->gemv_grid;
     a.debug = ctx->gemv_debug;
     a.pdl = ctx->gemv_pdl;
+    a.peer_rank = ctx->peer_rank;
+    a.peer_world = ctx->peer_world;
+    for (int r = 0; r < kPeerMaxWorld; ++r) a.peer_base[r] = ctx->peer_base[r];
     cudaError_t e = stream_launch(a, st);
     if (e != cudaSuccess) return cuda_fail(ctx, e, "streaming kernel launch");
     return B200Q_OK;
@@ -437,6 +444,8 @@ void b200q_ctx_destroy(b200q_ctx *ctx) {
         NcclApi *api = nccl_api();
         if (api) api->CommDestroy(ctx->comm);
     }
+    b200q_peer_detach(ctx);
+    if (ctx->peer_local) cudaFree(ctx->peer_local);
     if (ctx->hstream) cudaStreamDestroy(ctx->hstream);
     if (ctx->hx_dev) cudaFree(ctx->hx_dev);
     if (ctx->hy_dev) cudaFree(ctx->hy_dev);
@@ -749,9 +758,17 @@ b200q_status b200q_plan_create(b200q_ctx *ctx, const b200q_job *jobs, int32_t n_
             return fail(ctx, B200Q_ERR_INVALID_CONFIG, "job %d: K = 0 is not allowed in a plan", i);
         }
         if (!rows) continue;   // nothing to compute
+        int jflags = (j.flags & B200Q_JOB_WAITS_FOR_EARLIER) && !pl->jobs.empty() ? STREAM_JOB_WAITS : 0;
+        if (j.flags & B200Q_JOB_SUM_RANKS) {
+            if (j.n_weights != 1 || j.y_dtype != B200Q_TYPE_F32 || M * j.w[0]->N > kPeerSlotFloats) {
+                delete pl;
+                return fail(ctx, B200Q_ERR_INVALID_CONFIG,
+                            "job %d: a rank sum takes one weight, fp32 output and at most %d outputs", i, kPeerSlotFloats);
+            }
+            jflags |= STREAM_JOB_SUM_RANKS;
+        }
         StreamJob J;
-        fill_job(J, j.w, j.n_weights, j.x_dev, j.x_dtype, j.ldx, j.y_dev, j.y_dtype, j.ldy,
-                 (j.flags & B200Q_JOB_WAITS_FOR_EARLIER) && !pl->jobs.empty() ? STREAM_JOB_WAITS : 0);
+        fill_job(J, j.w, j.n_weights, j.x_dev, j.x_dtype, j.ldx, j.y_dev, j.y_dtype, j.ldy, jflags);
         pl->jobs.push_back(J);
     }
     if (!pl->jobs.empty()) {
@@ -828,11 +845,26 @@ b200q_status b200q_allreduce(b200q_ctx *ctx, void *y_dev, int64_t count, int32_t
     if (s != B200Q_OK) return s;
     if (!act_type(dtype) || count < 0 || (count > 0 && !y_dev))
         return fail(ctx, B200Q_ERR_INVALID_CONFIG, "bad all-reduce arguments");
-    if (!ctx->comm) {
-        if (ctx->tp_world == 1) return B200Q_OK;   // single rank: the sum is the input
-        return fail(ctx, B200Q_ERR_INVALID_CONFIG, "b200q_tp_init has not been called");
-    }
     if (count == 0) return B200Q_OK;
+    if (ctx->peer_world > 1 && dtype == B200Q_TYPE_F32 && count <= kPeerSlotFloats &&
+        !(reinterpret_cast<uintptr_t>(y_dev) & 3)) {
+        CU_TRY(ctx, cudaSetDevice(ctx->device));
+        PeerLaunch a{};
+        a.y = reinterpret_cast<float *>(y_dev);
+        a.count = (int)count;
+        a.rank = ctx->peer_rank;
+        a.world = ctx->peer_world;
+        for (int r = 0; r < ctx->peer_world; ++r) a.base[r] = ctx->peer_base[r];
+        a.status = ctx->status_dev;
+        cudaError_t e = peer_allreduce_launch(a, (cudaStream_t)stream);
+        if (e != cudaSuccess) return cuda_fail(ctx, e, "peer all-reduce launch");
+        return B200Q_OK;
+    }
+    if (!ctx->comm) {
+        if (ctx->tp_world == 1 && ctx->peer_world <= 1) return B200Q_OK;   // single rank: the sum is the input
+        return fail(ctx, B200Q_ERR_INVALID_CONFIG, "no exchange path for this call: b200q_tp_init has not been called"
+                                                   " (the peer path takes fp32 vectors of up to %d elements)", kPeerSlotFloats);
+    }
     NcclApi *api = nccl_api();
     int rc = api->AllReduce(y_dev, y_dev, (size_t)count, dtype == B200Q_TYPE_BF16 ? kNcclBfloat16 : kNcclFloat32,
                             kNcclSum, ctx->comm, (cudaStream_t)stream);
@@ -850,6 +882,71 @@ b200q_status b200q_tp_finalize(b200q_ctx *ctx) {
     }
     ctx->tp_world = 1;
     ctx->tp_rank = 0;
+    return B200Q_OK;
+}
+
+b200q_status b200q_peer_export(b200q_ctx *ctx, void *handle_out_64) {
+    b200q_status s = check_ctx(ctx);
+    if (s != B200Q_OK) return s;
+    if (!handle_out_64) return fail(ctx, B200Q_ERR_INVALID_CONFIG, "null handle buffer");
+    static_assert(sizeof(cudaIpcMemHandle_t) == B200Q_PEER_HANDLE_BYTES, "handle size");
+    static_assert(kPeerSlotFloats == B200Q_PEER_MAX_COUNT, "peer vector limit");
+    CU_TRY(ctx, cudaSetDevice(ctx->device));
+    if (!ctx->peer_local) {
+        void *ptr = nullptr;
+        cudaError_t e = cudaMalloc(&ptr, kPeerBufferBytes);
+        if (e != cudaSuccess) return cuda_fail(ctx, e, "exchange buffer");
+        e = cudaMemset(ptr, 0, kPeerBufferBytes);
+        if (e != cudaSuccess) {
+            cudaFree(ptr);
+            return cuda_fail(ctx, e, "exchange buffer clear");
+        }
+        ctx->peer_local = reinterpret_cast<uint8_t *>(ptr);
+    }
+    cudaIpcMemHandle_t h;
+    CU_TRY(ctx, cudaIpcGetMemHandle(&h, ctx->peer_local));
+    memcpy(handle_out_64, &h, sizeof(h));
+    return B200Q_OK;
+}
+
+b200q_status b200q_peer_attach(b200q_ctx *ctx, int32_t rank, int32_t world, const void *handles) {
+    b200q_status s = check_ctx(ctx);
+    if (s != B200Q_OK) return s;
+    if (world < 1 || world > kPeerMaxWorld || rank < 0 || rank >= world || !handles)
+        return fail(ctx, B200Q_ERR_INVALID_CONFIG, "bad peer arguments (rank %d of %d, at most %d ranks)", rank, world, kPeerMaxWorld);
+    if (!ctx->peer_local) return fail(ctx, B200Q_ERR_INVALID_CONFIG, "b200q_peer_export has not been called");
+    if (ctx->peer_world > 0) return fail(ctx, B200Q_ERR_INVALID_CONFIG, "peers are already attached");
+    CU_TRY(ctx, cudaSetDevice(ctx->device));
+    for (int r = 0; r < world; ++r) {
+        if (r == rank) {
+            ctx->peer_base[r] = ctx->peer_local;
+            continue;
+        }
+        cudaIpcMemHandle_t h;
+        memcpy(&h, reinterpret_cast<const char *>(handles) + (size_t)r * sizeof(h), sizeof(h));
+        void *ptr = nullptr;
+        cudaError_t e = cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess);
+        if (e != cudaSuccess) {
+            for (int q = 0; q < r; ++q)
+                if (q != rank && ctx->peer_base[q]) cudaIpcCloseMemHandle(ctx->peer_base[q]);
+            for (int q = 0; q < kPeerMaxWorld; ++q) ctx->peer_base[q] = nullptr;
+            return cuda_fail(ctx, e, "mapping a peer's exchange buffer");
+        }
+        ctx->peer_base[r] = reinterpret_cast<uint8_t *>(ptr);
+    }
+    ctx->peer_rank = rank;
+    ctx->peer_world = world;
+    return B200Q_OK;
+}
+
+b200q_status b200q_peer_detach(b200q_ctx *ctx) {
+    if (!ctx) return B200Q_ERR_INVALID_CONFIG;
+    cudaSetDevice(ctx->device);
+    for (int r = 0; r < ctx->peer_world; ++r)
+        if (r != ctx->peer_rank && ctx->peer_base[r]) cudaIpcCloseMemHandle(ctx->peer_base[r]);
+    for (int r = 0; r < kPeerMaxWorld; ++r) ctx->peer_base[r] = nullptr;
+    ctx->peer_rank = -1;
+    ctx->peer_world = 0;
     return B200Q_OK;
 }
 

@@ -58,9 +58,12 @@ struct StreamParams {
     int partial_bytes;       // ... for the per-(row, chunk) partial sums
     int has_dep;             // some job waits for earlier jobs: CTAs count completions
     int debug;               // experiments only: 1 stream without computing, 2 compute without
-                             // streaming, 4 skip the activation prologue, 8 skip the final pass
+                             // streaming, 4 skip the activation prologue, 8 skip the final pass,
+                             // 64 do not wait for the peers' partial sums
     int *status;
     unsigned *counter;       // grid-wide completion counter (zeroed before the launch)
+    uint8_t *peer_base[kPeerMaxWorld];   // exchange buffers of the tensor-parallel ranks (peer memory)
+    int peer_rank, peer_world;           // peer_world <= 1: jobs flagged SUM_RANKS store their own sums
 };
 
 // shared-memory header: barriers and failure bookkeeping (the job table follows it)
@@ -71,7 +74,20 @@ struct SmemHead {
     int decide;              // thread 0's sample of `fail`, taken before a barrier so all warps agree
     int prod_done;           // the producer warp has stopped issuing copies
     int issued[kMaxWarps];   // ... after issuing this many items into each consumer's ring
+    unsigned xepoch;         // exchanges this CTA has posted so far (loaded from the exchange buffer)
+    int xfail;               // a wait for a peer's partial sums ran out
 };
+
+// (value, exchange number) pairs of the in-launch rank sums: one 8-byte store / load each
+__device__ __forceinline__ void st_pair(unsigned long long *p, float v, unsigned e) {
+    const unsigned long long w = ((unsigned long long)e << 32) | __float_as_uint(v);
+    asm volatile("st.volatile.global.u64 [%0], %1;" ::"l"(p), "l"(w) : "memory");
+}
+__device__ __forceinline__ unsigned long long ld_pair(const unsigned long long *p) {
+    unsigned long long w;
+    asm volatile("ld.volatile.global.u64 %0, [%1];" : "=l"(w) : "l"(p) : "memory");
+    return w;
+}
 constexpr size_t kHeadBytes = (sizeof(SmemHead) + 127) & ~size_t(127);
 
 // (segment, row group inside it) of virtual group vg; segments are concatenated in launch order
@@ -168,7 +184,7 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1) stream_kernel(const S
         mbar_fence_init();
         fence_proxy_async();
     }
-    if (threadIdx.x == 0) { head.fail = 0; head.prod_done = 0; }
+    if (threadIdx.x == 0) { head.fail = 0; head.prod_done = 0; head.xfail = 0; }
     // the job table (written by the host when the plan was made) moves to shared memory once
     if (p.jobs) {
         const int words = p.njobs * (int)(sizeof(StreamJob) / 4);
@@ -277,6 +293,57 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1) stream_kernel(const S
         xs.x = Jx.x; xs.ldx = Jx.ldx; xs.x_is_bf16 = Jx.x_is_bf16; xs.x_vec_ok = Jx.x_vec_ok;
         xs.K = Jx.K; xs.Kpad = Jx.Kpad;
         return xs;
+    };
+
+    // ---- sums over tensor-parallel ranks, inside the launch -----------------------------------
+    // A job flagged SUM_RANKS does not store its row sums: every CTA writes them, as (value,
+    // exchange number) pairs, into its slot of every rank's exchange buffer (peer stores over
+    // NVLink) and later adds up, in rank order, what the same CTA of every rank delivered, into y;
+    // a pair that carries the current exchange number is complete, so there is no flag and no
+    // fence.  "Later" is just before the CTA posts its next exchange (or at the end of the launch),
+    // so the transfer hides behind the jobs in between; launches whose jobs wait for one another
+    // complete it at once.  Two slot sets alternate; a CTA posts exchange e + 1 only after it has
+    // read exchange e, and can only read e + 1 after the peers posted it, i.e. after they read e:
+    // no pair is overwritten before it has been read.  All ranks run the same plan on the same grid.
+    const bool xenabled = p.peer_world > 1;
+    unsigned xe = 0;
+    bool xe_loaded = false;
+    int xpending = -1;
+    auto exchange_complete = [&](int job, unsigned e) {
+        const StreamJob &Jc = jobs_s[job];
+        const unsigned long long *slots = reinterpret_cast<const unsigned long long *>(p.peer_base[p.peer_rank] + kPeerFusedSlotOff) +
+                                          (size_t)(e & 1) * kPeerMaxWorld * kPeerSlotFloats;
+        const int gbc = (int)((long long)Jc.total_groups * blockIdx.x / gridDim.x);
+        const int gec = (int)((long long)Jc.total_groups * (blockIdx.x + 1) / gridDim.x);
+        const int n = Jc.seg[0].n;
+        const int cells = (gec - gbc) * R * MT;
+        for (int t = threadIdx.x; t < cells; t += T) {
+            const int rl = t / MT, m = t - rl * MT;
+            const int row = gbc * R + rl;
+            if (row < n && m < p.M) {
+                const int si = m * n + row;
+                float acc = 0.f;
+                bool ok = !*reinterpret_cast<volatile int *>(&head.xfail);
+                for (int r = 0; r < p.peer_world && ok; ++r) {
+                    const unsigned long long *q = slots + (size_t)r * kPeerSlotFloats + si;
+                    unsigned long long w = ld_pair(q);
+                    if ((unsigned)(w >> 32) != e && !(p.debug & 64)) {
+                        const uint64_t t0 = globaltimer_ns();
+                        int spins = 0;
+                        while ((unsigned)((w = ld_pair(q)) >> 32) != e) {
+                            if ((++spins & 63) == 0 && globaltimer_ns() - t0 > kWaitLimitNs) {
+                                ok = false;
+                                head.xfail = 1;
+                                atomicMax(p.status, DEV_ERR_PIPE_TIMEOUT);
+                                break;
+                            }
+                        }
+                    }
+                    acc = r == 0 ? __uint_as_float((unsigned)w) : acc + __uint_as_float((unsigned)w);
+                }
+                if (ok) reinterpret_cast<float *>(Jc.seg[0].y)[(long long)m * Jc.seg[0].ldy + row] = acc;
+            }
+        }
     };
 
 #pragma unroll 1
@@ -457,6 +524,21 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1) stream_kernel(const S
         }
 
         // ---- final pass: sum the chunks of every row of this CTA in order and store ------------
+        const bool xsum = xenabled && (J.flags & STREAM_JOB_SUM_RANKS);
+        if (xsum) {
+            if (!xe_loaded) {   // exchanges posted by earlier launches (after pdl_wait: their last write is visible)
+                if (threadIdx.x == 0)
+                    head.xepoch = *(reinterpret_cast<const unsigned *>(p.peer_base[p.peer_rank] + kPeerFusedEpochOff) + blockIdx.x);
+                consumer_sync(T);
+                xe = head.xepoch;
+                xe_loaded = true;
+            }
+            if (xpending >= 0) {
+                exchange_complete(xpending, xe);
+                xpending = -1;
+            }
+            ++xe;
+        }
         const int cells = (p.debug & 8) ? 0 : (ge - gb) * R * MT;
         for (int t = threadIdx.x; t < cells; t += T) {
             const int rl = t / MT, m = t - rl * MT;      // rl = local group * 4 + row in group
@@ -466,12 +548,22 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1) stream_kernel(const S
             if (row < J.seg[sg].n && m < p.M) {
                 float v = 0.f;
                 for (int cc = 0; cc < nchunks; ++cc) v += partial[(rl * nchunks + cc) * MT + m];
+                if (xsum) {     // one segment, fp32 output (checked when the plan was made)
+                    const size_t si = (size_t)((xe & 1) * kPeerMaxWorld + p.peer_rank) * kPeerSlotFloats + m * J.seg[0].n + row;
+                    for (int r = 0; r < p.peer_world; ++r)
+                        st_pair(reinterpret_cast<unsigned long long *>(p.peer_base[r] + kPeerFusedSlotOff) + si, v, xe);
+                    continue;
+                }
                 const long long idx = (long long)m * J.seg[sg].ldy + row;
                 if (J.y_is_bf16)
                     reinterpret_cast<__nv_bfloat16 *>(J.seg[sg].y)[idx] = __float2bfloat16_rn(v);
                 else
                     reinterpret_cast<float *>(J.seg[sg].y)[idx] = v;
             }
+        }
+        if (xsum) {
+            if (p.has_dep) exchange_complete(jb, xe);   // a later job may read y: finish now
+            else xpending = jb;
         }
         if (p.has_dep) {
             // publish: this CTA's outputs of job jb are stored
@@ -482,6 +574,9 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1) stream_kernel(const S
             }
         }
     }
+    if (xpending >= 0) exchange_complete(xpending, xe);
+    if (xe_loaded && threadIdx.x == 0)
+        *(reinterpret_cast<unsigned *>(p.peer_base[p.peer_rank] + kPeerFusedEpochOff) + blockIdx.x) = xe;
 }
 
 }  // namespace
@@ -578,11 +673,23 @@ cudaError_t stream_launch_one(const StreamLaunch &a, cudaStream_t st) {
     p.debug = a.debug;
     p.status = a.status;
     p.counter = a.counter;
+    p.peer_rank = a.peer_rank;
+    p.peer_world = a.peer_world;
+    for (int r = 0; r < kPeerMaxWorld; ++r) p.peer_base[r] = a.peer_base[r];
     p.has_dep = 0;
     for (int i = 0; i < a.njobs; ++i)
         if (a.jobs_host[i].flags & STREAM_JOB_WAITS) p.has_dep = 1;
     const int grid = a.grid > 0 ? a.grid : a.sm_count;
     if (p.has_dep && grid > a.sm_count) return cudaErrorInvalidValue;   // the counter wait needs every CTA resident
+    if (p.peer_world > 1) {
+        for (int i = 0; i < a.njobs; ++i) {
+            const StreamJob &J = a.jobs_host[i];
+            if (!(J.flags & STREAM_JOB_SUM_RANKS)) continue;
+            // in-launch sums: per-CTA flags, one segment, fp32 outputs that fit one slot
+            if (grid > kPeerCtas || J.nseg != 1 || J.y_is_bf16 || (long long)a.M * J.seg[0].n > kPeerSlotFloats)
+                return cudaErrorInvalidValue;
+        }
+    }
     int types = 0;
     for (int i = 0; i < a.njobs; ++i) {
         const int qt = a.jobs_host[i].qt;

@@ -21,7 +21,10 @@ cudaError_t dequant_launch(int qt, const uint8_t *w, int64_t N, int64_t K, int64
 // The streaming kernel runs a list of jobs in one launch.  A job is 1..4 weights of one type and
 // K applied to one activation (M <= 4 rows, the same M for every job of a launch).
 constexpr int kStreamMaxSeg = 4;
-enum : int { STREAM_JOB_WAITS = 1 };   // the job reads what earlier jobs of the launch wrote
+enum : int {
+    STREAM_JOB_WAITS = 1,       // the job reads what earlier jobs of the launch wrote
+    STREAM_JOB_SUM_RANKS = 2,   // the job's outputs are summed over the attached peer ranks inside the launch
+};
 
 struct StreamSeg {
     const uint8_t *w;   // streaming-layout rows
@@ -58,6 +61,8 @@ struct StreamLaunch {
     int warps, depth, grid;       // 0 = default
     int debug;                    // experiments only (see gemv.cu)
     int pdl;                      // launch with programmatic stream serialization
+    uint8_t *peer_base[8];        // every rank's exchange buffer (jobs flagged STREAM_JOB_SUM_RANKS); null = none
+    int peer_rank, peer_world;
 };
 int gemv_max_m();
 void stream_job_finish(StreamJob &job);
@@ -87,5 +92,31 @@ cudaError_t gemm_launch(const GemmLaunch &a, cudaStream_t st);
 // describe the caller's activations (bf16 or fp32), nothing is allocated
 size_t gemm_static_scratch_elems();
 cudaError_t gemm_launch_static(GemmLaunch a, int x_is_bf16, cudaStream_t st);
+
+// ---- peer.cu --------------------------------------------------------------------------------
+// Exchange buffer of one GPU.  Every element travels as an 8-byte (value, call number) pair written
+// with one store, so the reader needs no separate flag and the writer no fence: a pair whose
+// number is the current call's is complete.  Two regions (the stand-alone all-reduce kernel, and
+// the sums inside the streaming kernel), each: call counters, then slots [2 sets][ranks][elements].
+constexpr int kPeerMaxWorld = 8;
+constexpr int kPeerBlocks = 16;                        // blocks of the stand-alone kernel
+constexpr int kPeerThreads = 128;
+constexpr int kPeerCtas = 160;                         // CTAs of the streaming kernel (one per SM)
+constexpr int kPeerSlotFloats = 16384;                 // largest vector summed over ranks
+constexpr size_t kPeerSlotBytes = size_t(kPeerSlotFloats) * 8;
+constexpr size_t kPeerRegionSlots = size_t(2) * kPeerMaxWorld * kPeerSlotBytes;      // 2 MB
+constexpr size_t kPeerEpochOff = 0;                    // [kPeerBlocks] u32
+constexpr size_t kPeerSlotOff = 4096;
+constexpr size_t kPeerFusedEpochOff = kPeerSlotOff + kPeerRegionSlots;               // [kPeerCtas] u32
+constexpr size_t kPeerFusedSlotOff = kPeerFusedEpochOff + 4096;
+constexpr size_t kPeerBufferBytes = kPeerFusedSlotOff + kPeerRegionSlots;
+struct PeerLaunch {
+    float *y;                       // in place: partial sums in, sums over ranks out
+    int count;
+    int rank, world;
+    uint8_t *base[kPeerMaxWorld];   // every rank's exchange buffer as mapped in this process
+    int *status;
+};
+cudaError_t peer_allreduce_launch(const PeerLaunch &a, cudaStream_t st);
 
 }  // namespace b200q

@@ -217,10 +217,11 @@ class Backend:
         )
         return outs
 
-    def plan(self, jobs, waits: Sequence[bool] | None = None) -> Plan:
+    def plan(self, jobs, waits: Sequence[bool] | None = None, sum_ranks: Sequence[bool] | None = None) -> Plan:
         """jobs: sequence of (weights, x, outs) with weights/outs sequences of equal length (1..4),
         x a CUDA tensor [M, K] (M <= 4, the same for every job).  waits[i] marks job i as reading
-        what earlier jobs of the plan write."""
+        what earlier jobs of the plan write; sum_ranks[i] marks job i's outputs as partial sums that
+        the launch adds up over the attached peer ranks (row-parallel projection)."""
         torch = _torch()
         n = len(jobs)
         arr = (B.Job * n)()
@@ -243,7 +244,7 @@ class Backend:
             j.x_dev = x.data_ptr()
             j.ldx = x.stride(0) if m > 1 else max(x.shape[1], 1)
             j.y_dtype = _TORCH_DTYPE[outs[0].dtype]
-            j.flags = B.JOB_WAITS_FOR_EARLIER if (waits and waits[i]) else 0
+            j.flags = (B.JOB_WAITS_FOR_EARLIER if (waits and waits[i]) else 0) | (B.JOB_SUM_RANKS if (sum_ranks and sum_ranks[i]) else 0)
             for k, (w, o) in enumerate(zip(ws, outs)):
                 if o.dim() == 1:
                     o = o.unsqueeze(0)
@@ -294,6 +295,29 @@ class Backend:
 
     def tp_finalize(self) -> None:
         self._check(B.lib().b200q_tp_finalize(self._h))
+
+    # -- peer-memory exchange (ranks = processes on one NVLink node) ---------------------------
+    def peer_export(self) -> bytes:
+        buf = ctypes.create_string_buffer(64)
+        self._check(B.lib().b200q_peer_export(self._h, buf))
+        return buf.raw
+
+    def peer_attach(self, rank: int, world: int, handles: Sequence[bytes]) -> None:
+        if len(handles) != world or any(len(h) != 64 for h in handles):
+            raise ValueError("peer_attach needs one 64-byte handle per rank")
+        buf = ctypes.create_string_buffer(b"".join(handles), 64 * world)
+        self._check(B.lib().b200q_peer_attach(self._h, rank, world, buf))
+
+    def peer_setup(self, dist) -> None:
+        """Exchanges the handles over an initialised torch.distributed group and attaches the peers."""
+        mine = self.peer_export()
+        handles = [None] * dist.get_world_size()
+        dist.all_gather_object(handles, mine)
+        self.peer_attach(dist.get_rank(), dist.get_world_size(), handles)
+        dist.barrier()
+
+    def peer_detach(self) -> None:
+        self._check(B.lib().b200q_peer_detach(self._h))
 
     def __del__(self):
         try:
