@@ -89,7 +89,7 @@ struct b200q_ctx {
     // prefill path: bf16 copy of fp32 activations
     void *gemm_scratch = nullptr;
     size_t gemm_scratch_bytes = 0;
-    int gemm_bn = 0, gemm_debug = 0;
+    int gemm_bn = 0, gemm_debug = 0, gemm_pair = 0;
     // tunables (environment overrides for experiments)
     int gemv_warps = 0, gemv_depth = 0, gemv_grid = 0, gemv_smem = 0, gemv_rows = 0, gemv_debug = 0, gemv_pdl = 1;
     // tensor parallel
@@ -298,6 +298,7 @@ b200q_status run_gemm(b200q_ctx *ctx, const b200q_weight *w, const void *x, int 
     a.sm_count = ctx->sm_count;
     a.bn_override = ctx->gemm_bn;
     a.debug = ctx->gemm_debug;
+    a.pair = ctx->gemm_pair;
     cudaError_t e = gemm_launch(a, st);
     if (e != cudaSuccess) return cuda_fail(ctx, e, "tensor-core GEMM launch");
     ++*launches;
@@ -433,6 +434,7 @@ b200q_status b200q_ctx_create(int32_t device, b200q_ctx **out) {
     ctx->gemv_pdl = env_int("B200Q_GEMV_PDL", 1);
     ctx->gemm_bn = env_int("B200Q_GEMM_BN", 0);
     ctx->gemm_debug = env_int("B200Q_GEMM_DEBUG", 0);
+    ctx->gemm_pair = env_int("B200Q_GEMM_PAIR", 1);
     *out = ctx;
     return B200Q_OK;
 }
@@ -715,6 +717,7 @@ b200q_status b200q_matmul_prefill_noalloc(b200q_ctx *ctx, const b200q_weight *w,
     a.sm_count = ctx->sm_count;
     a.bn_override = ctx->gemm_bn;
     a.debug = ctx->gemm_debug;
+    a.pair = ctx->gemm_pair;
     cudaError_t e = gemm_launch_static(a, x_dtype == B200Q_TYPE_BF16, (cudaStream_t)stream);
     if (e != cudaSuccess) return cuda_fail(ctx, e, "prefill launch (built-in scratch)");
     ctx->last_route = B200Q_ROUTE_GEMM;

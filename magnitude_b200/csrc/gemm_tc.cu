@@ -69,6 +69,9 @@ struct GemmParams {
     int m_tiles, n_tiles;
     int nchunks_full;        // chunks of 8 whole records per row; a shorter tail chunk may follow
     int *status;
+    int units_per_row;       // two-CTA kernel: 32-token units per 256-row stripe, ceil(M / 32)
+    int tps, extra;          // ... tiles per stripe; the first `extra` stripes have one more
+    int pair_tiles;          // ... tiles in all
     int debug;               // timing experiments only (results invalid): 1 no activation loads, 2 no dequant math,
                              // 4 no weight loads, 8 no MMA, 16 no epilogue body, 32 no proxy fence,
                              // 64 plain arrives instead of commits, 256 print per-role clock counts from block 0
@@ -617,6 +620,381 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const GemmParams p
     }
 }
 
+// ---- the two-CTA kernel -----------------------------------------------------------------------
+//
+// Two CTAs on neighbouring SMs (a cluster of two) share one 256-row x BN-token tile: each CTA
+// dequantizes 128 of the weight rows and stages half of the activation tile, and one thread of
+// the leader CTA issues tcgen05.mma.cta_group::2 (M = 256), which reads A from both CTAs' shared
+// memory and each half of B once for both tensor cores.  Per SM and K-step that halves the
+// activation bytes staged by TMA and read by the tensor core.  No multicast load anywhere: every
+// CTA loads its own bytes; only the completion signals cross the pair:
+//   * "stage full" barriers live in the leader: the peer's dequant warps arrive on them remotely
+//     (mapa + mbarrier.arrive.release.cluster) and both CTAs' activation loads count their bytes
+//     on the leader's barrier (cp.async.bulk.tensor ... .cta_group::2, no multicast);
+//   * "stage empty" and "accumulator full" are tcgen05.commit.cta_group::2 ... multicast::cluster
+//     arrivals on the same barrier offset in both CTAs;
+//   * "accumulator empty" lives in the leader: the peer's epilogue warps arrive remotely.
+// Tensor memory is allocated by each CTA for itself; a cluster barrier before the exit keeps either
+// CTA's shared and tensor memory alive until the other has finished using it.
+
+constexpr int kPairThreads = kThreads;
+__host__ __device__ constexpr int pair_b_stage_bytes() { return 128 * BK * 2; }       // half of a <= 256-token tile: 16 KB
+__host__ __device__ constexpr int pair_b_stages(int qt) { return qt == QT_Q8_0 ? 5 : 6; }
+constexpr int kMaxPairBStages = 6;
+__host__ __device__ constexpr int pair_smem_data_bytes(int qt) {
+    return kAStages * kStageABytes + pair_b_stages(qt) * pair_b_stage_bytes() + kWBufs * wbuf_bytes(qt) + (qt == QT_Q6_K ? 2 * kDBufBytes : 0);
+}
+
+struct PairSmem {
+    uint64_t afull[kAStages];          // leader's copy is used: 4 local + 4 remote warp arrivals
+    uint64_t aempty[kAStages];
+    uint64_t bfull[kMaxPairBStages];   // leader's copy is used: its own expect_tx arrival + both CTAs' bytes
+    uint64_t bempty[kMaxPairBStages];
+    uint64_t tmem_full[2];
+    uint64_t tmem_empty[2];            // leader's copy is used: 4 local + 4 remote warp arrivals
+    uint64_t wfull[kWBufs];
+    uint64_t wempty[kWBufs];
+    uint32_t tmem_base;
+    int abort;
+    int wait_ns;
+};
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// shared::cluster address of the same shared-memory location in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t mapa_rank(uint32_t saddr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// 2-D tiled TMA load into this CTA's shared memory whose bytes are counted on a barrier given by
+// its shared::cluster address (here: the leader's); no multicast
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar_cluster) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar_cluster), "r"(x), "r"(y)
+        : "memory");
+}
+__device__ __forceinline__ void umma_f16_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// arrives on the barrier at this offset in both CTAs once the MMAs issued so far have completed
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+    const uint16_t mask = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar), "h"(mask)
+                 : "memory");
+}
+
+// tensor-memory management of the pair: one warp of each CTA executes these (every tcgen05
+// instruction of a kernel names the same CTA group)
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t smem_dst, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+
+template <bool FAST>
+__device__ __forceinline__ bool pair_wait(uint32_t bar, uint32_t parity, PairSmem *sm, int *status) {
+    if (FAST) {
+#pragma unroll 1
+        for (int i = 0; i < (1 << 14); ++i)
+            if (mbar_try_wait_hint(bar, parity, 40)) return true;
+    } else if (mbar_try_wait(bar, parity)) {
+        return true;
+    }
+    volatile int *ab = &sm->abort;
+    const uint64_t t0 = globaltimer_ns();
+#pragma unroll 1
+    while (true) {
+#pragma unroll 1
+        for (int i = 0; i < 64; ++i)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (*ab) return false;
+        if (globaltimer_ns() - t0 > kWaitLimitNs) {
+            *ab = 1;
+            atomicMax(status, DEV_ERR_PIPE_TIMEOUT);
+            return false;
+        }
+    }
+}
+
+// Tiles of the pair kernel: a stripe (256 weight rows x all tokens) is cut into n tiles of nearly
+// equal width, widths being multiples of 32 tokens (a "unit") up to 256: the first `p.extra`
+// stripes get p.tps + 1 tiles, the others p.tps (see pick_pair_tiles).  Tile t goes to pair
+// t mod pairs.
+__device__ __forceinline__ void pair_tile(const GemmParams &p, int tile, int &stripe, int &t0, int &width) {
+    int idx, n;
+    const int big = p.extra * (p.tps + 1);
+    if (tile < big) {
+        n = p.tps + 1;
+        stripe = tile / n;
+        idx = tile - stripe * n;
+    } else {
+        n = p.tps;
+        const int t = tile - big;
+        const int q = t / n;
+        stripe = p.extra + q;
+        idx = t - q * n;
+    }
+    const int base = p.units_per_row / n, rem = p.units_per_row - base * n;   // `rem` tiles are one unit wider
+    const int w = base + (idx < rem ? 1 : 0);
+    t0 = 32 * (idx < rem ? idx * (base + 1) : rem * (base + 1) + (idx - rem) * base);
+    width = 32 * w;
+}
+
+// p.n_tiles counts 256-row stripes here
+template <int QT>
+__global__ void __launch_bounds__(kPairThreads, 1) gemm_tc_pair_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap,
+                                                                      const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap wtail,
+                                                                      const __grid_constant__ CUtensorMap dmap, const __grid_constant__ CUtensorMap dtail) {
+    constexpr int SB_ = pair_b_stages(QT);
+    constexpr int WBUF = wbuf_bytes(QT);
+    constexpr int REC = rec_bytes(QT);
+    constexpr int kStageBBytes = pair_b_stage_bytes();
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const uint32_t a_s = smem_u32(smem);
+    const uint32_t b_s = a_s + kAStages * kStageABytes;
+    const uint32_t w_s = b_s + SB_ * kStageBBytes;
+    const uint32_t d_s = w_s + kWBufs * WBUF;
+    PairSmem *sm = reinterpret_cast<PairSmem *>(smem + pair_smem_data_bytes(QT));
+    const uint32_t wfull_s = smem_u32(sm->wfull), wempty_s = smem_u32(sm->wempty);
+    const uint32_t afull_s = smem_u32(sm->afull), aempty_s = smem_u32(sm->aempty);
+    const uint32_t bfull_s = smem_u32(sm->bfull), bempty_s = smem_u32(sm->bempty);
+    const uint32_t tfull_s = smem_u32(sm->tmem_full), tempty_s = smem_u32(sm->tmem_empty);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();          // 0 = leader
+    const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+    const int ksteps = p.nsb * 4;
+    const int chunks_per_tile = (p.nsb + kChunkRecs - 1) / kChunkRecs;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < kAStages; ++i) {
+            mbar_init(afull_s + 8 * i, 2 * (kDequantWarps / 4));   // one unit group of each CTA
+            mbar_init(aempty_s + 8 * i, 1);
+        }
+        for (int i = 0; i < SB_; ++i) {
+            mbar_init(bfull_s + 8 * i, 1);
+            mbar_init(bempty_s + 8 * i, 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(tfull_s + 8 * i, 1);
+            mbar_init(tempty_s + 8 * i, 2 * kEpiWarps);
+        }
+        for (int i = 0; i < kWBufs; ++i) {
+            mbar_init(wfull_s + 8 * i, 1);
+            mbar_init(wempty_s + 8 * i, kDequantWarps);
+        }
+        sm->abort = 0;
+        sm->wait_ns = 40;
+        mbar_fence_init();
+        fence_proxy_async();
+    }
+    if (warp == 0) {
+        tmem_alloc_pair(smem_u32(&sm->tmem_base), kTmemCols);
+        tmem_relinquish_pair();
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();        // both CTAs' barriers exist before anything crosses the pair
+    tc_fence_after();
+    const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t *>(&sm->tmem_base);
+
+    if (warp == 0) {
+        // ===== TMA producer: this CTA's half of the activation tile ================================
+        if (lane == 0) {
+            // every load is a full 128-token box (rows past the tile's half are never read), so the
+            // byte count on the leader's barrier does not depend on the tile's width
+            const uint32_t bytes_pair = 2u * kStageBBytes;
+            const uint32_t bfull_leader = mapa_rank(bfull_s, 0);
+            int it = 0;
+            bool ok = true;
+            for (int tile = pair; tile < p.pair_tiles && ok; tile += n_pairs) {
+                int stripe, t0, width;
+                pair_tile(p, tile, stripe, t0, width);
+                for (int ks = 0; ks < ksteps; ++ks, ++it) {
+                    const int stage = it % SB_;
+                    ok = pair_wait<true>(bempty_s + 8 * stage, ((it / SB_) & 1) ^ 1, sm, p.status);
+                    if (!ok) break;
+                    if (rank == 0) mbar_expect_tx(bfull_s + 8 * stage, bytes_pair);
+                    tma_load_2d_pair(b_s + stage * kStageBBytes, &xmap, ks * BK, t0 + (int)rank * (width >> 1), bfull_leader + 8 * stage);
+                }
+            }
+        }
+    } else if (warp == 2) {
+        // ===== TMA producer: packed weight records of this CTA's 128 rows ==========================
+        if (lane == 0) {
+            int rs = 0, tcount = 0;
+            bool ok = true;
+            for (int tile = pair; tile < p.pair_tiles && ok; tile += n_pairs, ++tcount) {
+                int stripe, t0, width;
+                pair_tile(p, tile, stripe, t0, width);
+                const int group0 = (stripe * 2 * BM + (int)rank * BM) / kRowGroup;
+                for (int sb = 0; sb < p.nsb; ++sb, ++rs) {
+                    const int c = sb >> 3, s_in = sb & 7;
+                    const int wb = rs % kWBufs;
+                    ok = pair_wait<true>(wempty_s + 8 * wb, ((rs / kWBufs) & 1) ^ 1, sm, p.status);
+                    if (!ok) break;
+                    const bool tail = c >= p.nchunks_full;
+                    uint32_t tx = BM * REC;
+                    if (QT == QT_Q6_K && s_in == 0) tx += BM * 16;
+                    mbar_expect_tx(wfull_s + 8 * wb, tx);
+                    tma_load_4d(w_s + wb * WBUF, tail ? &wtail : &wmap, s_in * (REC / 4), 0, tail ? 0 : c, group0, wfull_s + 8 * wb);
+                    if (QT == QT_Q6_K && s_in == 0) {
+                        const int nrec = tail ? (p.nsb - c * kChunkRecs) : kChunkRecs;
+                        const int cs = tcount * chunks_per_tile + c;
+                        tma_load_4d(d_s + (cs & 1) * kDBufBytes, tail ? &dtail : &dmap, nrec * (REC / 4), 0, tail ? 0 : c, group0,
+                                    wfull_s + 8 * wb);
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ===== MMA issuer (leader CTA only) ========================================================
+        if (lane == 0 && rank == 0) {
+            int it = 0, tcount = 0;
+            bool rdy_a = false, rdy_b = false;
+            for (int tile = pair; tile < p.pair_tiles; tile += n_pairs, ++tcount) {
+                int stripe, t0, width;
+                pair_tile(p, tile, stripe, t0, width);
+                const uint32_t idesc = (1u << 4) | ((uint32_t)(width >> 3) << 17) | ((uint32_t)((2 * BM) >> 4) << 24);
+                const int buf = tcount & 1;
+                bool ok = pair_wait<true>(tempty_s + 8 * buf, ((tcount >> 1) & 1) ^ 1, sm, p.status);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + buf * 256;
+                for (int ks = 0; ks < ksteps; ++ks, ++it) {
+                    const int sa = it % kAStages, sb = it % SB_;
+                    ok = rdy_b || pair_wait<true>(bfull_s + 8 * sb, (it / SB_) & 1, sm, p.status);
+                    ok = ok && (rdy_a || pair_wait<true>(afull_s + 8 * sa, (it / kAStages) & 1, sm, p.status));
+                    if (!ok) break;
+                    tc_fence_after();
+                    {
+                        const int nx = it + 1;
+                        rdy_b = mbar_test_wait(bfull_s + 8 * (nx % SB_), (nx / SB_) & 1);
+                        rdy_a = mbar_test_wait(afull_s + 8 * (nx % kAStages), (nx / kAStages) & 1);
+                    }
+                    const uint64_t adesc = make_desc_sw128(a_s + sa * kStageABytes);
+                    const uint64_t bdesc = make_desc_sw128(b_s + sb * kStageBBytes);
+#pragma unroll
+                    for (int kk = 0; kk < BK / 16; ++kk)
+                        umma_f16_pair(d_tmem, adesc + 2 * kk, bdesc + 2 * kk, idesc, (ks | kk) != 0);
+                    umma_commit_pair(aempty_s + 8 * sa);
+                    umma_commit_pair(bempty_s + 8 * sb);
+                }
+                if (!ok) break;
+                umma_commit_pair(tfull_s + 8 * buf);
+            }
+        }
+    } else if (warp < kFirstEpiWarp) {
+        // ===== dequant producers: this CTA's 128 weight rows =======================================
+        const int t = threadIdx.x - kFirstDequantWarp * 32;
+        const int r = t & (BM - 1), j = t >> 7;
+        const int r7 = r & 7;
+        const uint32_t row_off = (r >> 3) * 1024 + r7 * 128;
+        const uint32_t afull_leader = mapa_rank(afull_s, 0);
+        const int my_tiles = pair < p.pair_tiles ? (p.pair_tiles - pair + n_pairs - 1) / n_pairs : 0;
+        const int total = my_tiles * p.nsb;
+        bool ok = true;
+        auto fetch = [&](int rs, Unit<QT> &u) {
+            const int wb = rs % kWBufs;
+            if (lane == 0) ok = pair_wait<true>(wfull_s + 8 * wb, (rs / kWBufs) & 1, sm, p.status);
+            ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
+            if (!ok) return;
+            const int tcount = rs / p.nsb, sb = rs - tcount * p.nsb;
+            const int cs = tcount * chunks_per_tile + (sb >> 3);
+            u.load(w_s + wb * WBUF + r * REC, d_s + (cs & 1) * kDBufBytes + r * 16 + 2 * (sb & 7), j);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(wempty_s + 8 * wb);
+        };
+        Unit<QT> cur, nxt;
+        if (total > 0) fetch(0, cur);
+        for (int rs = 0; rs < total && ok; ++rs) {
+            if (rs + 1 < total) {
+                fetch(rs + 1, nxt);
+                if (!ok) break;
+            }
+            uint32_t o[32];
+            cur.convert(j, o);
+            const int stage = j;
+            if (lane == 0) ok = pair_wait<true>(aempty_s + 8 * stage, (rs & 1) ^ 1, sm, p.status);
+            ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
+            if (!ok) break;
+            store_row(o, a_s + stage * kStageABytes + row_off, r7);
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(afull_leader + 8 * stage);
+            cur = nxt;
+        }
+    } else {
+        // ===== epilogue: this CTA's 128 rows of the accumulator ====================================
+        const int q = warp & 3;
+        const uint32_t tempty_leader = mapa_rank(tempty_s, 0);
+        int tcount = 0;
+        for (int tile = pair; tile < p.pair_tiles; tile += n_pairs, ++tcount) {
+            int stripe, t0, width;
+            pair_tile(p, tile, stripe, t0, width);
+            const int buf = tcount & 1;
+            bool ok = pair_wait<false>(tfull_s + 8 * buf, (tcount >> 1) & 1, sm, p.status);
+            ok = __all_sync(0xFFFFFFFFu, ok);
+            if (!ok) break;
+            tc_fence_after();
+            const int n = stripe * 2 * BM + (int)rank * BM + q * 32 + lane;
+            const int m0 = t0;
+            for (int c0 = 0; c0 < width; c0 += 32) {
+                uint32_t v[32];
+                tmem_ld32(tmem_base + buf * 256 + ((uint32_t)(q * 32) << 16) + c0, v);
+                tmem_ld_wait();
+                if (n < p.N) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const int m = m0 + c0 + i;
+                        if (m < p.M) {
+                            const long long idx = (long long)m * p.ldy + n;
+                            if (p.y_is_bf16)
+                                reinterpret_cast<__nv_bfloat16 *>(p.y)[idx] = __float2bfloat16_rn(__uint_as_float(v[i]));
+                            else
+                                reinterpret_cast<float *>(p.y)[idx] = __uint_as_float(v[i]);
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(tempty_leader + 8 * buf);
+        }
+    }
+
+    // both CTAs meet (also after an abort) before either releases shared or tensor memory
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();
+    if (warp == 0) {
+        __syncwarp();
+        tc_fence_after();
+        tmem_dealloc_pair(tmem_base, kTmemCols);
+    }
+}
+
 // Activations -> fp16, the format the weights are dequantized to (both tensor-core operands must
 // share one format).  bf16 activations convert exactly unless they exceed fp16's range, where they
 // saturate to +-65504; fp32 activations round to nearest even.
@@ -710,6 +1088,47 @@ cudaError_t launch_gemm(const GemmParams &p, const GemmMaps &m, int grid, cudaSt
     return cudaGetLastError();
 }
 
+template <int QT>
+cudaError_t launch_gemm_pair(const GemmParams &p, const GemmMaps &m, int grid, cudaStream_t st) {
+    auto kern = gemm_tc_pair_kernel<QT>;
+    constexpr size_t smem = pair_smem_data_bytes(QT) + sizeof(PairSmem) + 1024;
+    static_assert(smem <= 232448, "shared-memory plan exceeds the 227 KB a block may use");
+    static int configured_dev = -1;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev != configured_dev) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+        configured_dev = dev;
+    }
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(kPairThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kern, p, m.x, m.w, m.wtail, m.d, m.dtail);
+}
+
+// Number of tiles of the two-CTA kernel.  A K-step of this kernel costs about the same whatever
+// the tile's width (the dequantization of the 128 x 64 weight block and its hand-over bound it,
+// not the MMA), so the fewest, widest tiles win: every stripe is cut into ceil(units / 8) tiles of
+// nearly equal width.
+void pick_pair_tiles(GemmParams &p, int width_override) {
+    const int stripes = p.n_tiles, upr = p.units_per_row;
+    int tps = (upr + 7) / 8;
+    if (width_override >= 32 && width_override <= 256) tps = (upr + width_override / 32 - 1) / (width_override / 32);
+    p.tps = tps;
+    p.extra = 0;
+    p.pair_tiles = stripes * tps;
+}
+
 // Token-tile width: with more tiles than SMs the last wave is partly idle, so a slightly narrower
 // tile that fills the waves evenly can finish sooner.  Cost model: waves x (width + 90), the
 // constant standing for the part of a K-step's time that does not shrink with the tile (measured:
@@ -786,9 +1205,18 @@ cudaError_t gemm_launch(const GemmLaunch &a, cudaStream_t st) {
     p.y_is_bf16 = a.y_is_bf16;
     p.M = a.M;
     p.n_tiles = (a.N + BM - 1) / BM;
-    const int widest = bn_max(a.qt);
-    p.bn = pick_bn(a.M, p.n_tiles, a.sm_count, widest);
-    if (a.bn_override >= 16 && a.bn_override <= widest && a.bn_override % 16 == 0) p.bn = a.bn_override;
+    // large products run on CTA pairs (256-row tiles); small ones keep the one-CTA kernel
+    const bool use_pair = a.pair && a.M >= 128 && a.N > BM && a.sm_count >= 2;
+    if (use_pair) {
+        p.n_tiles = (a.N + 2 * BM - 1) / (2 * BM);       // 256-row stripes
+        p.units_per_row = (a.M + 31) / 32;
+        p.bn = 256;
+        pick_pair_tiles(p, a.bn_override);
+    } else {
+        const int widest = bn_max(a.qt);
+        p.bn = pick_bn(a.M, p.n_tiles, a.sm_count, widest);
+        if (a.bn_override >= 16 && a.bn_override <= widest && a.bn_override % 16 == 0) p.bn = a.bn_override;
+    }
     p.m_tiles = (a.M + p.bn - 1) / p.bn;
     p.status = a.status;
     p.debug = a.debug;
@@ -797,7 +1225,7 @@ cudaError_t gemm_launch(const GemmLaunch &a, cudaStream_t st) {
     CUtensorMap &map = maps.x;
     const cuuint64_t gdim[2] = {(cuuint64_t)a.K, (cuuint64_t)a.M};
     const cuuint64_t gstride[1] = {(cuuint64_t)a.ldx * 2};
-    const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)p.bn};
+    const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)(use_pair ? 128 : p.bn)};
     const cuuint32_t estride[2] = {1, 1};
     CUresult r = enc(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(a.x), gdim, gstride, box, estride,
                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -818,6 +1246,15 @@ cudaError_t gemm_launch(const GemmLaunch &a, cudaStream_t st) {
     if (!okm) return cudaErrorInvalidValue;
 
     const int tiles = p.m_tiles * p.n_tiles;
+    if (use_pair) {
+        const int grid2 = 2 * std::min(p.pair_tiles, a.sm_count / 2);
+        switch (a.qt) {
+        case QT_Q4_K: return launch_gemm_pair<QT_Q4_K>(p, maps, grid2, st);
+        case QT_Q6_K: return launch_gemm_pair<QT_Q6_K>(p, maps, grid2, st);
+        case QT_Q8_0: return launch_gemm_pair<QT_Q8_0>(p, maps, grid2, st);
+        default: return cudaErrorInvalidValue;
+        }
+    }
     const int grid = std::min(tiles, a.sm_count);
     switch (a.qt) {
     case QT_Q4_K: return launch_gemm<QT_Q4_K>(p, maps, grid, st);

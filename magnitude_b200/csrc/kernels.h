@@ -83,6 +83,7 @@ struct GemmLaunch {
     int sm_count;
     int bn_override;         // 0 = choose the token tile
     int debug;               // timing experiments (see GemmParams::debug); 0 in production
+    int pair;                // 1 = large products use the two-CTA kernel (256-row tiles)
 };
 size_t gemm_x_scratch_bytes(int M, int K);
 // activations (bf16 or fp32) -> fp16 rows of ((K + 7) & ~7) elements in `scratch`
