@@ -41,7 +41,7 @@ FALLBACK_TFLOPS = 1400.0
 # 4-layer launch and is proportional to the layers a launch streams, so it is kept as a ratio to
 # the algorithmic bytes; a prefill launch is one whole product whatever the number of copies.
 NCU_DECODE_TRAFFIC_PER_ALGORITHMIC_BYTE = 1.009
-NCU_PREFILL_TRAFFIC_BYTES_PER_LAUNCH = 74.4e6
+NCU_PREFILL_TRAFFIC_BYTES_PER_LAUNCH = 73.9e6
 
 
 def peaks():
@@ -608,7 +608,7 @@ def run_prefill(args):
         "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "fp16 x fp16 tcgen05.mma, fp32 accumulate in TMEM (weights dequantized exactly to fp16, activations bf16 -> fp16)",
         "data": "synthetic", "config": cfg,
-        "roofline": {"bound": "tensor", "kernel": "gemm_tc_kernel<Q4_K,fp16> (+ convert_x_kernel per product)", "achieved": value, "peak": peak,
+        "roofline": {"bound": "tensor", "kernel": "gemm_tc_pair_kernel<Q4_K> (+ convert_x_vec8_kernel per product)", "achieved": value, "peak": peak,
                      "unit": "TFLOP/s", "frac": value / peak, "peak_source": f"of {src}", "traffic": NCU_PREFILL_TRAFFIC_BYTES_PER_LAUNCH,
                      "us_per_launch": ms_step * 1e3 / copies,
                      "note": "2*M*N*K per product / device time per product, activation conversion launch included"},
