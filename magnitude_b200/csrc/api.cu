@@ -89,7 +89,8 @@ struct b200q_ctx {
     // prefill path: bf16 copy of fp32 activations
     void *gemm_scratch = nullptr;
     size_t gemm_scratch_bytes = 0;
-    int gemm_bn = 0, gemm_debug = 0, gemm_pair = 0;
+    float *gemm_part = nullptr;       // K-split partial products of skinny batches (allocated on first use)
+    int gemm_bn = 0, gemm_debug = 0, gemm_pair = 0, gemm_ksplit = 1;
     // tunables (environment overrides for experiments)
     int gemv_warps = 0, gemv_depth = 0, gemv_grid = 0, gemv_smem = 0, gemv_rows = 0, gemv_debug = 0, gemv_pdl = 1;
     // tensor parallel
@@ -299,6 +300,13 @@ b200q_status run_gemm(b200q_ctx *ctx, const b200q_weight *w, const void *x, int 
     a.bn_override = ctx->gemm_bn;
     a.debug = ctx->gemm_debug;
     a.pair = ctx->gemm_pair;
+    if (M <= 64 && !ctx->gemm_part && ctx->gemm_ksplit) {
+        void *ptr = nullptr;
+        if (cudaMalloc(&ptr, kGemmPartBytes) == cudaSuccess) ctx->gemm_part = reinterpret_cast<float *>(ptr);
+        else cudaGetLastError();      // no workspace: the product runs unsplit
+    }
+    a.part = ctx->gemm_ksplit ? ctx->gemm_part : nullptr;
+    a.part_bytes = kGemmPartBytes;
     cudaError_t e = gemm_launch(a, st);
     if (e != cudaSuccess) return cuda_fail(ctx, e, "tensor-core GEMM launch");
     ++*launches;
@@ -435,6 +443,7 @@ b200q_status b200q_ctx_create(int32_t device, b200q_ctx **out) {
     ctx->gemm_bn = env_int("B200Q_GEMM_BN", 0);
     ctx->gemm_debug = env_int("B200Q_GEMM_DEBUG", 0);
     ctx->gemm_pair = env_int("B200Q_GEMM_PAIR", 1);
+    ctx->gemm_ksplit = env_int("B200Q_GEMM_KSPLIT", 1);
     *out = ctx;
     return B200Q_OK;
 }
@@ -452,6 +461,7 @@ void b200q_ctx_destroy(b200q_ctx *ctx) {
     if (ctx->hx_dev) cudaFree(ctx->hx_dev);
     if (ctx->hy_dev) cudaFree(ctx->hy_dev);
     if (ctx->gemm_scratch) cudaFree(ctx->gemm_scratch);
+    if (ctx->gemm_part) cudaFree(ctx->gemm_part);
     if (ctx->status_dev) cudaFree(ctx->status_dev);
     delete ctx;
 }

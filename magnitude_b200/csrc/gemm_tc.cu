@@ -69,12 +69,13 @@ struct GemmParams {
     int m_tiles, n_tiles;
     int nchunks_full;        // chunks of 8 whole records per row; a shorter tail chunk may follow
     int *status;
+    int ksplit;              // one-CTA kernel: K ranges per tile (1 = none)
+    float *part;             // ... their partial products [ksplit][M][N] when ksplit > 1
     int units_per_row;       // two-CTA kernel: 32-token units per 256-row stripe, ceil(M / 32)
     int tps, extra;          // ... tiles per stripe; the first `extra` stripes have one more
     int pair_tiles;          // ... tiles in all
     int debug;               // timing experiments only (results invalid): 1 no activation loads, 2 no dequant math,
-                             // 4 no weight loads, 8 no MMA, 16 no epilogue body, 32 no proxy fence,
-                             // 64 plain arrives instead of commits, 256 print per-role clock counts from block 0
+                             // 4 no weight loads, 8 no MMA, 16 no epilogue body, 32 no proxy fence
 };
 
 struct GemmSmem {
@@ -349,6 +350,23 @@ __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, Gem
     }
 }
 
+// Split of the K range for small products: with few output tiles (a skinny batch against a
+// weight of a few thousand rows) most SMs would idle, so each tile's records are cut into
+// p.ksplit ranges that run as separate work units; their fp32 partial products go to a workspace
+// [ksplit][M][N] and a second kernel adds them up in split order (deterministic).
+struct TileK {
+    int tn, tm, r0, r1;      // weight-row tile, token tile, record range [r0, r1) of the row
+};
+__device__ __forceinline__ TileK tile_k(const GemmParams &p, int tile) {
+    TileK t;
+    const int s = tile % p.ksplit, q = tile / p.ksplit;
+    t.tn = q / p.m_tiles;
+    t.tm = q - t.tn * p.m_tiles;
+    t.r0 = (int)((long long)p.nsb * s / p.ksplit);
+    t.r1 = (int)((long long)p.nsb * (s + 1) / p.ksplit);
+    return t;
+}
+
 template <int QT>
 __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap,
                                                                const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap wtail,
@@ -363,7 +381,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const GemmParams p
     const uint32_t a_s = smem_u32(smem);
     const uint32_t b_s = a_s + kAStages * kStageABytes;
     const uint32_t w_s = b_s + SB_ * kStageBBytes;                // packed-weight buffers
-    const uint32_t d_s = w_s + kWBufs * WBUF;                     // Q6_K d groups, one buffer per chunk parity
+    const uint32_t d_s = w_s + kWBufs * WBUF;                     // Q6_K d groups, two buffers
     GemmSmem *sm = reinterpret_cast<GemmSmem *>(smem + smem_data_bytes(QT));
     const uint32_t wfull_s = smem_u32(sm->wfull), wempty_s = smem_u32(sm->wempty);
     const uint32_t afull_s = smem_u32(sm->afull), aempty_s = smem_u32(sm->aempty);
@@ -371,9 +389,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const GemmParams p
     const uint32_t tfull_s = smem_u32(sm->tmem_full), tempty_s = smem_u32(sm->tmem_empty);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n_tiles_total = p.m_tiles * p.n_tiles;
-    const int ksteps = p.nsb * 4;                 // K-steps per tile: four per 256-weight record
-    const int chunks_per_tile = (p.nsb + kChunkRecs - 1) / kChunkRecs;
+    const int n_units = p.m_tiles * p.n_tiles * p.ksplit;      // work units: (tile, K range)
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < kAStages; ++i) {
@@ -393,7 +409,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const GemmParams p
             mbar_init(wempty_s + 8 * i, kDequantWarps);
         }
         sm->abort = 0;
-        sm->wait_ns = (p.debug >> 12) ? (p.debug >> 12) : 40;
+        sm->wait_ns = 40;
         mbar_fence_init();
         fence_proxy_async();
     }
@@ -410,13 +426,12 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const GemmParams p
         // ===== TMA producer: activation tiles ======================================================
         if (lane == 0) {
             const uint32_t bytes = (uint32_t)p.bn * BK * 2;
-            int it = 0;             // K-steps issued so far (the ring runs across tiles)
+            int it = 0;             // K-steps issued so far (the ring runs across work units)
             bool ok = true;
-            for (int tile = blockIdx.x; tile < n_tiles_total && ok; tile += gridDim.x) {
-                const int tm = tile % p.m_tiles;
-                for (int ks = 0; ks < ksteps; ++ks, ++it) {
+            for (int unit = blockIdx.x; unit < n_units && ok; unit += gridDim.x) {
+                const TileK t = tile_k(p, unit);
+                for (int ks = 4 * t.r0; ks < 4 * t.r1; ++ks, ++it) {
                     const int stage = it % SB_;
-                    if (p.debug & 2048) continue;
                     ok = wait_or_abort<true>(bempty_s + 8 * stage, ((it / SB_) & 1) ^ 1, sm, p.status);
                     if (!ok) break;
                     if (p.debug & 1) {
@@ -424,18 +439,18 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const GemmParams p
                         continue;
                     }
                     mbar_expect_tx(bfull_s + 8 * stage, bytes);
-                    tma_load_2d(b_s + stage * kStageBBytes, &xmap, ks * BK, tm * p.bn, bfull_s + 8 * stage);
+                    tma_load_2d(b_s + stage * kStageBBytes, &xmap, ks * BK, t.tm * p.bn, bfull_s + 8 * stage);
                 }
             }
         }
     } else if (warp == 2) {
         // ===== TMA producer: packed weight records =================================================
         if (lane == 0) {
-            int rs = 0, tcount = 0;   // records issued so far, tiles started
+            int rs = 0, dcount = 0;   // records issued so far; d groups loaded so far (Q6_K)
             bool ok = true;
-            for (int tile = blockIdx.x; tile < n_tiles_total && ok; tile += gridDim.x, ++tcount) {
-                const int tn = tile / p.m_tiles;
-                for (int sb = 0; sb < p.nsb; ++sb, ++rs) {
+            for (int unit = blockIdx.x; unit < n_units && ok; unit += gridDim.x) {
+                const TileK t = tile_k(p, unit);
+                for (int sb = t.r0; sb < t.r1; ++sb, ++rs) {
                     // one record of each of the tile's 128 rows (four K-steps' worth)
                     const int c = sb >> 3, s_in = sb & 7;
                     const int wb = rs % kWBufs;
@@ -446,18 +461,19 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const GemmParams p
                         continue;
                     }
                     const bool tail = c >= p.nchunks_full;
+                    const bool need_d = QT == QT_Q6_K && (s_in == 0 || sb == t.r0);   // first record of a chunk (or of the range)
                     uint32_t tx = BM * REC;
-                    if (QT == QT_Q6_K && s_in == 0) tx += BM * 16;
+                    if (need_d) tx += BM * 16;
                     mbar_expect_tx(wfull_s + 8 * wb, tx);
                     tma_load_4d(w_s + wb * WBUF, tail ? &wtail : &wmap, s_in * (REC / 4), 0, tail ? 0 : c,
-                                tn * (BM / kRowGroup), wfull_s + 8 * wb);
-                    if (QT == QT_Q6_K && s_in == 0) {
-                        // the chunk's fp16 d values: the buffer of the chunk before last is free once the
-                        // record two back has been read, which the wait above has established
+                                t.tn * (BM / kRowGroup), wfull_s + 8 * wb);
+                    if (need_d) {
+                        // the chunk's fp16 d values go to the d buffer used two loads ago: every record that
+                        // read it is at least two records back, which the wait above has seen consumed
                         const int nrec = tail ? (p.nsb - c * kChunkRecs) : kChunkRecs;
-                        const int cs = tcount * chunks_per_tile + c;
-                        tma_load_4d(d_s + (cs & 1) * kDBufBytes, tail ? &dtail : &dmap, nrec * (REC / 4), 0, tail ? 0 : c,
-                                    tn * (BM / kRowGroup), wfull_s + 8 * wb);
+                        tma_load_4d(d_s + (dcount & 1) * kDBufBytes, tail ? &dtail : &dmap, nrec * (REC / 4), 0, tail ? 0 : c,
+                                    t.tn * (BM / kRowGroup), wfull_s + 8 * wb);
+                        ++dcount;
                     }
                 }
             }
@@ -467,30 +483,23 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const GemmParams p
         if (lane == 0) {
             const uint32_t idesc = (1u << 4) |                                   // C fp32; A and B fp16 (format 0)
                                     ((uint32_t)(p.bn >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-            int it = 0, tcount = 0;
-            long long tw_b = 0, tw_a = 0, t_iss = 0, tw_t = 0, t_com = 0;
+            int it = 0, ucount = 0;
             bool rdy_a = false, rdy_b = false;
-            const bool prof = (p.debug & 256) != 0;
-            const long long t_begin = clock64();
-            for (int tile = blockIdx.x; tile < n_tiles_total; tile += gridDim.x, ++tcount) {
-                const int buf = tcount & 1;
-                long long c0 = prof ? clock64() : 0;
-                bool ok = wait_or_abort<true>(tempty_s + 8 * buf, ((tcount >> 1) & 1) ^ 1, sm, p.status);
-                if (prof) tw_t += clock64() - c0;
+            for (int unit = blockIdx.x; unit < n_units; unit += gridDim.x, ++ucount) {
+                const TileK t = tile_k(p, unit);
+                const int buf = ucount & 1;
+                bool ok = wait_or_abort<true>(tempty_s + 8 * buf, ((ucount >> 1) & 1) ^ 1, sm, p.status);
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + buf * 256;
+                const int ksteps = 4 * (t.r1 - t.r0);
                 for (int ks = 0; ks < ksteps; ++ks, ++it) {
                     const int sa = it % kAStages, sb = it % SB_;
-                    if (prof) c0 = clock64();
                     // the probes for this K-step were issued before the previous one's MMAs
-                    ok = rdy_b || (p.debug & 2048) || wait_or_abort<true>(bfull_s + 8 * sb, (it / SB_) & 1, sm, p.status);
-                    long long c1 = prof ? clock64() : 0;
-                    ok = ok && (rdy_a || (p.debug & 1024) || wait_or_abort<true>(afull_s + 8 * sa, (it / kAStages) & 1, sm, p.status));
-                    long long c2 = prof ? clock64() : 0;
-                    if (prof) tw_b += c1 - c0, tw_a += c2 - c1;
+                    ok = rdy_b || wait_or_abort<true>(bfull_s + 8 * sb, (it / SB_) & 1, sm, p.status);
+                    ok = ok && (rdy_a || wait_or_abort<true>(afull_s + 8 * sa, (it / kAStages) & 1, sm, p.status));
                     if (!ok) break;
-                    if (p.debug & 512) tc_fence_after();
+                    tc_fence_after();
                     {   // probe the next K-step's barriers now; the answers arrive while the MMAs issue
                         const int nx = it + 1;
                         rdy_b = mbar_test_wait(bfull_s + 8 * (nx % SB_), (nx / SB_) & 1);
@@ -500,24 +509,14 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const GemmParams p
                     const uint64_t bdesc = make_desc_sw128(b_s + sb * kStageBBytes);
                     if (!(p.debug & 8))
 #pragma unroll
-                    for (int kk = 0; kk < BK / 16; ++kk)   // 16 fp16 = 32 bytes = +2 in the address field
-                        umma_f16(d_tmem, adesc + 2 * kk, bdesc + 2 * kk, idesc, (ks | kk) != 0);
-                    if (p.debug & 64) {
-                        mbar_arrive(aempty_s + 8 * sa);
-                        mbar_arrive(bempty_s + 8 * sb);
-                        continue;
-                    }
-                    long long c3 = prof ? clock64() : 0;
-                    if (!(p.debug & 1024)) umma_commit(aempty_s + 8 * sa);        // both stages may be refilled once these finish
-                    if (!(p.debug & 2048)) umma_commit(bempty_s + 8 * sb);
-                    if (prof) t_iss += c3 - c2, t_com += clock64() - c3;
+                        for (int kk = 0; kk < BK / 16; ++kk)   // 16 fp16 = 32 bytes = +2 in the address field
+                            umma_f16(d_tmem, adesc + 2 * kk, bdesc + 2 * kk, idesc, (ks | kk) != 0);
+                    umma_commit(aempty_s + 8 * sa);        // both stages may be refilled once these finish
+                    umma_commit(bempty_s + 8 * sb);
                 }
                 if (!ok) break;
                 umma_commit(tfull_s + 8 * buf);            // accumulator complete
             }
-            if (prof && blockIdx.x == 0 && it > 0)
-                printf("mma thread: %d k-steps, total %lld clk/k-step; wait B %lld, wait A %lld, probes+mma issue %lld, commits %lld, wait tmem %lld per tile\n",
-                       it, (clock64() - t_begin) / it, tw_b / it, tw_a / it, t_iss / it, t_com / it, tw_t / (tcount ? tcount : 1));
         }
     } else if (warp < kFirstEpiWarp) {
         // ===== dequant producers: weight tiles =====================================================
@@ -525,67 +524,76 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const GemmParams p
         const int r = t & (BM - 1), j = t >> 7;      // weight row of the tile; 64-weight unit of each record
         const int r7 = r & 7;
         const uint32_t row_off = (r >> 3) * 1024 + r7 * 128;
-        // Records are taken one ahead: the bytes of record rs + 1 move into registers before record rs
-        // is dequantized, so its buffer goes back to the TMA producer a whole record (four K-steps)
-        // before the ring would otherwise allow, and the refill latency stays off the critical path.
-        const int my_tiles = blockIdx.x < n_tiles_total ? (n_tiles_total - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-        const int total = my_tiles * p.nsb;
+        // Records are taken one ahead: the bytes of the next record move into registers before the
+        // current one is dequantized, so its buffer goes back to the TMA producer a whole record
+        // (four K-steps) before the ring would otherwise allow.
+        int f_unit = blockIdx.x, f_sb = 0, f_r1 = 0, f_r0 = 0;   // the record to fetch next
+        bool f_valid = f_unit < n_units;
+        if (f_valid) {
+            const TileK tk = tile_k(p, f_unit);
+            f_sb = f_r0 = tk.r0;
+            f_r1 = tk.r1;
+        }
+        int fetched = 0, dcount = 0;
         bool ok = true;
-        auto fetch = [&](int rs, Unit<QT> &u) {
-            const int wb = rs % kWBufs;
-            if (lane == 0) ok = wait_or_abort<true>(wfull_s + 8 * wb, (rs / kWBufs) & 1, sm, p.status);
+        auto fetch = [&](Unit<QT> &u) {
+            const int wb = fetched % kWBufs;
+            if (lane == 0) ok = wait_or_abort<true>(wfull_s + 8 * wb, (fetched / kWBufs) & 1, sm, p.status);
             ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
             if (!ok) return;
-            const int tcount = rs / p.nsb, sb = rs - tcount * p.nsb;
-            const int cs = tcount * chunks_per_tile + (sb >> 3);
-            u.load(w_s + wb * WBUF + r * REC, d_s + (cs & 1) * kDBufBytes + r * 16 + 2 * (sb & 7), j);
+            if (QT == QT_Q6_K && ((f_sb & 7) == 0 || f_sb == f_r0)) ++dcount;     // this record came with a new d group
+            u.load(w_s + wb * WBUF + r * REC, d_s + ((dcount - 1) & 1) * kDBufBytes + r * 16 + 2 * (f_sb & 7), j);
             __syncwarp();
             if (lane == 0) mbar_arrive(wempty_s + 8 * wb);     // the record is in registers
+            ++fetched;
+            if (++f_sb == f_r1) {                              // on to the next work unit of this CTA
+                f_unit += gridDim.x;
+                f_valid = f_unit < n_units;
+                if (f_valid) {
+                    const TileK tk = tile_k(p, f_unit);
+                    f_sb = f_r0 = tk.r0;
+                    f_r1 = tk.r1;
+                }
+            }
         };
         Unit<QT> cur, nxt;
-        const bool prof = (p.debug & 256) != 0;
-        long long t_fetch = 0, t_wait = 0, t_emit = 0;
-        const long long t_begin = clock64();
-        if (total > 0) fetch(0, cur);
-        for (int rs = 0; rs < total && ok; ++rs) {
-            long long c0 = prof ? clock64() : 0;
-            if (rs + 1 < total) {
-                fetch(rs + 1, nxt);
+        bool have_cur = f_valid;
+        if (have_cur) fetch(cur);
+        for (int rs = 0; have_cur && ok; ++rs) {
+            const bool have_next = f_valid;
+            if (have_next) {
+                fetch(nxt);
                 if (!ok) break;
             }
             // the arithmetic happens while the tensor core still reads the stage's previous contents:
             // once the stage is free only the eight stores remain before it can be handed over
             uint32_t o[32];
             if (!(p.debug & 2)) cur.convert(j, o);
-            long long c1 = prof ? clock64() : 0;
             const int stage = j;       // K-step 4 rs + j: kAStages == 4, so the group owns this stage
-            if (lane == 0 && !(p.debug & 1024)) ok = wait_or_abort<true>(aempty_s + 8 * stage, (rs & 1) ^ 1, sm, p.status);
+            if (lane == 0) ok = wait_or_abort<true>(aempty_s + 8 * stage, (rs & 1) ^ 1, sm, p.status);
             ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
             if (!ok) break;
-            long long c2 = prof ? clock64() : 0;
             if (!(p.debug & 2)) store_row(o, a_s + stage * kStageABytes + row_off, r7);
             if (!(p.debug & 32)) fence_proxy_async();       // generic-proxy stores -> visible to the tensor core's reads
             __syncwarp();
-            if (lane == 0 && !(p.debug & 1024)) mbar_arrive(afull_s + 8 * stage);
+            if (lane == 0) mbar_arrive(afull_s + 8 * stage);
             cur = nxt;
-            if (prof) t_fetch += c1 - c0, t_wait += c2 - c1, t_emit += clock64() - c2;
+            have_cur = have_next;
         }
-        if (prof && blockIdx.x == 0 && (t & 127) == 0 && total > 0)
-            printf("dequant group %d: %d records, total %lld clk/record; fetch+convert %lld, wait stage %lld, store+fence+arrive %lld\n", j, total,
-                   (clock64() - t_begin) / total, t_fetch / total, t_wait / total, t_emit / total);
     } else {
         // ===== epilogue ============================================================================
         const int q = warp & 3;            // TMEM lane quadrant this warp may read
-        int tcount = 0;
-        for (int tile = blockIdx.x; tile < n_tiles_total; tile += gridDim.x, ++tcount) {
-            const int tn = tile / p.m_tiles, tm = tile % p.m_tiles;
-            const int buf = tcount & 1;
-            bool ok = wait_or_abort<false>(tfull_s + 8 * buf, (tcount >> 1) & 1, sm, p.status);
+        int ucount = 0;
+        for (int unit = blockIdx.x; unit < n_units; unit += gridDim.x, ++ucount) {
+            const TileK t = tile_k(p, unit);
+            const int buf = ucount & 1;
+            bool ok = wait_or_abort<false>(tfull_s + 8 * buf, (ucount >> 1) & 1, sm, p.status);
             ok = __all_sync(0xFFFFFFFFu, ok);
             if (!ok) break;
             tc_fence_after();
-            const int n = tn * BM + q * 32 + lane;
-            const int m0 = tm * p.bn;
+            const int n = t.tn * BM + q * 32 + lane;
+            const int m0 = t.tm * p.bn;
+            float *part = p.ksplit > 1 ? p.part + (size_t)(unit % p.ksplit) * p.M * p.N : nullptr;
             for (int c0 = 0; c0 < ((p.debug & 16) ? 0 : p.bn); c0 += 32) {
                 uint32_t v[32];
                 tmem_ld32(tmem_base + buf * 256 + ((uint32_t)(q * 32) << 16) + c0, v);
@@ -595,6 +603,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const GemmParams p
                     for (int i = 0; i < 32; ++i) {
                         const int m = m0 + c0 + i;
                         if (m < p.M && c0 + i < p.bn) {
+                            if (part) {
+                                part[(size_t)m * p.N + n] = __uint_as_float(v[i]);
+                                continue;
+                            }
                             const long long idx = (long long)m * p.ldy + n;
                             if (p.y_is_bf16)
                                 reinterpret_cast<__nv_bfloat16 *>(p.y)[idx] = __float2bfloat16_rn(__uint_as_float(v[i]));
@@ -617,6 +629,18 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const GemmParams p
         __syncwarp();
         tc_fence_after();
         tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+// sums the K-range partial products of a split launch in split order and stores the output
+__global__ void gemm_ksplit_sum_kernel(const float *__restrict__ part, int ksplit, int M, int N, void *y, long long ldy, int y_is_bf16) {
+    const long long total = (long long)M * N;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        float v = part[i];
+        for (int s = 1; s < ksplit; ++s) v += part[(long long)s * total + i];
+        const long long m = i / N, n = i - m * N;
+        if (y_is_bf16) reinterpret_cast<__nv_bfloat16 *>(y)[m * ldy + n] = __float2bfloat16_rn(v);
+        else reinterpret_cast<float *>(y)[m * ldy + n] = v;
     }
 }
 
@@ -1246,6 +1270,17 @@ cudaError_t gemm_launch(const GemmLaunch &a, cudaStream_t st) {
     if (!okm) return cudaErrorInvalidValue;
 
     const int tiles = p.m_tiles * p.n_tiles;
+    p.ksplit = 1;
+    p.part = nullptr;
+    if (!use_pair && a.part && a.M <= 64 && tiles * 2 <= a.sm_count) {
+        // few tiles: cut K so that every SM gets a work unit (one round)
+        int ks = std::min(p.nsb, a.sm_count / tiles);
+        while (ks > 1 && (size_t)ks * a.M * a.N * sizeof(float) > a.part_bytes) --ks;
+        if (ks > 1) {
+            p.ksplit = ks;
+            p.part = a.part;
+        }
+    }
     if (use_pair) {
         const int grid2 = 2 * std::min(p.pair_tiles, a.sm_count / 2);
         switch (a.qt) {
@@ -1255,13 +1290,19 @@ cudaError_t gemm_launch(const GemmLaunch &a, cudaStream_t st) {
         default: return cudaErrorInvalidValue;
         }
     }
-    const int grid = std::min(tiles, a.sm_count);
+    const int grid = std::min(tiles * p.ksplit, a.sm_count);
+    cudaError_t e;
     switch (a.qt) {
-    case QT_Q4_K: return launch_gemm<QT_Q4_K>(p, maps, grid, st);
-    case QT_Q6_K: return launch_gemm<QT_Q6_K>(p, maps, grid, st);
-    case QT_Q8_0: return launch_gemm<QT_Q8_0>(p, maps, grid, st);
+    case QT_Q4_K: e = launch_gemm<QT_Q4_K>(p, maps, grid, st); break;
+    case QT_Q6_K: e = launch_gemm<QT_Q6_K>(p, maps, grid, st); break;
+    case QT_Q8_0: e = launch_gemm<QT_Q8_0>(p, maps, grid, st); break;
     default: return cudaErrorInvalidValue;
     }
+    if (e != cudaSuccess || p.ksplit == 1) return e;
+    const long long total = (long long)a.M * a.N;
+    gemm_ksplit_sum_kernel<<<(int)std::min<long long>((total + 255) / 256, 148 * 4), 256, 0, st>>>(p.part, p.ksplit, a.M, a.N, a.y, a.ldy,
+                                                                                             a.y_is_bf16);
+    return cudaGetLastError();
 }
 
 // ---------------------------------------------------------------------------------------------
