@@ -92,7 +92,7 @@ struct b200q_ctx {
     float *gemm_part = nullptr;       // K-split partial products of skinny batches (allocated on first use)
     int gemm_bn = 0, gemm_debug = 0, gemm_pair = 0, gemm_ksplit = 1;
     // tunables (environment overrides for experiments)
-    int gemv_warps = 0, gemv_depth = 0, gemv_grid = 0, gemv_smem = 0, gemv_rows = 0, gemv_debug = 0, gemv_pdl = 1;
+    int gemv_warps = 0, gemv_depth = 0, gemv_grid = 0, gemv_smem = 0, gemv_rows = 0, gemv_debug = 0, gemv_pdl = 1, gemv_teams = 2;
     // tensor parallel
     NcclComm comm = nullptr;
     int tp_rank = 0, tp_world = 1;
@@ -225,6 +225,7 @@ void fill_job(StreamJob &J, const b200q_weight *const *w, int nw, const void *x,
     J.x_vec_ok = ((reinterpret_cast<uintptr_t>(x) & 15) == 0) && ((ldx * xelt) % 16 == 0);
     J.y_is_bf16 = y_dtype == B200Q_TYPE_BF16;
     J.flags = flags;
+    J.team = 0;
     stream_job_finish(J);
 }
 
@@ -244,6 +245,7 @@ b200q_status run_stream(b200q_ctx *ctx, const StreamJob *jobs_host, const Stream
     a.grid = ctx->gemv_grid;
     a.debug = ctx->gemv_debug;
     a.pdl = ctx->gemv_pdl;
+    a.teams = ctx->gemv_teams;
     a.peer_rank = ctx->peer_rank;
     a.peer_world = ctx->peer_world;
     for (int r = 0; r < kPeerMaxWorld; ++r) a.peer_base[r] = ctx->peer_base[r];
@@ -440,6 +442,7 @@ b200q_status b200q_ctx_create(int32_t device, b200q_ctx **out) {
     ctx->gemv_rows = env_int("B200Q_GEMV_ROWS", 0);
     ctx->gemv_debug = env_int("B200Q_GEMV_DEBUG", 0);
     ctx->gemv_pdl = env_int("B200Q_GEMV_PDL", 1);
+    ctx->gemv_teams = env_int("B200Q_GEMV_TEAMS", 2);
     ctx->gemm_bn = env_int("B200Q_GEMM_BN", 0);
     ctx->gemm_debug = env_int("B200Q_GEMM_DEBUG", 0);
     ctx->gemm_pair = env_int("B200Q_GEMM_PAIR", 1);
@@ -785,6 +788,7 @@ b200q_status b200q_plan_create(b200q_ctx *ctx, const b200q_job *jobs, int32_t n_
         pl->jobs.push_back(J);
     }
     if (!pl->jobs.empty()) {
+        stream_assign_teams(pl->jobs.data(), (int)pl->jobs.size());
         const size_t bytes = pl->jobs.size() * sizeof(StreamJob);
         cudaError_t e = cudaMalloc(&pl->jobs_dev, bytes);
         if (e == cudaSuccess) e = cudaMemcpy(pl->jobs_dev, pl->jobs.data(), bytes, cudaMemcpyHostToDevice);

@@ -57,6 +57,7 @@ struct StreamParams {
     int x_bytes;             // ... reserved for the fixed-point activation
     int partial_bytes;       // ... for the per-(row, chunk) partial sums
     int has_dep;             // some job waits for earlier jobs: CTAs count completions
+    int teams;               // 2: the consumer warps work as two teams on different jobs at the same time
     int debug;               // experiments only: 1 stream without computing, 2 compute without
                              // streaming, 4 skip the activation prologue, 8 skip the final pass,
                              // 64 do not wait for the peers' partial sums
@@ -71,10 +72,10 @@ struct SmemHead {
     uint64_t full[kMaxWarps * kMaxDepth];
     uint64_t empty[kMaxWarps * kMaxDepth];
     int fail;                // raised by any warp that gave up a wait; everybody then drains and leaves
-    int decide;              // thread 0's sample of `fail`, taken before a barrier so all warps agree
+    int decide[2];           // per team: its first thread's sample of `fail`, taken before a barrier so all its warps agree
     int prod_done;           // the producer warp has stopped issuing copies
     int issued[kMaxWarps];   // ... after issuing this many items into each consumer's ring
-    unsigned xepoch;         // exchanges this CTA has posted so far (loaded from the exchange buffer)
+    unsigned xepoch[2];      // per team: exchanges posted so far (loaded from the exchange buffer)
     int xfail;               // a wait for a peer's partial sums ran out
 };
 
@@ -99,7 +100,8 @@ __device__ __forceinline__ void locate_group(const StreamJob &J, int vg, int &s,
     g = vg - J.seg[s].group_begin;
 }
 
-__device__ __forceinline__ void consumer_sync(int T) { asm volatile("bar.sync 1, %0;" ::"r"(T) : "memory"); }
+// barrier of one consumer team (hardware barrier 1 + team; barrier 0 is __syncthreads)
+__device__ __forceinline__ void team_sync(int team, int T) { asm volatile("bar.sync %0, %1;" ::"r"(1 + team), "r"(T) : "memory"); }
 
 // one item (a tile: up to 4 rows x one chunk) of one job for this lane's 64-weight unit;
 // `sl` = shared address of the tile, `stride` = byte distance between its rows
@@ -170,9 +172,13 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1) stream_kernel(const S
     SmemHead &head = *reinterpret_cast<SmemHead *>(smem);
     const uint32_t full0 = smem_u32(head.full), empty0 = smem_u32(head.empty);
     StreamJob *jobs_s = reinterpret_cast<StreamJob *>(smem + kHeadBytes);
-    uint8_t *xbase = smem + kHeadBytes + p.jobs_bytes;
-    float *partial = reinterpret_cast<float *>(xbase + p.x_bytes);          // [row][chunk][MT]
-    uint8_t *rings = reinterpret_cast<uint8_t *>(partial) + p.partial_bytes;
+    uint8_t *xbase0 = smem + kHeadBytes + p.jobs_bytes;                       // one activation area per team
+    float *partial0 = reinterpret_cast<float *>(xbase0 + p.teams * p.x_bytes); // [row][chunk][MT], one per team
+    uint8_t *rings = reinterpret_cast<uint8_t *>(partial0) + p.teams * p.partial_bytes;
+    // Two teams: while one team sums, stores and prepares the next activation (the per-job work
+    // that keeps no data moving), the other is in the middle of its own job, so the SM always has
+    // warps doing block dots.  Team 0 = consumer warps [0, cw0), team 1 = [cw0, CW).
+    const int cw0 = p.teams == 2 ? (CW + 1) / 2 : CW;
     const int slot_bytes = R * p.chunk_stride;
     const int ring_bytes = D * slot_bytes;
 
@@ -207,64 +213,78 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1) stream_kernel(const S
         const bool feeder = lane < CW && !(p.debug & 2);
         const uint32_t ring_s = smem_u32(rings + lane * ring_bytes);
         const uint32_t fbar = full0 + lane * kMaxDepth * 8, ebar = empty0 + lane * kMaxDepth * 8;
+        // the consumer this lane feeds: its team, its index and the number of warps in that team
+        const int my_team = lane >= cw0 ? 1 : 0;
+        const int twarp = lane - (my_team ? cw0 : 0), tcw = my_team ? CW - cw0 : cw0;
         int slot = 0, k = 0;
         uint32_t phase = 0;            // parity of the release this slot's next reuse waits for
         bool dead = false;
-#pragma unroll 1
-        for (int jb = 0; jb < p.njobs && !dead; ++jb) {
+        // every lane walks its own team's jobs: job cursor, item cursor inside the job
+        int jb = -1, n_items = 0, item = 0, g = 0, c = 0, gb = 0;
+        auto next_job = [&]() {
+            do { ++jb; } while (jb < p.njobs && p.teams == 2 && jobs_s[jb].team != my_team);
+            if (!feeder) jb = p.njobs;
+            if (jb >= p.njobs) return;
             const StreamJob &J = jobs_s[jb];
-            const int gb = (int)((long long)J.total_groups * blockIdx.x / gridDim.x);
+            gb = (int)((long long)J.total_groups * blockIdx.x / gridDim.x);
             const int ge = (int)((long long)J.total_groups * (blockIdx.x + 1) / gridDim.x);
-            const int n_items = (ge - gb) * J.nchunks;
-            int item = feeder ? lane : n_items;
-            int g = 0, c = lane;       // item = g * nchunks + c, kept without dividing
+            n_items = (ge - gb) * J.nchunks;
+            item = twarp;
+            g = 0, c = twarp;          // item = g * nchunks + c, kept without dividing
             while (c >= J.nchunks) { c -= J.nchunks; ++g; }
-            uint64_t t_first = 0;
-            bool timing = false;
-            int idle = 0;
+        };
+        next_job();
+        uint64_t t_first = 0;
+        bool timing = false;
+        int idle = 0;
 #pragma unroll 1
-            while (true) {
-                bool progressed = false;
-                if (*reinterpret_cast<volatile int *>(&head.fail)) { dead = true; break; }
-                if (item < n_items) {
+        while (true) {
+            bool progressed = false;
+            if (*reinterpret_cast<volatile int *>(&head.fail)) { dead = true; break; }
+            if (jb < p.njobs) {
+                if (item >= n_items) {
+                    next_job();
+                    progressed = true;
+                } else {
+                    const StreamJob &J = jobs_s[jb];
                     const bool free_slot = (k < D) || mbar_test_wait(ebar + 8 * slot, phase ^ 1u);
                     if (free_slot) {
                         int sg, lg;
                         locate_group(J, gb + g, sg, lg);
-                        const int nr = group_rows(lg, J.seg[sg].n);
                         const uint32_t bytes = R * ((c == J.nchunks - 1) ? J.bytes_tail : J.bytes_full);   // whole tile, padding rows included
                         const uint32_t bar = fbar + 8 * slot;
                         fence_proxy_async();   // the consumer's reads of this slot precede the engine's writes
                         mbar_expect_tx(bar, bytes);
                         bulk_g2s(ring_s + slot * slot_bytes, J.seg[sg].w + tile_off(J.qt, lg, c, J.seg[sg].n, J.nsb),
                                  bytes, bar);
-                        item += CW;
-                        c += CW;
+                        item += tcw;
+                        c += tcw;
                         while (c >= J.nchunks) { c -= J.nchunks; ++g; }
                         ++k;
                         if (++slot == D) { slot = 0; phase ^= 1u; }
                         progressed = true;
                     }
                 }
-                if (__all_sync(mask, item >= n_items)) break;
-                if (__any_sync(mask, progressed)) {
-                    idle = 0;
-                    timing = false;
-                } else if (++idle >= 1024) {   // nobody moved for a while: look at the clock
-                    idle = 0;
-                    const uint64_t now = globaltimer_ns();
-                    if (!timing) {
-                        timing = true;
-                        t_first = now;
-                    } else if (now - t_first > kWaitLimitNs) {
-                        if (lane == 0) atomicMax(p.status, DEV_ERR_PIPE_TIMEOUT);
-                        *reinterpret_cast<volatile int *>(&head.fail) = 1;
-                        dead = true;
-                        break;
-                    }
+            }
+            if (__all_sync(mask, jb >= p.njobs)) break;
+            if (__any_sync(mask, progressed)) {
+                idle = 0;
+                timing = false;
+            } else if (++idle >= 1024) {   // nobody moved for a while: look at the clock
+                idle = 0;
+                const uint64_t now = globaltimer_ns();
+                if (!timing) {
+                    timing = true;
+                    t_first = now;
+                } else if (now - t_first > kWaitLimitNs) {
+                    if (lane == 0) atomicMax(p.status, DEV_ERR_PIPE_TIMEOUT);
+                    *reinterpret_cast<volatile int *>(&head.fail) = 1;
+                    dead = true;
+                    break;
                 }
             }
         }
+        (void)dead;
         // tell the consumers how much is (or was) in flight, so a failing CTA can wait for exactly
         // those copies before its shared memory is released
         if (lane < CW) head.issued[lane] = k;
@@ -279,7 +299,14 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1) stream_kernel(const S
     // =========================================================================================
     // consumer warps
     // =========================================================================================
-    const int T = CW * 32;
+    const int team = warp >= cw0 ? 1 : 0;
+    const int tw0 = team ? cw0 : 0;                 // first warp of this thread's team
+    const int tcw = team ? CW - cw0 : cw0;          // warps in the team
+    const int T = tcw * 32;                         // threads in the team
+    const int tid = threadIdx.x - tw0 * 32;         // thread index inside the team
+    const int twarp = warp - tw0;
+    uint8_t *xbase = xbase0 + team * p.x_bytes;
+    float *partial = partial0 + team * (p.partial_bytes >> 2);
     const uint32_t ring_sa = smem_u32(rings + warp * ring_bytes);
     const uint32_t fbar = full0 + warp * kMaxDepth * 8, ebar = empty0 + warp * kMaxDepth * 8;
     const int lsb = lane >> 2, j = lane & 3;   // this lane's record and 64-weight group in a chunk
@@ -312,12 +339,12 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1) stream_kernel(const S
     auto exchange_complete = [&](int job, unsigned e) {
         const StreamJob &Jc = jobs_s[job];
         const unsigned long long *slots = reinterpret_cast<const unsigned long long *>(p.peer_base[p.peer_rank] + kPeerFusedSlotOff) +
-                                          (size_t)(e & 1) * kPeerMaxWorld * kPeerSlotFloats;
+                                          (size_t)(team * 2 + (e & 1)) * kPeerMaxWorld * kPeerSlotFloats;
         const int gbc = (int)((long long)Jc.total_groups * blockIdx.x / gridDim.x);
         const int gec = (int)((long long)Jc.total_groups * (blockIdx.x + 1) / gridDim.x);
         const int n = Jc.seg[0].n;
         const int cells = (gec - gbc) * R * MT;
-        for (int t = threadIdx.x; t < cells; t += T) {
+        for (int t = tid; t < cells; t += T) {
             const int rl = t / MT, m = t - rl * MT;
             const int row = gbc * R + rl;
             if (row < n && m < p.M) {
@@ -346,15 +373,18 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1) stream_kernel(const S
         }
     };
 
+    bool first_job = true;
 #pragma unroll 1
     for (int jb = 0; jb < p.njobs; ++jb) {
         const StreamJob &J = jobs_s[jb];
+        if (p.teams == 2 && J.team != team) continue;      // the other team's job
 
         // ---- dependencies --------------------------------------------------------------------
-        if (jb == 0) pdl_wait();   // the previous kernel's writes (activations) are visible from here
+        if (first_job) pdl_wait();   // the previous kernel's writes (activations) are visible from here
+        first_job = false;
         if (J.flags & STREAM_JOB_WAITS) {
             // every CTA has stored all earlier jobs' outputs once the counter reaches grid * jb
-            if (threadIdx.x == 0) {
+            if (tid == 0) {
                 const unsigned target = gridDim.x * (unsigned)jb;
                 const uint64_t t0 = globaltimer_ns();
                 unsigned seen;
@@ -369,7 +399,7 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1) stream_kernel(const S
                     }
                 }
             }
-            consumer_sync(T);
+            team_sync(team, T);
         }
 
         // ---- this job's geometry -------------------------------------------------------------
@@ -398,16 +428,16 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1) stream_kernel(const S
                 if (m < p.M && !(p.debug & 4)) {
                     const bool q6 = (TYPES & TY_Q6K) && (TYPES == TY_Q6K || qt == QT_Q6_K);
                     if (MT == 1 && have_raw) {
-                        if (q6) prep_from_raw<QT_Q6_K>(xs, T, xraw, b, b + plane, sxp, isp, units16);
-                        else if (TYPES & ~TY_Q6K) prep_from_raw<QT_Q4_K>(xs, T, xraw, b, b + plane, sxp, isp, units16);
+                        if (q6) prep_from_raw<QT_Q6_K>(xs, tid, T, xraw, b, b + plane, sxp, isp, units16);
+                        else if (TYPES & ~TY_Q6K) prep_from_raw<QT_Q4_K>(xs, tid, T, xraw, b, b + plane, sxp, isp, units16);
                     } else {
-                        if (q6) prep_row<QT_Q6_K>(xs, m, T, b, b + plane, sxp, isp, units16);
-                        else if (TYPES & ~TY_Q6K) prep_row<QT_Q4_K>(xs, m, T, b, b + plane, sxp, isp, units16);
+                        if (q6) prep_row<QT_Q6_K>(xs, m, tid, T, b, b + plane, sxp, isp, units16);
+                        else if (TYPES & ~TY_Q6K) prep_row<QT_Q4_K>(xs, m, tid, T, b, b + plane, sxp, isp, units16);
                     }
                 }
             }
         }
-        consumer_sync(T);
+        team_sync(team, T);
 
         // ---- items ---------------------------------------------------------------------------
         // The cross-lane sum of an item's results is taken one iteration late, after the next
@@ -439,10 +469,10 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1) stream_kernel(const S
         };
 
         // item = g * nchunks + c; stepping by CW items without dividing in the loop
-        const int step_g = CW / nchunks, step_c = CW - step_g * nchunks;
-        int g = warp / nchunks, c = warp - g * nchunks;
+        const int step_g = tcw / nchunks, step_c = tcw - step_g * nchunks;
+        int g = twarp / nchunks, c = twarp - g * nchunks;
 #pragma unroll 1
-        for (int item = (p.debug & 16) ? n_items : warp; item < n_items; item += CW) {
+        for (int item = (p.debug & 16) ? n_items : twarp; item < n_items; item += tcw) {
             bool ok = (p.debug & 2) ? true : mbar_wait_bounded(fbar + 8 * slot, phase);
             ok = __all_sync(0xFFFFFFFFu, ok && !*fail_flag);
             if (!ok) {
@@ -498,18 +528,22 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1) stream_kernel(const S
         // start loading the next job's activation now: the loads fly while this job is summed and
         // stored (not possible when that activation is still being produced by this launch)
         have_raw = false;
-        if (MT == 1 && jb + 1 < p.njobs && !(p.debug & 4)) {
-            const StreamJob &Jn = jobs_s[jb + 1];
-            const XSrc xn = job_xsrc(Jn);
-            if (!(Jn.flags & STREAM_JOB_WAITS) && prep_can_prefetch(xn, T)) {
-                prep_prefetch(xn, T, xraw);
-                have_raw = true;
+        if (MT == 1 && !(p.debug & 4)) {
+            int jn = jb + 1;
+            while (jn < p.njobs && p.teams == 2 && jobs_s[jn].team != team) ++jn;
+            if (jn < p.njobs) {
+                const StreamJob &Jn = jobs_s[jn];
+                const XSrc xn = job_xsrc(Jn);
+                if (!(Jn.flags & STREAM_JOB_WAITS) && prep_can_prefetch(xn, T)) {
+                    prep_prefetch(xn, tid, T, xraw);
+                    have_raw = true;
+                }
             }
         }
-        if (threadIdx.x == 0) head.decide = *fail_flag;
-        consumer_sync(T);
+        if (tid == 0) head.decide[team] = *fail_flag;
+        team_sync(team, T);
 
-        if (head.decide) {
+        if (head.decide[team]) {
             // Some wait ran out.  Copies already issued into this warp's ring must land before
             // the CTA's shared memory is released: learn from the producer how many were issued
             // and wait for exactly those, each wait again with a limit.
@@ -527,10 +561,10 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1) stream_kernel(const S
         const bool xsum = xenabled && (J.flags & STREAM_JOB_SUM_RANKS);
         if (xsum) {
             if (!xe_loaded) {   // exchanges posted by earlier launches (after pdl_wait: their last write is visible)
-                if (threadIdx.x == 0)
-                    head.xepoch = *(reinterpret_cast<const unsigned *>(p.peer_base[p.peer_rank] + kPeerFusedEpochOff) + blockIdx.x);
-                consumer_sync(T);
-                xe = head.xepoch;
+                if (tid == 0)
+                    head.xepoch[team] = *(reinterpret_cast<const unsigned *>(p.peer_base[p.peer_rank] + kPeerFusedEpochOff) + team * kPeerCtas + blockIdx.x);
+                team_sync(team, T);
+                xe = head.xepoch[team];
                 xe_loaded = true;
             }
             if (xpending >= 0) {
@@ -540,7 +574,7 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1) stream_kernel(const S
             ++xe;
         }
         const int cells = (p.debug & 8) ? 0 : (ge - gb) * R * MT;
-        for (int t = threadIdx.x; t < cells; t += T) {
+        for (int t = tid; t < cells; t += T) {
             const int rl = t / MT, m = t - rl * MT;      // rl = local group * 4 + row in group
             int sg, lg;
             locate_group(J, gb + rl / R, sg, lg);
@@ -549,7 +583,7 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1) stream_kernel(const S
                 float v = 0.f;
                 for (int cc = 0; cc < nchunks; ++cc) v += partial[(rl * nchunks + cc) * MT + m];
                 if (xsum) {     // one segment, fp32 output (checked when the plan was made)
-                    const size_t si = (size_t)((xe & 1) * kPeerMaxWorld + p.peer_rank) * kPeerSlotFloats + m * J.seg[0].n + row;
+                    const size_t si = (size_t)((team * 2 + (xe & 1)) * kPeerMaxWorld + p.peer_rank) * kPeerSlotFloats + m * J.seg[0].n + row;
                     for (int r = 0; r < p.peer_world; ++r)
                         st_pair(reinterpret_cast<unsigned long long *>(p.peer_base[r] + kPeerFusedSlotOff) + si, v, xe);
                     continue;
@@ -567,16 +601,16 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1) stream_kernel(const S
         }
         if (p.has_dep) {
             // publish: this CTA's outputs of job jb are stored
-            consumer_sync(T);
-            if (threadIdx.x == 0) {
+            team_sync(team, T);
+            if (tid == 0) {
                 __threadfence();
                 atomicAdd(p.counter, 1u);
             }
         }
     }
     if (xpending >= 0) exchange_complete(xpending, xe);
-    if (xe_loaded && threadIdx.x == 0)
-        *(reinterpret_cast<unsigned *>(p.peer_base[p.peer_rank] + kPeerFusedEpochOff) + blockIdx.x) = xe;
+    if (xe_loaded && tid == 0)
+        *(reinterpret_cast<unsigned *>(p.peer_base[p.peer_rank] + kPeerFusedEpochOff) + team * kPeerCtas + blockIdx.x) = xe;
 }
 
 }  // namespace
@@ -609,8 +643,11 @@ cudaError_t launch_t(const StreamLaunch &a, StreamParams &p, int grid, cudaStrea
     p.partial_bytes = (int)partial;
     p.chunk_stride = stride;
     p.jobs_bytes = (int)(((size_t)a.njobs * sizeof(StreamJob) + 127) & ~size_t(127));
-    const size_t fixed = kHeadBytes + p.jobs_bytes + x_bytes + partial;
     const size_t budget = a.smem_limit;
+    // two consumer teams need two activation areas; keep them only while two ring slots per warp still fit
+    if (p.teams == 2 && kHeadBytes + p.jobs_bytes + 2 * (x_bytes + partial) + (size_t)warps * 2 * R * stride > budget) p.teams = 1;
+    if (warps < 4) p.teams = 1;
+    const size_t fixed = kHeadBytes + p.jobs_bytes + p.teams * (x_bytes + partial);
     // fewer consumer warps when two slots each do not fit (very long rows, several activation rows)
     while (warps > 4 && fixed + (size_t)warps * 2 * R * stride > budget) --warps;
     if (fixed + (size_t)warps * 2 * R * stride > budget) return cudaErrorInvalidValue;
@@ -679,6 +716,13 @@ cudaError_t stream_launch_one(const StreamLaunch &a, cudaStream_t st) {
     p.has_dep = 0;
     for (int i = 0; i < a.njobs; ++i)
         if (a.jobs_host[i].flags & STREAM_JOB_WAITS) p.has_dep = 1;
+    // two teams when the launch holds jobs for both and no job waits for another
+    p.teams = 1;
+    if (!p.has_dep && a.teams != 1) {
+        bool t0 = false, t1 = false;
+        for (int i = 0; i < a.njobs; ++i) (a.jobs_host[i].team ? t1 : t0) = true;
+        if (t0 && t1) p.teams = 2;
+    }
     const int grid = a.grid > 0 ? a.grid : a.sm_count;
     if (p.has_dep && grid > a.sm_count) return cudaErrorInvalidValue;   // the counter wait needs every CTA resident
     if (p.peer_world > 1) {
@@ -717,6 +761,20 @@ void stream_job_finish(StreamJob &J) {
     J.nchunks = (J.nsb + KC - 1) / KC;
     J.bytes_full = (unsigned)chunk_row_bytes(J.qt, 0, J.nsb);
     J.bytes_tail = (unsigned)chunk_row_bytes(J.qt, J.nchunks - 1, J.nsb);
+}
+
+void stream_assign_teams(StreamJob *jobs, int n) {
+    // greedy: each job goes to the team whose streamed bytes per warp are lower so far
+    // (team 0 has 8 of the 15 consumer warps, team 1 has 7)
+    const double warps[2] = {(kMaxWarps + 1) / 2, kMaxWarps / 2};
+    double load[2] = {0, 0};
+    for (int i = 0; i < n; ++i) {
+        double bytes = 0;
+        for (int s = 0; s < jobs[i].nseg; ++s) bytes += (double)jobs[i].seg[s].n * jobs[i].row_bytes;
+        const int t = (load[1] + bytes) / warps[1] < (load[0] + bytes) / warps[0] ? 1 : 0;
+        jobs[i].team = t;
+        load[t] += bytes;
+    }
 }
 
 // Returns cudaSuccess, or cudaErrorInvalidValue when the shapes cannot be staged in shared memory.

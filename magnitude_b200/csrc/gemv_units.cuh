@@ -283,14 +283,14 @@ __device__ __forceinline__ void prep_store8(const float (&v)[8], int k0, uint8_t
         sx[k0 >> 5] = blk_bad ? __int_as_float(0x7FC00000) : amax * (1.0f / kXMax);
 }
 
-// Threads [0, T) convert activation row m.  Loads are issued four deep before any is used so a
+// Threads tid = 0 .. T-1 (whole warps) convert activation row m.  Loads are issued four deep before any is used so a
 // long row costs one trip to L2, not one per 8 * T elements.
 template <int QT>
-__device__ __forceinline__ void prep_row(const XSrc &p, int m, int T, uint8_t *xh, uint8_t *xl,
+__device__ __forceinline__ void prep_row(const XSrc &p, int m, int tid, int T, uint8_t *xh, uint8_t *xl,
                                          float *sx, int *isum, int units16) {
     constexpr int PB = 4;
     const int stride = T * 8;
-    for (int base = threadIdx.x * 8; base < p.Kpad; base += stride * PB) {
+    for (int base = tid * 8; base < p.Kpad; base += stride * PB) {
         float v[PB][8];
 #pragma unroll
         for (int b = 0; b < PB; ++b)
@@ -313,21 +313,21 @@ __device__ __forceinline__ bool prep_can_prefetch(const XSrc &p, int T) {
     return p.x_is_bf16 && p.x_vec_ok && p.Kpad <= kPrepBatch * T * 8;
 }
 
-__device__ __forceinline__ void prep_prefetch(const XSrc &p, int T, XRaw &raw) {
+__device__ __forceinline__ void prep_prefetch(const XSrc &p, int tid, int T, XRaw &raw) {
     const __nv_bfloat16 *x = reinterpret_cast<const __nv_bfloat16 *>(p.x);
 #pragma unroll
     for (int b = 0; b < kPrepBatch; ++b) {
-        const int k0 = threadIdx.x * 8 + b * T * 8;
+        const int k0 = tid * 8 + b * T * 8;
         raw.r[b] = (k0 < p.K) ? *reinterpret_cast<const uint4 *>(x + k0) : make_uint4(0, 0, 0, 0);
     }
 }
 
 template <int QT>
-__device__ __forceinline__ void prep_from_raw(const XSrc &p, int T, const XRaw &raw, uint8_t *xh, uint8_t *xl,
+__device__ __forceinline__ void prep_from_raw(const XSrc &p, int tid, int T, const XRaw &raw, uint8_t *xh, uint8_t *xl,
                                               float *sx, int *isum, int units16) {
 #pragma unroll
     for (int b = 0; b < kPrepBatch; ++b) {
-        const int k0 = threadIdx.x * 8 + b * T * 8;
+        const int k0 = tid * 8 + b * T * 8;
         if (k0 < p.Kpad) {   // warp-uniform: a warp covers 256 consecutive elements
             const uint32_t w[4] = {raw.r[b].x, raw.r[b].y, raw.r[b].z, raw.r[b].w};
             float v[8];

@@ -47,6 +47,7 @@ struct StreamJob {
     long long ldx;
     int x_is_bf16, x_vec_ok, y_is_bf16;
     int flags;                         // STREAM_JOB_*
+    int team;                          // which half of the consumer warps runs the job (see stream_assign_teams)
 };
 
 struct StreamLaunch {
@@ -61,11 +62,14 @@ struct StreamLaunch {
     int warps, depth, grid;       // 0 = default
     int debug;                    // experiments only (see gemv.cu)
     int pdl;                      // launch with programmatic stream serialization
+    int teams;                    // 1 = never split the consumer warps into two teams
     uint8_t *peer_base[8];        // every rank's exchange buffer (jobs flagged STREAM_JOB_SUM_RANKS); null = none
     int peer_rank, peer_world;
 };
 int gemv_max_m();
 void stream_job_finish(StreamJob &job);
+// Spreads the jobs of a plan over the two consumer-warp teams of a CTA, balancing streamed bytes.
+void stream_assign_teams(StreamJob *jobs, int n);
 cudaError_t stream_launch(const StreamLaunch &a, cudaStream_t st);
 
 // ---- gemm_tc.cu -----------------------------------------------------------------------------
@@ -112,9 +116,9 @@ constexpr size_t kPeerSlotBytes = size_t(kPeerSlotFloats) * 8;
 constexpr size_t kPeerRegionSlots = size_t(2) * kPeerMaxWorld * kPeerSlotBytes;      // 2 MB
 constexpr size_t kPeerEpochOff = 0;                    // [kPeerBlocks] u32
 constexpr size_t kPeerSlotOff = 4096;
-constexpr size_t kPeerFusedEpochOff = kPeerSlotOff + kPeerRegionSlots;               // [kPeerCtas] u32
-constexpr size_t kPeerFusedSlotOff = kPeerFusedEpochOff + 4096;
-constexpr size_t kPeerBufferBytes = kPeerFusedSlotOff + kPeerRegionSlots;
+constexpr size_t kPeerFusedEpochOff = kPeerSlotOff + kPeerRegionSlots;               // [2 teams][kPeerCtas] u32
+constexpr size_t kPeerFusedSlotOff = kPeerFusedEpochOff + 4096;                      // [2 teams][2 sets][ranks][elements]
+constexpr size_t kPeerBufferBytes = kPeerFusedSlotOff + 2 * kPeerRegionSlots;
 struct PeerLaunch {
     float *y;                       // in place: partial sums in, sums over ranks out
     int count;
