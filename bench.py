@@ -432,7 +432,8 @@ def run_b200(args):
         os._exit(0)
 
     peak, peak_src = peaks()
-    # dominant (only) kernel: stream_kernel<M=1, Q4_K> running the step's 64 projection jobs;
+    # dominant kernel: stream_kernel<M=1, Q4_K> running the step's 64 projection jobs (the
+    # activation-prep launch before it takes about 1 % of the step);
     # achieved = algorithmic bytes of this rank's launches / their device time
     rank_bytes = bytes_step / world
     achieved = rank_bytes / (ms_step * 1e-3) / 1e9
@@ -474,7 +475,9 @@ def run_b200(args):
         "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "u8 x s16 integer block dots (dp4a), fp32 accumulate", "data": "synthetic",
         "config": workload_config(world), "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e,
-        "gpu_launches": launches_per_step * (2 if (use_peer and not fused) else 1) * args.steps, "cuda_graph": used_graph,
+        # a plan run = the activation-prep launch + the streaming launch; the unfused TP mode adds the all-reduce kernel
+        "gpu_launches": launches_per_step * ((2 if plans is not None else 1) + (1 if (use_peer and not fused) else 0)) * args.steps,
+        "cuda_graph": used_graph,
         "clocks": clocks.summary(),
     }
     print(json.dumps(mark_diagnostic(line, args)))

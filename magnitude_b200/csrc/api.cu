@@ -92,7 +92,7 @@ struct b200q_ctx {
     float *gemm_part = nullptr;       // K-split partial products of skinny batches (allocated on first use)
     int gemm_bn = 0, gemm_debug = 0, gemm_pair = 0, gemm_ksplit = 1;
     // tunables (environment overrides for experiments)
-    int gemv_warps = 0, gemv_depth = 0, gemv_grid = 0, gemv_smem = 0, gemv_rows = 0, gemv_debug = 0, gemv_pdl = 1, gemv_teams = 2;
+    int gemv_warps = 0, gemv_depth = 0, gemv_grid = 0, gemv_smem = 0, gemv_rows = 0, gemv_debug = 0, gemv_pdl = 1, gemv_teams = 2, gemv_xprep = 1;
     // tensor parallel
     NcclComm comm = nullptr;
     int tp_rank = 0, tp_world = 1;
@@ -106,6 +106,8 @@ struct b200q_plan {
     b200q_ctx *ctx = nullptr;
     std::vector<StreamJob> jobs;
     StreamJob *jobs_dev = nullptr;
+    uint8_t *xq_dev = nullptr;        // fixed-point activation images of the jobs (filled by the prep launch of every run)
+    bool has_xq = false;
     int M = 0;
 };
 
@@ -226,6 +228,7 @@ void fill_job(StreamJob &J, const b200q_weight *const *w, int nw, const void *x,
     J.y_is_bf16 = y_dtype == B200Q_TYPE_BF16;
     J.flags = flags;
     J.team = 0;
+    J.xq = nullptr;
     stream_job_finish(J);
 }
 
@@ -443,6 +446,7 @@ b200q_status b200q_ctx_create(int32_t device, b200q_ctx **out) {
     ctx->gemv_debug = env_int("B200Q_GEMV_DEBUG", 0);
     ctx->gemv_pdl = env_int("B200Q_GEMV_PDL", 1);
     ctx->gemv_teams = env_int("B200Q_GEMV_TEAMS", 2);
+    ctx->gemv_xprep = env_int("B200Q_GEMV_XPREP", 1);
     ctx->gemm_bn = env_int("B200Q_GEMM_BN", 0);
     ctx->gemm_debug = env_int("B200Q_GEMM_DEBUG", 0);
     ctx->gemm_pair = env_int("B200Q_GEMM_PAIR", 1);
@@ -787,6 +791,24 @@ b200q_status b200q_plan_create(b200q_ctx *ctx, const b200q_job *jobs, int32_t n_
         fill_job(J, j.w, j.n_weights, j.x_dev, j.x_dtype, j.ldx, j.y_dev, j.y_dtype, j.ldy, jflags);
         pl->jobs.push_back(J);
     }
+    if (pl->jobs.size() >= 2 && ctx->gemv_xprep) {
+        // activations that no job of the plan writes are converted to fixed point once per run by a
+        // small launch of its own, instead of by every CTA
+        size_t total = 0;
+        for (const StreamJob &J : pl->jobs)
+            if (!(J.flags & STREAM_JOB_WAITS)) total += stream_xq_bytes(J, (int)M);
+        if (total > 0 && cudaMalloc(reinterpret_cast<void **>(&pl->xq_dev), total) == cudaSuccess) {
+            size_t off = 0;
+            for (StreamJob &J : pl->jobs) {
+                if (J.flags & STREAM_JOB_WAITS) continue;
+                J.xq = pl->xq_dev + off;
+                off += stream_xq_bytes(J, (int)M);
+            }
+            pl->has_xq = true;
+        } else {
+            cudaGetLastError();
+        }
+    }
     if (!pl->jobs.empty()) {
         stream_assign_teams(pl->jobs.data(), (int)pl->jobs.size());
         const size_t bytes = pl->jobs.size() * sizeof(StreamJob);
@@ -809,19 +831,22 @@ b200q_status b200q_plan_run(b200q_ctx *ctx, b200q_plan *plan, void *stream) {
     ctx->last_route = B200Q_ROUTE_NONE;
     ctx->last_launches = 0;
     if (plan->jobs.empty()) return B200Q_OK;
+    if (plan->has_xq) {
+        cudaError_t e = stream_xprep_launch(plan->jobs_dev, (int)plan->jobs.size(), plan->M, (cudaStream_t)stream);
+        if (e != cudaSuccess) return cuda_fail(ctx, e, "activation prep launch");
+    }
     s = run_stream(ctx, plan->jobs.data(), plan->jobs_dev, (int)plan->jobs.size(), plan->M, (cudaStream_t)stream);
     if (s != B200Q_OK) return s;
     ctx->last_route = B200Q_ROUTE_GEMV;
-    ctx->last_launches = 1;
+    ctx->last_launches = plan->has_xq ? 2 : 1;
     return B200Q_OK;
 }
 
 void b200q_plan_destroy(b200q_plan *plan) {
     if (!plan) return;
-    if (plan->jobs_dev) {
-        if (plan->ctx) cudaSetDevice(plan->ctx->device);
-        cudaFree(plan->jobs_dev);
-    }
+    if (plan->ctx) cudaSetDevice(plan->ctx->device);
+    if (plan->jobs_dev) cudaFree(plan->jobs_dev);
+    if (plan->xq_dev) cudaFree(plan->xq_dev);
     delete plan;
 }
 

@@ -58,6 +58,7 @@ struct StreamParams {
     int partial_bytes;       // ... for the per-(row, chunk) partial sums
     int has_dep;             // some job waits for earlier jobs: CTAs count completions
     int teams;               // 2: the consumer warps work as two teams on different jobs at the same time
+    int has_xq;              // some job's activation arrives already in fixed point (StreamJob::xq)
     int debug;               // experiments only: 1 stream without computing, 2 compute without
                              // streaming, 4 skip the activation prologue, 8 skip the final pass,
                              // 64 do not wait for the peers' partial sums
@@ -71,6 +72,8 @@ struct StreamParams {
 struct SmemHead {
     uint64_t full[kMaxWarps * kMaxDepth];
     uint64_t empty[kMaxWarps * kMaxDepth];
+    uint64_t xfull[2];       // per team: the job's pre-quantized activation has landed in the team's area
+    uint64_t xempty[2];      // per team: every warp of the team is done with the area's previous contents
     int fail;                // raised by any warp that gave up a wait; everybody then drains and leaves
     int decide[2];           // per team: its first thread's sample of `fail`, taken before a barrier so all its warps agree
     int prod_done;           // the producer warp has stopped issuing copies
@@ -167,6 +170,7 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1) stream_kernel(const S
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int CW = (blockDim.x >> 5) - 1;     // consumer warps; warp CW is the producer
     const int D = p.depth;
+    const int cw0 = p.teams == 2 ? (CW + 1) / 2 : CW;     // team 0 = consumer warps [0, cw0), team 1 = [cw0, CW)
 
     // shared-memory carve-up: header, activation planes, partial sums, rings
     SmemHead &head = *reinterpret_cast<SmemHead *>(smem);
@@ -178,7 +182,7 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1) stream_kernel(const S
     // Two teams: while one team sums, stores and prepares the next activation (the per-job work
     // that keeps no data moving), the other is in the middle of its own job, so the SM always has
     // warps doing block dots.  Team 0 = consumer warps [0, cw0), team 1 = [cw0, CW).
-    const int cw0 = p.teams == 2 ? (CW + 1) / 2 : CW;
+
     const int slot_bytes = R * p.chunk_stride;
     const int ring_bytes = D * slot_bytes;
 
@@ -190,7 +194,15 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1) stream_kernel(const S
         mbar_fence_init();
         fence_proxy_async();
     }
-    if (threadIdx.x == 0) { head.fail = 0; head.prod_done = 0; head.xfail = 0; }
+    if (threadIdx.x == 0) {
+        head.fail = 0; head.prod_done = 0; head.xfail = 0;
+        for (int t = 0; t < 2; ++t) {
+            mbar_init(smem_u32(&head.xfull[t]), 1);
+            mbar_init(smem_u32(&head.xempty[t]), t == 0 ? cw0 : max(CW - cw0, 1));
+        }
+        mbar_fence_init();
+        fence_proxy_async();
+    }
     // the job table (written by the host when the plan was made) moves to shared memory once
     if (p.jobs) {
         const int words = p.njobs * (int)(sizeof(StreamJob) / 4);
@@ -234,6 +246,19 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1) stream_kernel(const S
             while (c >= J.nchunks) { c -= J.nchunks; ++g; }
         };
         next_job();
+        // Lanes 30 and 31 feed the activation areas of team 0 and team 1: one bulk copy per job whose
+        // activation was converted to fixed point by the prep launch, as soon as the team has left
+        // the area's previous contents behind.
+        const bool xfeeder = p.has_xq && lane >= 30 && (lane - 30) < p.teams && !(p.debug & 2);
+        const int xteam = lane - 30;
+        int xjb = -1, xseq = 0;        // job cursor; how many of the team's jobs lie before it
+        auto next_xjob = [&]() {
+            if (xjb >= 0) ++xseq;
+            do { ++xjb; } while (xjb < p.njobs && p.teams == 2 && jobs_s[xjb].team != xteam);
+        };
+        if (xfeeder) next_xjob();
+        else xjb = p.njobs;
+        if (p.has_xq) pdl_wait();      // the prep launch's output is visible from here
         uint64_t t_first = 0;
         bool timing = false;
         int idle = 0;
@@ -266,7 +291,23 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1) stream_kernel(const S
                     }
                 }
             }
-            if (__all_sync(mask, jb >= p.njobs)) break;
+            if (xjb < p.njobs) {
+                const StreamJob &J = jobs_s[xjb];
+                if (!J.xq) {
+                    next_xjob();
+                    progressed = true;
+                } else if (xseq == 0 || mbar_test_wait(smem_u32(&head.xempty[xteam]), (uint32_t)(xseq - 1) & 1u)) {
+                    const int n_isum = (J.qt == QT_Q6_K) ? (J.Kpad >> 4) : (J.Kpad >> 5);
+                    const uint32_t bytes = (uint32_t)p.M * (uint32_t)(2 * J.Kpad + (J.Kpad >> 5) * 4 + n_isum * 4);
+                    const uint32_t bar = smem_u32(&head.xfull[xteam]);
+                    fence_proxy_async();
+                    mbar_expect_tx(bar, bytes);
+                    bulk_g2s(smem_u32(xbase0 + xteam * p.x_bytes), J.xq, bytes, bar);
+                    next_xjob();
+                    progressed = true;
+                }
+            }
+            if (__all_sync(mask, jb >= p.njobs && xjb >= p.njobs)) break;
             if (__any_sync(mask, progressed)) {
                 idle = 0;
                 timing = false;
@@ -306,7 +347,8 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1) stream_kernel(const S
     const int tid = threadIdx.x - tw0 * 32;         // thread index inside the team
     const int twarp = warp - tw0;
     uint8_t *xbase = xbase0 + team * p.x_bytes;
-    float *partial = partial0 + team * (p.partial_bytes >> 2);
+    float *partial_t = partial0 + team * (p.partial_bytes >> 2);      // two copies, used by alternate jobs
+    int tjobs = 0, xq_seen = 0;                                         // the team's jobs so far; those with a pre-quantized activation
     const uint32_t ring_sa = smem_u32(rings + warp * ring_bytes);
     const uint32_t fbar = full0 + warp * kMaxDepth * 8, ebar = empty0 + warp * kMaxDepth * 8;
     const int lsb = lane >> 2, j = lane & 3;   // this lane's record and 64-weight group in a chunk
@@ -413,6 +455,11 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1) stream_kernel(const S
         const int per_m = 2 * plane + (J.Kpad >> 5) * 4 + n_isum * 4;        // xh, xl, sx, isum
 
         // ---- prologue: activation rows -> fixed point ----------------------------------------
+        // partial sums alternate between two copies: the previous job's are still being added up by
+        // slower threads of the team when this job's first items are flushed
+        float *partial = partial_t + (tjobs & 1) * (p.partial_bytes >> 3);
+        ++tjobs;
+        const bool pre_x = J.xq != nullptr && !(p.debug & 2);
         XView xv[MT];
         {
             const XSrc xs = job_xsrc(J);
@@ -425,7 +472,7 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1) stream_kernel(const S
                 xv[m].xl = smem_u32(b + plane);
                 xv[m].sx = smem_u32(sxp);
                 xv[m].isum = smem_u32(isp);
-                if (m < p.M && !(p.debug & 4)) {
+                if (m < p.M && !(p.debug & 4) && !pre_x) {
                     const bool q6 = (TYPES & TY_Q6K) && (TYPES == TY_Q6K || qt == QT_Q6_K);
                     if (MT == 1 && have_raw) {
                         if (q6) prep_from_raw<QT_Q6_K>(xs, tid, T, xraw, b, b + plane, sxp, isp, units16);
@@ -437,7 +484,17 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1) stream_kernel(const S
                 }
             }
         }
-        team_sync(team, T);
+        if (pre_x) {
+            // the fixed-point image arrives by bulk copy: every thread waits for it itself, no team barrier
+            bool okx = mbar_wait_bounded(smem_u32(&head.xfull[team]), (uint32_t)xq_seen & 1u);
+            ++xq_seen;
+            if (!okx) {
+                atomicMax(p.status, DEV_ERR_PIPE_TIMEOUT);
+                *fail_flag = 1;
+            }
+        } else {
+            team_sync(team, T);
+        }
 
         // ---- items ---------------------------------------------------------------------------
         // The cross-lane sum of an item's results is taken one iteration late, after the next
@@ -527,6 +584,11 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1) stream_kernel(const S
         flush_pending();
         // start loading the next job's activation now: the loads fly while this job is summed and
         // stored (not possible when that activation is still being produced by this launch)
+        // this warp is done with the activation area: the next pre-quantized image may overwrite it
+        if (p.has_xq) {
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&head.xempty[team]));
+        }
         have_raw = false;
         if (MT == 1 && !(p.debug & 4)) {
             int jn = jb + 1;
@@ -534,7 +596,7 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1) stream_kernel(const S
             if (jn < p.njobs) {
                 const StreamJob &Jn = jobs_s[jn];
                 const XSrc xn = job_xsrc(Jn);
-                if (!(Jn.flags & STREAM_JOB_WAITS) && prep_can_prefetch(xn, T)) {
+                if (!(Jn.flags & STREAM_JOB_WAITS) && !Jn.xq && prep_can_prefetch(xn, T)) {
                     prep_prefetch(xn, tid, T, xraw);
                     have_raw = true;
                 }
@@ -623,6 +685,46 @@ int gemv_max_m() { return 4; }
 
 namespace {
 
+// Converts the activation of every job that has an image buffer (StreamJob::xq) to the fixed-point
+// form the streaming kernel works on, once per job instead of once per CTA and job: block (job, part)
+// handles every `parts`-th run of 8 elements.  The image has the layout of the kernel's
+// shared-memory activation area ([row][xh | xl | sx | isum]), so a CTA fetches it with one bulk copy.
+__global__ void __launch_bounds__(256) xprep_kernel(const StreamJob *jobs, int M) {
+    pdl_launch_dependents();       // the streaming launch may start (it waits before reading the images)
+    const StreamJob &J = jobs[blockIdx.x];
+    if (!J.xq) return;
+    XSrc xs;
+    xs.x = J.x; xs.ldx = J.ldx; xs.x_is_bf16 = J.x_is_bf16; xs.x_vec_ok = J.x_vec_ok;
+    xs.K = J.K; xs.Kpad = J.Kpad;
+    const int units16 = (J.Kpad >> 6) * 16, plane = J.Kpad;
+    const int n_isum = (J.qt == QT_Q6_K) ? (J.Kpad >> 4) : (J.Kpad >> 5);
+    const int per_m = 2 * plane + (J.Kpad >> 5) * 4 + n_isum * 4;
+    const int tid = blockIdx.y * blockDim.x + threadIdx.x, T = gridDim.y * blockDim.x;
+    for (int m = 0; m < M; ++m) {
+        uint8_t *b = const_cast<uint8_t *>(J.xq) + (size_t)m * per_m;
+        float *sxp = reinterpret_cast<float *>(b + 2 * plane);
+        int *isp = reinterpret_cast<int *>(b + 2 * plane + (J.Kpad >> 5) * 4);
+        if (J.qt == QT_Q6_K) prep_row<QT_Q6_K>(xs, m, tid, T, b, b + plane, sxp, isp, units16);
+        else prep_row<QT_Q4_K>(xs, m, tid, T, b, b + plane, sxp, isp, units16);
+    }
+}
+
+}  // namespace
+
+size_t stream_xq_bytes(const StreamJob &J, int M) {
+    const size_t n_isum = J.qt == QT_Q6_K ? J.Kpad / 16 : J.Kpad / 32;
+    const size_t per_m = 2 * (size_t)J.Kpad + (J.Kpad / 32) * 4 + n_isum * 4;
+    return ((size_t)M * per_m + 255) & ~size_t(255);
+}
+
+cudaError_t stream_xprep_launch(const StreamJob *jobs_dev, int njobs, int M, cudaStream_t st) {
+    if (njobs < 1) return cudaSuccess;
+    xprep_kernel<<<dim3((unsigned)njobs, 4), 256, 0, st>>>(jobs_dev, M);
+    return cudaGetLastError();
+}
+
+namespace {
+
 template <int MT, int TYPES>
 cudaError_t launch_t(const StreamLaunch &a, StreamParams &p, int grid, cudaStream_t st) {
     int warps = a.warps > 0 ? a.warps : kMaxWarps;
@@ -640,14 +742,14 @@ cudaError_t launch_t(const StreamLaunch &a, StreamParams &p, int grid, cudaStrea
         stride = std::max(stride, chunk_bytes(J.qt));
     }
     p.x_bytes = (int)x_bytes;
-    p.partial_bytes = (int)partial;
+    p.partial_bytes = (int)(2 * partial);          // two copies per team, used by alternate jobs
     p.chunk_stride = stride;
     p.jobs_bytes = (int)(((size_t)a.njobs * sizeof(StreamJob) + 127) & ~size_t(127));
     const size_t budget = a.smem_limit;
     // two consumer teams need two activation areas; keep them only while two ring slots per warp still fit
-    if (p.teams == 2 && kHeadBytes + p.jobs_bytes + 2 * (x_bytes + partial) + (size_t)warps * 2 * R * stride > budget) p.teams = 1;
+    if (p.teams == 2 && kHeadBytes + p.jobs_bytes + 2 * (x_bytes + 2 * partial) + (size_t)warps * 2 * R * stride > budget) p.teams = 1;
     if (warps < 4) p.teams = 1;
-    const size_t fixed = kHeadBytes + p.jobs_bytes + p.teams * (x_bytes + partial);
+    const size_t fixed = kHeadBytes + p.jobs_bytes + p.teams * (x_bytes + 2 * partial);
     // fewer consumer warps when two slots each do not fit (very long rows, several activation rows)
     while (warps > 4 && fixed + (size_t)warps * 2 * R * stride > budget) --warps;
     if (fixed + (size_t)warps * 2 * R * stride > budget) return cudaErrorInvalidValue;
@@ -716,6 +818,9 @@ cudaError_t stream_launch_one(const StreamLaunch &a, cudaStream_t st) {
     p.has_dep = 0;
     for (int i = 0; i < a.njobs; ++i)
         if (a.jobs_host[i].flags & STREAM_JOB_WAITS) p.has_dep = 1;
+    p.has_xq = 0;
+    for (int i = 0; i < a.njobs; ++i)
+        if (a.jobs_host[i].xq) p.has_xq = 1;
     // two teams when the launch holds jobs for both and no job waits for another
     p.teams = 1;
     if (!p.has_dep && a.teams != 1) {

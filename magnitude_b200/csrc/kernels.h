@@ -48,6 +48,8 @@ struct StreamJob {
     int x_is_bf16, x_vec_ok, y_is_bf16;
     int flags;                         // STREAM_JOB_*
     int team;                          // which half of the consumer warps runs the job (see stream_assign_teams)
+    const uint8_t *xq;                 // device buffer for the activation in fixed point, filled by stream_xprep_launch
+                                       // before the streaming launch (stream_xq_bytes); null = converted inside the kernel
 };
 
 struct StreamLaunch {
@@ -70,6 +72,8 @@ int gemv_max_m();
 void stream_job_finish(StreamJob &job);
 // Spreads the jobs of a plan over the two consumer-warp teams of a CTA, balancing streamed bytes.
 void stream_assign_teams(StreamJob *jobs, int n);
+size_t stream_xq_bytes(const StreamJob &J, int M);
+cudaError_t stream_xprep_launch(const StreamJob *jobs_dev, int njobs, int M, cudaStream_t st);
 cudaError_t stream_launch(const StreamLaunch &a, cudaStream_t st);
 
 // ---- gemm_tc.cu -----------------------------------------------------------------------------

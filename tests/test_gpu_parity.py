@@ -238,7 +238,8 @@ def test_plan_matches_single_calls_mixed_types(backend, orc):
     plan = backend.plan([([gate, up], x1, outs[0:2]), ([v], x1, outs[2:3]), ([q8], x2, outs[3:4])])
     plan.run()
     backend.sync()
-    assert backend.last_route() == (mb.ROUTE_GEMV, 1)
+    # one streaming launch for the whole plan, preceded by the small activation-prep launch
+    assert backend.last_route() == (mb.ROUTE_GEMV, 2)
     singles = [backend.project(gate, x1), backend.project(up, x1), backend.project(v, x1), backend.project(q8, x2)]
     backend.sync()
     for a, b in zip(outs, singles):
