@@ -305,7 +305,7 @@ b200q_status run_gemm(b200q_ctx *ctx, const b200q_weight *w, const void *x, int 
     a.bn_override = ctx->gemm_bn;
     a.debug = ctx->gemm_debug;
     a.pair = ctx->gemm_pair;
-    if (M <= 64 && !ctx->gemm_part && ctx->gemm_ksplit) {
+    if (M < 128 && !ctx->gemm_part && ctx->gemm_ksplit) {
         void *ptr = nullptr;
         if (cudaMalloc(&ptr, kGemmPartBytes) == cudaSuccess) ctx->gemm_part = reinterpret_cast<float *>(ptr);
         else cudaGetLastError();      // no workspace: the product runs unsplit

@@ -1272,7 +1272,7 @@ cudaError_t gemm_launch(const GemmLaunch &a, cudaStream_t st) {
     const int tiles = p.m_tiles * p.n_tiles;
     p.ksplit = 1;
     p.part = nullptr;
-    if (!use_pair && a.part && a.M <= 64 && tiles * 2 <= a.sm_count) {
+    if (!use_pair && a.part && a.M < 128 && tiles * 2 <= a.sm_count) {
         // few tiles: cut K so that every SM gets a work unit (one round)
         int ks = std::min(p.nsb, a.sm_count / tiles);
         while (ks > 1 && (size_t)ks * a.M * a.N * sizeof(float) > a.part_bytes) --ks;

@@ -96,8 +96,8 @@ struct GemmLaunch {
     size_t part_bytes;
 };
 size_t gemm_x_scratch_bytes(int M, int K);
-// K ranges x rows never exceed SMs x 128 (one work unit per SM), tokens 64: 148 x 128 x 64 x 4 bytes < 8 MB
-constexpr size_t kGemmPartBytes = size_t(8) << 20;
+// K ranges x rows never exceed SMs x 128 (one work unit per SM), tokens < 128: 148 x 128 x 127 x 4 bytes < 16 MB
+constexpr size_t kGemmPartBytes = size_t(16) << 20;
 // activations (bf16 or fp32) -> fp16 rows of ((K + 7) & ~7) elements in `scratch`
 cudaError_t gemm_convert_x(const void *x, int x_is_bf16, long long ldx, void *scratch, int M, int K, cudaStream_t st);
 cudaError_t gemm_launch(const GemmLaunch &a, cudaStream_t st);
