@@ -75,7 +75,8 @@ struct GemmParams {
     int tps, extra;          // ... tiles per stripe; the first `extra` stripes have one more
     int pair_tiles;          // ... tiles in all
     int debug;               // timing experiments only (results invalid): 1 no activation loads, 2 no dequant math,
-                             // 4 no weight loads, 8 no MMA, 16 no epilogue body, 32 no proxy fence
+                             // 4 no weight loads, 8 no MMA, 16 no epilogue body, 32 no proxy fence (one-CTA kernel);
+                             // two-CTA kernel also: 1024 / 2048 no weight-stage / activation-stage hand-shakes
 };
 
 struct GemmSmem {
@@ -857,8 +858,13 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_tc_pair_kernel(const Gem
                 pair_tile(p, tile, stripe, t0, width);
                 for (int ks = 0; ks < ksteps; ++ks, ++it) {
                     const int stage = it % SB_;
+                    if (p.debug & 2048) continue;
                     ok = pair_wait<true>(bempty_s + 8 * stage, ((it / SB_) & 1) ^ 1, sm, p.status);
                     if (!ok) break;
+                    if (p.debug & 1) {
+                        if (rank == 0) mbar_arrive(bfull_s + 8 * stage);
+                        continue;
+                    }
                     if (rank == 0) mbar_expect_tx(bfull_s + 8 * stage, bytes_pair);
                     tma_load_2d_pair(b_s + stage * kStageBBytes, &xmap, ks * BK, t0 + (int)rank * (width >> 1), bfull_leader + 8 * stage);
                 }
@@ -878,6 +884,10 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_tc_pair_kernel(const Gem
                     const int wb = rs % kWBufs;
                     ok = pair_wait<true>(wempty_s + 8 * wb, ((rs / kWBufs) & 1) ^ 1, sm, p.status);
                     if (!ok) break;
+                    if (p.debug & 4) {
+                        mbar_arrive(wfull_s + 8 * wb);
+                        continue;
+                    }
                     const bool tail = c >= p.nchunks_full;
                     uint32_t tx = BM * REC;
                     if (QT == QT_Q6_K && s_in == 0) tx += BM * 16;
@@ -908,8 +918,8 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_tc_pair_kernel(const Gem
                 const uint32_t d_tmem = tmem_base + buf * 256;
                 for (int ks = 0; ks < ksteps; ++ks, ++it) {
                     const int sa = it % kAStages, sb = it % SB_;
-                    ok = rdy_b || pair_wait<true>(bfull_s + 8 * sb, (it / SB_) & 1, sm, p.status);
-                    ok = ok && (rdy_a || pair_wait<true>(afull_s + 8 * sa, (it / kAStages) & 1, sm, p.status));
+                    ok = rdy_b || (p.debug & 2048) || pair_wait<true>(bfull_s + 8 * sb, (it / SB_) & 1, sm, p.status);
+                    ok = ok && (rdy_a || (p.debug & 1024) || pair_wait<true>(afull_s + 8 * sa, (it / kAStages) & 1, sm, p.status));
                     if (!ok) break;
                     tc_fence_after();
                     {
@@ -921,9 +931,9 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_tc_pair_kernel(const Gem
                     const uint64_t bdesc = make_desc_sw128(b_s + sb * kStageBBytes);
 #pragma unroll
                     for (int kk = 0; kk < BK / 16; ++kk)
-                        umma_f16_pair(d_tmem, adesc + 2 * kk, bdesc + 2 * kk, idesc, (ks | kk) != 0);
-                    umma_commit_pair(aempty_s + 8 * sa);
-                    umma_commit_pair(bempty_s + 8 * sb);
+                        if (!(p.debug & 8)) umma_f16_pair(d_tmem, adesc + 2 * kk, bdesc + 2 * kk, idesc, (ks | kk) != 0);
+                    if (!(p.debug & 1024)) umma_commit_pair(aempty_s + 8 * sa);
+                    if (!(p.debug & 2048)) umma_commit_pair(bempty_s + 8 * sb);
                 }
                 if (!ok) break;
                 umma_commit_pair(tfull_s + 8 * buf);
@@ -958,15 +968,15 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_tc_pair_kernel(const Gem
                 if (!ok) break;
             }
             uint32_t o[32];
-            cur.convert(j, o);
+            if (!(p.debug & 2)) cur.convert(j, o);
             const int stage = j;
-            if (lane == 0) ok = pair_wait<true>(aempty_s + 8 * stage, (rs & 1) ^ 1, sm, p.status);
+            if (lane == 0 && !(p.debug & 1024)) ok = pair_wait<true>(aempty_s + 8 * stage, (rs & 1) ^ 1, sm, p.status);
             ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
             if (!ok) break;
-            store_row(o, a_s + stage * kStageABytes + row_off, r7);
+            if (!(p.debug & 2)) store_row(o, a_s + stage * kStageABytes + row_off, r7);
             fence_proxy_async();
             __syncwarp();
-            if (lane == 0) mbar_arrive_cluster(afull_leader + 8 * stage);
+            if (lane == 0 && !(p.debug & 1024)) mbar_arrive_cluster(afull_leader + 8 * stage);
             cur = nxt;
         }
     } else {
@@ -984,21 +994,24 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_tc_pair_kernel(const Gem
             tc_fence_after();
             const int n = stripe * 2 * BM + (int)rank * BM + q * 32 + lane;
             const int m0 = t0;
-            for (int c0 = 0; c0 < width; c0 += 32) {
+            // lane = one output column n; its 32 accumulator columns per load are 32 consecutive tokens,
+            // i.e. 32 stores one output row (ldy elements) apart: the pointer just steps by ldy
+            const bool full_tile = m0 + width <= p.M;
+            for (int c0 = 0; c0 < ((p.debug & 16) ? 0 : width); c0 += 32) {
                 uint32_t v[32];
                 tmem_ld32(tmem_base + buf * 256 + ((uint32_t)(q * 32) << 16) + c0, v);
                 tmem_ld_wait();
                 if (n < p.N) {
+                    if (p.y_is_bf16) {
+                        __nv_bfloat16 *yp = reinterpret_cast<__nv_bfloat16 *>(p.y) + (long long)(m0 + c0) * p.ldy + n;
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        const int m = m0 + c0 + i;
-                        if (m < p.M) {
-                            const long long idx = (long long)m * p.ldy + n;
-                            if (p.y_is_bf16)
-                                reinterpret_cast<__nv_bfloat16 *>(p.y)[idx] = __float2bfloat16_rn(__uint_as_float(v[i]));
-                            else
-                                reinterpret_cast<float *>(p.y)[idx] = __uint_as_float(v[i]);
-                        }
+                        for (int i = 0; i < 32; ++i, yp += p.ldy)
+                            if (full_tile || m0 + c0 + i < p.M) *yp = __float2bfloat16_rn(__uint_as_float(v[i]));
+                    } else {
+                        float *yp = reinterpret_cast<float *>(p.y) + (long long)(m0 + c0) * p.ldy + n;
+#pragma unroll
+                        for (int i = 0; i < 32; ++i, yp += p.ldy)
+                            if (full_tile || m0 + c0 + i < p.M) *yp = __uint_as_float(v[i]);
                     }
                 }
             }
