@@ -623,6 +623,85 @@ def run_prefill(args):
     }
     print(json.dumps(line))
 
+# ------------------------------------------------------------------------------------------------
+# secondary line: skinny batches (configs[2]) — speculative-decode verify, M in {2, 4, 8, 16}
+# ------------------------------------------------------------------------------------------------
+
+def run_skinny(args):
+    """Fused-QKV Q4_K 6144x4096 and down Q6_K 4096x14336 against M = 2, 4, 8, 16 bf16 tokens.
+
+    Every case multiplies the tokens by 16 distinct copies of the weight (more than L2 for both
+    shapes) inside one CUDA graph, so the time is the device's, not the launching host's.
+    """
+    import torch
+
+    rank, local_rank, world = dist_env()
+    if world > 1 or args.impl == "reference":
+        if rank == 0:
+            print(json.dumps({"metric": "skinny_gemm_weight_bandwidth", "unavailable": "the skinny line is single-GPU and has no CPU arm"}))
+        return
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the projection path has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    import magnitude_b200 as mb
+    from magnitude_b200 import ggml_quant as gq
+
+    be = mb.Backend(local_rank)
+    peak, src = peaks()
+    copies = 16
+    stream = torch.cuda.Stream(device=dev)
+    cases, tot_bytes, tot_s = [], 0.0, 0.0
+    with ClockSampler(local_rank) as clocks:
+        for qt, name, n, k, blk in ((Q4_K, "Q4_K qkv", 6144, 4096, 144), (14, "Q6_K down", 4096, 14336, 210)):
+            w0 = be.upload(qt, gq.synth_weights(qt, n, k, 0), n, k)
+            ws = [w0] + [w0.clone() for _ in range(copies - 1)]
+            wbytes = n * (k // 256) * blk
+            for m in (2, 4, 8, 16):
+                x = torch.randn(m, k, device=dev).to(torch.bfloat16)
+                y = torch.empty((m, n), dtype=torch.float32, device=dev)
+
+                def step():
+                    for w in ws:
+                        be.project(w, x, out=y, stream=stream)
+
+                for _ in range(max(args.warmup, 3)):
+                    step()
+                stream.synchronize()
+                route = be.last_route()[0]
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=stream):
+                    step()
+                ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                with torch.cuda.stream(stream):
+                    g.replay()
+                    ev0.record(stream)
+                    for _ in range(args.steps):
+                        g.replay()
+                    ev1.record(stream)
+                stream.synchronize()
+                be.sync(stream)
+                us = ev0.elapsed_time(ev1) * 1e3 / (args.steps * copies)
+                algo = wbytes + m * k * 2 + m * n * 4
+                cases.append({"weight": name, "N": n, "K": k, "M": m, "us_per_product": us, "GB/s": algo / us / 1e3,
+                              "frac_of_hbm_peak": algo / us / 1e3 / peak,
+                              "route": "dp4a stream kernel" if route == mb.ROUTE_GEMV else "tcgen05 GEMM, K split"})
+                tot_bytes += algo
+                tot_s += us * 1e-6
+                del g
+            del ws, w0
+    value = tot_bytes / tot_s / 1e9
+    print(json.dumps({
+        "metric": "skinny_gemm_weight_bandwidth", "value": value, "unit": UNIT, "n_gpus": 1, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": tot_s * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "M <= 4: u8 x s16 dp4a; M >= 5: fp16 tcgen05.mma, fp32 accumulate", "data": "synthetic",
+        "config": {"workload": "configs[2]: skinny verify batches, Q4_K 6144x4096 and Q6_K 4096x14336, M in {2,4,8,16}, bf16 tokens, fp32 out",
+                   "l2": f"{copies} distinct weight copies per case", "parallelism": "single"},
+        "roofline": {"bound": "hbm", "achieved": value, "peak": peak, "unit": UNIT, "frac": value / peak, "peak_source": f"of {src}",
+                     "traffic": None, "note": "algorithmic bytes of all eight cases / their device time"},
+        "cases": cases, "cpu_baseline": None, "e2e": None, "gpu_launches": None, "clocks": clocks.summary(),
+    }))
+
 
 def main():
     ap = argparse.ArgumentParser()
@@ -640,7 +719,7 @@ def main():
                     help="N > 1 diagnostic: skip the all-reduce (partial sums only; the line is marked invalid)")
     ap.add_argument("--layers", type=int, default=32,
                     help="layers per step (default 32 = the benchmark; a smaller count is a profiling case, named as such in config)")
-    ap.add_argument("--workload", choices=["decode", "prefill"], default="decode",
+    ap.add_argument("--workload", choices=["decode", "prefill", "skinny"], default="decode",
                     help="decode = the headline Q4_K GEMV step; prefill = the M=2048 Q4_K GEMM (secondary line, TFLOP/s)")
     args = ap.parse_args()
     # last resort against a stuck collective or teardown: never hold a GPU box for more than 20 minutes
@@ -651,6 +730,8 @@ def main():
     LAYERS = max(1, min(args.layers, 32))
     if args.workload == "prefill":
         run_prefill(args)
+    elif args.workload == "skinny":
+        run_skinny(args)
     elif args.impl == "reference":
         run_reference(args)
     else:
