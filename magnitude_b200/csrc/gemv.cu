@@ -125,7 +125,7 @@ __device__ __forceinline__ void item_dot(int nsb, uint32_t sl, int stride, int s
         if constexpr (QT == QT_Q6_K) w.load(rec0 + r * stride, j, d6[r]);
         else w.load(rec0 + r * stride, j);
     };
-    if constexpr (MT <= 2) {
+    if constexpr (MT <= 1 || (MT == 2 && QT != QT_Q6_K)) {
         // one or two activation rows: keep their bytes in registers, stream the weight rows past them
         XRegs<QT> xr[MT];
 #pragma unroll
