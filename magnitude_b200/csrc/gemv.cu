@@ -140,6 +140,30 @@ __device__ __forceinline__ void item_dot(int nsb, uint32_t sl, int stride, int s
                 for (int m = 0; m < MT; ++m) acc[r][m] += w.dot(xr[m]);
             }
         }
+    } else if constexpr (QT != QT_Q6_K && MT >= 3) {
+        // three or four activation rows: two passes over the tile, two rows resident in each
+        if (whole) flush_pending();
+#pragma unroll 1
+        for (int m0 = 0; m0 < MT; m0 += 2) {
+            XRegs<QT> xa, xb;
+            xa.load(xv[m0], gu, gsb, j, units16);
+            const bool two = m0 + 1 < MT;
+            if (two) xb.load(xv[m0 + 1 < MT ? m0 + 1 : m0], gu, gsb, j, units16);
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                if (r < nr) {
+                    WRegs<QT> w;
+                    load_w(w, r);
+                    const float va = w.dot(xa);
+                    const float vb = two ? w.dot(xb) : 0.f;
+#pragma unroll
+                    for (int m = 0; m < MT; ++m) {
+                        if (m == m0) acc[r][m] += va;
+                        if (m == m0 + 1) acc[r][m] += vb;
+                    }
+                }
+            }
+        }
     } else {
         // more activation rows than registers can hold: one weight row at a time, activations re-read
         if (whole) flush_pending();
