@@ -651,6 +651,8 @@ def run_skinny(args):
     from magnitude_b200 import ggml_quant as gq
 
     be = mb.Backend(local_rank)
+    if args.skinny_min_m:
+        be.set_option(1, args.skinny_min_m)
     peak, src = peaks()
     copies = 16
     stream = torch.cuda.Stream(device=dev)
@@ -664,7 +666,12 @@ def run_skinny(args):
                 x = torch.randn(m, k, device=dev).to(torch.bfloat16)
                 y = torch.empty((m, n), dtype=torch.float32, device=dev)
 
+                plan = be.plan([([w], x, [y]) for w in ws]) if args.skinny_plan else None
+
                 def step():
+                    if plan is not None:       # the 16 independent products as one decode plan
+                        plan.run(stream=stream)
+                        return
                     for w in ws:
                         be.project(w, x, out=y, stream=stream)
 
@@ -688,16 +695,17 @@ def run_skinny(args):
                 algo = wbytes + m * k * 2 + m * n * 4
                 cases.append({"weight": name, "N": n, "K": k, "M": m, "us_per_product": us, "GB/s": algo / us / 1e3,
                               "frac_of_hbm_peak": algo / us / 1e3 / peak,
-                              "route": "dp4a stream kernel" if route == mb.ROUTE_GEMV else "tcgen05 GEMM, K split"})
+                              "route": {mb.ROUTE_GEMV: "dp4a stream kernel", mb.ROUTE_SKINNY: "skinny kernel (mma.sync, exact bf16)",
+                                        mb.ROUTE_GEMM: "tcgen05 GEMM, K split"}.get(route, str(route))})
                 tot_bytes += algo
                 tot_s += us * 1e-6
-                del g
+                del g, plan
             del ws, w0
     value = tot_bytes / tot_s / 1e9
     print(json.dumps({
         "metric": "skinny_gemm_weight_bandwidth", "value": value, "unit": UNIT, "n_gpus": 1, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": tot_s * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-        "dtype": "M <= 4: u8 x s16 dp4a; M >= 5: fp16 tcgen05.mma, fp32 accumulate", "data": "synthetic",
+        "dtype": "M <= 4: u8 x s16 dp4a; M >= 5: exact integer weights x bf16 in mma.sync, fp32 accumulate", "data": "synthetic",
         "config": {"workload": "configs[2]: skinny verify batches, Q4_K 6144x4096 and Q6_K 4096x14336, M in {2,4,8,16}, bf16 tokens, fp32 out",
                    "l2": f"{copies} distinct weight copies per case", "parallelism": "single"},
         "roofline": {"bound": "hbm", "achieved": value, "peak": peak, "unit": UNIT, "frac": value / peak, "peak_source": f"of {src}",
@@ -722,6 +730,10 @@ def main():
                     help="N > 1 diagnostic: skip the all-reduce (partial sums only; the line is marked invalid)")
     ap.add_argument("--layers", type=int, default=32,
                     help="layers per step (default 32 = the benchmark; a smaller count is a profiling case, named as such in config)")
+    ap.add_argument("--skinny-plan", action="store_true",
+                    help="skinny workload: run the 16 weight copies of a case as one decode plan instead of 16 calls")
+    ap.add_argument("--skinny-min-m", type=int, default=0,
+                    help="skinny workload: smallest M sent to the skinny kernel (default: the library's, 5)")
     ap.add_argument("--workload", choices=["decode", "prefill", "skinny"], default="decode",
                     help="decode = the headline Q4_K GEMV step; prefill = the M=2048 Q4_K GEMM (secondary line, TFLOP/s)")
     args = ap.parse_args()

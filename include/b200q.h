@@ -70,9 +70,18 @@ enum {
 /* Which kernel family b200q_matmul picked (b200q_last_route). */
 enum {
     B200Q_ROUTE_NONE = 0,
-    B200Q_ROUTE_GEMV = 1,   /* M <= 4: dp4a streaming kernel, HBM-bound */
-    B200Q_ROUTE_SKINNY = 2, /* M <= 16: int8 tensor-core streaming kernel, HBM-bound */
-    B200Q_ROUTE_GEMM = 3    /* larger M: tcgen05 / TMEM bf16 GEMM with in-kernel dequantization */
+    B200Q_ROUTE_GEMV = 1,   /* M <= 2 (up to 4 on request): dp4a streaming kernel on 16-bit fixed-point activations, HBM-bound */
+    B200Q_ROUTE_SKINNY = 2, /* 3 <= M <= 16: streaming kernel, exact integer weights x exact bf16 activations in
+                               mma.sync with fp32 accumulation, HBM-bound */
+    B200Q_ROUTE_GEMM = 3    /* larger M: tcgen05 / TMEM GEMM, weights dequantized to fp16 in shared memory,
+                               activations converted to fp16, fp32 accumulation */
+};
+
+/* Per-context settings (b200q_ctx_set_option). */
+enum {
+    /* smallest M that takes the SKINNY route (2..17; 17 = never); smaller batches use the GEMV kernel.
+     * Default 3. */
+    B200Q_OPT_SKINNY_MIN_M = 1
 };
 
 typedef struct b200q_ctx b200q_ctx;
@@ -94,6 +103,11 @@ int64_t b200q_tensor_storage_bytes(int32_t type, int64_t n_elements);
  * (icn-engine/src/lib.rs:141, 990) for this path. */
 b200q_status b200q_ctx_create(int32_t device, b200q_ctx **out);
 void b200q_ctx_destroy(b200q_ctx *ctx);
+
+/* Changes a per-context setting (B200Q_OPT_*); B200Q_ERR_INVALID_CONFIG for an unknown option or a
+ * value outside its range.  No counterpart in the reference, whose backend takes its settings as
+ * LlamaContextParams at creation (icn-engine/src/lib.rs:990). */
+b200q_status b200q_ctx_set_option(b200q_ctx *ctx, int32_t option, int64_t value);
 
 /* Copies the last error text of this context (NUL-terminated, truncated to n). */
 b200q_status b200q_last_error(const b200q_ctx *ctx, char *buf, size_t n);

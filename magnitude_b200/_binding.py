@@ -29,6 +29,8 @@ TYPE_F32, TYPE_Q8_0, TYPE_Q4_K, TYPE_Q6_K, TYPE_BF16 = 0, 8, 12, 14, 30
 SPLIT_COLUMN, SPLIT_ROW = 0, 1
 ROUTE_NONE, ROUTE_GEMV, ROUTE_SKINNY, ROUTE_GEMM = 0, 1, 2, 3
 
+OPT_SKINNY_MIN_M = 1
+
 JOB_WAITS_FOR_EARLIER = 1
 JOB_SUM_RANKS = 2
 
@@ -55,6 +57,7 @@ SIGNATURES = {
     "b200q_tensor_storage_bytes": (c_int64, [c_int32, c_int64]),
     "b200q_ctx_create": (c_int32, [c_int32, POINTER(c_void_p)]),
     "b200q_ctx_destroy": (None, [c_void_p]),
+    "b200q_ctx_set_option": (c_int32, [c_void_p, c_int32, c_int64]),
     "b200q_last_error": (c_int32, [c_void_p, c_char_p, c_size_t]),
     "b200q_sync": (c_int32, [c_void_p, c_void_p, c_uint64]),
     "b200q_last_route": (c_int32, [c_void_p, POINTER(c_int32), POINTER(c_int32)]),

@@ -90,6 +90,10 @@ struct b200q_ctx {
     void *gemm_scratch = nullptr;
     size_t gemm_scratch_bytes = 0;
     float *gemm_part = nullptr;       // K-split partial products of skinny batches (allocated on first use)
+    // skinny route (2..16 rows): chunk sums, row-block counters, job table
+    uint8_t *sk_ws = nullptr;
+    size_t sk_ws_bytes = 0;
+    int skinny_min_m = 3;             // smallest M that takes the skinny route (smaller batches: the dp4a kernel)
     int gemm_bn = 0, gemm_debug = 0, gemm_pair = 0, gemm_ksplit = 1;
     // tunables (environment overrides for experiments)
     int gemv_warps = 0, gemv_depth = 0, gemv_grid = 0, gemv_smem = 0, gemv_rows = 0, gemv_debug = 0, gemv_pdl = 1, gemv_teams = 2, gemv_xprep = 1;
@@ -109,6 +113,10 @@ struct b200q_plan {
     uint8_t *xq_dev = nullptr;        // fixed-point activation images of the jobs (filled by the prep launch of every run)
     bool has_xq = false;
     int M = 0;
+    // plans of 5..16 rows: groups of products run by the skinny kernel, one launch pair per group
+    std::vector<SkinnySet *> sets;
+    uint8_t *sk_ws = nullptr;
+    uint8_t *sk_jobs = nullptr;
 };
 
 struct b200q_weight {
@@ -318,6 +326,54 @@ b200q_status run_gemm(b200q_ctx *ctx, const b200q_weight *w, const void *x, int 
     return B200Q_OK;
 }
 
+// skinny route: 2..16 activation rows, mma.sync on exact integer weights (skinny.cu); all weights of
+// the call share x, type and K
+b200q_status run_skinny(b200q_ctx *ctx, const b200q_weight *const *w, int nw, const void *x, int x_dtype, int M,
+                        int64_t ldx, void *const *y, int y_dtype, const int64_t *ldy, cudaStream_t st) {
+    SkinnyProduct prods[4];
+    int n = 0;
+    size_t need = 0;
+    for (int i = 0; i < nw; ++i) {
+        if (w[i]->N == 0) continue;
+        SkinnyProduct &a = prods[n++];
+        a.qt = w[i]->type;
+        a.w = w[i]->dev;
+        a.N = (int)w[i]->N;
+        a.K = (int)w[i]->K;
+        a.Kpad = (int)w[i]->Kpad;
+        a.x = x;
+        a.ldx = ldx;
+        a.x_is_bf16 = x_dtype == B200Q_TYPE_BF16;
+        a.y = y[i];
+        a.ldy = ldy[i];
+        a.y_is_bf16 = y_dtype == B200Q_TYPE_BF16;
+        a.M = M;
+        need += skinny_part_bytes(a);
+    }
+    if (n == 0) return B200Q_OK;
+    if (need > ctx->sk_ws_bytes) {
+        if (ctx->sk_ws) {
+            CU_TRY(ctx, cudaStreamSynchronize(st));   // earlier launches may still use the old buffer
+            cudaFree(ctx->sk_ws);
+            ctx->sk_ws = nullptr;
+            ctx->sk_ws_bytes = 0;
+        }
+        const size_t grow = std::max(need, size_t(4) << 20);
+        CU_TRY(ctx, cudaMalloc(reinterpret_cast<void **>(&ctx->sk_ws), grow));
+        ctx->sk_ws_bytes = grow;
+    }
+    SkinnyBuffers buf{};
+    buf.ws = ctx->sk_ws;
+    buf.ws_bytes = ctx->sk_ws_bytes;
+    buf.jobs_dev = nullptr;      // at most four products: their descriptions travel in the kernel parameters
+    buf.status = ctx->status_dev;
+    buf.sm_count = ctx->sm_count;
+    buf.smem_limit = ctx->smem_optin;
+    cudaError_t e = skinny_run(prods, n, buf, st, &ctx->last_launches);
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "skinny kernel launch");
+    return B200Q_OK;
+}
+
 b200q_status validate_mm(b200q_ctx *ctx, const b200q_weight *w, const void *x, int x_dtype, int64_t M,
                          int64_t ldx, const void *y, int y_dtype, int64_t ldy) {
     if (!w) return fail(ctx, B200Q_ERR_INVALID_CONFIG, "null weight");
@@ -349,6 +405,21 @@ b200q_status matmul_any(b200q_ctx *ctx, const b200q_weight *const *w, int nw, co
         return B200Q_OK;
     }
     const int mt = gemv_max_m();
+    if (M >= ctx->skinny_min_m && M <= skinny_max_m()) {
+        // verify / small continuous batches: one pass over the packed weights, exact bf16 activations
+        ctx->last_route = B200Q_ROUTE_SKINNY;
+        const bool f32 = x_dtype != B200Q_TYPE_BF16;
+        const int step = f32 ? 8 : 16;     // fp32 rows take two token slots each (high and low halves)
+        for (int64_t m0 = 0; m0 < M; m0 += step) {
+            const int mc = (int)std::min<int64_t>(step, M - m0);
+            void *yy[4];
+            for (int i = 0; i < nw; ++i) yy[i] = (char *)y[i] + m0 * ldy[i] * act_size(y_dtype);
+            const void *xx = (const char *)x + m0 * ldx * act_size(x_dtype);
+            b200q_status s = run_skinny(ctx, w, nw, xx, x_dtype, mc, ldx, yy, y_dtype, ldy, st);
+            if (s != B200Q_OK) return s;
+        }
+        return B200Q_OK;
+    }
     if (M > mt) {   // prefill / verify batches: tensor cores, one launch per weight
         ctx->last_route = B200Q_ROUTE_GEMM;
         bool converted = false;
@@ -388,6 +459,77 @@ b200q_status ensure_host_path(b200q_ctx *ctx, size_t xb, size_t yb) {
         ctx->hy_bytes = 0;
         CU_TRY(ctx, cudaMalloc(&ctx->hy_dev, yb));
         ctx->hy_bytes = yb;
+    }
+    return B200Q_OK;
+}
+
+// A plan of 5..16 activation rows: consecutive products of one block type form a group that one
+// skinny launch runs (a job that reads what earlier jobs wrote starts a new group, so stream order
+// provides the dependency); the plan owns the groups' images, chunk sums, counters and job tables.
+b200q_status plan_create_skinny(b200q_ctx *ctx, b200q_plan *pl, const b200q_job *jobs, int n_jobs, int M) {
+    struct Group { std::vector<SkinnyProduct> prods; };
+    std::vector<Group> groups;
+    for (int i = 0; i < n_jobs; ++i) {
+        const b200q_job &j = jobs[i];
+        if (j.n_weights < 1 || j.n_weights > 4) return fail(ctx, B200Q_ERR_INVALID_CONFIG, "job %d: 1..4 weights", i);
+        if (j.flags & B200Q_JOB_SUM_RANKS)
+            return fail(ctx, B200Q_ERR_INVALID_CONFIG, "job %d: sums over ranks inside the launch need M <= %d", i, gemv_max_m());
+        if (j.x_dtype != B200Q_TYPE_BF16 && M > 8)
+            return fail(ctx, B200Q_ERR_INVALID_CONFIG, "job %d: plans of more than 8 rows take bf16 activations", i);
+        for (int k = 0; k < j.n_weights; ++k) {
+            b200q_status s = validate_mm(ctx, j.w[k], j.x_dev, j.x_dtype, M, j.ldx, j.y_dev[k], j.y_dtype, j.ldy[k]);
+            if (s == B200Q_OK && (j.w[k]->type != j.w[0]->type || j.w[k]->K != j.w[0]->K))
+                s = fail(ctx, B200Q_ERR_INVALID_CONFIG, "job %d: weights of one job must share type and K", i);
+            if (s != B200Q_OK) return s;
+        }
+        if (j.w[0]->K == 0) return fail(ctx, B200Q_ERR_INVALID_CONFIG, "job %d: K = 0 is not allowed in a plan", i);
+        const bool waits = (j.flags & B200Q_JOB_WAITS_FOR_EARLIER) != 0;
+        for (int k = 0; k < j.n_weights; ++k) {
+            const b200q_weight *w = j.w[k];
+            if (w->N == 0) continue;
+            SkinnyProduct a{};
+            a.qt = w->type;
+            a.w = w->dev;
+            a.N = (int)w->N;
+            a.K = (int)w->K;
+            a.Kpad = (int)w->Kpad;
+            a.x = j.x_dev;
+            a.ldx = j.ldx;
+            a.x_is_bf16 = j.x_dtype == B200Q_TYPE_BF16;
+            a.y = j.y_dev[k];
+            a.ldy = j.ldy[k];
+            a.y_is_bf16 = j.y_dtype == B200Q_TYPE_BF16;
+            a.M = M;
+            const bool fresh = groups.empty() || (waits && k == 0) || groups.back().prods[0].qt != a.qt ||
+                               groups.back().prods[0].x_is_bf16 != a.x_is_bf16 ||
+                               (int)groups.back().prods.size() >= skinny_max_products();
+            if (fresh) groups.emplace_back();
+            groups.back().prods.push_back(a);
+        }
+    }
+    size_t ws = 0;
+    for (const Group &g : groups)
+        for (const SkinnyProduct &a : g.prods) ws += skinny_part_bytes(a);
+    if (groups.empty()) return B200Q_OK;
+    CU_TRY(ctx, cudaMalloc(reinterpret_cast<void **>(&pl->sk_ws), std::max<size_t>(ws, 256)));
+    CU_TRY(ctx, cudaMalloc(reinterpret_cast<void **>(&pl->sk_jobs), groups.size() * skinny_job_table_bytes()));
+    size_t ws_off = 0;
+    for (size_t gi = 0; gi < groups.size(); ++gi) {
+        const Group &g = groups[gi];
+        size_t gws = 0;
+        for (const SkinnyProduct &a : g.prods) gws += skinny_part_bytes(a);
+        SkinnyBuffers buf{};
+        buf.ws = pl->sk_ws + ws_off;
+        buf.ws_bytes = gws;
+        buf.jobs_dev = pl->sk_jobs + gi * skinny_job_table_bytes();
+        buf.status = ctx->status_dev;
+        buf.sm_count = ctx->sm_count;
+        buf.smem_limit = ctx->smem_optin;
+        SkinnySet *set = nullptr;
+        cudaError_t e = skinny_set_create(g.prods.data(), (int)g.prods.size(), buf, &set);
+        if (e != cudaSuccess) return cuda_fail(ctx, e, "skinny plan group");
+        pl->sets.push_back(set);
+        ws_off += gws;
     }
     return B200Q_OK;
 }
@@ -469,8 +611,21 @@ void b200q_ctx_destroy(b200q_ctx *ctx) {
     if (ctx->hy_dev) cudaFree(ctx->hy_dev);
     if (ctx->gemm_scratch) cudaFree(ctx->gemm_scratch);
     if (ctx->gemm_part) cudaFree(ctx->gemm_part);
+    if (ctx->sk_ws) cudaFree(ctx->sk_ws);
     if (ctx->status_dev) cudaFree(ctx->status_dev);
     delete ctx;
+}
+
+b200q_status b200q_ctx_set_option(b200q_ctx *ctx, int32_t option, int64_t value) {
+    if (!ctx) return B200Q_ERR_INVALID_CONFIG;
+    switch (option) {
+    case B200Q_OPT_SKINNY_MIN_M:
+        if (value < 2 || value > skinny_max_m() + 1) return fail(ctx, B200Q_ERR_INVALID_CONFIG, "SKINNY_MIN_M must be 2..%d", skinny_max_m() + 1);
+        ctx->skinny_min_m = (int)value;
+        return B200Q_OK;
+    default:
+        return fail(ctx, B200Q_ERR_INVALID_CONFIG, "unknown option %d", option);
+    }
 }
 
 b200q_status b200q_last_error(const b200q_ctx *ctx, char *buf, size_t n) {
@@ -751,11 +906,24 @@ b200q_status b200q_plan_create(b200q_ctx *ctx, const b200q_job *jobs, int32_t n_
     if (!out) return fail(ctx, B200Q_ERR_INVALID_CONFIG, "null out pointer");
     *out = nullptr;
     if (!jobs || n_jobs < 1) return fail(ctx, B200Q_ERR_INVALID_CONFIG, "a plan needs at least one job");
-    if (M < 1 || M > gemv_max_m()) return fail(ctx, B200Q_ERR_INVALID_CONFIG, "plans take 1..%d activation rows", gemv_max_m());
+    if (M < 1 || M > skinny_max_m()) return fail(ctx, B200Q_ERR_INVALID_CONFIG, "plans take 1..%d activation rows", skinny_max_m());
     b200q_plan *pl = new (std::nothrow) b200q_plan();
     if (!pl) return fail(ctx, B200Q_ERR_OVERLOADED, "out of host memory");
     pl->ctx = ctx;
     pl->M = (int)M;
+    bool rank_sums = false;
+    for (int i = 0; i < n_jobs; ++i) rank_sums |= (jobs[i].flags & B200Q_JOB_SUM_RANKS) != 0;
+    // 3 or more rows run on the skinny kernel, like single calls; plans that add partial sums over
+    // ranks inside the launch stay on the streaming kernel (up to 4 rows)
+    if (M > gemv_max_m() || (M >= ctx->skinny_min_m && !rank_sums)) {
+        s = plan_create_skinny(ctx, pl, jobs, n_jobs, (int)M);
+        if (s != B200Q_OK) {
+            b200q_plan_destroy(pl);
+            return s;
+        }
+        *out = pl;
+        return B200Q_OK;
+    }
     for (int i = 0; i < n_jobs; ++i) {
         const b200q_job &j = jobs[i];
         if (j.n_weights < 1 || j.n_weights > 4) {
@@ -830,6 +998,15 @@ b200q_status b200q_plan_run(b200q_ctx *ctx, b200q_plan *plan, void *stream) {
     if (!plan || plan->ctx != ctx) return fail(ctx, B200Q_ERR_INVALID_CONFIG, "bad plan");
     ctx->last_route = B200Q_ROUTE_NONE;
     ctx->last_launches = 0;
+    if (!plan->sets.empty()) {
+        for (const SkinnySet *set : plan->sets) {
+            cudaError_t e = skinny_set_launch(set, (cudaStream_t)stream);
+            if (e != cudaSuccess) return cuda_fail(ctx, e, "skinny plan launch");
+            ctx->last_launches += skinny_set_launches(set);
+        }
+        ctx->last_route = B200Q_ROUTE_SKINNY;
+        return B200Q_OK;
+    }
     if (plan->jobs.empty()) return B200Q_OK;
     if (plan->has_xq) {
         cudaError_t e = stream_xprep_launch(plan->jobs_dev, (int)plan->jobs.size(), plan->M, (cudaStream_t)stream);
@@ -847,6 +1024,9 @@ void b200q_plan_destroy(b200q_plan *plan) {
     if (plan->ctx) cudaSetDevice(plan->ctx->device);
     if (plan->jobs_dev) cudaFree(plan->jobs_dev);
     if (plan->xq_dev) cudaFree(plan->xq_dev);
+    for (SkinnySet *set : plan->sets) skinny_set_destroy(set);
+    if (plan->sk_ws) cudaFree(plan->sk_ws);
+    if (plan->sk_jobs) cudaFree(plan->sk_jobs);
     delete plan;
 }
 

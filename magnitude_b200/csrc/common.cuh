@@ -181,6 +181,36 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity)
     }
 }
 
+// try_wait with a cap (ns) on how long the hardware may keep the thread suspended.  Without the hint
+// a suspended waiter may resume only about a microsecond after the phase completes, which is most
+// of an item's time in the pipelines that wait once per item.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity), "r"(ns)
+        : "memory");
+    return ok != 0;
+}
+
+// bounded wait for waits on a pipeline's critical path: re-checks every few dozen nanoseconds
+__device__ __forceinline__ bool mbar_wait_bounded_fast(uint32_t bar, uint32_t parity) {
+#pragma unroll 1
+    for (int i = 0; i < (1 << 12); ++i)
+        if (mbar_try_wait_hint(bar, parity, 32)) return true;
+    const uint64_t t0 = globaltimer_ns();
+#pragma unroll 1
+    while (true) {
+#pragma unroll 1
+        for (int i = 0; i < 128; ++i)
+            if (mbar_try_wait_hint(bar, parity, 64)) return true;
+        if (globaltimer_ns() - t0 > kWaitLimitNs) return false;
+    }
+}
+
 // 1-D bulk copy global -> shared, completion counted in bytes on an mbarrier.
 // dst, src 16-byte aligned, bytes a multiple of 16.  No cluster multicast anywhere.
 __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {

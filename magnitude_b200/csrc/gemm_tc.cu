@@ -306,22 +306,6 @@ template <> struct Unit<QT_Q6_K> {
 
 // ---- the kernel -------------------------------------------------------------------------------
 
-// try_wait with a cap on how long the hardware may keep the thread suspended: without the hint a
-// suspended waiter was seen to resume only about a microsecond after the phase completed (several
-// K-steps' worth of time), and a crowd of threads spinning on the non-suspending test_wait slowed
-// every barrier operation of the CTA down to a few hundred cycles.
-__device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t ns) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity), "r"(ns)
-        : "memory");
-    return ok != 0;
-}
-
 // Bounded wait.  FAST waits sit on the critical path (tensor-core issue, dequant hand-over, TMA
 // issue) and re-check every few dozen nanoseconds; the others (the epilogue's, long by design)
 // let the hardware suspend them for as long as it likes.  After the limit the waiter raises the

@@ -76,6 +76,44 @@ size_t stream_xq_bytes(const StreamJob &J, int M);
 cudaError_t stream_xprep_launch(const StreamJob *jobs_dev, int njobs, int M, cudaStream_t st);
 cudaError_t stream_launch(const StreamLaunch &a, cudaStream_t st);
 
+// ---- skinny.cu ------------------------------------------------------------------------------
+// 2..16 activation rows against one or more weights of one block type: the packed weights stream
+// through shared memory once and meet the exact bf16 activations in mma.sync with fp32 accumulation;
+// products whose K spans several 2048-weight chunks end with a small chunk-sum launch.
+struct SkinnyProduct {
+    int qt;
+    const uint8_t *w;        // streaming-layout weights
+    int N, K, Kpad;
+    const void *x;           // activations [M][K], bf16 (M <= 16) or fp32 (M <= 8: hi/lo halves take two token slots)
+    long long ldx;
+    int x_is_bf16;
+    void *y;
+    long long ldy;
+    int y_is_bf16;
+    int M;
+};
+struct SkinnyBuffers {
+    uint8_t *ws;             // chunk sums of the call (skinny_part_bytes per product)
+    size_t ws_bytes;
+    void *jobs_dev;          // skinny_job_table_bytes() of device memory for calls with more than one product
+    int *status;
+    int sm_count;
+    size_t smem_limit;
+};
+int skinny_max_m();
+int skinny_max_products();
+size_t skinny_part_bytes(const SkinnyProduct &a);
+size_t skinny_job_table_bytes();
+// at most four products (their descriptions travel in the kernel parameters): prepare, launch, forget
+cudaError_t skinny_run(const SkinnyProduct *prods, int n, const SkinnyBuffers &buf, cudaStream_t st, int *launches);
+// up to skinny_max_products() products prepared once and launched many times (plans): buf.jobs_dev,
+// and buf.ws stay owned by the caller and must outlive the set
+struct SkinnySet;
+cudaError_t skinny_set_create(const SkinnyProduct *prods, int n, const SkinnyBuffers &buf, SkinnySet **out);
+cudaError_t skinny_set_launch(const SkinnySet *set, cudaStream_t st);
+int skinny_set_launches(const SkinnySet *set);
+void skinny_set_destroy(SkinnySet *set);
+
 // ---- gemm_tc.cu -----------------------------------------------------------------------------
 struct GemmLaunch {
     int qt;

@@ -10,7 +10,8 @@
 // Calls alternate between two slot sets: block b of a rank stores call e + 2 only after it has read
 // block b's range of call e + 1 from every rank, and a rank stores call e + 1 only after reading
 // call e, so a pair is never overwritten before it has been read.  The call number lives in device
-// memory (one counter per block), which keeps a launch replayable from a CUDA graph.
+// memory (one counter per block), which keeps a launch replayable from a CUDA graph.  Block b owns a
+// fixed element range and every block counts every call, so counts may change from call to call.
 // Every rank must make the same sequence of calls with the same counts.
 #include <algorithm>
 
@@ -52,7 +53,10 @@ __global__ void __launch_bounds__(kPeerThreads) peer_allreduce_kernel(const Peer
     __syncthreads();
     const unsigned e = s_epoch;
     const size_t set_off = (size_t)(e & 1) * kPeerMaxWorld * kPeerSlotFloats;
-    const int per = (p.count + (int)gridDim.x - 1) / (int)gridDim.x;
+    // Block b always owns elements [1024 b, 1024 b + 1024), whatever the call's count, and every
+    // block counts every call: a pair found under the current number can then only have been
+    // stored by the same block of a peer for this very call.
+    constexpr int per = kPeerSlotFloats / kPeerBlocks;
     const int lo = b * per, hi = min(lo + per, p.count);
 
     // 1. my partial sums -> slot [set][my rank] of every rank
@@ -106,9 +110,8 @@ cudaError_t peer_allreduce_launch(const PeerLaunch &a, cudaStream_t st) {
         p.base[r] = a.base[r];
     }
     p.status = a.status;
-    // every rank derives the same grid from the count alone: one block per 1024 elements
-    const int blocks = std::min(kPeerBlocks, (a.count + 1023) / 1024);
-    peer_allreduce_kernel<<<blocks, kPeerThreads, 0, st>>>(p);
+    // always the full grid, so that every block's call counter advances on every call
+    peer_allreduce_kernel<<<kPeerBlocks, kPeerThreads, 0, st>>>(p);
     return cudaGetLastError();
 }
 

@@ -121,6 +121,10 @@ class Backend:
             B.lib().b200q_ctx_destroy(self._h)
             self._h = c_void_p()
 
+    def set_option(self, option: int, value: int) -> None:
+        """Per-context setting (B.OPT_*), e.g. the smallest M that takes the skinny route."""
+        self._check(B.lib().b200q_ctx_set_option(self._h, option, value))
+
     def last_route(self) -> tuple[int, int]:
         r, n = c_int32(), c_int32()
         B.lib().b200q_last_route(self._h, byref(r), byref(n))

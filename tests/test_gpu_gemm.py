@@ -1,8 +1,8 @@
-"""GPU parity of the tensor-core prefill route (M > 4) against the CPU oracle.
+"""GPU parity of the tensor-core prefill route (M > 16) against the CPU oracle.
 
 Tolerance (fixed by the task statement): fp32-accumulated outputs within max relative error 5e-3
-for the bf16 prefill path, "relative" meaning |err| <= rel * max(|ref|, rms(ref)).  The weights
-enter the tensor cores rounded to bf16, the activations are bf16, accumulation is fp32.
+for the prefill path, "relative" meaning |err| <= rel * max(|ref|, rms(ref)).  The weights enter
+the tensor cores dequantized to fp16, the activations converted to fp16, accumulation is fp32.
 """
 import numpy as np
 import pytest
@@ -23,7 +23,7 @@ def _acts(m, k, seed):
 
 
 @pytest.mark.parametrize("qt", TYPES)
-@pytest.mark.parametrize("m,n,k", [(16, 128, 256), (5, 128, 512), (64, 256, 1024), (17, 130, 768), (100, 3, 2304),
+@pytest.mark.parametrize("m,n,k", [(24, 128, 256), (20, 128, 512), (64, 256, 1024), (17, 130, 768), (100, 3, 2304),
                                    (300, 260, 5120), (512, 384, 4096)])
 def test_prefill_small_shapes(backend, orc, qt, m, n, k):
     rng = np.random.default_rng(m + n + k)

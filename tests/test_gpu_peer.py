@@ -1,6 +1,7 @@
-"""Peer-memory all-reduce on two GPUs (skipped on a single-GPU box): sums equal the rank-ordered
-fp32 sum bit for bit on every rank, for aligned, ragged and tiny vectors, eagerly and replayed from a
-CUDA graph."""
+"""Peer-memory all-reduce on 2, 4 and 8 GPUs (skipped where the box has fewer): sums equal the
+rank-ordered fp32 sum bit for bit on every rank, for aligned, ragged and tiny vectors whose length
+changes from call to call, eagerly and replayed from a CUDA graph; and the sums over ranks inside a
+decode plan."""
 import os
 import socket
 
@@ -35,7 +36,7 @@ def _worker(rank, world, port, out_dir):
     be.peer_setup(dist)
     ok = True
     stream = torch.cuda.Stream()
-    for it, count in enumerate([4096, 1000, 16384, 5, 4096, 4096, 14336, 3]):
+    for it, count in enumerate([4096, 1000, 16384, 5, 4096, 4096, 14336, 3, 3584, 7168, 10752, 1000, 10752, 7168]):
         gens = [torch.Generator().manual_seed(100 * it + r) for r in range(world)]
         parts = [torch.randn(count, generator=g) for g in gens]          # every rank knows all partial vectors
         want = parts[0].clone()
@@ -118,10 +119,10 @@ def _worker(rank, world, port, out_dir):
     dist.destroy_process_group()
 
 
-def test_peer_allreduce_two_gpus(tmp_path):
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs two GPUs")
-    world = 2
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_peer_allreduce_and_plan_sums(tmp_path, world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     mp.spawn(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
     for r in range(world):
         assert (tmp_path / f"ok{r}").read_text() == "1"
