@@ -111,6 +111,62 @@ class ClockSampler:
         }
 
 
+def sample_stats(samples_ms):
+    """Median, median absolute deviation and spread of per-step device times (the reference keeps raw
+    repetitions: inference/parity/cases/performance/backend-ops/native-perf-qualification.json:37-43)."""
+    a = np.asarray(samples_ms, dtype=np.float64)
+    med = float(np.median(a))
+    mad = float(np.median(np.abs(a - med)))
+    return {"median_ms": med, "mad_ms": mad, "min_ms": float(a.min()), "max_ms": float(a.max()),
+            "relative_spread": float((a.max() - a.min()) / med) if med > 0 else None,
+            "samples_ms": [round(float(v), 6) for v in a]}
+
+
+def physical_cores():
+    """Distinct (physical id, core id) pairs of /proc/cpuinfo; falls back to the logical count."""
+    try:
+        seen, phys, core = set(), None, None
+        for line in open("/proc/cpuinfo"):
+            if line.startswith("physical id"):
+                phys = line.split(":")[1].strip()
+            elif line.startswith("core id"):
+                core = line.split(":")[1].strip()
+            elif not line.strip():
+                if phys is not None and core is not None:
+                    seen.add((phys, core))
+                phys = core = None
+        if seen:
+            return len(seen)
+    except Exception:
+        pass
+    return os.cpu_count() or 1
+
+
+def load_quant_module():
+    """magnitude_b200/ggml_quant.py by file path: the CPU arm needs the synthetic-weight encoders but must
+    not load the CUDA library that importing the package would."""
+    import importlib.util
+
+    spec = importlib.util.spec_from_file_location("b200q_ggml_quant", ROOT / "magnitude_b200" / "ggml_quant.py")
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def calibration_row(tensor_type, bytes_per_second, launch_us, spread, count):
+    """One row in the shape of the reference's hardware-calibration metric
+    (inference/crates/icn-hardware/src/lib.rs:4043-4055; consumed at :1380-1382)."""
+    return {"tensor_type": tensor_type, "routed": False, "bytes_per_second": bytes_per_second,
+            "launch_microseconds": launch_us, "relative_spread": spread, "sample_count": count,
+            "stable": bool(spread is not None and spread < 0.05)}
+
+
+def p0_row(time_us, flops, bytes_moved, memory_bytes, n_runs):
+    """The reference's backend-op performance row (inference/crates/icn-parity/src/decode.rs:548-562)."""
+    return {"time_us": time_us, "flops": flops, "bandwidth_gb_s": bytes_moved / (time_us * 1e-6) / 1e9,
+            "memory_kb": memory_bytes / 1024.0, "n_runs": n_runs}
+
+
 def dist_env():
     return int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
 
@@ -128,8 +184,9 @@ def cpu_reference_pass(orc, mats, xs, reps):
     return (time.perf_counter() - t0) / reps
 
 
-def make_host_layer(seed=0):
-    from magnitude_b200 import ggml_quant as gq
+def make_host_layer(seed=0, gq=None):
+    if gq is None:
+        from magnitude_b200 import ggml_quant as gq
 
     gate = gq.synth_weights(Q4_K, INTER, HIDDEN, seed)
     up = gq.synth_weights(Q4_K, INTER, HIDDEN, seed + 1)
@@ -146,9 +203,9 @@ def run_reference(args):
     from oracle import oracle as orc  # the CPU restatement of the reference's path, timed here
 
     orc.build()
-    from magnitude_b200 import ggml_quant as gq
+    gq = load_quant_module()
 
-    gate, up, down = make_host_layer()
+    gate, up, down = make_host_layer(gq=gq)
     rng = np.random.default_rng(1)
     xh = gq.f32_to_bf16_bits(rng.standard_normal((1, HIDDEN), dtype=np.float32)).astype(np.uint32) << 16
     xi = gq.f32_to_bf16_bits(rng.standard_normal((1, INTER), dtype=np.float32)).astype(np.uint32) << 16
@@ -169,12 +226,22 @@ def run_reference(args):
     value = bytes_pass / sec / 1e9
     cores = orc.num_threads()
     sample = f"{layers} of {LAYERS} layers per step (gate, up, down each), all {cores} host threads"
+    # the reference's CPU-resident parity cases run one thread (single-batch-logits.json:24-25): same pass, one layer
+    one = []
+    for _ in range(3):
+        t0 = time.perf_counter()
+        for (pk, n, k), x in zip(mats[:3], xs[:3]):
+            orc.matmul_cpu(Q4_K, pk, n, k, x, threads=1)
+        one.append(time.perf_counter() - t0)
+    one_thread = sum(algorithmic_bytes(n, k) for _, n, k in mats[:3]) / float(np.median(one)) / 1e9
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3 * (LAYERS / layers),
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "u8/int32 block dots, fp32 accumulate",
         "data": "synthetic", "config": workload_config(args.gpus),
-        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample,
+                         "physical_cores": physical_cores(), "one_thread_value": one_thread,
+                         "stats": sample_stats([p_ * 1e3 for p_ in per])},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line))
@@ -330,23 +397,93 @@ def run_b200(args):
     for _ in range(max(args.warmup, 3)):
         run_step()
     barrier()
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    evs = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
     with ClockSampler(local_rank) as clocks:
         barrier()
         with torch.cuda.stream(stream):
-            ev0.record(stream)
-        for _ in range(args.steps):
+            evs[0].record(stream)
+        for i in range(args.steps):
             run_step()
-        with torch.cuda.stream(stream):
-            ev1.record(stream)
+            with torch.cuda.stream(stream):
+                evs[i + 1].record(stream)
         barrier()
-        ms_total = ev0.elapsed_time(ev1)
+        ms_total = evs[0].elapsed_time(evs[-1])
+        step_samples = [evs[i].elapsed_time(evs[i + 1]) for i in range(args.steps)]
         # keep sampling clocks under the same load for a moment so short runs still get samples
         t_end = time.time() + 0.6
         while time.time() < t_end:
             run_step()
         torch.cuda.synchronize()
     be.sync(stream)
+
+    # ---- result check on the box that was timed (outside the timed region) -------------------------
+    # every layer holds the same encoded matrices, so after a step y_d is the full down product
+    # (summed over the ranks) and y_g this rank's rows of the gate product: compare with the exact
+    # host product of the decoded blocks (numpy, fp64 accumulation).
+    check = None
+    if not args.no_exchange and not args.no_check:
+        run_step()
+        torch.cuda.synchronize()
+        wd = gq.dequantize_q4_k(down_h, INTER).astype(np.float64)
+        ref_d = (wd @ x_i.float().numpy().astype(np.float64).T).T
+        r0, r1 = mb.shard_range(Q4_K, INTER, HIDDEN, mb.SPLIT_COLUMN, rank, world, 256) if world > 1 else (0, INTER)
+        wg = gq.dequantize_q4_k(gate_h[r0:r1], HIDDEN).astype(np.float64)
+        ref_g = (wg @ x_h.float().numpy().astype(np.float64).T).T
+
+        def worst(got, ref):
+            rms = float(np.sqrt(np.mean(ref * ref)))
+            return float(np.max(np.abs(got - ref) / (1e-3 * np.maximum(np.abs(ref), rms))))
+
+        w_d, w_g = worst(y_d.cpu().numpy().astype(np.float64), ref_d), worst(y_g.cpu().numpy().astype(np.float64), ref_g)
+        check = {"max_err_over_tol": max(w_d, w_g), "down_summed_over_ranks": w_d, "gate_rows_of_this_rank": w_g,
+                 "tolerance": "|err| <= 1e-3 * max(|ref|, rms(ref))", "ok": bool(max(w_d, w_g) <= 1.0)}
+        if world > 1:
+            t = torch.tensor([check["max_err_over_tol"]], dtype=torch.float64, device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            check["max_err_over_tol"] = float(t.item())
+            check["ok"] = bool(check["max_err_over_tol"] <= 1.0)
+            check["ranks_checked"] = world
+
+    # ---- two figures beside the headline (N = 1): the step with its real dependency, and a long run ----
+    dependent = sustained = None
+    if world == 1 and plans is not None and not args.quick:
+        dep_plan = be.plan(jobs, waits=[i % 2 == 1 for i in range(len(jobs))])     # down waits for gate/up
+        with torch.cuda.stream(stream):
+            for _ in range(3):
+                dep_plan.run(stream=stream)
+        stream.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = max(5, min(args.steps, 20))
+        with torch.cuda.stream(stream):
+            e0.record(stream)
+            for _ in range(reps):
+                dep_plan.run(stream=stream)
+            e1.record(stream)
+        stream.synchronize()
+        be.sync(stream)
+        ms_dep = e0.elapsed_time(e1) / reps
+        dependent = {"ms_per_step": ms_dep, "value": LAYERS * (2 * algorithmic_bytes(INTER, HIDDEN) + algorithmic_bytes(HIDDEN, INTER)) / (ms_dep * 1e-3) / 1e9,
+                     "unit": UNIT, "note": "same step, every down projection flagged as reading what gate/up wrote (one consumer team, grid counter between jobs)"}
+        dep_plan.close()
+        with ClockSampler(local_rank) as long_clocks:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            n_long = 0
+            with torch.cuda.stream(stream):
+                e0.record(stream)
+            t_end = time.time() + 2.5
+            while time.time() < t_end:
+                for _ in range(50):
+                    run_step()
+                n_long += 50
+                stream.synchronize()
+            with torch.cuda.stream(stream):
+                e1.record(stream)
+            stream.synchronize()
+        ms_long = e0.elapsed_time(e1) / n_long
+        lc = long_clocks.summary()
+        sustained = {"ms_per_step": ms_long, "steps": n_long, "seconds": e0.elapsed_time(e1) / 1e3, "sm_mhz": lc["sm_mhz"], "reasons": lc["reasons"],
+                     "ms_x_mhz": ms_long * lc["sm_mhz"] if lc["sm_mhz"] else None,
+                     "value": LAYERS * (2 * algorithmic_bytes(INTER, HIDDEN) + algorithmic_bytes(HIDDEN, INTER)) / (ms_long * 1e-3) / 1e9, "unit": UNIT}
     if world > 1:
         t = torch.tensor([ms_total], dtype=torch.float64, device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -452,23 +589,16 @@ def run_b200(args):
 
     cpu_baseline = None
     if world == 1 and not args.no_cpu_baseline:
-        from oracle import oracle as orc  # CPU-baseline leg only
-
-        orc.build()
-        xh32 = x_h.float().numpy()
-        xi32 = x_i.float().numpy()
-        mats = [(gate_h, INTER, HIDDEN), (up_h, INTER, HIDDEN), (down_h, HIDDEN, INTER)]
-        xs = [xh32, xh32, xi32]
-        cpu_reference_pass(orc, mats, xs, 1)
-        reps, spent, t_start = 0, [], time.perf_counter()
-        while time.perf_counter() - t_start < 10.0 and reps < 400:
-            spent.append(cpu_reference_pass(orc, mats, xs, 1))
-            reps += 1
-        sec = float(np.median(spent))
-        cpu_baseline = {
-            "value": per_layer / sec / 1e9, "unit": UNIT, "cores": orc.num_threads(), "kind": "port",
-            "sample": f"one layer (gate, up, down) x {reps} passes, median; integer block-dot CPU path, OpenMP over rows",
-        }
+        # the CPU path is timed by this script's own reference arm in a process of its own, so that this
+        # figure and the reference arm's are taken in the same process state (no CUDA runtime, one OpenMP pool)
+        try:
+            env = dict(os.environ)
+            env.pop("OMP_NUM_THREADS", None)
+            out = subprocess.run([sys.executable, str(ROOT / "bench.py"), "--impl", "reference", "--steps", "20", "--warmup", "2"],
+                                 capture_output=True, text=True, timeout=600, env=env).stdout.strip().splitlines()
+            cpu_baseline = json.loads(out[-1])["cpu_baseline"]
+        except Exception as exc:  # pragma: no cover
+            cpu_baseline = {"value": None, "unit": UNIT, "cores": os.cpu_count(), "kind": "port", "sample": f"failed: {exc}"}
 
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
@@ -479,7 +609,30 @@ def run_b200(args):
         "gpu_launches": launches_per_step * ((2 if plans is not None else 1) + (1 if (use_peer and not fused) else 0)) * args.steps,
         "cuda_graph": used_graph,
         "clocks": clocks.summary(),
+        "stats": sample_stats(step_samples),
+        "check": check,
+        "dependent": dependent,
+        "sustained": sustained,
     }
+    st = line["stats"]
+    launch_us = None
+    line["p0"] = p0_row(st["median_ms"] * 1e3 / (3 * LAYERS), 2.0 * INTER * HIDDEN, rank_bytes / (3 * LAYERS),
+                        LAYERS * 3 * (INTER * HIDDEN // 256 * 144) / world, args.steps)
+    line["p0"]["note"] = "per projection (MUL_MAT, Q4_K, M = 1): median step time / 96 projections"
+    line["calibration"] = [calibration_row("Q4_K", rank_bytes / (st["median_ms"] * 1e-3), launch_us, st["relative_spread"], args.steps)]
+    if world == 1 and not args.quick and args.workload == "decode":
+        # the other two halves of the metric, measured after the headline region on the same box
+        sec_args = argparse.Namespace(**vars(args))
+        sec_args.steps, sec_args.warmup = min(args.steps, 10), 3
+        line["secondary"] = {}
+        for name, fn in (("prefill", run_prefill), ("skinny", run_skinny), ("calibration", run_calibration)):
+            try:
+                line["secondary"][name] = fn(sec_args, emit=False)
+            except Exception as exc:  # pragma: no cover
+                line["secondary"][name] = {"unavailable": f"{type(exc).__name__}: {exc}"}
+        cal = line["secondary"].get("calibration")
+        if isinstance(cal, dict) and "rows" in cal:
+            line["calibration"] = cal["rows"]
     print(json.dumps(mark_diagnostic(line, args)))
     sys.stdout.flush()
     if dist is not None:
@@ -490,7 +643,7 @@ def run_b200(args):
 # secondary line: the prefill GEMM (configs[3]) — tcgen05 route, reported in TFLOP/s
 # ------------------------------------------------------------------------------------------------
 
-def run_prefill(args):
+def run_prefill(args, emit=True):
     """M=2048 tokens x Q4_K 14336x4096, bf16 activations (1% of channels x20), bf16 output.
 
     A step multiplies the same activations by `copies` distinct weight buffers (default 8, 264 MB,
@@ -613,9 +766,10 @@ def run_prefill(args):
         "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "fp16 x fp16 tcgen05.mma, fp32 accumulate in TMEM (weights dequantized exactly to fp16, activations bf16 -> fp16)",
         "data": "synthetic", "config": cfg,
-        "roofline": {"bound": "tensor", "kernel": "gemm_tc_pair_kernel<Q4_K> (+ convert_x_vec8_kernel per product)", "achieved": value, "peak": peak,
-                     "unit": "TFLOP/s", "frac": value / peak, "peak_source": f"of {src}", "peak_burst": burst,
-                     "frac_of_burst": (value / burst) if burst else None, "traffic": NCU_PREFILL_TRAFFIC_BYTES_PER_LAUNCH,
+        "roofline": {"bound": "tensor", "kernel": "gemm_tc_pair_kernel<Q4_K> (+ convert_x_vec8_kernel per product)", "achieved": value,
+                     "peak": burst or peak, "unit": "TFLOP/s", "frac": value / (burst or peak),
+                     "peak_source": f"of {'measured (burst: the timed region lasts tens of milliseconds)' if burst else src}",
+                     "peak_sustained": peak, "frac_of_sustained": value / peak, "traffic": NCU_PREFILL_TRAFFIC_BYTES_PER_LAUNCH,
                      "us_per_launch": ms_step * 1e3 / copies,
                      "note": "2*M*N*K per product / device time per product, activation conversion launch included"},
         "cpu_baseline": None,
@@ -623,14 +777,19 @@ def run_prefill(args):
                 "d2h_bytes_per_step": M * N * 2, "ms_per_step": e2e_s * 1e3,
                 "api": "pinned host activations -> device, b200q_matmul per weight, last result -> pinned host, synchronize"},
         "gpu_launches": 2 * copies * args.steps, "clocks": clocks.summary(),
+        "p0": p0_row(ms_step * 1e3 / copies, flops_one, N * K // 256 * 144 + M * K * 2 + M * N * 2, N * K // 256 * 144 + M * K * 2 + M * N * 2, args.steps * copies),
     }
+    del ws, w0, x, y
+    be.close()
+    if not emit:
+        return line
     print(json.dumps(line))
 
 # ------------------------------------------------------------------------------------------------
 # secondary line: skinny batches (configs[2]) — speculative-decode verify, M in {2, 4, 8, 16}
 # ------------------------------------------------------------------------------------------------
 
-def run_skinny(args):
+def run_skinny(args, emit=True):
     """Fused-QKV Q4_K 6144x4096 and down Q6_K 4096x14336 against M = 2, 4, 8, 16 bf16 tokens.
 
     Every case multiplies the tokens by 16 distinct copies of the weight (more than L2 for both
@@ -702,7 +861,8 @@ def run_skinny(args):
                 del g, plan
             del ws, w0
     value = tot_bytes / tot_s / 1e9
-    print(json.dumps({
+    be.close()
+    line = {
         "metric": "skinny_gemm_weight_bandwidth", "value": value, "unit": UNIT, "n_gpus": 1, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": tot_s * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "M <= 4: u8 x s16 dp4a; M >= 5: exact integer weights x bf16 in mma.sync, fp32 accumulate", "data": "synthetic",
@@ -711,7 +871,78 @@ def run_skinny(args):
         "roofline": {"bound": "hbm", "achieved": value, "peak": peak, "unit": UNIT, "frac": value / peak, "peak_source": f"of {src}",
                      "traffic": None, "note": "algorithmic bytes of all eight cases / their device time"},
         "cases": cases, "cpu_baseline": None, "e2e": None, "gpu_launches": None, "clocks": clocks.summary(),
-    }))
+    }
+    if not emit:
+        return line
+    print(json.dumps(line))
+
+
+# ------------------------------------------------------------------------------------------------
+# calibration rows: sustained mat-vec bytes per second and launch cost per block type
+# ------------------------------------------------------------------------------------------------
+
+def run_calibration(args, emit=True):
+    """Per block type a synthetic 4096 x 4096 mat-vec (M = 1, bf16 in, fp32 out) over 24 distinct weight
+    copies in one decode plan, and the cost of an (almost) empty launch: the quantities the reference's
+    hardware calibration records per tensor type (icn-hardware/src/lib.rs:4043-4055;
+    producer icn-server/src/main.rs:2989)."""
+    import torch
+
+    rank, local_rank, world = dist_env()
+    if world > 1:
+        return {"unavailable": "calibration rows are single-GPU"}
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    import magnitude_b200 as mb
+    from magnitude_b200 import ggml_quant as gq
+
+    be = mb.Backend(local_rank)
+    stream = torch.cuda.Stream(device=dev)
+    n = k = 4096
+    copies, reps = 24, 12
+    rows = []
+    x = torch.randn(1, k, device=dev).to(torch.bfloat16)
+    y = torch.empty((1, n), dtype=torch.float32, device=dev)
+    tiny = be.upload(Q4_K, gq.synth_weights(Q4_K, 4, 256, 0), 4, 256)
+    xt = torch.randn(1, 256, device=dev).to(torch.bfloat16)
+    yt = torch.empty((1, 4), dtype=torch.float32, device=dev)
+
+    def timed(fn, count):
+        out = []
+        for _ in range(count):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            with torch.cuda.stream(stream):
+                e0.record(stream)
+                fn()
+                e1.record(stream)
+            stream.synchronize()
+            out.append(e0.elapsed_time(e1))
+        return out
+
+    for _ in range(3):
+        be.project(tiny, xt, out=yt, stream=stream)
+    launch_us = float(np.median(timed(lambda: be.project(tiny, xt, out=yt, stream=stream), 20))) * 1e3
+    for qt, name, blk_e, blk_b in ((Q4_K, "Q4_K", 256, 144), (14, "Q6_K", 256, 210), (8, "Q8_0", 32, 34)):
+        w0 = be.upload(qt, gq.synth_weights(qt, n, k, 0), n, k)
+        ws = [w0] + [w0.clone() for _ in range(copies - 1)]
+        plan = be.plan([([w], x, [y]) for w in ws])
+        for _ in range(3):
+            plan.run(stream=stream)
+        stream.synchronize()
+        t = timed(lambda: plan.run(stream=stream), reps)
+        st = sample_stats(t)
+        nbytes = copies * (n * (k // blk_e) * blk_b + k * 2 + n * 4)
+        rows.append(calibration_row(name, nbytes / (st["median_ms"] * 1e-3), launch_us, st["relative_spread"], reps))
+        plan.close()
+        del ws, w0
+    be.sync(stream)
+    tiny.close()
+    be.close()
+    line = {"metric": "hardware_calibration_rows", "rows": rows, "shape": "4096 x 4096, M = 1, 24 weight copies per run (one decode plan)",
+            "launch_microseconds_definition": "device time of one call on a 4 x 256 weight"}
+    if emit:
+        print(json.dumps(line))
+    return line
 
 
 def main():
@@ -734,7 +965,9 @@ def main():
                     help="skinny workload: run the 16 weight copies of a case as one decode plan instead of 16 calls")
     ap.add_argument("--skinny-min-m", type=int, default=0,
                     help="skinny workload: smallest M sent to the skinny kernel (default: the library's, 5)")
-    ap.add_argument("--workload", choices=["decode", "prefill", "skinny"], default="decode",
+    ap.add_argument("--quick", action="store_true", help="headline figure only: no dependent / sustained / secondary measurements")
+    ap.add_argument("--no-check", action="store_true", help="skip the host check of the step's results")
+    ap.add_argument("--workload", choices=["decode", "prefill", "skinny", "calibration"], default="decode",
                     help="decode = the headline Q4_K GEMV step; prefill = the M=2048 Q4_K GEMM (secondary line, TFLOP/s)")
     args = ap.parse_args()
     # last resort against a stuck collective or teardown: never hold a GPU box for more than 20 minutes
@@ -747,6 +980,8 @@ def main():
         run_prefill(args)
     elif args.workload == "skinny":
         run_skinny(args)
+    elif args.workload == "calibration":
+        run_calibration(args)
     elif args.impl == "reference":
         run_reference(args)
     else:

@@ -73,13 +73,14 @@ struct SmemHead {
     uint64_t full[kMaxWarps * kMaxDepth];
     uint64_t empty[kMaxWarps * kMaxDepth];
     uint64_t xfull[2];       // per team: the job's pre-quantized activation has landed in the team's area
-    uint64_t xempty[2];      // per team: every warp of the team is done with the area's previous contents
     int fail;                // raised by any warp that gave up a wait; everybody then drains and leaves
     int decide[2];           // per team: its first thread's sample of `fail`, taken before a barrier so all its warps agree
     int prod_done;           // the producer warp has stopped issuing copies
     int issued[kMaxWarps];   // ... after issuing this many items into each consumer's ring
     unsigned xepoch[2];      // per team: exchanges posted so far (loaded from the exchange buffer)
     int xfail;               // a wait for a peer's partial sums ran out
+    int xdone[2];            // per team: warps x jobs finished so far (a job's activation area may be refilled once all
+                             // the team's warps have left the job before it)
 };
 
 // (value, exchange number) pairs of the in-launch rank sums: one 8-byte store / load each
@@ -220,10 +221,8 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1) stream_kernel(const S
     }
     if (threadIdx.x == 0) {
         head.fail = 0; head.prod_done = 0; head.xfail = 0;
-        for (int t = 0; t < 2; ++t) {
-            mbar_init(smem_u32(&head.xfull[t]), 1);
-            mbar_init(smem_u32(&head.xempty[t]), t == 0 ? cw0 : max(CW - cw0, 1));
-        }
+        head.xdone[0] = head.xdone[1] = 0;
+        for (int t = 0; t < 2; ++t) mbar_init(smem_u32(&head.xfull[t]), 1);
         mbar_fence_init();
         fence_proxy_async();
     }
@@ -317,10 +316,17 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1) stream_kernel(const S
             }
             if (xjb < p.njobs) {
                 const StreamJob &J = jobs_s[xjb];
-                if (!J.xq) {
+                // Every job, with or without an image, is passed only once all warps of the team have
+                // finished the job before it (a plain count: nothing to confuse however far either side
+                // runs ahead).  Passing earlier would overwrite the activation area of a job still in
+                // progress and arrive twice in one phase of the image barrier.
+                const int xwarps = xteam ? CW - cw0 : cw0;
+                if (xseq != 0 && *reinterpret_cast<volatile int *>(&head.xdone[xteam]) < xseq * xwarps) {
+                    // the previous job of the team is still running
+                } else if (!J.xq) {
                     next_xjob();
                     progressed = true;
-                } else if (xseq == 0 || mbar_test_wait(smem_u32(&head.xempty[xteam]), (uint32_t)(xseq - 1) & 1u)) {
+                } else {
                     const int n_isum = (J.qt == QT_Q6_K) ? (J.Kpad >> 4) : (J.Kpad >> 5);
                     const uint32_t bytes = (uint32_t)p.M * (uint32_t)(2 * J.Kpad + (J.Kpad >> 5) * 4 + n_isum * 4);
                     const uint32_t bar = smem_u32(&head.xfull[xteam]);
@@ -611,7 +617,10 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1) stream_kernel(const S
         // this warp is done with the activation area: the next pre-quantized image may overwrite it
         if (p.has_xq) {
             __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&head.xempty[team]));
+            if (lane == 0) {
+                __threadfence_block();
+                atomicAdd(&head.xdone[team], 1);
+            }
         }
         have_raw = false;
         if (MT == 1 && !(p.debug & 4)) {

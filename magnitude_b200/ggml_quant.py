@@ -101,6 +101,26 @@ def quantize(qtype: int, w: np.ndarray) -> np.ndarray:
     raise ValueError(f"unsupported ggml type id {qtype}")
 
 
+def dequantize_q4_k(packed: np.ndarray, k: int) -> np.ndarray:
+    """fp32 [N, K] of Q4_K blocks: w = (d * sc) * q - (dmin * m), each product rounded to fp32 (the format's rule)."""
+    rows = np.ascontiguousarray(packed, dtype=np.uint8).reshape(-1, k // 256, 144)
+    n, nb = rows.shape[:2]
+    d = rows[..., 0:2].copy().view(np.float16).astype(np.float32)[..., 0]
+    dmin = rows[..., 2:4].copy().view(np.float16).astype(np.float32)[..., 0]
+    sc = rows[..., 4:16]
+    ls = np.empty((n, nb, 8), np.uint8)
+    lm = np.empty((n, nb, 8), np.uint8)
+    ls[..., 0:4] = sc[..., 0:4] & 63
+    lm[..., 0:4] = sc[..., 4:8] & 63
+    ls[..., 4:8] = (sc[..., 8:12] & 0xF) | ((sc[..., 0:4] >> 6) << 4)
+    lm[..., 4:8] = (sc[..., 8:12] >> 4) | ((sc[..., 4:8] >> 6) << 4)
+    qs = rows[..., 16:].reshape(n, nb, 4, 32)
+    q = np.stack([qs & 0xF, qs >> 4], axis=3).reshape(n, nb, 8, 32).astype(np.float32)
+    dl = (d[..., None] * ls.astype(np.float32)).astype(np.float32)
+    ml = (dmin[..., None] * lm.astype(np.float32)).astype(np.float32)
+    return ((dl[..., None] * q).astype(np.float32) - ml[..., None]).astype(np.float32).reshape(n, k)
+
+
 def f32_to_bf16_bits(a: np.ndarray) -> np.ndarray:
     """Round-to-nearest-even bf16 bit patterns (uint16) of an fp32 array."""
     u = np.ascontiguousarray(a, dtype=np.float32).view(np.uint32)

@@ -278,6 +278,40 @@ def test_plan_with_dependent_job(backend, orc, m):
     assert orc.within_tolerance(out.cpu().numpy(), ref, REL_DECODE)[0]
 
 
+@pytest.mark.parametrize("m", [1, 2])
+def test_plan_alternating_independent_and_dependent_jobs(backend, orc, m):
+    # six jobs: three layers of gate/up (own input, converted once by the prep launch) and down (reads
+    # what gate wrote: converted inside the launch after the grid-wide wait).  The activation areas of
+    # consecutive jobs are refilled in lock step with the consumers, whatever the mix.
+    k0, n0, n1 = 1024, 2048, 256
+    layers = []
+    for l in range(3):
+        pg, pu = _weights(orc, mb.TYPE_Q4_K, n0, k0, 20 + l), _weights(orc, mb.TYPE_Q4_K, n0, k0, 30 + l)
+        pd = _weights(orc, mb.TYPE_Q4_K, n1, n0, 40 + l)
+        layers.append((backend.upload(mb.TYPE_Q4_K, pg, n0, k0), backend.upload(mb.TYPE_Q4_K, pu, n0, k0),
+                       backend.upload(mb.TYPE_Q4_K, pd, n1, n0)))
+    xs = [_acts(m, k0, 50 + l, torch.bfloat16) for l in range(3)]
+    ygs = [torch.zeros((m, n0), device="cuda") for _ in range(3)]
+    yus = [torch.zeros((m, n0), device="cuda") for _ in range(3)]
+    outs = [torch.zeros((m, n1), device="cuda") for _ in range(3)]
+    jobs, waits = [], []
+    for l, (g, u, d) in enumerate(layers):
+        jobs += [([g, u], xs[l], [ygs[l], yus[l]]), ([d], ygs[l], [outs[l]])]
+        waits += [False, True]
+    plan = backend.plan(jobs, waits=waits)
+    for _ in range(3):
+        for t in ygs + yus + outs:
+            t.zero_()
+        plan.run()
+        backend.sync()
+        for l, (g, u, d) in enumerate(layers):
+            rg, ru = backend.project(g, xs[l]), backend.project(u, xs[l])
+            rd = backend.project(d, rg)
+            backend.sync()
+            assert torch.equal(ygs[l], rg) and torch.equal(yus[l], ru)
+            assert torch.equal(outs[l], rd)
+
+
 def test_plan_argument_checks(backend, orc):
     k = 512
     w = backend.upload(mb.TYPE_Q4_K, _weights(orc, mb.TYPE_Q4_K, 8, k, 1), 8, k)
