@@ -97,6 +97,11 @@ const char *b200q_version(void);
  * at inference/crates/icn-models/src/gguf.rs:129. */
 int64_t b200q_tensor_storage_bytes(int32_t type, int64_t n_elements);
 
+/* The same rule from the tensor's shape, as the reference calls it (type, shape): dims[0] is the row
+ * length and must be a multiple of the type's block; every ggml tensor type a GGUF file may carry is
+ * known here, not only the three the kernels multiply.  -1 for an unknown type or a bad shape. */
+int64_t b200q_tensor_storage_bytes_shape(int32_t type, int32_t n_dims, const int64_t *dims);
+
 /* -- context -------------------------------------------------------------------------------- */
 
 /* One context per GPU / executor thread.  Replaces LlamaBackend::init + model.new_context
@@ -165,6 +170,58 @@ void b200q_weight_destroy(b200q_weight *w);
  * no fused multiply-add.  (Qualified upstream by the dependency's test-quantize-fns,
  * inference/parity/upstream/targets.toml:38.) */
 b200q_status b200q_dequantize(b200q_ctx *ctx, const b200q_weight *w, float *out_dev, void *stream);
+
+/* -- GGUF files ----------------------------------------------------------------------------- */
+
+/* A parsed GGUF header: metadata keys and the tensor table.  Mirrors the bounded walk of the
+ * reference's inspector (inference/crates/icn-models/src/gguf.rs:75-149): magic, version 2..3,
+ * counts within the same bounds, every metadata value type, per tensor name / dimensions / type /
+ * offset with overflow checks, alignment from general.alignment (default 32, power of two), header
+ * rounded up to the alignment and inside the file.  No GPU is needed until b200q_gguf_upload. */
+typedef struct b200q_gguf b200q_gguf;
+
+typedef struct b200q_gguf_summary_t {
+    uint32_t version;
+    uint32_t alignment;
+    uint64_t tensor_count;
+    uint64_t metadata_count;
+    uint64_t tensor_storage_bytes; /* sum over tensors, the figure of GgufInspection::tensor_storage_bytes (gguf.rs:34-35) */
+    uint64_t header_bytes;         /* where the tensor data starts (gguf.rs:138-149) */
+    uint64_t parameter_count;      /* general.parameter_count, else the sum of the tensors' elements */
+    uint64_t file_bytes;
+} b200q_gguf_summary_t;
+
+typedef struct b200q_gguf_tensor_t {
+    const char *name;     /* owned by the handle */
+    uint32_t type;        /* ggml tensor type id */
+    uint32_t n_dims;
+    uint64_t dims[8];     /* dims[0] = row length K, dims[1] = rows N; unused entries are 1 */
+    uint64_t elements;
+    uint64_t bytes;
+    uint64_t file_offset; /* absolute position of the tensor's data in the file */
+} b200q_gguf_tensor_t;
+
+/* Opens and parses `path`.  On failure *out is NULL and `err` (if given) holds the reason in the
+ * reference's words ("file is not GGUF", "unsupported GGUF version 7", "GGUF header is
+ * structurally invalid: ..."); B200Q_ERR_BACKEND for I/O errors, B200Q_ERR_INVALID_CONFIG for a
+ * malformed file. */
+b200q_status b200q_gguf_open(const char *path, b200q_gguf **out, char *err, size_t err_n);
+void b200q_gguf_close(b200q_gguf *g);
+b200q_status b200q_gguf_last_error(const b200q_gguf *g, char *buf, size_t n);
+b200q_status b200q_gguf_summary(const b200q_gguf *g, b200q_gguf_summary_t *out);
+/* A string-valued metadata key (e.g. "general.architecture"), or NULL; owned by the handle. */
+const char *b200q_gguf_metadata_string(const b200q_gguf *g, const char *key);
+/* An unsigned-integer-valued key with the reference's widening rules (gguf.rs:297-316). */
+b200q_status b200q_gguf_metadata_u64(const b200q_gguf *g, const char *key, uint64_t *out);
+b200q_status b200q_gguf_tensor_info(const b200q_gguf *g, uint64_t index, b200q_gguf_tensor_t *out);
+b200q_status b200q_gguf_find(const b200q_gguf *g, const char *name, uint64_t *index);
+/* Copies the tensor's packed bytes into dst (dst_bytes must equal its byte count). */
+b200q_status b200q_gguf_read_tensor(b200q_gguf *g, uint64_t index, void *dst, size_t dst_bytes);
+/* Reads tensor `index` (a Q8_0 / Q4_K / Q6_K matrix) and uploads it, whole (world = 1) or as the
+ * shard of `rank` under the rule of b200q_weight_upload_shard.  Replaces, for one tensor, what
+ * LlamaModel::load_from_file does for the whole file (icn-engine/src/lib.rs:972). */
+b200q_status b200q_gguf_upload(b200q_ctx *ctx, b200q_gguf *g, uint64_t index, int32_t split, int32_t rank, int32_t world,
+                               int64_t align_rows, b200q_weight **out);
 
 /* -- the projection -------------------------------------------------------------------------- */
 

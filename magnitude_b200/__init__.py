@@ -19,7 +19,16 @@ from ._binding import (  # noqa: F401
     TYPE_Q6_K,
     TYPE_Q8_0,
 )
-from .projection import Backend, Plan, ProjectionWeight, shard_range, tensor_storage_bytes, tp_unique_id  # noqa: F401
+from .projection import (  # noqa: F401
+    Backend,
+    GgufFile,
+    Plan,
+    ProjectionWeight,
+    shard_range,
+    tensor_storage_bytes,
+    tensor_storage_bytes_shape,
+    tp_unique_id,
+)
 
 _binding.lib()  # fail loudly at import time when the native library is absent
 

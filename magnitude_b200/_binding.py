@@ -114,6 +114,36 @@ SIGNATURES = {
 }
 
 
+class GgufSummary(ctypes.Structure):
+    """struct b200q_gguf_summary_t of include/b200q.h."""
+
+    _fields_ = [("version", ctypes.c_uint32), ("alignment", ctypes.c_uint32), ("tensor_count", c_uint64),
+                ("metadata_count", c_uint64), ("tensor_storage_bytes", c_uint64), ("header_bytes", c_uint64),
+                ("parameter_count", c_uint64), ("file_bytes", c_uint64)]
+
+
+class GgufTensor(ctypes.Structure):
+    """struct b200q_gguf_tensor_t of include/b200q.h."""
+
+    _fields_ = [("name", c_char_p), ("type", ctypes.c_uint32), ("n_dims", ctypes.c_uint32), ("dims", c_uint64 * 8),
+                ("elements", c_uint64), ("bytes", c_uint64), ("file_offset", c_uint64)]
+
+
+SIGNATURES.update({
+    "b200q_tensor_storage_bytes_shape": (c_int64, [c_int32, c_int32, POINTER(c_int64)]),
+    "b200q_gguf_open": (c_int32, [c_char_p, POINTER(c_void_p), c_char_p, c_size_t]),
+    "b200q_gguf_close": (None, [c_void_p]),
+    "b200q_gguf_last_error": (c_int32, [c_void_p, c_char_p, c_size_t]),
+    "b200q_gguf_summary": (c_int32, [c_void_p, POINTER(GgufSummary)]),
+    "b200q_gguf_metadata_string": (c_char_p, [c_void_p, c_char_p]),
+    "b200q_gguf_metadata_u64": (c_int32, [c_void_p, c_char_p, POINTER(c_uint64)]),
+    "b200q_gguf_tensor_info": (c_int32, [c_void_p, c_uint64, POINTER(GgufTensor)]),
+    "b200q_gguf_find": (c_int32, [c_void_p, c_char_p, POINTER(c_uint64)]),
+    "b200q_gguf_read_tensor": (c_int32, [c_void_p, c_uint64, c_void_p, c_size_t]),
+    "b200q_gguf_upload": (c_int32, [c_void_p, c_void_p, c_uint64, c_int32, c_int32, c_int32, c_int64, POINTER(c_void_p)]),
+})
+
+
 class B200QError(RuntimeError):
     """A non-zero b200q_status.  `.status` is the code, `.kind` mirrors the reference's InferenceError variants."""
 

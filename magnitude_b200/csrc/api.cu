@@ -96,7 +96,7 @@ struct b200q_ctx {
     int skinny_min_m = 3;             // smallest M that takes the skinny route (smaller batches: the dp4a kernel)
     int gemm_bn = 0, gemm_debug = 0, gemm_pair = 0, gemm_ksplit = 1;
     // tunables (environment overrides for experiments)
-    int gemv_warps = 0, gemv_depth = 0, gemv_grid = 0, gemv_smem = 0, gemv_rows = 0, gemv_debug = 0, gemv_pdl = 1, gemv_teams = 2, gemv_xprep = 1;
+    int gemv_warps = 0, gemv_depth = 0, gemv_grid = 0, gemv_smem = 0, gemv_rows = 0, gemv_debug = 0, gemv_pdl = 1, gemv_teams = 2, gemv_xprep = 1, gemv_nap = 0;
     // tensor parallel
     NcclComm comm = nullptr;
     int tp_rank = 0, tp_world = 1;
@@ -257,6 +257,7 @@ b200q_status run_stream(b200q_ctx *ctx, const StreamJob *jobs_host, const Stream
     a.debug = ctx->gemv_debug;
     a.pdl = ctx->gemv_pdl;
     a.teams = ctx->gemv_teams;
+    a.producer_nap = ctx->gemv_nap;
     a.peer_rank = ctx->peer_rank;
     a.peer_world = ctx->peer_world;
     for (int r = 0; r < kPeerMaxWorld; ++r) a.peer_base[r] = ctx->peer_base[r];
@@ -589,6 +590,7 @@ b200q_status b200q_ctx_create(int32_t device, b200q_ctx **out) {
     ctx->gemv_pdl = env_int("B200Q_GEMV_PDL", 1);
     ctx->gemv_teams = env_int("B200Q_GEMV_TEAMS", 2);
     ctx->gemv_xprep = env_int("B200Q_GEMV_XPREP", 1);
+    ctx->gemv_nap = env_int("B200Q_GEMV_NAP", 0);
     ctx->gemm_bn = env_int("B200Q_GEMM_BN", 0);
     ctx->gemm_debug = env_int("B200Q_GEMM_DEBUG", 0);
     ctx->gemm_pair = env_int("B200Q_GEMM_PAIR", 1);

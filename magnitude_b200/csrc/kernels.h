@@ -65,6 +65,7 @@ struct StreamLaunch {
     int debug;                    // experiments only (see gemv.cu)
     int pdl;                      // launch with programmatic stream serialization
     int teams;                    // 1 = never split the consumer warps into two teams
+    int producer_nap;             // ns the producer warp sleeps when it finds nothing to do (0 = spin)
     uint8_t *peer_base[8];        // every rank's exchange buffer (jobs flagged STREAM_JOB_SUM_RANKS); null = none
     int peer_rank, peer_world;
 };

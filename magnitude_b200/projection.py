@@ -330,6 +330,94 @@ class Backend:
             pass
 
 
+class GgufFile:
+    """A parsed GGUF header (b200q_gguf_open): tensor table, metadata, and upload of its quantized matrices.
+
+    Mirrors what the reference's bounded inspector reads (inference/crates/icn-models/src/gguf.rs:75-149);
+    parsing needs no GPU.
+    """
+
+    def __init__(self, path):
+        h = c_void_p()
+        err = ctypes.create_string_buffer(512)
+        st = B.lib().b200q_gguf_open(str(path).encode(), byref(h), err, 512)
+        if st:
+            raise B.B200QError(st, err.value.decode(errors="replace"))
+        self._h = h
+        s = B.GgufSummary()
+        B.lib().b200q_gguf_summary(self._h, byref(s))
+        self.version, self.alignment = s.version, s.alignment
+        self.tensor_count, self.metadata_count = s.tensor_count, s.metadata_count
+        self.tensor_storage_bytes, self.header_bytes = s.tensor_storage_bytes, s.header_bytes
+        self.parameter_count, self.file_bytes = s.parameter_count, s.file_bytes
+
+    def _error(self) -> str:
+        buf = ctypes.create_string_buffer(512)
+        B.lib().b200q_gguf_last_error(self._h, buf, 512)
+        return buf.value.decode(errors="replace")
+
+    def metadata_string(self, key: str):
+        v = B.lib().b200q_gguf_metadata_string(self._h, key.encode())
+        return None if v is None else v.decode(errors="replace")
+
+    def metadata_u64(self, key: str):
+        out = ctypes.c_uint64()
+        return out.value if B.lib().b200q_gguf_metadata_u64(self._h, key.encode(), byref(out)) == 0 else None
+
+    def tensor(self, index_or_name) -> dict:
+        idx = index_or_name if isinstance(index_or_name, int) else self.index_of(index_or_name)
+        t = B.GgufTensor()
+        st = B.lib().b200q_gguf_tensor_info(self._h, idx, byref(t))
+        if st:
+            raise B.B200QError(st, f"no tensor {index_or_name!r}")
+        return {"index": idx, "name": t.name.decode(errors="replace"), "type": t.type, "dims": list(t.dims[: t.n_dims]),
+                "elements": t.elements, "bytes": t.bytes, "file_offset": t.file_offset}
+
+    def tensors(self) -> list:
+        return [self.tensor(i) for i in range(self.tensor_count)]
+
+    def index_of(self, name: str) -> int:
+        out = ctypes.c_uint64()
+        st = B.lib().b200q_gguf_find(self._h, name.encode(), byref(out))
+        if st:
+            raise B.B200QError(st, f"no tensor named {name!r}")
+        return out.value
+
+    def read(self, index_or_name) -> np.ndarray:
+        t = self.tensor(index_or_name)
+        out = np.empty(t["bytes"], dtype=np.uint8)
+        st = B.lib().b200q_gguf_read_tensor(self._h, t["index"], c_void_p(out.ctypes.data), out.size)
+        if st:
+            raise B.B200QError(st, self._error())
+        return out
+
+    def upload(self, backend: "Backend", index_or_name, split: int = B.SPLIT_COLUMN, rank: int = 0, world: int = 1,
+               align_rows: int = 0) -> ProjectionWeight:
+        t = self.tensor(index_or_name)
+        out = c_void_p()
+        st = B.lib().b200q_gguf_upload(backend._h, self._h, t["index"], split, rank, world, align_rows, byref(out))
+        if st:
+            raise B.B200QError(st, self._error())
+        return ProjectionWeight(backend, out.value)
+
+    def close(self) -> None:
+        if self._h:
+            B.lib().b200q_gguf_close(self._h)
+            self._h = c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def tensor_storage_bytes_shape(qtype: int, dims) -> int:
+    """GGUF byte count from (type, shape), dims[0] the row length — the call at icn-models/src/gguf.rs:129."""
+    arr = (c_int64 * len(dims))(*dims)
+    return int(B.lib().b200q_tensor_storage_bytes_shape(qtype, len(dims), arr))
+
+
 def tp_unique_id() -> bytes:
     buf = ctypes.create_string_buffer(128)
     st = B.lib().b200q_tp_unique_id(buf)
