@@ -81,7 +81,12 @@ enum {
 enum {
     /* smallest M that takes the SKINNY route (2..17; 17 = never); smaller batches use the GEMV kernel.
      * Default 3. */
-    B200Q_OPT_SKINNY_MIN_M = 1
+    B200Q_OPT_SKINNY_MIN_M = 1,
+    /* limit, in milliseconds, of every bounded wait inside the kernels (default 2000).  The value is
+     * held per GPU and process, not per context: it applies to every context on the device. */
+    B200Q_OPT_WAIT_LIMIT_MS = 2,
+    /* host deadline of b200q_tp_init in milliseconds (default 60000) */
+    B200Q_OPT_TP_INIT_TIMEOUT_MS = 3
 };
 
 typedef struct b200q_ctx b200q_ctx;
@@ -318,7 +323,11 @@ b200q_status b200q_tp_unique_id(void *id_out_128);
 
 /* Joins a `world`-rank NCCL communicator on this context's device.  The reference has no
  * collective of its own (its multi-GPU is llama.cpp's in-process split); this is the single
- * all-reduce a row-parallel projection (O, down) needs. */
+ * all-reduce a row-parallel projection (O, down) needs.  Gives up with B200Q_ERR_TIMEOUT after
+ * B200Q_OPT_TP_INIT_TIMEOUT_MS when some rank never joins.  While a communicator is attached,
+ * b200q_sync also asks NCCL for asynchronous errors and aborts the communicator when one is
+ * reported or when its own deadline passes, so a collective that a failed rank never enters does
+ * not hold the stream for ever. */
 b200q_status b200q_tp_init(b200q_ctx *ctx, int32_t rank, int32_t world, const void *id_128);
 
 /* In-place sum over ranks of y_dev[count] (dtype F32 or BF16) on `stream`. */
@@ -339,6 +348,16 @@ b200q_status b200q_tp_finalize(b200q_ctx *ctx);
 b200q_status b200q_peer_export(b200q_ctx *ctx, void *handle_out_64);
 b200q_status b200q_peer_attach(b200q_ctx *ctx, int32_t rank, int32_t world, const void *handles);
 b200q_status b200q_peer_detach(b200q_ctx *ctx);
+
+/* The same exchange for ONE process that drives several GPUs (or several contexts) itself: the
+ * exchange buffers are passed as device pointers instead of IPC handles.
+ *   1. every context: b200q_peer_buffer -> its own buffer;
+ *   2. the caller enables peer access between the devices (cudaDeviceEnablePeerAccess);
+ *   3. every context: b200q_peer_attach_buffers(rank, world, buffers) with buffers[rank] its own.
+ * After B200Q_ERR_TIMEOUT from an exchange the ranks' call counters may disagree: further exchanges
+ * fail with B200Q_ERR_STOPPED until every rank has detached and attached again (both forms). */
+b200q_status b200q_peer_buffer(b200q_ctx *ctx, void **buffer_out);
+b200q_status b200q_peer_attach_buffers(b200q_ctx *ctx, int32_t rank, int32_t world, void *const *buffers);
 
 #ifdef __cplusplus
 }

@@ -29,7 +29,7 @@ TYPE_F32, TYPE_Q8_0, TYPE_Q4_K, TYPE_Q6_K, TYPE_BF16 = 0, 8, 12, 14, 30
 SPLIT_COLUMN, SPLIT_ROW = 0, 1
 ROUTE_NONE, ROUTE_GEMV, ROUTE_SKINNY, ROUTE_GEMM = 0, 1, 2, 3
 
-OPT_SKINNY_MIN_M = 1
+OPT_SKINNY_MIN_M, OPT_WAIT_LIMIT_MS, OPT_TP_INIT_TIMEOUT_MS = 1, 2, 3
 
 JOB_WAITS_FOR_EARLIER = 1
 JOB_SUM_RANKS = 2
@@ -111,6 +111,8 @@ SIGNATURES = {
     "b200q_peer_export": (c_int32, [c_void_p, c_void_p]),
     "b200q_peer_attach": (c_int32, [c_void_p, c_int32, c_int32, c_void_p]),
     "b200q_peer_detach": (c_int32, [c_void_p]),
+    "b200q_peer_buffer": (c_int32, [c_void_p, POINTER(c_void_p)]),
+    "b200q_peer_attach_buffers": (c_int32, [c_void_p, c_int32, c_int32, POINTER(c_void_p)]),
 }
 
 

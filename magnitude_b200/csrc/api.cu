@@ -6,7 +6,11 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <atomic>
 #include <chrono>
+#include <future>
+#include <memory>
+#include <mutex>
 #include <new>
 #include <thread>
 #include <vector>
@@ -34,13 +38,12 @@ struct NcclApi {
     int (*CommGetAsyncError)(NcclComm, int *) = nullptr;
     const char *(*GetErrorString)(int) = nullptr;
 };
-constexpr int kNcclFloat32 = 7, kNcclBfloat16 = 9, kNcclSum = 0;
+constexpr int kNcclFloat32 = 7, kNcclBfloat16 = 9, kNcclSum = 0, kNcclInProgress = 7;
 
 NcclApi *nccl_api() {
     static NcclApi api;
-    static bool tried = false;
-    if (!tried) {
-        tried = true;
+    static std::once_flag once;
+    std::call_once(once, [] {
         const char *names[] = {"libnccl.so.2", "libnccl.so"};
         for (const char *n : names) {
             api.handle = dlopen(n, RTLD_NOW | RTLD_GLOBAL);
@@ -59,7 +62,7 @@ NcclApi *nccl_api() {
                 api.handle = nullptr;
             }
         }
-    }
+    });
     return api.handle ? &api : nullptr;
 }
 
@@ -93,6 +96,9 @@ struct b200q_ctx {
     // skinny route (2..16 rows): chunk sums, row-block counters, job table
     uint8_t *sk_ws = nullptr;
     size_t sk_ws_bytes = 0;
+    uint64_t tp_timeout_ms = 60000;   // host deadline of b200q_tp_init
+    bool peer_stale = false;          // a peer exchange timed out: the ranks' call counters no longer agree
+    bool peer_ipc = true;             // peer buffers were mapped through CUDA IPC (else given as pointers)
     int skinny_min_m = 3;             // smallest M that takes the skinny route (smaller batches: the dp4a kernel)
     int gemm_bn = 0, gemm_debug = 0, gemm_pair = 0, gemm_ksplit = 1;
     // tunables (environment overrides for experiments)
@@ -586,13 +592,15 @@ b200q_status b200q_ctx_create(int32_t device, b200q_ctx **out) {
     ctx->gemv_grid = env_int("B200Q_GEMV_GRID", 0);
     ctx->gemv_smem = env_int("B200Q_GEMV_SMEM", 0);
     ctx->gemv_rows = env_int("B200Q_GEMV_ROWS", 0);
+#ifdef B200Q_TIMING_EXPERIMENTS      // pipeline parts switched off for timing: results are invalid, never in a shipped build
     ctx->gemv_debug = env_int("B200Q_GEMV_DEBUG", 0);
+    ctx->gemm_debug = env_int("B200Q_GEMM_DEBUG", 0);
+#endif
     ctx->gemv_pdl = env_int("B200Q_GEMV_PDL", 1);
     ctx->gemv_teams = env_int("B200Q_GEMV_TEAMS", 2);
     ctx->gemv_xprep = env_int("B200Q_GEMV_XPREP", 1);
     ctx->gemv_nap = env_int("B200Q_GEMV_NAP", 0);
     ctx->gemm_bn = env_int("B200Q_GEMM_BN", 0);
-    ctx->gemm_debug = env_int("B200Q_GEMM_DEBUG", 0);
     ctx->gemm_pair = env_int("B200Q_GEMM_PAIR", 1);
     ctx->gemm_ksplit = env_int("B200Q_GEMM_KSPLIT", 1);
     *out = ctx;
@@ -625,6 +633,21 @@ b200q_status b200q_ctx_set_option(b200q_ctx *ctx, int32_t option, int64_t value)
         if (value < 2 || value > skinny_max_m() + 1) return fail(ctx, B200Q_ERR_INVALID_CONFIG, "SKINNY_MIN_M must be 2..%d", skinny_max_m() + 1);
         ctx->skinny_min_m = (int)value;
         return B200Q_OK;
+    case B200Q_OPT_WAIT_LIMIT_MS: {
+        if (value < 1 || value > 600000) return fail(ctx, B200Q_ERR_INVALID_CONFIG, "WAIT_LIMIT_MS must be 1..600000");
+        b200q_status s = check_ctx(ctx);
+        if (s != B200Q_OK) return s;
+        const unsigned long long ns = (unsigned long long)value * 1000000ull;
+        CU_TRY(ctx, gemv_set_wait_limit_ns(ns));
+        CU_TRY(ctx, skinny_set_wait_limit_ns(ns));
+        CU_TRY(ctx, gemm_set_wait_limit_ns(ns));
+        CU_TRY(ctx, peer_set_wait_limit_ns(ns));
+        return B200Q_OK;
+    }
+    case B200Q_OPT_TP_INIT_TIMEOUT_MS:
+        if (value < 1) return fail(ctx, B200Q_ERR_INVALID_CONFIG, "TP_INIT_TIMEOUT_MS must be positive");
+        ctx->tp_timeout_ms = (uint64_t)value;
+        return B200Q_OK;
     default:
         return fail(ctx, B200Q_ERR_INVALID_CONFIG, "unknown option %d", option);
     }
@@ -655,15 +678,34 @@ b200q_status b200q_sync(b200q_ctx *ctx, void *stream, uint64_t timeout_ms) {
             ctx->poisoned = true;
             return cuda_fail(ctx, e, "stream");
         }
+        NcclApi *api = ctx->comm ? nccl_api() : nullptr;
+        if (api && api->CommGetAsyncError) {      // a collective that failed on some rank never finishes: ask NCCL
+            int async_err = 0;
+            if (api->CommGetAsyncError(ctx->comm, &async_err) == 0 && async_err != 0 && async_err != kNcclInProgress) {
+                if (api->CommAbort) api->CommAbort(ctx->comm);
+                ctx->comm = nullptr;
+                ctx->tp_world = 1;
+                return fail(ctx, B200Q_ERR_BACKEND, "NCCL reported an asynchronous error (%s); the communicator was aborted",
+                            api->GetErrorString ? api->GetErrorString(async_err) : "error");
+            }
+        }
         const auto ms = std::chrono::duration_cast<std::chrono::milliseconds>(std::chrono::steady_clock::now() - t0).count();
-        if (timeout_ms && (uint64_t)ms > timeout_ms)
+        if (timeout_ms && (uint64_t)ms > timeout_ms) {
+            if (api && api->CommAbort) {          // the deadline passed with a communicator attached: its kernels are
+                api->CommAbort(ctx->comm);        // told to stop, so the stream can drain and the context be reused
+                ctx->comm = nullptr;
+                ctx->tp_world = 1;
+                return fail(ctx, B200Q_ERR_TIMEOUT, "stream not finished after %llu ms; the NCCL communicator was aborted", (unsigned long long)timeout_ms);
+            }
             return fail(ctx, B200Q_ERR_TIMEOUT, "stream not finished after %llu ms", (unsigned long long)timeout_ms);
+        }
         std::this_thread::yield();
     }
     int status = 0;
     CU_TRY(ctx, cudaMemcpy(&status, ctx->status_dev, sizeof(int), cudaMemcpyDeviceToHost));
     if (status != DEV_OK) {
         cudaMemset(ctx->status_dev, 0, sizeof(int));
+        if (ctx->peer_world > 1) ctx->peer_stale = true;     // some rank may have skipped an exchange: counters disagree
         return fail(ctx, B200Q_ERR_TIMEOUT, "a kernel gave up a bounded wait (device status %d); results are invalid", status);
     }
     return B200Q_OK;
@@ -1010,6 +1052,11 @@ b200q_status b200q_plan_run(b200q_ctx *ctx, b200q_plan *plan, void *stream) {
         return B200Q_OK;
     }
     if (plan->jobs.empty()) return B200Q_OK;
+    if (ctx->peer_stale && ctx->peer_world > 1) {
+        for (const StreamJob &J : plan->jobs)
+            if (J.flags & STREAM_JOB_SUM_RANKS)
+                return fail(ctx, B200Q_ERR_STOPPED, "a peer exchange timed out earlier: detach and attach the peers again on every rank");
+    }
     if (plan->has_xq) {
         cudaError_t e = stream_xprep_launch(plan->jobs_dev, (int)plan->jobs.size(), plan->M, (cudaStream_t)stream);
         if (e != cudaSuccess) return cuda_fail(ctx, e, "activation prep launch");
@@ -1054,11 +1101,41 @@ b200q_status b200q_tp_init(b200q_ctx *ctx, int32_t rank, int32_t world, const vo
     if (!api) return fail(ctx, B200Q_ERR_BACKEND, "libnccl.so.2 could not be loaded");
     NcclUniqueId id;
     memcpy(&id, id_128, sizeof(id));
-    int rc = api->CommInitRank(&ctx->comm, world, id, rank);
+    // The rendezvous blocks until every rank has joined.  It runs on a helper thread so that this call
+    // can give up at the deadline (a rank that never joins must not hang the executor: the reference
+    // kills and replaces a backend that misses its one absolute deadline,
+    // design/icn/calibration-model-assessment.md:164-177); the helper is then left to finish or fail
+    // on its own and its communicator, if it ever gets one, is aborted.
+    struct InitState {
+        std::promise<int> done;
+        NcclComm comm = nullptr;
+        std::atomic<bool> abandoned{false};
+    };
+    auto state = std::make_shared<InitState>();
+    std::future<int> fut = state->done.get_future();
+    const int device = ctx->device;
+    std::thread([state, api, world, id, rank, device] {
+        cudaSetDevice(device);
+        NcclComm c = nullptr;
+        const int rc = api->CommInitRank(&c, world, id, rank);
+        state->comm = c;
+        if (state->abandoned.load() && rc == 0 && c) {
+            if (api->CommAbort) api->CommAbort(c);
+            else api->CommDestroy(c);
+        }
+        state->done.set_value(rc);
+    }).detach();
+    if (fut.wait_for(std::chrono::milliseconds(ctx->tp_timeout_ms)) != std::future_status::ready) {
+        state->abandoned.store(true);
+        return fail(ctx, B200Q_ERR_TIMEOUT, "ncclCommInitRank did not finish within %llu ms (rank %d of %d)",
+                    (unsigned long long)ctx->tp_timeout_ms, rank, world);
+    }
+    const int rc = fut.get();
     if (rc != 0) {
         ctx->comm = nullptr;
         return fail(ctx, B200Q_ERR_BACKEND, "ncclCommInitRank: %s", api->GetErrorString ? api->GetErrorString(rc) : "error");
     }
+    ctx->comm = state->comm;
     ctx->tp_rank = rank;
     ctx->tp_world = world;
     return B200Q_OK;
@@ -1072,6 +1149,8 @@ b200q_status b200q_allreduce(b200q_ctx *ctx, void *y_dev, int64_t count, int32_t
     if (count == 0) return B200Q_OK;
     if (ctx->peer_world > 1 && dtype == B200Q_TYPE_F32 && count <= kPeerSlotFloats &&
         !(reinterpret_cast<uintptr_t>(y_dev) & 3)) {
+        if (ctx->peer_stale)
+            return fail(ctx, B200Q_ERR_STOPPED, "a peer exchange timed out earlier: detach and attach the peers again on every rank");
         CU_TRY(ctx, cudaSetDevice(ctx->device));
         PeerLaunch a{};
         a.y = reinterpret_cast<float *>(y_dev);
@@ -1160,17 +1239,53 @@ b200q_status b200q_peer_attach(b200q_ctx *ctx, int32_t rank, int32_t world, cons
     }
     ctx->peer_rank = rank;
     ctx->peer_world = world;
+    ctx->peer_ipc = true;
+    ctx->peer_stale = false;
+    return B200Q_OK;
+}
+
+b200q_status b200q_peer_buffer(b200q_ctx *ctx, void **buffer_out) {
+    b200q_status s = check_ctx(ctx);
+    if (s != B200Q_OK) return s;
+    if (!buffer_out) return fail(ctx, B200Q_ERR_INVALID_CONFIG, "null out pointer");
+    char handle[B200Q_PEER_HANDLE_BYTES];
+    if ((s = b200q_peer_export(ctx, handle)) != B200Q_OK) return s;     // allocates and clears the buffer on first use
+    *buffer_out = ctx->peer_local;
+    return B200Q_OK;
+}
+
+b200q_status b200q_peer_attach_buffers(b200q_ctx *ctx, int32_t rank, int32_t world, void *const *buffers) {
+    b200q_status s = check_ctx(ctx);
+    if (s != B200Q_OK) return s;
+    if (world < 1 || world > kPeerMaxWorld || rank < 0 || rank >= world || !buffers)
+        return fail(ctx, B200Q_ERR_INVALID_CONFIG, "bad peer arguments (rank %d of %d, at most %d ranks)", rank, world, kPeerMaxWorld);
+    if (!ctx->peer_local) return fail(ctx, B200Q_ERR_INVALID_CONFIG, "b200q_peer_buffer has not been called");
+    if (ctx->peer_world > 0) return fail(ctx, B200Q_ERR_INVALID_CONFIG, "peers are already attached");
+    if (buffers[rank] != ctx->peer_local) return fail(ctx, B200Q_ERR_INVALID_CONFIG, "buffers[rank] must be this context's own buffer");
+    for (int r = 0; r < world; ++r) {
+        if (!buffers[r]) return fail(ctx, B200Q_ERR_INVALID_CONFIG, "null buffer of rank %d", r);
+        ctx->peer_base[r] = reinterpret_cast<uint8_t *>(buffers[r]);
+    }
+    ctx->peer_rank = rank;
+    ctx->peer_world = world;
+    ctx->peer_ipc = false;
+    ctx->peer_stale = false;
     return B200Q_OK;
 }
 
 b200q_status b200q_peer_detach(b200q_ctx *ctx) {
     if (!ctx) return B200Q_ERR_INVALID_CONFIG;
     cudaSetDevice(ctx->device);
-    for (int r = 0; r < ctx->peer_world; ++r)
-        if (r != ctx->peer_rank && ctx->peer_base[r]) cudaIpcCloseMemHandle(ctx->peer_base[r]);
+    if (ctx->peer_ipc)
+        for (int r = 0; r < ctx->peer_world; ++r)
+            if (r != ctx->peer_rank && ctx->peer_base[r]) cudaIpcCloseMemHandle(ctx->peer_base[r]);
     for (int r = 0; r < kPeerMaxWorld; ++r) ctx->peer_base[r] = nullptr;
+    // the next attachment starts from call number zero on every rank: clear what this one left behind
+    if (ctx->peer_local && ctx->peer_world > 0) cudaMemset(ctx->peer_local, 0, kPeerBufferBytes);
     ctx->peer_rank = -1;
     ctx->peer_world = 0;
+    ctx->peer_ipc = true;
+    ctx->peer_stale = false;
     return B200Q_OK;
 }
 

@@ -164,8 +164,11 @@ __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
 }
 
 // Wait limit for every device-side spin: after this long the waiter gives up, raises the status
-// word and the kernel drains and returns instead of hanging the GPU.
-constexpr uint64_t kWaitLimitNs = 2000000000ull;
+// word and the kernel drains and returns instead of hanging the GPU.  A variable (one copy per
+// source file and device; the context option B200Q_OPT_WAIT_LIMIT_MS sets them all) so that a host
+// can choose its own deadline and a test can make a wait run out quickly.
+static __device__ unsigned long long s_wait_limit_ns = 2000000000ull;
+#define kWaitLimitNs s_wait_limit_ns
 
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
 #pragma unroll 1

@@ -25,6 +25,7 @@
 #include <stdlib.h>
 
 #include <algorithm>
+#include <atomic>
 
 #include "common.cuh"
 #include "kernels.h"
@@ -1074,17 +1075,16 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t
                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
+EncodeTiledFn lookup_encode_fn() {
+    void *ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+        return reinterpret_cast<EncodeTiledFn>(ptr);
+    return nullptr;
+}
 EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    static bool tried = false;
-    if (!tried) {
-        tried = true;
-        void *ptr = nullptr;
-        cudaDriverEntryPointQueryResult qres;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
-            qres == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(ptr);
-    }
+    static const EncodeTiledFn fn = lookup_encode_fn();     // initialised once, also under concurrent first calls
     return fn;
 }
 
@@ -1097,7 +1097,7 @@ cudaError_t launch_gemm(const GemmParams &p, const GemmMaps &m, int grid, cudaSt
     auto kern = gemm_tc_kernel<QT>;
     constexpr size_t smem = smem_data_bytes(QT) + sizeof(GemmSmem) + 1024;
     static_assert(smem <= 232448, "shared-memory plan exceeds the 227 KB a block may use");
-    static int configured_dev = -1;
+    static std::atomic<int> configured_dev{-1};     // contexts on several threads may launch at once
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev != configured_dev) {
@@ -1114,7 +1114,7 @@ cudaError_t launch_gemm_pair(const GemmParams &p, const GemmMaps &m, int grid, c
     auto kern = gemm_tc_pair_kernel<QT>;
     constexpr size_t smem = pair_smem_data_bytes(QT) + sizeof(PairSmem) + 1024;
     static_assert(smem <= 232448, "shared-memory plan exceeds the 227 KB a block may use");
-    static int configured_dev = -1;
+    static std::atomic<int> configured_dev{-1};     // contexts on several threads may launch at once
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev != configured_dev) {
@@ -1320,12 +1320,12 @@ size_t gemm_static_scratch_elems() { return kStaticScratchBytes / 2; }
 // module on that device, so that first call should happen outside any stream capture).
 cudaError_t gemm_launch_static(GemmLaunch a, int x_is_bf16, cudaStream_t st) {
     constexpr int kMaxDevices = 64;
-    static void *dev_ptr[kMaxDevices] = {nullptr};
+    static std::atomic<void *> dev_ptr[kMaxDevices];     // zero-initialised; racing first calls store the same address
     int dev = -1;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
     if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
-    if (!dev_ptr[dev]) {
+    if (!dev_ptr[dev].load()) {
         void *ptr = nullptr;
         e = cudaGetSymbolAddress(&ptr, g_static_x_scratch);
         if (e != cudaSuccess) return e;
@@ -1333,11 +1333,13 @@ cudaError_t gemm_launch_static(GemmLaunch a, int x_is_bf16, cudaStream_t st) {
     }
     const long long ldd = (a.K + 7) & ~7;
     if ((size_t)a.M * (size_t)ldd > gemm_static_scratch_elems()) return cudaErrorInvalidValue;
-    e = gemm_convert_x(a.x, x_is_bf16, a.ldx, dev_ptr[dev], a.M, a.K, st);
+    e = gemm_convert_x(a.x, x_is_bf16, a.ldx, dev_ptr[dev].load(), a.M, a.K, st);
     if (e != cudaSuccess) return e;
-    a.x = dev_ptr[dev];
+    a.x = dev_ptr[dev].load();
     a.ldx = ldd;
     return gemm_launch(a, st);
 }
+
+cudaError_t gemm_set_wait_limit_ns(unsigned long long ns) { return cudaMemcpyToSymbol(s_wait_limit_ns, &ns, sizeof(ns)); }
 
 }  // namespace b200q

@@ -31,6 +31,7 @@
 #include <stdlib.h>
 
 #include <algorithm>
+#include <atomic>
 
 #include "gemv_units.cuh"
 #include "kernels.h"
@@ -799,11 +800,11 @@ cudaError_t launch_t(const StreamLaunch &a, StreamParams &p, int grid, cudaStrea
     const size_t smem = fixed + (size_t)warps * depth * R * stride;
 
     auto kern = stream_kernel<MT, TYPES>;
-    static size_t configured = 0;   // per instantiation; a context on another device re-sets it
-    static int configured_dev = -1;
+    static std::atomic<size_t> configured{0};   // per instantiation; a context on another device re-sets it
+    static std::atomic<int> configured_dev{-1};  // (contexts on several threads may launch at once)
     int dev = 0;
     cudaGetDevice(&dev);
-    if (smem > configured || dev != configured_dev) {
+    if (smem > configured.load() || dev != configured_dev.load()) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
         configured = smem;
@@ -936,5 +937,7 @@ cudaError_t stream_launch(const StreamLaunch &a, cudaStream_t st) {
     }
     return cudaSuccess;
 }
+
+cudaError_t gemv_set_wait_limit_ns(unsigned long long ns) { return cudaMemcpyToSymbol(s_wait_limit_ns, &ns, sizeof(ns)); }
 
 }  // namespace b200q

@@ -7,6 +7,12 @@
 
 namespace b200q {
 
+// ---- device wait limit (one variable per source file with bounded waits; all set together) --------
+cudaError_t gemv_set_wait_limit_ns(unsigned long long ns);
+cudaError_t skinny_set_wait_limit_ns(unsigned long long ns);
+cudaError_t gemm_set_wait_limit_ns(unsigned long long ns);
+cudaError_t peer_set_wait_limit_ns(unsigned long long ns);
+
 // ---- layout.cu ------------------------------------------------------------------------------
 // Host: re-lay rows [r0, r0 + n) x superblocks [sb0, sb1) of a GGUF tensor (row length K) into the
 // streaming layout at dst (n * row_bytes_for(qt, sb1 - sb0) bytes).  Only shard rows [ra, rb) are

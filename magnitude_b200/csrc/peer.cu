@@ -115,4 +115,6 @@ cudaError_t peer_allreduce_launch(const PeerLaunch &a, cudaStream_t st) {
     return cudaGetLastError();
 }
 
+cudaError_t peer_set_wait_limit_ns(unsigned long long ns) { return cudaMemcpyToSymbol(s_wait_limit_ns, &ns, sizeof(ns)); }
+
 }  // namespace b200q

@@ -26,6 +26,7 @@
 // Every mbarrier wait is bounded; a wait that runs out raises the status word and a flag that every
 // role polls, copies in flight are awaited (again bounded) and the kernel returns.
 #include <algorithm>
+#include <atomic>
 #include <new>
 #include <vector>
 
@@ -704,7 +705,7 @@ cudaError_t sk_launch_t(const SkParams &p, int grid, size_t smem_limit, cudaStre
     q.depth = depth;
     const size_t smem = L::kRingOff + (size_t)depth * L::kStageBytes;
     auto kern = skinny_kernel<QT, NT>;
-    static int configured_dev = -1;
+    static std::atomic<int> configured_dev{-1};     // contexts on several threads may launch at once
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev != configured_dev) {
@@ -897,5 +898,7 @@ extern "C" int b200q_debug_skinny_trace(unsigned long long *out_4096) {
 
 size_t skinny_job_table_bytes() { return sizeof(SkJob) * kSkMaxJobs; }
 int skinny_max_products() { return kSkMaxJobs; }
+
+cudaError_t skinny_set_wait_limit_ns(unsigned long long ns) { return cudaMemcpyToSymbol(s_wait_limit_ns, &ns, sizeof(ns)); }
 
 }  // namespace b200q

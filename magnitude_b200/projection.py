@@ -320,6 +320,16 @@ class Backend:
         self.peer_attach(dist.get_rank(), dist.get_world_size(), handles)
         dist.barrier()
 
+    def peer_buffer(self) -> int:
+        """Device address of this context's exchange buffer (single-process form of the peer exchange)."""
+        out = c_void_p()
+        self._check(B.lib().b200q_peer_buffer(self._h, byref(out)))
+        return out.value
+
+    def peer_attach_buffers(self, rank: int, world: int, buffers: Sequence[int]) -> None:
+        arr = (c_void_p * world)(*[c_void_p(b) for b in buffers])
+        self._check(B.lib().b200q_peer_attach_buffers(self._h, rank, world, arr))
+
     def peer_detach(self) -> None:
         self._check(B.lib().b200q_peer_detach(self._h))
 

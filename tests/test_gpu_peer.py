@@ -111,6 +111,19 @@ def _worker(rank, world, port, out_dir):
     ok &= check_outs()
     del g2
     dist.barrier()
+    # the NCCL path: joined with a host deadline, used for bf16 and for vectors beyond the peer limit
+    uid = [mb.tp_unique_id() if rank == 0 else None]
+    dist.broadcast_object_list(uid, src=0)
+    be.tp_init(rank, world, uid[0])
+    for count, dtype in ((40000, torch.float32), (8192, torch.bfloat16)):
+        parts = [torch.randn(count, generator=torch.Generator().manual_seed(900 + r)).to(dtype) for r in range(world)]
+        want = torch.stack([p.float() for p in parts]).sum(0)
+        yv = parts[rank].cuda()
+        be.allreduce(yv, stream=stream)
+        be.sync(stream)
+        ok &= bool(torch.allclose(yv.float().cpu(), want, rtol=2e-2 if dtype == torch.bfloat16 else 1e-5, atol=1e-2 if dtype == torch.bfloat16 else 1e-5))
+    be.tp_finalize()
+    dist.barrier()
     with open(os.path.join(out_dir, f"ok{rank}"), "w") as f:
         f.write("1" if ok else "0")
     del g
