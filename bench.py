@@ -184,13 +184,15 @@ def cpu_reference_pass(orc, mats, xs, reps):
     return (time.perf_counter() - t0) / reps
 
 
-def make_host_layer(seed=0, gq=None):
+def make_host_layer(seed=0, gq=None, encoder=None):
+    """gate, up, down of one layer: N(0, 0.02) from seeds 0, 1, 2, encoded with the format's reference
+    quantizer (the CUDA arm passes the library's, the CPU arm the oracle's: the same bytes)."""
     if gq is None:
         from magnitude_b200 import ggml_quant as gq
 
-    gate = gq.synth_weights(Q4_K, INTER, HIDDEN, seed)
-    up = gq.synth_weights(Q4_K, INTER, HIDDEN, seed + 1)
-    down = gq.synth_weights(Q4_K, HIDDEN, INTER, seed + 2)
+    gate = gq.synth_weights(Q4_K, INTER, HIDDEN, seed, encoder=encoder)
+    up = gq.synth_weights(Q4_K, INTER, HIDDEN, seed + 1, encoder=encoder)
+    down = gq.synth_weights(Q4_K, HIDDEN, INTER, seed + 2, encoder=encoder)
     return gate, up, down
 
 
@@ -205,7 +207,7 @@ def run_reference(args):
     orc.build()
     gq = load_quant_module()
 
-    gate, up, down = make_host_layer(gq=gq)
+    gate, up, down = make_host_layer(gq=gq, encoder=orc.quantize)
     rng = np.random.default_rng(1)
     xh = gq.f32_to_bf16_bits(rng.standard_normal((1, HIDDEN), dtype=np.float32)).astype(np.uint32) << 16
     xi = gq.f32_to_bf16_bits(rng.standard_normal((1, INTER), dtype=np.float32)).astype(np.uint32) << 16
@@ -295,7 +297,7 @@ def run_b200(args):
     use_peer = world > 1 and not args.nccl
     if use_peer:
         be.peer_setup(dist)
-    gate_h, up_h, down_h = make_host_layer()
+    gate_h, up_h, down_h = make_host_layer(encoder=mb.quantize)
     if world > 1:
         g0 = be.upload_shard(Q4_K, gate_h, INTER, HIDDEN, mb.SPLIT_COLUMN, rank, world, 256)
         u0 = be.upload_shard(Q4_K, up_h, INTER, HIDDEN, mb.SPLIT_COLUMN, rank, world, 256)
@@ -658,7 +660,7 @@ def run_prefill(args, emit=True):
         return
     from magnitude_b200 import ggml_quant as gq
 
-    w_h = gq.synth_weights(Q4_K, N, K, 0)
+    w_h = None       # encoded below by whichever arm runs
     rng = np.random.default_rng(3)
     x32 = rng.standard_normal((M, K), dtype=np.float32)
     x32[:, rng.choice(K, K // 100, replace=False)] *= np.float32(20.0)
@@ -672,6 +674,7 @@ def run_prefill(args, emit=True):
         from oracle import oracle as orc
 
         orc.build()
+        w_h = load_quant_module().synth_weights(Q4_K, N, K, 0, encoder=orc.quantize)
         rows = 8                                         # bounded sample: 8 of the 2048 token rows
         xs = np.ascontiguousarray((gq.f32_to_bf16_bits(x32[:rows]).astype(np.uint32) << 16).view(np.float32))
         for _ in range(max(args.warmup, 1)):
@@ -700,6 +703,7 @@ def run_prefill(args, emit=True):
     import magnitude_b200 as mb
 
     be = mb.Backend(local_rank)
+    w_h = gq.synth_weights(Q4_K, N, K, 0, encoder=mb.quantize)
     w0 = be.upload(Q4_K, w_h, N, K)
     ws = [w0] + [w0.clone() for _ in range(copies - 1)]
     x_host = torch.from_numpy(x32).to(torch.bfloat16)
@@ -818,7 +822,7 @@ def run_skinny(args, emit=True):
     cases, tot_bytes, tot_s = [], 0.0, 0.0
     with ClockSampler(local_rank) as clocks:
         for qt, name, n, k, blk in ((Q4_K, "Q4_K qkv", 6144, 4096, 144), (14, "Q6_K down", 4096, 14336, 210)):
-            w0 = be.upload(qt, gq.synth_weights(qt, n, k, 0), n, k)
+            w0 = be.upload(qt, gq.synth_weights(qt, n, k, 0, encoder=mb.quantize), n, k)
             ws = [w0] + [w0.clone() for _ in range(copies - 1)]
             wbytes = n * (k // 256) * blk
             for m in (2, 4, 8, 16):
@@ -923,7 +927,7 @@ def run_calibration(args, emit=True):
         be.project(tiny, xt, out=yt, stream=stream)
     launch_us = float(np.median(timed(lambda: be.project(tiny, xt, out=yt, stream=stream), 20))) * 1e3
     for qt, name, blk_e, blk_b in ((Q4_K, "Q4_K", 256, 144), (14, "Q6_K", 256, 210), (8, "Q8_0", 32, 34)):
-        w0 = be.upload(qt, gq.synth_weights(qt, n, k, 0), n, k)
+        w0 = be.upload(qt, gq.synth_weights(qt, n, k, 0, encoder=mb.quantize), n, k)
         ws = [w0] + [w0.clone() for _ in range(copies - 1)]
         plan = be.plan([([w], x, [y]) for w in ws])
         for _ in range(3):

@@ -176,6 +176,14 @@ void b200q_weight_destroy(b200q_weight *w);
  * inference/parity/upstream/targets.toml:38.) */
 b200q_status b200q_dequantize(b200q_ctx *ctx, const b200q_weight *w, float *out_dev, void *stream);
 
+/* The format's reference quantizer: N rows of K fp32 weights -> packed blocks in GGUF order
+ * (out_bytes must equal b200q_tensor_storage_bytes(type, N * K)).  Host code, `threads` <= 0 = all
+ * cores.  This is the encoder a model converter runs upstream of LlamaModel::load_from_file
+ * (icn-engine/src/lib.rs:972); here it makes synthetic tensors for tests and benchmarks
+ * ("quantized with the reference quantizer") without a model file. */
+b200q_status b200q_quantize(int32_t type, const float *weights, int64_t N, int64_t K, void *packed_out, size_t out_bytes,
+                            int32_t threads);
+
 /* -- GGUF files ----------------------------------------------------------------------------- */
 
 /* A parsed GGUF header: metadata keys and the tensor table.  Mirrors the bounded walk of the

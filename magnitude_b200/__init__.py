@@ -24,6 +24,7 @@ from .projection import (  # noqa: F401
     GgufFile,
     Plan,
     ProjectionWeight,
+    quantize,
     shard_range,
     tensor_storage_bytes,
     tensor_storage_bytes_shape,

@@ -133,6 +133,7 @@ class GgufTensor(ctypes.Structure):
 
 SIGNATURES.update({
     "b200q_tensor_storage_bytes_shape": (c_int64, [c_int32, c_int32, POINTER(c_int64)]),
+    "b200q_quantize": (c_int32, [c_int32, c_void_p, c_int64, c_int64, c_void_p, c_size_t, c_int32]),
     "b200q_gguf_open": (c_int32, [c_char_p, POINTER(c_void_p), c_char_p, c_size_t]),
     "b200q_gguf_close": (None, [c_void_p]),
     "b200q_gguf_last_error": (c_int32, [c_void_p, c_char_p, c_size_t]),

@@ -128,12 +128,16 @@ def f32_to_bf16_bits(a: np.ndarray) -> np.ndarray:
     return r.astype(np.uint16)
 
 
-def synth_weights(qtype: int, n: int, k: int, seed: int, std: float = 0.02) -> np.ndarray:
-    """Packed blocks of W ~ N(0, std) drawn with numpy.random.default_rng(seed)."""
+def synth_weights(qtype: int, n: int, k: int, seed: int, std: float = 0.02, encoder=None) -> np.ndarray:
+    """Packed blocks of W ~ N(0, std) drawn with numpy.random.default_rng(seed).
+
+    `encoder(qtype, w)` turns fp32 rows into packed rows; the default is this module's plain min/max
+    encoder, the benchmark passes the format's reference quantizer (magnitude_b200.quantize)."""
     rng = np.random.default_rng(seed)
+    enc = encoder or quantize
     out = []
     step = max(1, (1 << 24) // max(k, 1))             # bound the fp32 scratch to ~64 MB
     for r0 in range(0, n, step):
         w = rng.standard_normal((min(step, n - r0), k), dtype=np.float32) * np.float32(std)
-        out.append(quantize(qtype, w))
+        out.append(enc(qtype, w))
     return np.concatenate(out, axis=0) if out else np.zeros((0, k // BLOCK[qtype][0] * BLOCK[qtype][1]), np.uint8)

@@ -422,6 +422,22 @@ class GgufFile:
             pass
 
 
+def quantize(qtype: int, w: np.ndarray, threads: int = 0) -> np.ndarray:
+    """fp32 [N, K] -> packed uint8 [N, row bytes] with the format's reference quantizer (b200q_quantize)."""
+    w = np.ascontiguousarray(w, dtype=np.float32)
+    if w.ndim != 2:
+        raise B.B200QError(B.ERR_INVALID_CONFIG, "quantize takes a matrix [N, K]")
+    n, k = w.shape
+    nbytes = tensor_storage_bytes(qtype, n * k)
+    if nbytes < 0:
+        raise B.B200QError(B.ERR_INVALID_CONFIG, f"type {qtype} with K = {k}: unknown type or K is not a block multiple")
+    out = np.empty((n, nbytes // max(n, 1)) if n else (0, 0), dtype=np.uint8)
+    st = B.lib().b200q_quantize(qtype, c_void_p(w.ctypes.data), n, k, c_void_p(out.ctypes.data), out.size, threads)
+    if st:
+        raise B.B200QError(st, "quantize")
+    return out
+
+
 def tensor_storage_bytes_shape(qtype: int, dims) -> int:
     """GGUF byte count from (type, shape), dims[0] the row length — the call at icn-models/src/gguf.rs:129."""
     arr = (c_int64 * len(dims))(*dims)

@@ -73,7 +73,7 @@ def test_config4_prefill_with_outlier_channels(backend, orc):
     # M = 2048, K = 4096, N = 14336, 1 % of the channels scaled x20; bf16 output.
     # The full product is checked on a sample of 192 weight rows (the oracle is a CPU loop).
     m, n, k = 2048, 14336, 4096
-    packed = gq.synth_weights(mb.TYPE_Q4_K, n, k, seed=0)
+    packed = gq.synth_weights(mb.TYPE_Q4_K, n, k, seed=0, encoder=orc.quantize)      # the restated reference quantizer
     x = np.random.default_rng(1).standard_normal((m, k), dtype=np.float32)
     ch = np.random.default_rng(2).choice(k, size=41, replace=False)
     x[:, ch] *= 20.0

@@ -118,7 +118,7 @@ def test_config1_q8_0_reference_cpu_case(backend, orc):
 
 @pytest.mark.parametrize("n,k", [(14336, 4096), (4096, 14336)])
 def test_config2_q4_k_decode_full_size(backend, orc, n, k):
-    packed = gq.synth_weights(mb.TYPE_Q4_K, n, k, seed=0)
+    packed = gq.synth_weights(mb.TYPE_Q4_K, n, k, seed=0, encoder=orc.quantize)      # the restated reference quantizer
     w = backend.upload(mb.TYPE_Q4_K, packed, n, k)
     x = _acts(1, k, seed=1, dtype=torch.bfloat16)
     y = backend.project(w, x)
@@ -134,7 +134,7 @@ def test_config2_q4_k_decode_full_size(backend, orc, n, k):
 def test_linearity_full_size(backend):
     # size-independent property: W(a*x1 + x2) = a*W x1 + W x2 (up to the decode tolerance)
     n, k = 4096, 14336
-    packed = gq.synth_weights(mb.TYPE_Q6_K, n, k, seed=6)
+    packed = gq.synth_weights(mb.TYPE_Q6_K, n, k, seed=6, encoder=orc.quantize)
     w = backend.upload(mb.TYPE_Q6_K, packed, n, k)
     x1 = _acts(1, k, seed=11, dtype=torch.float32)
     x2 = _acts(1, k, seed=12, dtype=torch.float32)

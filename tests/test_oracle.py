@@ -131,3 +131,19 @@ def test_tolerance_rule(orc):
     assert orc.within_tolerance(ref * (1 + 5e-4), ref, 1e-3)[0]
     assert not orc.within_tolerance(ref * (1 + 5e-3), ref, 1e-3)[0]
     assert not orc.within_tolerance(np.array([1.0, np.nan, -2.0]), ref, 1e-3)[0]
+
+
+def test_library_quantizer_is_the_oracles_quantizer_byte_for_byte(orc):
+    # the product ships the same reference quantizer (b200q_quantize, used to make benchmark tensors):
+    # identical bytes on random, constant, tiny, huge and all-zero rows
+    import magnitude_b200 as mb
+
+    rng = np.random.default_rng(11)
+    for qt in (orc.Q8_0, orc.Q4_K, orc.Q6_K):
+        for n, k, scale in ((33, 1024, 0.02), (5, 256, 1.0), (4, 512, 1e-9), (6, 768, 300.0)):
+            w = (rng.standard_normal((n, k)) * scale).astype(np.float32)
+            w[0] = 0.0
+            w[-1] = w[-1, 0]
+            assert np.array_equal(mb.quantize(qt, w), orc.quantize(qt, w)), (qt, n, k, scale)
+    with pytest.raises(mb.B200QError):
+        mb.quantize(orc.Q4_K, np.zeros((2, 100), np.float32))
