@@ -882,6 +882,232 @@ def run_skinny(args, emit=True):
 
 
 # ------------------------------------------------------------------------------------------------
+# configs[4]: one decoder layer of a 32B-class dense model under tensor parallelism, M = 1 and M = 4096
+# ------------------------------------------------------------------------------------------------
+
+L32_H, L32_I = 5120, 25600
+L32 = [("q", Q4_K, 8192, L32_H), ("k", Q4_K, 1024, L32_H), ("v", 14, 1024, L32_H), ("o", Q4_K, L32_H, 8192),
+       ("gate", Q4_K, L32_I, L32_H), ("up", Q4_K, L32_I, L32_H), ("down", 14, L32_H, L32_I)]
+BLK_BYTES = {Q4_K: 144, 14: 210}
+
+
+def run_layer32b(args, emit=True):
+    """All seven projections of one layer (Q4_K_M mix), split tensor-parallel: q / k / v by heads and
+    gate / up by rows in the 256-row units that match down's cut (no exchange); o and down along K at
+    superblocks, their partial results added over the ranks.  Decode (M = 1): one plan per rank, the sums
+    made inside the launch (peer memory).  Prefill (M = 4096): tcgen05 GEMMs, the row-parallel partials
+    (bf16) summed by one NCCL all-reduce per projection, issued per M-chunk on a second stream so that it
+    overlaps the next chunk's GEMM.  `--layers L` distinct copies of the layer per step (default 4: 1.24 GB)."""
+    import torch
+
+    rank, local_rank, world = dist_env()
+    if args.impl == "reference":
+        if rank == 0:
+            print(json.dumps({"impl": "reference", "metric": "layer32b", "unavailable": "the layer workload has no CPU arm (see the decode line)"}))
+        return None
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+
+        dist = dist_mod
+        dist.init_process_group("nccl", device_id=dev)
+    import magnitude_b200 as mb
+    from magnitude_b200 import ggml_quant as gq
+
+    be = mb.Backend(local_rank)
+    if world > 1:
+        be.peer_setup(dist)
+        uid = [mb.tp_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(uid, src=0)
+        be.tp_init(rank, world, uid[0])
+    layers = max(1, min(args.layers if args.layers != 32 else 4, 8))
+    host = {name: gq.synth_weights(qt, n, k, seed, encoder=mb.quantize) for seed, (name, qt, n, k) in enumerate(L32)}
+    split = {"q": (mb.SPLIT_COLUMN, 128), "k": (mb.SPLIT_COLUMN, 128), "v": (mb.SPLIT_COLUMN, 128), "o": (mb.SPLIT_ROW, 0),
+             "gate": (mb.SPLIT_COLUMN, 256), "up": (mb.SPLIT_COLUMN, 256), "down": (mb.SPLIT_ROW, 0)}
+    shards = []
+    for _ in range(layers):
+        if not shards:
+            shards.append({name: be.upload_shard(qt, host[name], n, k, split[name][0], rank, world, split[name][1]) for name, qt, n, k in L32})
+        else:
+            shards.append({name: w.clone() for name, w in shards[0].items()})
+    w0 = shards[0]
+    weight_bytes = sum(n * (k // 256) * BLK_BYTES[qt] for _, qt, n, k in L32)
+    stream = torch.cuda.Stream(device=dev)
+    rng = np.random.default_rng(1)
+    result = {}
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps, warm=3):
+        for _ in range(warm):
+            fn()
+        barrier()
+        evs = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+        with torch.cuda.stream(stream):
+            evs[0].record(stream)
+        for i in range(steps):
+            fn()
+            with torch.cuda.stream(stream):
+                evs[i + 1].record(stream)
+        barrier()
+        be.sync(stream)
+        total = evs[0].elapsed_time(evs[-1])
+        if world > 1:
+            t = torch.tensor([total], dtype=torch.float64, device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            total = float(t.item())
+        return total / steps, [evs[i].elapsed_time(evs[i + 1]) for i in range(steps)]
+
+    def worst(got, ref, rel):
+        rms = float(np.sqrt(np.mean(ref * ref)))
+        return float(np.max(np.abs(got - ref) / (rel * np.maximum(np.abs(ref), rms))))
+
+    with ClockSampler(local_rank) as clocks:
+        # ---------------- decode, M = 1 ----------------
+        xh = torch.from_numpy(rng.standard_normal((1, L32_H), dtype=np.float32)).to(torch.bfloat16)
+        xo = torch.from_numpy(rng.standard_normal((1, 8192), dtype=np.float32)).to(torch.bfloat16)
+        xd = torch.from_numpy(rng.standard_normal((1, L32_I), dtype=np.float32)).to(torch.bfloat16)
+        lo_o, hi_o = mb.shard_range(Q4_K, L32_H, 8192, mb.SPLIT_ROW, rank, world) if world > 1 else (0, 8192)
+        lo_d, hi_d = mb.shard_range(14, L32_H, L32_I, mb.SPLIT_ROW, rank, world) if world > 1 else (0, L32_I)
+        xh_d, xo_d, xd_d = xh.to(dev), xo[:, lo_o:hi_o].contiguous().to(dev), xd[:, lo_d:hi_d].contiguous().to(dev)
+        yq = torch.empty((1, w0["q"].n), device=dev)
+        yk = torch.empty((1, w0["k"].n), device=dev)
+        yv = torch.empty((1, w0["v"].n), device=dev)
+        yo = torch.empty((1, L32_H), device=dev)
+        yg = torch.empty((1, w0["gate"].n), device=dev)
+        yu = torch.empty((1, w0["up"].n), device=dev)
+        yd = torch.empty((1, L32_H), device=dev)
+        jobs, sums = [], []
+        for s in shards:
+            jobs += [([s["q"], s["k"]], xh_d, [yq, yk]), ([s["v"]], xh_d, [yv]), ([s["o"]], xo_d, [yo]),
+                     ([s["gate"], s["up"]], xh_d, [yg, yu]), ([s["down"]], xd_d, [yd])]
+            sums += [False, False, world > 1, False, world > 1]
+        plan = be.plan(jobs, sum_ranks=sums)
+        graph = None
+        with torch.cuda.stream(stream):
+            plan.run(stream=stream)
+        stream.synchronize()
+        try:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream):
+                plan.run(stream=stream)
+            graph = g
+        except Exception:
+            torch.cuda.synchronize()
+
+        def step_decode():
+            if graph is not None:
+                with torch.cuda.stream(stream):
+                    graph.replay()
+            else:
+                plan.run(stream=stream)
+
+        ms, samples = timed(step_decode, args.steps)
+        step_decode()
+        torch.cuda.synchronize()
+        ref_o = (gq.dequantize(Q4_K, host["o"], 8192).astype(np.float64) @ xo.float().numpy().astype(np.float64).T).T
+        ref_d = (gq.dequantize(14, host["down"], L32_I).astype(np.float64) @ xd.float().numpy().astype(np.float64).T).T
+        chk = max(worst(yo.cpu().numpy().astype(np.float64), ref_o, 1e-3), worst(yd.cpu().numpy().astype(np.float64), ref_d, 1e-3))
+        bytes_step = layers * (weight_bytes + 2 * (3 * L32_H + 8192 + L32_I) + 4 * (8192 + 2 * 1024 + 2 * L32_H + 2 * L32_I))
+        peak, src = peaks()
+        result["decode"] = {"ms_per_step": ms, "value": bytes_step / (ms * 1e-3) / 1e9, "unit": UNIT,
+                            "roofline": {"bound": "hbm", "achieved": bytes_step / world / (ms * 1e-3) / 1e9, "peak": peak,
+                                         "frac": bytes_step / world / (ms * 1e-3) / 1e9 / peak, "peak_source": f"of {src}",
+                                         "note": "per-rank algorithmic bytes / device time, rank sums of o and down inside the launch"},
+                            "stats": sample_stats(samples), "check": {"max_err_over_tol": chk, "ok": bool(chk <= 1.0)},
+                            "jobs_per_launch": len(jobs), "cuda_graph": graph is not None}
+        graph = None
+        plan.close()
+
+        # ---------------- prefill, M = 4096 ----------------
+        M, chunks = 4096, 4
+        mc = M // chunks
+        X = torch.from_numpy(rng.standard_normal((M, L32_H), dtype=np.float32)).to(torch.bfloat16).to(dev)
+        Xo = torch.from_numpy(rng.standard_normal((M, 8192), dtype=np.float32)).to(torch.bfloat16)
+        Xd = torch.from_numpy(rng.standard_normal((M, 512), dtype=np.float32)).to(torch.bfloat16).repeat(1, L32_I // 512)
+        Xo_d, Xd_d = Xo[:, lo_o:hi_o].contiguous().to(dev), Xd[:, lo_d:hi_d].contiguous().to(dev)
+        Yq = torch.empty((M, w0["q"].n), dtype=torch.bfloat16, device=dev)
+        Yk = torch.empty((M, w0["k"].n), dtype=torch.bfloat16, device=dev)
+        Yv = torch.empty((M, w0["v"].n), dtype=torch.bfloat16, device=dev)
+        Yg = torch.empty((M, w0["gate"].n), dtype=torch.bfloat16, device=dev)
+        Yu = torch.empty((M, w0["up"].n), dtype=torch.bfloat16, device=dev)
+        Yo = torch.empty((M, L32_H), dtype=torch.bfloat16, device=dev)
+        Yd = torch.empty((M, L32_H), dtype=torch.bfloat16, device=dev)
+        comm = torch.cuda.Stream(device=dev)
+
+        def row_parallel(w, x, y):
+            # partial products chunk by chunk; each chunk's sum over the ranks runs on the second stream
+            # while the next chunk multiplies
+            for c in range(chunks):
+                be.project(w, x[c * mc:(c + 1) * mc], out=y[c * mc:(c + 1) * mc], stream=stream)
+                if world > 1:
+                    ev = torch.cuda.Event()
+                    ev.record(stream)
+                    comm.wait_event(ev)
+                    be.allreduce(y[c * mc:(c + 1) * mc], stream=comm)
+            if world > 1:
+                ev = torch.cuda.Event()
+                ev.record(comm)
+                stream.wait_event(ev)
+
+        def step_prefill():
+            for s in shards:
+                be.project(s["q"], X, out=Yq, stream=stream)
+                be.project(s["k"], X, out=Yk, stream=stream)
+                be.project(s["v"], X, out=Yv, stream=stream)
+                row_parallel(s["o"], Xo_d, Yo)
+                be.project(s["gate"], X, out=Yg, stream=stream)
+                be.project(s["up"], X, out=Yu, stream=stream)
+                row_parallel(s["down"], Xd_d, Yd)
+
+        ms, samples = timed(step_prefill, max(3, min(args.steps, 5)), warm=2)
+        torch.cuda.synchronize()
+        rows = np.sort(np.random.default_rng(4).choice(L32_H, size=16, replace=False))
+        wd = gq.dequantize(14, host["down"][rows], L32_I).astype(np.float64)
+        ref = (Xd.float().numpy().astype(np.float64)[:256] @ wd.T)
+        chk = worst(Yd[:256][:, torch.from_numpy(rows).to(dev)].float().cpu().numpy().astype(np.float64), ref, 5e-3 * (1 + 0.5 * (world > 1)))
+        flops = layers * 2.0 * M * sum(n * k for _, _, n, k in L32)
+        tpeak, tsrc = FALLBACK_TFLOPS, "fallback"
+        pk = ROOT / "MEASURED_PEAKS.json"
+        if pk.exists():
+            try:
+                tpeak, tsrc = float(json.loads(pk.read_text())["bf16_tflops"]), "measured (burst)"
+            except Exception:
+                pass
+        result["prefill"] = {"ms_per_step": ms, "value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+                             "roofline": {"bound": "tensor", "achieved": flops / world / (ms * 1e-3) / 1e12, "peak": tpeak,
+                                          "frac": flops / world / (ms * 1e-3) / 1e12 / tpeak, "peak_source": f"of {tsrc}",
+                                          "note": "per-rank 2 M N K / device time; includes activation conversions and, for N > 1, "
+                                                  f"{2 * chunks} NCCL all-reduces per layer ({M * L32_H * 2} bytes per projection) on a second stream"},
+                             "stats": sample_stats(samples),
+                             "check": {"max_err_over_tol": chk, "ok": bool(chk <= 1.0), "what": "16 sampled rows of down, 256 tokens, summed over ranks (bf16 partials)"},
+                             "allreduce_bytes_per_projection": M * L32_H * 2 if world > 1 else 0, "m_chunks": chunks}
+    used = clocks.summary()
+    if world > 1:
+        be.tp_finalize()
+        dist.barrier()
+    line = {"metric": "layer32b_projection_throughput", "value": result["decode"]["value"], "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": 3, "ms_per_step": result["decode"]["ms_per_step"], "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "decode: u8 x s16 dp4a; prefill: fp16 tcgen05.mma; fp32 accumulate", "data": "synthetic",
+            "config": {"workload": "configs[4]: all projections of one decoder layer of a 32B-class dense model (Q4_K_M mix), M = 1 and M = 4096",
+                       "layers_per_step": layers, "weight_bytes_per_layer": weight_bytes, "parallelism": f"tp{world}" if world > 1 else "single",
+                       "l2": f"{layers} distinct copies of the layer per step ({layers * weight_bytes / world / 1e6:.0f} MB per rank)"},
+            "decode": result["decode"], "prefill": result["prefill"], "clocks": used, "cpu_baseline": None, "e2e": None}
+    if rank == 0 and emit:
+        print(json.dumps(line))
+        sys.stdout.flush()
+    if dist is not None:
+        sys.stdout.flush()
+        os._exit(0)
+    return line
+
+
+# ------------------------------------------------------------------------------------------------
 # calibration rows: sustained mat-vec bytes per second and launch cost per block type
 # ------------------------------------------------------------------------------------------------
 
@@ -971,7 +1197,7 @@ def main():
                     help="skinny workload: smallest M sent to the skinny kernel (default: the library's, 5)")
     ap.add_argument("--quick", action="store_true", help="headline figure only: no dependent / sustained / secondary measurements")
     ap.add_argument("--no-check", action="store_true", help="skip the host check of the step's results")
-    ap.add_argument("--workload", choices=["decode", "prefill", "skinny", "calibration"], default="decode",
+    ap.add_argument("--workload", choices=["decode", "prefill", "skinny", "calibration", "layer32b"], default="decode",
                     help="decode = the headline Q4_K GEMV step; prefill = the M=2048 Q4_K GEMM (secondary line, TFLOP/s)")
     args = ap.parse_args()
     # last resort against a stuck collective or teardown: never hold a GPU box for more than 20 minutes
@@ -986,6 +1212,8 @@ def main():
         run_skinny(args)
     elif args.workload == "calibration":
         run_calibration(args)
+    elif args.workload == "layer32b":
+        run_layer32b(args)
     elif args.impl == "reference":
         run_reference(args)
     else:

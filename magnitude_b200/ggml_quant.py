@@ -121,6 +121,32 @@ def dequantize_q4_k(packed: np.ndarray, k: int) -> np.ndarray:
     return ((dl[..., None] * q).astype(np.float32) - ml[..., None]).astype(np.float32).reshape(n, k)
 
 
+def dequantize_q6_k(packed: np.ndarray, k: int) -> np.ndarray:
+    """fp32 [N, K] of Q6_K blocks: w = (d * sc) * (q - 32), the product d * sc rounded to fp32 first."""
+    rows = np.ascontiguousarray(packed, dtype=np.uint8).reshape(-1, k // 256, 210)
+    n, nb = rows.shape[:2]
+    ql = rows[..., 0:128].reshape(n, nb, 2, 2, 32)            # half, (l | l + 32), l
+    qh = rows[..., 128:192].reshape(n, nb, 2, 32)
+    sc = rows[..., 192:208].copy().view(np.int8).astype(np.float32)
+    d = rows[..., 208:210].copy().view(np.float16).astype(np.float32)[..., 0]
+    q = np.empty((n, nb, 2, 4, 32), np.int16)
+    q[:, :, :, 0] = (ql[:, :, :, 0] & 0xF) | ((qh & 3) << 4)
+    q[:, :, :, 1] = (ql[:, :, :, 1] & 0xF) | (((qh >> 2) & 3) << 4)
+    q[:, :, :, 2] = (ql[:, :, :, 0] >> 4) | (((qh >> 4) & 3) << 4)
+    q[:, :, :, 3] = (ql[:, :, :, 1] >> 4) | (((qh >> 6) & 3) << 4)
+    dl = (d[..., None] * sc).astype(np.float32)                # [n, nb, 16]
+    w = (q.reshape(n, nb, 16, 16).astype(np.float32) - np.float32(32.0)) * dl[..., None]
+    return w.astype(np.float32).reshape(n, k)
+
+
+def dequantize(qtype: int, packed: np.ndarray, k: int) -> np.ndarray:
+    if qtype == Q4_K:
+        return dequantize_q4_k(packed, k)
+    if qtype == Q6_K:
+        return dequantize_q6_k(packed, k)
+    raise ValueError(f"no numpy decoder for ggml type id {qtype}")
+
+
 def f32_to_bf16_bits(a: np.ndarray) -> np.ndarray:
     """Round-to-nearest-even bf16 bit patterns (uint16) of an fp32 array."""
     u = np.ascontiguousarray(a, dtype=np.float32).view(np.uint32)
