@@ -163,6 +163,21 @@ __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 
+// both barriers' phases complete?  One instruction sequence, so the two probes' latencies overlap.
+__device__ __forceinline__ bool mbar_test_wait_both(uint32_t bar0, uint32_t parity0, uint32_t bar1, uint32_t parity1) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 q, [%3], %4;\n\t"
+        "and.pred p, p, q;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar0), "r"(parity0), "r"(bar1), "r"(parity1)
+        : "memory");
+    return ok != 0;
+}
+
 // Wait limit for every device-side spin: after this long the waiter gives up, raises the status
 // word and the kernel drains and returns instead of hanging the GPU.  A variable (one copy per
 // source file and device; the context option B200Q_OPT_WAIT_LIMIT_MS sets them all) so that a host

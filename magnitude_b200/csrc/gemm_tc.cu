@@ -32,6 +32,16 @@
 
 namespace b200q {
 
+#ifdef B200Q_GEMM_TRACE
+// timing experiments only: the first CTA pair records its pipeline events (SM clock) into this array
+__device__ long long g_gemm_trace[16384];
+#define GEMM_TRACE(slot) do { if (blockIdx.x == 0 && (slot) < 16384) g_gemm_trace[(slot)] = clock64(); } while (0)
+#define GEMM_TRACE_DECL(...) __VA_ARGS__
+#else
+#define GEMM_TRACE(slot) do { } while (0)
+#define GEMM_TRACE_DECL(...)
+#endif
+
 namespace {
 
 constexpr int BM = 128;          // weight rows per tile (MMA M)
@@ -647,17 +657,47 @@ __global__ void gemm_ksplit_sum_kernel(const float *__restrict__ part, int kspli
 // Tensor memory is allocated by each CTA for itself; a cluster barrier before the exit keeps either
 // CTA's shared and tensor memory alive until the other has finished using it.
 
+// Second form of the same kernel (TS = true): the dequantized weights never touch shared memory.
+// A dequant thread holds one weight row's 64 values of a K-step in 32 registers, which is exactly
+// one tcgen05.st.32x32b.x32 into the row's lane of tensor memory; the MMA then takes its A operand
+// from tensor memory.  Per K-step that removes 16 KB of shared-memory stores and 16 KB of operand
+// reads per SM, the two largest items on the shared-memory port after the activation operand, and
+// the proxy fence that went with the stores.  Tensor memory (512 columns) then holds four A stages
+// (32 columns each) and two accumulators of 192 columns, so token tiles are at most 192 wide and
+// each CTA stages 96-token halves of the activation tile.
 constexpr int kPairThreads = kThreads;
-__host__ __device__ constexpr int pair_b_stage_bytes() { return 128 * BK * 2; }       // half of a <= 256-token tile: 16 KB
-__host__ __device__ constexpr int pair_b_stages(int qt) { return qt == QT_Q8_0 ? 5 : 6; }
-constexpr int kMaxPairBStages = 6;
-__host__ __device__ constexpr int pair_smem_data_bytes(int qt) {
-    return kAStages * kStageABytes + pair_b_stages(qt) * pair_b_stage_bytes() + kWBufs * wbuf_bytes(qt) + (qt == QT_Q6_K ? 2 * kDBufBytes : 0);
+constexpr int kTsAccCols = 192;                     // accumulator buffer stride in TS form
+constexpr int kTsACol0 = 2 * kTsAccCols;            // first A-stage column in TS form (4 stages x 32 columns)
+// Stages of the pair kernel.  Dequantized-weight stages are used round robin by K-step (group j of
+// the dequant warps fills K-steps j, j + 4, ...); with more than four, the hand-over after a stage is
+// released (stores, proxy fence, arrival across the pair: more than a thousand cycles) is off the
+// tensor cores' path.  Activation stages hide the latency of the TMA loads.  Q4_K's small records
+// leave room for 11 stages of 16 KB, split 6 + 5 (8 + 3 and 7 + 4 measured within 1 % of it); the
+// larger packed-record buffers of Q6_K and Q8_0 and the TS form's tensor-memory budget leave four
+// weight stages.  B200Q_PAIR_SA / B200Q_PAIR_SB override Q4_K's split at compile time.
+constexpr int kMaxPairAStages = 8;
+// timing experiments (parts of the pipeline switched off; results invalid) exist only in builds that ask for them
+#ifdef B200Q_TIMING_EXPERIMENTS
+#define PAIR_DBG(bit) (p.debug & (bit))
+#else
+#define PAIR_DBG(bit) (false)
+#endif
+#ifndef B200Q_PAIR_SA
+#define B200Q_PAIR_SA 6
+#define B200Q_PAIR_SB 5
+#endif
+__host__ __device__ constexpr int pair_a_stages(int qt, bool ts) { return (!ts && qt == QT_Q4_K) ? B200Q_PAIR_SA : 4; }
+__host__ __device__ constexpr int pair_b_rows(bool ts) { return ts ? 96 : 128; }       // tokens each CTA stages per K-step
+__host__ __device__ constexpr int pair_b_stage_bytes(bool ts = false) { return ((pair_b_rows(ts) * BK * 2 + 1023) / 1024) * 1024; }
+__host__ __device__ constexpr int pair_b_stages(int qt, bool ts = false) { return ts ? 8 : qt == QT_Q8_0 ? 5 : qt == QT_Q6_K ? 6 : B200Q_PAIR_SB; }
+constexpr int kMaxPairBStages = 8;
+__host__ __device__ constexpr int pair_smem_data_bytes(int qt, bool ts = false) {
+    return (ts ? 0 : pair_a_stages(qt, ts) * kStageABytes) + pair_b_stages(qt, ts) * pair_b_stage_bytes(ts) + kWBufs * wbuf_bytes(qt) + (qt == QT_Q6_K ? 2 * kDBufBytes : 0);
 }
 
 struct PairSmem {
-    uint64_t afull[kAStages];          // leader's copy is used: 4 local + 4 remote warp arrivals
-    uint64_t aempty[kAStages];
+    uint64_t afull[kMaxPairAStages];   // leader's copy is used: 4 local + 4 remote warp arrivals
+    uint64_t aempty[kMaxPairAStages];
     uint64_t bfull[kMaxPairBStages];   // leader's copy is used: its own expect_tx arrival + both CTAs' bytes
     uint64_t bempty[kMaxPairBStages];
     uint64_t tmem_full[2];
@@ -708,6 +748,29 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar), "h"(mask)
                  : "memory");
 }
+
+// the same MMA with the A operand in tensor memory (this CTA's 128 rows in its own lanes, the peer's in its)
+__device__ __forceinline__ void umma_f16_pair_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// 32 registers of one thread -> 32 consecutive columns of the thread's tensor-memory lane
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+          "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]),
+          "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]),
+          "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // tensor-memory management of the pair: one warp of each CTA executes these (every tcgen05
 // instruction of a kernel names the same CTA group)
@@ -771,21 +834,23 @@ __device__ __forceinline__ void pair_tile(const GemmParams &p, int tile, int &st
 }
 
 // p.n_tiles counts 256-row stripes here
-template <int QT>
+template <int QT, bool TS>
 __global__ void __launch_bounds__(kPairThreads, 1) gemm_tc_pair_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap,
                                                                       const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap wtail,
                                                                       const __grid_constant__ CUtensorMap dmap, const __grid_constant__ CUtensorMap dtail) {
-    constexpr int SB_ = pair_b_stages(QT);
+    constexpr int SB_ = pair_b_stages(QT, TS);
     constexpr int WBUF = wbuf_bytes(QT);
     constexpr int REC = rec_bytes(QT);
-    constexpr int kStageBBytes = pair_b_stage_bytes();
+    constexpr int kStageBBytes = pair_b_stage_bytes(TS);
+    constexpr int kAccCols = TS ? kTsAccCols : 256;         // tensor-memory columns between the two accumulators
+    constexpr int SA_ = pair_a_stages(QT, TS);              // weight stages: 4 (one per dequant group) or 8 (two per group)
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    const uint32_t a_s = smem_u32(smem);
-    const uint32_t b_s = a_s + kAStages * kStageABytes;
+    const uint32_t a_s = smem_u32(smem);                    // TS: no weight stages in shared memory
+    const uint32_t b_s = a_s + (TS ? 0 : SA_ * kStageABytes);
     const uint32_t w_s = b_s + SB_ * kStageBBytes;
     const uint32_t d_s = w_s + kWBufs * WBUF;
-    PairSmem *sm = reinterpret_cast<PairSmem *>(smem + pair_smem_data_bytes(QT));
+    PairSmem *sm = reinterpret_cast<PairSmem *>(smem + pair_smem_data_bytes(QT, TS));
     const uint32_t wfull_s = smem_u32(sm->wfull), wempty_s = smem_u32(sm->wempty);
     const uint32_t afull_s = smem_u32(sm->afull), aempty_s = smem_u32(sm->aempty);
     const uint32_t bfull_s = smem_u32(sm->bfull), bempty_s = smem_u32(sm->bempty);
@@ -798,7 +863,7 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_tc_pair_kernel(const Gem
     const int chunks_per_tile = (p.nsb + kChunkRecs - 1) / kChunkRecs;
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < kAStages; ++i) {
+        for (int i = 0; i < SA_; ++i) {
             mbar_init(afull_s + 8 * i, 2 * (kDequantWarps / 4));   // one unit group of each CTA
             mbar_init(aempty_s + 8 * i, 1);
         }
@@ -832,9 +897,9 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_tc_pair_kernel(const Gem
     if (warp == 0) {
         // ===== TMA producer: this CTA's half of the activation tile ================================
         if (lane == 0) {
-            // every load is a full 128-token box (rows past the tile's half are never read), so the
-            // byte count on the leader's barrier does not depend on the tile's width
-            const uint32_t bytes_pair = 2u * kStageBBytes;
+            // every load is a full box of 128 (TS: 96) tokens (rows past the tile's half are never read), so
+            // the byte count on the leader's barrier does not depend on the tile's width
+            const uint32_t bytes_pair = 2u * pair_b_rows(TS) * BK * 2;
             const uint32_t bfull_leader = mapa_rank(bfull_s, 0);
             int it = 0;
             bool ok = true;
@@ -843,10 +908,10 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_tc_pair_kernel(const Gem
                 pair_tile(p, tile, stripe, t0, width);
                 for (int ks = 0; ks < ksteps; ++ks, ++it) {
                     const int stage = it % SB_;
-                    if (p.debug & 2048) continue;
+                    if PAIR_DBG(2048) continue;
                     ok = pair_wait<true>(bempty_s + 8 * stage, ((it / SB_) & 1) ^ 1, sm, p.status);
                     if (!ok) break;
-                    if (p.debug & 1) {
+                    if PAIR_DBG(1) {
                         if (rank == 0) mbar_arrive(bfull_s + 8 * stage);
                         continue;
                     }
@@ -869,7 +934,7 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_tc_pair_kernel(const Gem
                     const int wb = rs % kWBufs;
                     ok = pair_wait<true>(wempty_s + 8 * wb, ((rs / kWBufs) & 1) ^ 1, sm, p.status);
                     if (!ok) break;
-                    if (p.debug & 4) {
+                    if PAIR_DBG(4) {
                         mbar_arrive(wfull_s + 8 * wb);
                         continue;
                     }
@@ -889,9 +954,18 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_tc_pair_kernel(const Gem
         }
     } else if (warp == 1) {
         // ===== MMA issuer (leader CTA only) ========================================================
+        // One thread, in order: whatever it executes between two K-steps leaves the tensor cores with
+        // only the few MMAs still queued, so the loop is kept to a handful of instructions.  Stage
+        // indices, parities and descriptors advance incrementally, and the barriers of the NEXT K-step
+        // are probed (without blocking) before this K-step's MMAs are issued: in the steady state the
+        // probe succeeds and the thread never executes a blocking wait.
         if (lane == 0 && rank == 0) {
-            int it = 0, tcount = 0;
-            bool rdy_a = false, rdy_b = false;
+            constexpr uint32_t kADescStep = kStageABytes >> 4, kBDescStep = kStageBBytes >> 4;
+            const uint64_t adesc0 = make_desc_sw128(a_s), bdesc0 = make_desc_sw128(b_s);
+            uint32_t sa = 0, sb = 0, pa = 0, pb = 0;      // stage and phase parity of the K-step about to be issued
+            int tcount = 0;
+            bool seen = false;                            // this K-step's operands were found ready by the previous probe
+            GEMM_TRACE_DECL(int it = 0;)
             for (int tile = pair; tile < p.pair_tiles; tile += n_pairs, ++tcount) {
                 int stripe, t0, width;
                 pair_tile(p, tile, stripe, t0, width);
@@ -899,26 +973,33 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_tc_pair_kernel(const Gem
                 const int buf = tcount & 1;
                 bool ok = pair_wait<true>(tempty_s + 8 * buf, ((tcount >> 1) & 1) ^ 1, sm, p.status);
                 if (!ok) break;
-                tc_fence_after();
-                const uint32_t d_tmem = tmem_base + buf * 256;
-                for (int ks = 0; ks < ksteps; ++ks, ++it) {
-                    const int sa = it % kAStages, sb = it % SB_;
-                    ok = rdy_b || (p.debug & 2048) || pair_wait<true>(bfull_s + 8 * sb, (it / SB_) & 1, sm, p.status);
-                    ok = ok && (rdy_a || (p.debug & 1024) || pair_wait<true>(afull_s + 8 * sa, (it / kAStages) & 1, sm, p.status));
-                    if (!ok) break;
-                    tc_fence_after();
-                    {
-                        const int nx = it + 1;
-                        rdy_b = mbar_test_wait(bfull_s + 8 * (nx % SB_), (nx / SB_) & 1);
-                        rdy_a = mbar_test_wait(afull_s + 8 * (nx % kAStages), (nx / kAStages) & 1);
+                const uint32_t d_tmem = tmem_base + buf * kAccCols;
+                for (int ks = 0; ks < ksteps; ++ks) {
+                    GEMM_TRACE(4 * it);
+                    if (!seen) {
+                        ok = PAIR_DBG(2048) || pair_wait<true>(bfull_s + 8 * sb, pb, sm, p.status);
+                        ok = ok && (PAIR_DBG(1024) || pair_wait<true>(afull_s + 8 * sa, pa, sm, p.status));
+                        if (!ok) break;
                     }
-                    const uint64_t adesc = make_desc_sw128(a_s + sa * kStageABytes);
-                    const uint64_t bdesc = make_desc_sw128(b_s + sb * kStageBBytes);
+                    GEMM_TRACE(4 * it + 1);
+                    tc_fence_after();
+                    const uint32_t nsa = sa + 1 == SA_ ? 0 : sa + 1, nsb = sb + 1 == SB_ ? 0 : sb + 1;
+                    const uint32_t npa = pa ^ (nsa == 0), npb = pb ^ (nsb == 0);
+                    seen = mbar_test_wait_both(bfull_s + 8 * nsb, npb, afull_s + 8 * nsa, npa);
+                    GEMM_TRACE(4 * it + 2);
+                    const uint64_t adesc = adesc0 + sa * kADescStep, bdesc = bdesc0 + sb * kBDescStep;
 #pragma unroll
-                    for (int kk = 0; kk < BK / 16; ++kk)
-                        if (!(p.debug & 8)) umma_f16_pair(d_tmem, adesc + 2 * kk, bdesc + 2 * kk, idesc, (ks | kk) != 0);
-                    if (!(p.debug & 1024)) umma_commit_pair(aempty_s + 8 * sa);
-                    if (!(p.debug & 2048)) umma_commit_pair(bempty_s + 8 * sb);
+                    for (int kk = 0; kk < BK / 16; ++kk) {     // 16 fp16 = 32 bytes = +2 in the address field
+                        if (PAIR_DBG(8)) continue;
+                        // TS: 16 fp16 of a row = 8 columns of its tensor-memory lane
+                        if (TS) umma_f16_pair_ts(d_tmem, tmem_base + kTsACol0 + sa * 32 + 8 * kk, bdesc + 2 * kk, idesc, (ks | kk) != 0);
+                        else umma_f16_pair(d_tmem, adesc + 2 * kk, bdesc + 2 * kk, idesc, (ks | kk) != 0);
+                    }
+                    if (!PAIR_DBG(1024)) umma_commit_pair(aempty_s + 8 * sa);
+                    if (!PAIR_DBG(2048)) umma_commit_pair(bempty_s + 8 * sb);
+                    GEMM_TRACE(4 * it + 3);
+                    GEMM_TRACE_DECL(++it;)
+                    sa = nsa, sb = nsb, pa = npa, pb = npb;
                 }
                 if (!ok) break;
                 umma_commit_pair(tfull_s + 8 * buf);
@@ -927,7 +1008,8 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_tc_pair_kernel(const Gem
     } else if (warp < kFirstEpiWarp) {
         // ===== dequant producers: this CTA's 128 weight rows =======================================
         const int t = threadIdx.x - kFirstDequantWarp * 32;
-        const int r = t & (BM - 1), j = t >> 7;
+        // TS: a warp may only touch the tensor-memory lanes of its quadrant (warp index mod 4), so it takes those rows
+        const int r = TS ? 32 * (warp & 3) + lane : t & (BM - 1), j = t >> 7;
         const int r7 = r & 7;
         const uint32_t row_off = (r >> 3) * 1024 + r7 * 128;
         const uint32_t afull_leader = mapa_rank(afull_s, 0);
@@ -947,21 +1029,44 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_tc_pair_kernel(const Gem
         };
         Unit<QT> cur, nxt;
         if (total > 0) fetch(0, cur);
+        const bool tracer = warp == kFirstDequantWarp && lane == 0;
         for (int rs = 0; rs < total && ok; ++rs) {
+            if (tracer) GEMM_TRACE(8192 + 8 * rs);
             if (rs + 1 < total) {
                 fetch(rs + 1, nxt);
                 if (!ok) break;
             }
+            if (tracer) GEMM_TRACE(8192 + 8 * rs + 1);
             uint32_t o[32];
-            if (!(p.debug & 2)) cur.convert(j, o);
-            const int stage = j;
-            if (lane == 0 && !(p.debug & 1024)) ok = pair_wait<true>(aempty_s + 8 * stage, (rs & 1) ^ 1, sm, p.status);
+            if (!PAIR_DBG(2)) cur.convert(j, o);
+            // K-step 4 rs + j, and the stages are used round robin by K-step
+            const int stage = (4 * rs + j) % SA_;
+            const uint32_t use = (uint32_t)((4 * rs + j) / SA_);       // how often this stage has been filled before
+            if (tracer) GEMM_TRACE(8192 + 8 * rs + 2);
+            if (lane == 0 && !PAIR_DBG(1024)) ok = pair_wait<true>(aempty_s + 8 * stage, (use & 1) ^ 1, sm, p.status);
             ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
             if (!ok) break;
-            if (!(p.debug & 2)) store_row(o, a_s + stage * kStageABytes + row_off, r7);
-            fence_proxy_async();
+            if (tracer) GEMM_TRACE(8192 + 8 * rs + 3);
+            if (TS) {
+                tc_fence_after();      // the stage's previous reader (the tensor core) is done: ordered before these stores
+                // the row's 64 values -> 32 columns of its lane; the MMA reads them once the stores have landed
+                if (!PAIR_DBG(2)) tmem_st32(tmem_base + kTsACol0 + stage * 32 + ((uint32_t)(32 * (warp & 3)) << 16), o);
+                if (tracer) GEMM_TRACE(8192 + 8 * rs + 4);
+                tmem_st_wait();
+                tc_fence_before();
+            } else {
+                if (!PAIR_DBG(2)) store_row(o, a_s + stage * kStageABytes + row_off, r7);
+                if (tracer) GEMM_TRACE(8192 + 8 * rs + 4);
+                fence_proxy_async();
+            }
+            if (tracer) GEMM_TRACE(8192 + 8 * rs + 5);
             __syncwarp();
-            if (lane == 0 && !(p.debug & 1024)) mbar_arrive_cluster(afull_leader + 8 * stage);
+            if (lane == 0 && !PAIR_DBG(1024)) {
+                // the leader's own warps arrive locally; only the peer's arrival has to cross the pair
+                if (rank == 0) mbar_arrive(afull_s + 8 * stage);
+                else mbar_arrive_cluster(afull_leader + 8 * stage);
+            }
+            if (tracer) GEMM_TRACE(8192 + 8 * rs + 6);
             cur = nxt;
         }
     } else {
@@ -982,9 +1087,9 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_tc_pair_kernel(const Gem
             // lane = one output column n; its 32 accumulator columns per load are 32 consecutive tokens,
             // i.e. 32 stores one output row (ldy elements) apart: the pointer just steps by ldy
             const bool full_tile = m0 + width <= p.M;
-            for (int c0 = 0; c0 < ((p.debug & 16) ? 0 : width); c0 += 32) {
+            for (int c0 = 0; c0 < (PAIR_DBG(16) ? 0 : width); c0 += 32) {
                 uint32_t v[32];
-                tmem_ld32(tmem_base + buf * 256 + ((uint32_t)(q * 32) << 16) + c0, v);
+                tmem_ld32(tmem_base + buf * kAccCols + ((uint32_t)(q * 32) << 16) + c0, v);
                 tmem_ld_wait();
                 if (n < p.N) {
                     if (p.y_is_bf16) {
@@ -1109,10 +1214,10 @@ cudaError_t launch_gemm(const GemmParams &p, const GemmMaps &m, int grid, cudaSt
     return cudaGetLastError();
 }
 
-template <int QT>
+template <int QT, bool TS>
 cudaError_t launch_gemm_pair(const GemmParams &p, const GemmMaps &m, int grid, cudaStream_t st) {
-    auto kern = gemm_tc_pair_kernel<QT>;
-    constexpr size_t smem = pair_smem_data_bytes(QT) + sizeof(PairSmem) + 1024;
+    auto kern = gemm_tc_pair_kernel<QT, TS>;
+    constexpr size_t smem = pair_smem_data_bytes(QT, TS) + sizeof(PairSmem) + 1024;
     static_assert(smem <= 232448, "shared-memory plan exceeds the 227 KB a block may use");
     static std::atomic<int> configured_dev{-1};     // contexts on several threads may launch at once
     int dev = 0;
@@ -1141,10 +1246,10 @@ cudaError_t launch_gemm_pair(const GemmParams &p, const GemmMaps &m, int grid, c
 // the tile's width (the dequantization of the 128 x 64 weight block and its hand-over bound it,
 // not the MMA), so the fewest, widest tiles win: every stripe is cut into ceil(units / 8) tiles of
 // nearly equal width.
-void pick_pair_tiles(GemmParams &p, int width_override) {
+void pick_pair_tiles(GemmParams &p, int width_override, int max_units) {
     const int stripes = p.n_tiles, upr = p.units_per_row;
-    int tps = (upr + 7) / 8;
-    if (width_override >= 32 && width_override <= 256) tps = (upr + width_override / 32 - 1) / (width_override / 32);
+    int tps = (upr + max_units - 1) / max_units;
+    if (width_override >= 32 && width_override <= 32 * max_units) tps = (upr + width_override / 32 - 1) / (width_override / 32);
     p.tps = tps;
     p.extra = 0;
     p.pair_tiles = stripes * tps;
@@ -1183,6 +1288,12 @@ bool encode_weight_map(EncodeTiledFn enc, CUtensorMap *map, const uint8_t *w, in
 }
 
 }  // namespace
+
+#ifdef B200Q_GEMM_TRACE
+extern "C" int b200q_debug_gemm_trace(long long *out_16384) {
+    return (int)cudaMemcpyFromSymbol(out_16384, g_gemm_trace, sizeof(long long) * 16384);
+}
+#endif
 
 size_t gemm_x_scratch_bytes(int M, int K) { return ((size_t)M * ((K + 7) & ~7) * 2 + 255) & ~size_t(255); }
 
@@ -1228,11 +1339,12 @@ cudaError_t gemm_launch(const GemmLaunch &a, cudaStream_t st) {
     p.n_tiles = (a.N + BM - 1) / BM;
     // large products run on CTA pairs (256-row tiles); small ones keep the one-CTA kernel
     const bool use_pair = a.pair && a.M >= 128 && a.N > BM && a.sm_count >= 2;
+    const bool use_ts = use_pair && a.pair >= 2;          // A operand from tensor memory, token tiles up to 192
     if (use_pair) {
         p.n_tiles = (a.N + 2 * BM - 1) / (2 * BM);       // 256-row stripes
         p.units_per_row = (a.M + 31) / 32;
         p.bn = 256;
-        pick_pair_tiles(p, a.bn_override);
+        pick_pair_tiles(p, a.bn_override, use_ts ? 6 : 8);
     } else {
         const int widest = bn_max(a.qt);
         p.bn = pick_bn(a.M, p.n_tiles, a.sm_count, widest);
@@ -1246,7 +1358,7 @@ cudaError_t gemm_launch(const GemmLaunch &a, cudaStream_t st) {
     CUtensorMap &map = maps.x;
     const cuuint64_t gdim[2] = {(cuuint64_t)a.K, (cuuint64_t)a.M};
     const cuuint64_t gstride[1] = {(cuuint64_t)a.ldx * 2};
-    const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)(use_pair ? 128 : p.bn)};
+    const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)(use_pair ? pair_b_rows(use_ts) : p.bn)};
     const cuuint32_t estride[2] = {1, 1};
     CUresult r = enc(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(a.x), gdim, gstride, box, estride,
                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -1281,9 +1393,9 @@ cudaError_t gemm_launch(const GemmLaunch &a, cudaStream_t st) {
     if (use_pair) {
         const int grid2 = 2 * std::min(p.pair_tiles, a.sm_count / 2);
         switch (a.qt) {
-        case QT_Q4_K: return launch_gemm_pair<QT_Q4_K>(p, maps, grid2, st);
-        case QT_Q6_K: return launch_gemm_pair<QT_Q6_K>(p, maps, grid2, st);
-        case QT_Q8_0: return launch_gemm_pair<QT_Q8_0>(p, maps, grid2, st);
+        case QT_Q4_K: return use_ts ? launch_gemm_pair<QT_Q4_K, true>(p, maps, grid2, st) : launch_gemm_pair<QT_Q4_K, false>(p, maps, grid2, st);
+        case QT_Q6_K: return use_ts ? launch_gemm_pair<QT_Q6_K, true>(p, maps, grid2, st) : launch_gemm_pair<QT_Q6_K, false>(p, maps, grid2, st);
+        case QT_Q8_0: return use_ts ? launch_gemm_pair<QT_Q8_0, true>(p, maps, grid2, st) : launch_gemm_pair<QT_Q8_0, false>(p, maps, grid2, st);
         default: return cudaErrorInvalidValue;
         }
     }
