@@ -672,7 +672,8 @@ constexpr int kTsACol0 = 2 * kTsAccCols;            // first A-stage column in T
 // the dequant warps fills K-steps j, j + 4, ...); with more than four, the hand-over after a stage is
 // released (stores, proxy fence, arrival across the pair: more than a thousand cycles) is off the
 // tensor cores' path.  Activation stages hide the latency of the TMA loads.  Q4_K's small records
-// leave room for 11 stages of 16 KB, split 6 + 5 (8 + 3 and 7 + 4 measured within 1 % of it); the
+// leave room for 11 stages of 16 KB; 6 + 4 (both in two-stage hand-over units, see the kernel)
+// measured fastest: 1026 TFLOP/s on 2048 x 4096 x 14336 against 956 for 6 + 5 and 833 for 4 + 6.  The
 // larger packed-record buffers of Q6_K and Q8_0 and the TS form's tensor-memory budget leave four
 // weight stages.  B200Q_PAIR_SA / B200Q_PAIR_SB override Q4_K's split at compile time.
 constexpr int kMaxPairAStages = 8;
@@ -684,12 +685,14 @@ constexpr int kMaxPairAStages = 8;
 #endif
 #ifndef B200Q_PAIR_SA
 #define B200Q_PAIR_SA 6
-#define B200Q_PAIR_SB 5
+#define B200Q_PAIR_SB 4
 #endif
 __host__ __device__ constexpr int pair_a_stages(int qt, bool ts) { return (!ts && qt == QT_Q4_K) ? B200Q_PAIR_SA : 4; }
 __host__ __device__ constexpr int pair_b_rows(bool ts) { return ts ? 96 : 128; }       // tokens each CTA stages per K-step
 __host__ __device__ constexpr int pair_b_stage_bytes(bool ts = false) { return ((pair_b_rows(ts) * BK * 2 + 1023) / 1024) * 1024; }
 __host__ __device__ constexpr int pair_b_stages(int qt, bool ts = false) { return ts ? 8 : qt == QT_Q8_0 ? 5 : qt == QT_Q6_K ? 6 : B200Q_PAIR_SB; }
+// activation stages per hand-over unit: two when the stages pair up
+__host__ __device__ constexpr int pair_b_group(int qt, bool ts = false) { return pair_b_stages(qt, ts) % 2 == 0 ? 2 : 1; }
 constexpr int kMaxPairBStages = 8;
 __host__ __device__ constexpr int pair_smem_data_bytes(int qt, bool ts = false) {
     return (ts ? 0 : pair_a_stages(qt, ts) * kStageABytes) + pair_b_stages(qt, ts) * pair_b_stage_bytes(ts) + kWBufs * wbuf_bytes(qt) + (qt == QT_Q6_K ? 2 * kDBufBytes : 0);
@@ -843,7 +846,14 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_tc_pair_kernel(const Gem
     constexpr int REC = rec_bytes(QT);
     constexpr int kStageBBytes = pair_b_stage_bytes(TS);
     constexpr int kAccCols = TS ? kTsAccCols : 256;         // tensor-memory columns between the two accumulators
-    constexpr int SA_ = pair_a_stages(QT, TS);              // weight stages: 4 (one per dequant group) or 8 (two per group)
+    constexpr int SA_ = pair_a_stages(QT, TS);              // dequantized-weight stages, used round robin by K-step
+    // Hand-over granularity.  The tensor cores take two K-steps (eight MMAs) per turn of the issuing
+    // thread's loop, so what that thread executes between MMAs is paid once per 128 weights: a weight
+    // unit is two consecutive stages with one pair of barriers; an activation unit is two stages when
+    // their number is even, one otherwise.
+    constexpr int GA = 2, GB = pair_b_group(QT, TS);
+    constexpr int UA = SA_ / GA, UB = SB_ / GB;
+    static_assert(SA_ % GA == 0 && SB_ % GB == 0, "stages must fill whole hand-over units");
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const uint32_t a_s = smem_u32(smem);                    // TS: no weight stages in shared memory
@@ -863,11 +873,11 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_tc_pair_kernel(const Gem
     const int chunks_per_tile = (p.nsb + kChunkRecs - 1) / kChunkRecs;
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < SA_; ++i) {
-            mbar_init(afull_s + 8 * i, 2 * (kDequantWarps / 4));   // one unit group of each CTA
+        for (int i = 0; i < UA; ++i) {
+            mbar_init(afull_s + 8 * i, GA * 2 * (kDequantWarps / 4));   // GA groups of four warps in each CTA
             mbar_init(aempty_s + 8 * i, 1);
         }
-        for (int i = 0; i < SB_; ++i) {
+        for (int i = 0; i < UB; ++i) {
             mbar_init(bfull_s + 8 * i, 1);
             mbar_init(bempty_s + 8 * i, 1);
         }
@@ -907,16 +917,20 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_tc_pair_kernel(const Gem
                 int stripe, t0, width;
                 pair_tile(p, tile, stripe, t0, width);
                 for (int ks = 0; ks < ksteps; ++ks, ++it) {
-                    const int stage = it % SB_;
-                    if PAIR_DBG(2048) continue;
-                    ok = pair_wait<true>(bempty_s + 8 * stage, ((it / SB_) & 1) ^ 1, sm, p.status);
-                    if (!ok) break;
-                    if PAIR_DBG(1) {
-                        if (rank == 0) mbar_arrive(bfull_s + 8 * stage);
+                    const int stage = it % SB_, unit = stage / GB;
+                    if (PAIR_DBG(2048)) continue;
+                    if (stage % GB == 0) {      // first stage of a unit: the unit is free, and its barrier expects all its loads
+                        ok = pair_wait<true>(bempty_s + 8 * unit, ((it / SB_) & 1) ^ 1, sm, p.status);
+                        if (!ok) break;
+                        if (PAIR_DBG(1)) {
+                            if (rank == 0) mbar_arrive(bfull_s + 8 * unit);
+                            continue;
+                        }
+                        if (rank == 0) mbar_expect_tx(bfull_s + 8 * unit, GB * bytes_pair);
+                    } else if (PAIR_DBG(1)) {
                         continue;
                     }
-                    if (rank == 0) mbar_expect_tx(bfull_s + 8 * stage, bytes_pair);
-                    tma_load_2d_pair(b_s + stage * kStageBBytes, &xmap, ks * BK, t0 + (int)rank * (width >> 1), bfull_leader + 8 * stage);
+                    tma_load_2d_pair(b_s + stage * kStageBBytes, &xmap, ks * BK, t0 + (int)rank * (width >> 1), bfull_leader + 8 * unit);
                 }
             }
         }
@@ -934,7 +948,7 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_tc_pair_kernel(const Gem
                     const int wb = rs % kWBufs;
                     ok = pair_wait<true>(wempty_s + 8 * wb, ((rs / kWBufs) & 1) ^ 1, sm, p.status);
                     if (!ok) break;
-                    if PAIR_DBG(4) {
+                    if (PAIR_DBG(4)) {
                         mbar_arrive(wfull_s + 8 * wb);
                         continue;
                     }
@@ -954,17 +968,21 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_tc_pair_kernel(const Gem
         }
     } else if (warp == 1) {
         // ===== MMA issuer (leader CTA only) ========================================================
-        // One thread, in order: whatever it executes between two K-steps leaves the tensor cores with
-        // only the few MMAs still queued, so the loop is kept to a handful of instructions.  Stage
-        // indices, parities and descriptors advance incrementally, and the barriers of the NEXT K-step
-        // are probed (without blocking) before this K-step's MMAs are issued: in the steady state the
-        // probe succeeds and the thread never executes a blocking wait.
+        // One thread, in order: whatever it executes between two turns leaves the tensor cores with
+        // only the few MMAs still queued, so the loop is kept to a handful of instructions and takes
+        // two K-steps (eight MMAs) per turn.  Units, parities and descriptors advance incrementally, and
+        // the barriers of the NEXT turn are probed (without blocking) before this turn's MMAs are
+        // issued: in the steady state the probe succeeds and the thread never executes a blocking wait.
         if (lane == 0 && rank == 0) {
             constexpr uint32_t kADescStep = kStageABytes >> 4, kBDescStep = kStageBBytes >> 4;
+            constexpr int NB = GA / GB;                   // activation units taken per turn
             const uint64_t adesc0 = make_desc_sw128(a_s), bdesc0 = make_desc_sw128(b_s);
-            uint32_t sa = 0, sb = 0, pa = 0, pb = 0;      // stage and phase parity of the K-step about to be issued
+            auto advance = [](uint32_t &u, uint32_t &par, uint32_t units) {
+                if (++u == units) u = 0, par ^= 1;
+            };
+            uint32_t ua = 0, pa = 0, ub = 0, pb = 0;      // unit and phase parity of the operands about to be used
             int tcount = 0;
-            bool seen = false;                            // this K-step's operands were found ready by the previous probe
+            bool seen = false;                            // this turn's operands were found ready by the previous probe
             GEMM_TRACE_DECL(int it = 0;)
             for (int tile = pair; tile < p.pair_tiles; tile += n_pairs, ++tcount) {
                 int stripe, t0, width;
@@ -974,32 +992,49 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_tc_pair_kernel(const Gem
                 bool ok = pair_wait<true>(tempty_s + 8 * buf, ((tcount >> 1) & 1) ^ 1, sm, p.status);
                 if (!ok) break;
                 const uint32_t d_tmem = tmem_base + buf * kAccCols;
-                for (int ks = 0; ks < ksteps; ++ks) {
+                for (int turn = 0; turn < ksteps / GA; ++turn) {
                     GEMM_TRACE(4 * it);
+                    uint32_t ub1 = ub, pb1 = pb;          // second activation unit of the turn (NB == 2)
+                    if (NB == 2) advance(ub1, pb1, UB);
                     if (!seen) {
-                        ok = PAIR_DBG(2048) || pair_wait<true>(bfull_s + 8 * sb, pb, sm, p.status);
-                        ok = ok && (PAIR_DBG(1024) || pair_wait<true>(afull_s + 8 * sa, pa, sm, p.status));
+                        ok = PAIR_DBG(2048) || (pair_wait<true>(bfull_s + 8 * ub, pb, sm, p.status) &&
+                                                (NB == 1 || pair_wait<true>(bfull_s + 8 * ub1, pb1, sm, p.status)));
+                        ok = ok && (PAIR_DBG(1024) || pair_wait<true>(afull_s + 8 * ua, pa, sm, p.status));
                         if (!ok) break;
                     }
                     GEMM_TRACE(4 * it + 1);
                     tc_fence_after();
-                    const uint32_t nsa = sa + 1 == SA_ ? 0 : sa + 1, nsb = sb + 1 == SB_ ? 0 : sb + 1;
-                    const uint32_t npa = pa ^ (nsa == 0), npb = pb ^ (nsb == 0);
-                    seen = mbar_test_wait_both(bfull_s + 8 * nsb, npb, afull_s + 8 * nsa, npa);
-                    GEMM_TRACE(4 * it + 2);
-                    const uint64_t adesc = adesc0 + sa * kADescStep, bdesc = bdesc0 + sb * kBDescStep;
-#pragma unroll
-                    for (int kk = 0; kk < BK / 16; ++kk) {     // 16 fp16 = 32 bytes = +2 in the address field
-                        if (PAIR_DBG(8)) continue;
-                        // TS: 16 fp16 of a row = 8 columns of its tensor-memory lane
-                        if (TS) umma_f16_pair_ts(d_tmem, tmem_base + kTsACol0 + sa * 32 + 8 * kk, bdesc + 2 * kk, idesc, (ks | kk) != 0);
-                        else umma_f16_pair(d_tmem, adesc + 2 * kk, bdesc + 2 * kk, idesc, (ks | kk) != 0);
+                    uint32_t nua = ua, npa = pa, nub = ub1, npb = pb1;
+                    advance(nua, npa, UA);
+                    advance(nub, npb, UB);
+                    if (NB == 2) {
+                        uint32_t nub1 = nub, npb1 = npb;
+                        advance(nub1, npb1, UB);
+                        seen = mbar_test_wait_both(bfull_s + 8 * nub, npb, bfull_s + 8 * nub1, npb1) && mbar_test_wait(afull_s + 8 * nua, npa);
+                    } else {
+                        seen = mbar_test_wait_both(bfull_s + 8 * nub, npb, afull_s + 8 * nua, npa);
                     }
-                    if (!PAIR_DBG(1024)) umma_commit_pair(aempty_s + 8 * sa);
-                    if (!PAIR_DBG(2048)) umma_commit_pair(bempty_s + 8 * sb);
+                    GEMM_TRACE(4 * it + 2);
+#pragma unroll
+                    for (int h = 0; h < GA; ++h) {
+                        const uint32_t sa = GA * ua + h, sb = GB == 2 ? 2 * ub + h : (h == 0 ? ub : ub1);
+                        const uint64_t adesc = adesc0 + sa * kADescStep, bdesc = bdesc0 + sb * kBDescStep;
+#pragma unroll
+                        for (int kk = 0; kk < BK / 16; ++kk) {     // 16 fp16 = 32 bytes = +2 in the address field
+                            if (PAIR_DBG(8)) continue;
+                            // TS: 16 fp16 of a row = 8 columns of its tensor-memory lane
+                            if (TS) umma_f16_pair_ts(d_tmem, tmem_base + kTsACol0 + sa * 32 + 8 * kk, bdesc + 2 * kk, idesc, (turn | h | kk) != 0);
+                            else umma_f16_pair(d_tmem, adesc + 2 * kk, bdesc + 2 * kk, idesc, (turn | h | kk) != 0);
+                        }
+                    }
+                    if (!PAIR_DBG(1024)) umma_commit_pair(aempty_s + 8 * ua);
+                    if (!PAIR_DBG(2048)) {
+                        umma_commit_pair(bempty_s + 8 * ub);
+                        if (NB == 2) umma_commit_pair(bempty_s + 8 * ub1);
+                    }
                     GEMM_TRACE(4 * it + 3);
                     GEMM_TRACE_DECL(++it;)
-                    sa = nsa, sb = nsb, pa = npa, pb = npb;
+                    ua = nua, pa = npa, ub = nub, pb = npb;
                 }
                 if (!ok) break;
                 umma_commit_pair(tfull_s + 8 * buf);
@@ -1043,7 +1078,7 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_tc_pair_kernel(const Gem
             const int stage = (4 * rs + j) % SA_;
             const uint32_t use = (uint32_t)((4 * rs + j) / SA_);       // how often this stage has been filled before
             if (tracer) GEMM_TRACE(8192 + 8 * rs + 2);
-            if (lane == 0 && !PAIR_DBG(1024)) ok = pair_wait<true>(aempty_s + 8 * stage, (use & 1) ^ 1, sm, p.status);
+            if (lane == 0 && !PAIR_DBG(1024)) ok = pair_wait<true>(aempty_s + 8 * (stage / GA), (use & 1) ^ 1, sm, p.status);
             ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
             if (!ok) break;
             if (tracer) GEMM_TRACE(8192 + 8 * rs + 3);
@@ -1063,8 +1098,8 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_tc_pair_kernel(const Gem
             __syncwarp();
             if (lane == 0 && !PAIR_DBG(1024)) {
                 // the leader's own warps arrive locally; only the peer's arrival has to cross the pair
-                if (rank == 0) mbar_arrive(afull_s + 8 * stage);
-                else mbar_arrive_cluster(afull_leader + 8 * stage);
+                if (rank == 0) mbar_arrive(afull_s + 8 * (stage / GA));
+                else mbar_arrive_cluster(afull_leader + 8 * (stage / GA));
             }
             if (tracer) GEMM_TRACE(8192 + 8 * rs + 6);
             cur = nxt;
