@@ -20,7 +20,13 @@
  *   - every function returns b200q_status (0 = OK); out-parameters come last;
  *   - handles are opaque; the library owns device memory until *_destroy;
  *   - `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream);
- *   - a b200q_ctx is single-thread-affine; distinct contexts are independent;
+ *   - a b200q_ctx is used by one thread at a time; distinct contexts may be used from distinct
+ *     threads (the library's one-time set-up is thread-safe);
+ *   - calls are stream-ordered: each enqueues on the stream it is given and returns.  The scratch a
+ *     context owns (fp16 activation copy, partial sums, dependency counters) is shared by all its
+ *     b200q_matmul* calls, so keep one context's calls on one stream or order them with events;
+ *     a plan owns its scratch, but two runs of one plan must not overlap.  The first call with a
+ *     larger M x K may allocate: make it before any stream capture;
  *   - weights are W[N][K] in GGUF order: N output rows, each K/blk consecutive packed blocks;
  *   - activations X[M][K] and outputs Y[M][N] are row-major with leading dimensions in elements.
  *   - there is no CPU fallback: without a CUDA device every compute call fails with

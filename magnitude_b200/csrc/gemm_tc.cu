@@ -346,6 +346,18 @@ __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, Gem
     }
 }
 
+// After an abort the roles have left their loops, but TMA loads and MMAs they issued may still be
+// in flight towards this CTA's shared memory: give them a fixed time (far above a load's latency)
+// to land before the CTA exits and its shared memory goes to another CTA.
+__device__ __forceinline__ void drain_after_abort(const int *abort_flag) {
+    if (*reinterpret_cast<const volatile int *>(abort_flag)) {
+        const uint64_t t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 100000) {
+        }
+        __syncthreads();
+    }
+}
+
 // Split of the K range for small products: with few output tiles (a skinny batch against a
 // weight of a few thousand rows) most SMs would idle, so each tile's records are cut into
 // p.ksplit ranges that run as separate work units; their fp32 partial products go to a workspace
@@ -621,6 +633,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const GemmParams p
     // everyone meets here (also after an abort); then the allocating warp frees tensor memory
     tc_fence_before();
     __syncthreads();
+    drain_after_abort(&sm->abort);
     if (warp == 0) {
         __syncwarp();
         tc_fence_after();
@@ -1149,6 +1162,7 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_tc_pair_kernel(const Gem
     // both CTAs meet (also after an abort) before either releases shared or tensor memory
     tc_fence_before();
     __syncthreads();
+    drain_after_abort(&sm->abort);
     cluster_sync_all();
     if (warp == 0) {
         __syncwarp();
@@ -1158,8 +1172,9 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_tc_pair_kernel(const Gem
 }
 
 // Activations -> fp16, the format the weights are dequantized to (both tensor-core operands must
-// share one format).  bf16 activations convert exactly unless they exceed fp16's range, where they
-// saturate to +-65504; fp32 activations round to nearest even.
+// share one format), rounding to nearest even.  fp16 has three more mantissa bits than bf16 but a
+// narrower exponent: bf16 values between 2^-14 and 65504 in magnitude convert exactly, larger ones
+// saturate to +-65504, smaller ones lose bits as fp16 subnormals or flush to zero (below 2^-25).
 __device__ __forceinline__ uint32_t to_h2_sat(float lo, float hi) {
     lo = fminf(fmaxf(lo, -65504.f), 65504.f);   // NaN passes through both
     hi = fminf(fmaxf(hi, -65504.f), 65504.f);

@@ -131,7 +131,7 @@ def test_config2_q4_k_decode_full_size(backend, orc, n, k):
     assert np.array_equal(got.view(np.uint32), orc.dequantize(mb.TYPE_Q4_K, packed, k).view(np.uint32))
 
 
-def test_linearity_full_size(backend):
+def test_linearity_full_size(backend, orc):
     # size-independent property: W(a*x1 + x2) = a*W x1 + W x2 (up to the decode tolerance)
     n, k = 4096, 14336
     packed = gq.synth_weights(mb.TYPE_Q6_K, n, k, seed=6, encoder=orc.quantize)
