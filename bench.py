@@ -1036,8 +1036,11 @@ def run_layer32b(args, emit=True):
         Yv = torch.empty((M, w0["v"].n), dtype=torch.bfloat16, device=dev)
         Yg = torch.empty((M, w0["gate"].n), dtype=torch.bfloat16, device=dev)
         Yu = torch.empty((M, w0["up"].n), dtype=torch.bfloat16, device=dev)
-        Yo = torch.empty((M, L32_H), dtype=torch.bfloat16, device=dev)
-        Yd = torch.empty((M, L32_H), dtype=torch.bfloat16, device=dev)
+        # row-parallel partial products are summed over the ranks in fp32: bf16 partials (2^-9 each, and
+        # again at every addition of the reduction) leave the 5e-3 bound at 2 and 4 ranks
+        part_dtype = torch.float32 if world > 1 else torch.bfloat16
+        Yo = torch.empty((M, L32_H), dtype=part_dtype, device=dev)
+        Yd = torch.empty((M, L32_H), dtype=part_dtype, device=dev)
         comm = torch.cuda.Stream(device=dev)
 
         def row_parallel(w, x, y):
@@ -1070,7 +1073,7 @@ def run_layer32b(args, emit=True):
         rows = np.sort(np.random.default_rng(4).choice(L32_H, size=16, replace=False))
         wd = gq.dequantize(14, host["down"][rows], L32_I).astype(np.float64)
         ref = (Xd.float().numpy().astype(np.float64)[:256] @ wd.T)
-        chk = worst(Yd[:256][:, torch.from_numpy(rows).to(dev)].float().cpu().numpy().astype(np.float64), ref, 5e-3 * (1 + 0.5 * (world > 1)))
+        chk = worst(Yd[:256][:, torch.from_numpy(rows).to(dev)].float().cpu().numpy().astype(np.float64), ref, 5e-3)
         flops = layers * 2.0 * M * sum(n * k for _, _, n, k in L32)
         tpeak, tsrc = FALLBACK_TFLOPS, "fallback"
         pk = ROOT / "MEASURED_PEAKS.json"
@@ -1085,8 +1088,8 @@ def run_layer32b(args, emit=True):
                                           "note": "per-rank 2 M N K / device time; includes activation conversions and, for N > 1, "
                                                   f"{2 * chunks} NCCL all-reduces per layer ({M * L32_H * 2} bytes per projection) on a second stream"},
                              "stats": sample_stats(samples),
-                             "check": {"max_err_over_tol": chk, "ok": bool(chk <= 1.0), "what": "16 sampled rows of down, 256 tokens, summed over ranks (bf16 partials)"},
-                             "allreduce_bytes_per_projection": M * L32_H * 2 if world > 1 else 0, "m_chunks": chunks}
+                             "check": {"max_err_over_tol": chk, "ok": bool(chk <= 1.0), "what": "16 sampled rows of down, 256 tokens" + (", fp32 partials summed over the ranks" if world > 1 else "")},
+                             "allreduce_bytes_per_projection": M * L32_H * 4 if world > 1 else 0, "m_chunks": chunks}
     used = clocks.summary()
     if world > 1:
         be.tp_finalize()

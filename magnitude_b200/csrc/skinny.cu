@@ -49,7 +49,12 @@ constexpr int kSkWarps = 8;                       // consumer warps = records pe
 constexpr int kSkThreads = (kSkWarps + 2) * 32;   // + the producer warp and the reducer warp
 constexpr int kSkRows = 16;                       // weight rows per item (MMA M)
 constexpr int kSkMaxDepth = 12;
-constexpr int kSkMaxCtas = 160;
+constexpr int kSkMaxCtas = 320;     // two CTAs per SM for the 8-token tile
+#ifndef B200Q_SKINNY_CTAS_PER_SM
+#define B200Q_SKINNY_CTAS_PER_SM 2
+#endif
+// CTAs per SM by token tile: the 16-token form's resident activation fragments leave registers for one
+__host__ __device__ constexpr int sk_ctas_per_sm(int nt) { return nt == 1 ? B200Q_SKINNY_CTAS_PER_SM : 1; }
 constexpr int kSkMaxJobs = 32;
 constexpr int kSkInline = 4;                      // products whose descriptions travel in the kernel parameters
 constexpr int kRedStride = 20;                    // floats between the tokens of a partial tile (bank spread)
@@ -467,7 +472,7 @@ __device__ __forceinline__ bool sk_wait(uint32_t bar, uint32_t parity, volatile 
 }
 
 template <int QT, int NT>
-__global__ void __launch_bounds__(kSkThreads, 1) skinny_kernel(const __grid_constant__ SkParams p) {
+__global__ void __launch_bounds__(kSkThreads, sk_ctas_per_sm(NT)) skinny_kernel(const __grid_constant__ SkParams p) {
     using L = SkLayout<QT, NT>;
     constexpr int SBK = L::SBK, S = L::S;
     extern __shared__ __align__(128) uint8_t smem[];
@@ -699,6 +704,9 @@ template <int QT, int NT>
 cudaError_t sk_launch_t(const SkParams &p, int grid, size_t smem_limit, cudaStream_t st) {
     using L = SkLayout<QT, NT>;
     SkParams q = p;
+    // co-resident CTAs share the SM's shared memory (1 KB per CTA is the system's)
+    constexpr int kPerSm = sk_ctas_per_sm(NT);
+    if (kPerSm > 1) smem_limit = (smem_limit + 1024) / kPerSm - 1024;
     int depth = (int)((smem_limit - L::kRingOff) / L::kStageBytes);
     if (depth > kSkMaxDepth) depth = kSkMaxDepth;
     if (depth < 2) return cudaErrorInvalidValue;
@@ -800,7 +808,7 @@ cudaError_t skinny_set_create(const SkinnyProduct *prods, int n, const SkinnyBuf
     }
     // contiguous runs of items of (nearly) equal weight per CTA; an item's weight is its chunk's
     // record count plus a constant for the per-item work that does not shrink with a short chunk
-    const int grid = std::min(std::min(buf.sm_count, kSkMaxCtas), items);
+    const int grid = std::min(std::min(buf.sm_count * sk_ctas_per_sm(NT), kSkMaxCtas), items);
     {
         double total = 0;
         for (const SkJob &J : jobs)
