@@ -310,7 +310,15 @@ enum {
      * and loads from inside the kernel, no separate all-reduce).  One weight, fp32 output, M x N at
      * most B200Q_PEER_MAX_COUNT; every rank must run the same plan.  Without attached peers the
      * flag does nothing (the sum over one rank is the output itself). */
-    B200Q_JOB_SUM_RANKS = 2
+    B200Q_JOB_SUM_RANKS = 2,
+    /* gated MLP: the job has exactly two weights of equal shape, w[0] = gate and w[1] = up, and writes
+     * y_dev[0][m][n] = silu(gate x)[n] * (up x)[n] (silu(v) = v / (1 + exp(-v)), in fp32); y_dev[1] is not
+     * used.  The activation function llama-style models apply between the two projections and `down`
+     * (the reference runs it as a separate ggml op of the same graph).  Streaming plans only (M <= 4). */
+    B200Q_JOB_SWIGLU = 4,
+    /* residual connection: the job adds its result to what y_dev holds instead of overwriting it; with
+     * B200Q_JOB_SUM_RANKS the sum over the ranks is added once, on every rank.  Streaming plans only. */
+    B200Q_JOB_ACCUMULATE = 8
 };
 
 typedef struct b200q_job {

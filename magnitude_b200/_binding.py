@@ -33,6 +33,8 @@ OPT_SKINNY_MIN_M, OPT_WAIT_LIMIT_MS, OPT_TP_INIT_TIMEOUT_MS = 1, 2, 3
 
 JOB_WAITS_FOR_EARLIER = 1
 JOB_SUM_RANKS = 2
+JOB_SWIGLU = 4
+JOB_ACCUMULATE = 8
 
 
 class Job(ctypes.Structure):

@@ -955,11 +955,16 @@ b200q_status b200q_plan_create(b200q_ctx *ctx, const b200q_job *jobs, int32_t n_
     if (!pl) return fail(ctx, B200Q_ERR_OVERLOADED, "out of host memory");
     pl->ctx = ctx;
     pl->M = (int)M;
-    bool rank_sums = false;
-    for (int i = 0; i < n_jobs; ++i) rank_sums |= (jobs[i].flags & B200Q_JOB_SUM_RANKS) != 0;
+    bool rank_sums = false;      // ... or another epilogue only the streaming kernel has
+    for (int i = 0; i < n_jobs; ++i)
+        rank_sums |= (jobs[i].flags & (B200Q_JOB_SUM_RANKS | B200Q_JOB_SWIGLU | B200Q_JOB_ACCUMULATE)) != 0;
     // 3 or more rows run on the skinny kernel, like single calls; plans that add partial sums over
     // ranks inside the launch stay on the streaming kernel (up to 4 rows)
     if (M > gemv_max_m() || (M >= ctx->skinny_min_m && !rank_sums)) {
+        if (rank_sums) {
+            delete pl;
+            return fail(ctx, B200Q_ERR_INVALID_CONFIG, "rank sums, SWIGLU and ACCUMULATE jobs need a streaming plan (M <= %d)", gemv_max_m());
+        }
         s = plan_create_skinny(ctx, pl, jobs, n_jobs, (int)M);
         if (s != B200Q_OK) {
             b200q_plan_destroy(pl);
@@ -974,9 +979,15 @@ b200q_status b200q_plan_create(b200q_ctx *ctx, const b200q_job *jobs, int32_t n_
             delete pl;
             return fail(ctx, B200Q_ERR_INVALID_CONFIG, "job %d: 1..4 weights", i);
         }
+        const bool glu = (j.flags & B200Q_JOB_SWIGLU) != 0;
+        if (glu && (j.n_weights != 2 || !j.w[0] || !j.w[1] || j.w[0]->N != j.w[1]->N || (j.flags & B200Q_JOB_SUM_RANKS))) {
+            delete pl;
+            return fail(ctx, B200Q_ERR_INVALID_CONFIG, "job %d: SWIGLU takes two weights of equal shape (gate, up) and no rank sum", i);
+        }
         bool rows = false;
         for (int k = 0; k < j.n_weights; ++k) {
-            s = validate_mm(ctx, j.w[k], j.x_dev, j.x_dtype, M, j.ldx, j.y_dev[k], j.y_dtype, j.ldy[k]);
+            const int ky = glu ? 0 : k;      // SWIGLU writes y_dev[0] only
+            s = validate_mm(ctx, j.w[k], j.x_dev, j.x_dtype, M, j.ldx, j.y_dev[ky], j.y_dtype, j.ldy[ky]);
             if (s == B200Q_OK && (j.w[k]->type != j.w[0]->type || j.w[k]->K != j.w[0]->K))
                 s = fail(ctx, B200Q_ERR_INVALID_CONFIG, "job %d: weights of one job must share type and K", i);
             if (s != B200Q_OK) {
@@ -999,6 +1010,8 @@ b200q_status b200q_plan_create(b200q_ctx *ctx, const b200q_job *jobs, int32_t n_
             }
             jflags |= STREAM_JOB_SUM_RANKS;
         }
+        if (glu) jflags |= STREAM_JOB_SWIGLU;
+        if (j.flags & B200Q_JOB_ACCUMULATE) jflags |= STREAM_JOB_ACCUM;
         StreamJob J;
         fill_job(J, j.w, j.n_weights, j.x_dev, j.x_dtype, j.ldx, j.y_dev, j.y_dtype, j.ldy, jflags);
         pl->jobs.push_back(J);

@@ -40,6 +40,13 @@ namespace b200q {
 
 namespace {
 
+// timing experiments (parts of the pipeline switched off; results invalid) exist only in builds that ask for them
+#ifdef B200Q_TIMING_EXPERIMENTS
+#define GEMV_DBG(bit) (p.debug & (bit))
+#else
+#define GEMV_DBG(bit) (false)
+#endif
+
 constexpr int kMaxWarps = 15;    // consumer warps (+1 producer = 512 threads, 128 registers each)
 constexpr int kMaxDepth = 8;
 constexpr int KC = kChunkRecs;   // superblock records per chunk: 32 units of 64 weights, one per lane
@@ -97,13 +104,34 @@ __device__ __forceinline__ unsigned long long ld_pair(const unsigned long long *
 }
 constexpr size_t kHeadBytes = (sizeof(SmemHead) + 127) & ~size_t(127);
 
-// (segment, row group inside it) of virtual group vg; segments are concatenated in launch order
-__device__ __forceinline__ void locate_group(const StreamJob &J, int vg, int &s, int &g) {
+// (segment, row group inside it) of virtual group vg; segments are concatenated in launch order.
+// A SWIGLU job interleaves its two segments instead (even groups gate, odd groups up), so that a
+// CTA's contiguous range holds the gate rows and the up rows of the same outputs.
+// (`glu`: the job's SWIGLU flag, read once per job by the caller: this runs once per work item.)
+__device__ __forceinline__ void locate_group(const StreamJob &J, int vg, int &s, int &g, bool glu) {
+    if (glu) {
+        s = vg & 1;
+        g = vg >> 1;
+        return;
+    }
     s = 0;
 #pragma unroll
     for (int i = 1; i < kStreamMaxSeg; ++i)
         if (i < J.nseg && vg >= J.seg[i].group_begin) s = i;
     g = vg - J.seg[s].group_begin;
+}
+
+// virtual groups [gb, ge) of job J that CTA b of `grid` works on (whole gate/up pairs for SWIGLU)
+template <bool FUSED = true>
+__host__ __device__ __forceinline__ void cta_groups(const StreamJob &J, int b, int grid, int &gb, int &ge) {
+    if (FUSED && (J.flags & STREAM_JOB_SWIGLU)) {
+        const long long pairs = J.total_groups >> 1;
+        gb = 2 * (int)(pairs * b / grid);
+        ge = 2 * (int)(pairs * (b + 1) / grid);
+    } else {
+        gb = (int)((long long)J.total_groups * b / grid);
+        ge = (int)((long long)J.total_groups * (b + 1) / grid);
+    }
 }
 
 // barrier of one consumer team (hardware barrier 1 + team; barrier 0 is __syncthreads)
@@ -191,7 +219,9 @@ __device__ __forceinline__ void item_dot(int nsb, uint32_t sl, int stride, int s
 // single-type launch compiles only that type's unpacking, which keeps it free of register spills.
 constexpr int TY_Q4K = 1, TY_Q6K = 2, TY_Q80 = 4;
 
-template <int MT, int TYPES>
+// FUSED: some job of the launch has a fused epilogue (SWIGLU, ACCUM); launches without any run the
+// instantiation that carries none of that code.
+template <int MT, int TYPES, bool FUSED>
 __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1) stream_kernel(const StreamParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -247,7 +277,7 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1) stream_kernel(const S
     // =========================================================================================
     if (warp == CW) {
         const unsigned mask = 0xFFFFFFFFu;
-        const bool feeder = lane < CW && !(p.debug & 2);
+        const bool feeder = lane < CW && !GEMV_DBG(2);
         const uint32_t ring_s = smem_u32(rings + lane * ring_bytes);
         const uint32_t fbar = full0 + lane * kMaxDepth * 8, ebar = empty0 + lane * kMaxDepth * 8;
         // the consumer this lane feeds: its team, its index and the number of warps in that team
@@ -258,13 +288,15 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1) stream_kernel(const S
         bool dead = false;
         // every lane walks its own team's jobs: job cursor, item cursor inside the job
         int jb = -1, n_items = 0, item = 0, g = 0, c = 0, gb = 0;
+        bool glu = false;
         auto next_job = [&]() {
             do { ++jb; } while (jb < p.njobs && p.teams == 2 && jobs_s[jb].team != my_team);
             if (!feeder) jb = p.njobs;
             if (jb >= p.njobs) return;
             const StreamJob &J = jobs_s[jb];
-            gb = (int)((long long)J.total_groups * blockIdx.x / gridDim.x);
-            const int ge = (int)((long long)J.total_groups * (blockIdx.x + 1) / gridDim.x);
+            glu = FUSED && (J.flags & STREAM_JOB_SWIGLU) != 0;
+            int ge;
+            cta_groups<FUSED>(J, blockIdx.x, gridDim.x, gb, ge);
             n_items = (ge - gb) * J.nchunks;
             item = twarp;
             g = 0, c = twarp;          // item = g * nchunks + c, kept without dividing
@@ -274,7 +306,7 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1) stream_kernel(const S
         // Lanes 30 and 31 feed the activation areas of team 0 and team 1: one bulk copy per job whose
         // activation was converted to fixed point by the prep launch, as soon as the team has left
         // the area's previous contents behind.
-        const bool xfeeder = p.has_xq && lane >= 30 && (lane - 30) < p.teams && !(p.debug & 2);
+        const bool xfeeder = p.has_xq && lane >= 30 && (lane - 30) < p.teams && !GEMV_DBG(2);
         const int xteam = lane - 30;
         int xjb = -1, xseq = 0;        // job cursor; how many of the team's jobs lie before it
         auto next_xjob = [&]() {
@@ -300,7 +332,7 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1) stream_kernel(const S
                     const bool free_slot = (k < D) || mbar_test_wait(ebar + 8 * slot, phase ^ 1u);
                     if (free_slot) {
                         int sg, lg;
-                        locate_group(J, gb + g, sg, lg);
+                        locate_group(J, gb + g, sg, lg, glu);
                         const uint32_t bytes = R * ((c == J.nchunks - 1) ? J.bytes_tail : J.bytes_full);   // whole tile, padding rows included
                         const uint32_t bar = fbar + 8 * slot;
                         fence_proxy_async();   // the consumer's reads of this slot precede the engine's writes
@@ -419,9 +451,10 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1) stream_kernel(const S
         const StreamJob &Jc = jobs_s[job];
         const unsigned long long *slots = reinterpret_cast<const unsigned long long *>(p.peer_base[p.peer_rank] + kPeerFusedSlotOff) +
                                           (size_t)(team * 2 + (e & 1)) * kPeerMaxWorld * kPeerSlotFloats;
-        const int gbc = (int)((long long)Jc.total_groups * blockIdx.x / gridDim.x);
-        const int gec = (int)((long long)Jc.total_groups * (blockIdx.x + 1) / gridDim.x);
+        int gbc, gec;
+        cta_groups<FUSED>(Jc, blockIdx.x, gridDim.x, gbc, gec);
         const int n = Jc.seg[0].n;
+        const bool accum = FUSED && (Jc.flags & STREAM_JOB_ACCUM) != 0;
         const int cells = (gec - gbc) * R * MT;
         for (int t = tid; t < cells; t += T) {
             const int rl = t / MT, m = t - rl * MT;
@@ -433,7 +466,7 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1) stream_kernel(const S
                 for (int r = 0; r < p.peer_world && ok; ++r) {
                     const unsigned long long *q = slots + (size_t)r * kPeerSlotFloats + si;
                     unsigned long long w = ld_pair(q);
-                    if ((unsigned)(w >> 32) != e && !(p.debug & 64)) {
+                    if ((unsigned)(w >> 32) != e && !GEMV_DBG(64)) {
                         const uint64_t t0 = globaltimer_ns();
                         int spins = 0;
                         while ((unsigned)((w = ld_pair(q)) >> 32) != e) {
@@ -447,7 +480,10 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1) stream_kernel(const S
                     }
                     acc = r == 0 ? __uint_as_float((unsigned)w) : acc + __uint_as_float((unsigned)w);
                 }
-                if (ok) reinterpret_cast<float *>(Jc.seg[0].y)[(long long)m * Jc.seg[0].ldy + row] = acc;
+                if (ok) {
+                    float *yp = reinterpret_cast<float *>(Jc.seg[0].y) + (long long)m * Jc.seg[0].ldy + row;
+                    *yp = accum ? *yp + acc : acc;
+                }
             }
         }
     };
@@ -482,10 +518,11 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1) stream_kernel(const S
         }
 
         // ---- this job's geometry -------------------------------------------------------------
-        const int gb = (int)((long long)J.total_groups * blockIdx.x / gridDim.x);
-        const int ge = (int)((long long)J.total_groups * (blockIdx.x + 1) / gridDim.x);
+        int gb, ge;
+        cta_groups<FUSED>(J, blockIdx.x, gridDim.x, gb, ge);
         const int n_items = (ge - gb) * J.nchunks;
         const int nchunks = J.nchunks, nsb = J.nsb, qt = J.qt;
+        const bool glu = FUSED && (J.flags & STREAM_JOB_SWIGLU) != 0;
         const int units16 = (J.Kpad >> 6) * 16;
         const int plane = J.Kpad;
         const int n_isum = (qt == QT_Q6_K) ? (J.Kpad >> 4) : (J.Kpad >> 5);
@@ -496,7 +533,7 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1) stream_kernel(const S
         // slower threads of the team when this job's first items are flushed
         float *partial = partial_t + (tjobs & 1) * (p.partial_bytes >> 3);
         ++tjobs;
-        const bool pre_x = J.xq != nullptr && !(p.debug & 2);
+        const bool pre_x = J.xq != nullptr && !GEMV_DBG(2);
         XView xv[MT];
         {
             const XSrc xs = job_xsrc(J);
@@ -509,7 +546,7 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1) stream_kernel(const S
                 xv[m].xl = smem_u32(b + plane);
                 xv[m].sx = smem_u32(sxp);
                 xv[m].isum = smem_u32(isp);
-                if (m < p.M && !(p.debug & 4) && !pre_x) {
+                if (m < p.M && !GEMV_DBG(4) && !pre_x) {
                     const bool q6 = (TYPES & TY_Q6K) && (TYPES == TY_Q6K || qt == QT_Q6_K);
                     if (MT == 1 && have_raw) {
                         if (q6) prep_from_raw<QT_Q6_K>(xs, tid, T, xraw, b, b + plane, sxp, isp, units16);
@@ -566,9 +603,14 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1) stream_kernel(const S
         const int step_g = tcw / nchunks, step_c = tcw - step_g * nchunks;
         int g = twarp / nchunks, c = twarp - g * nchunks;
 #pragma unroll 1
-        for (int item = (p.debug & 16) ? n_items : twarp; item < n_items; item += tcw) {
-            bool ok = (p.debug & 2) ? true : mbar_wait_bounded(fbar + 8 * slot, phase);
-            ok = __all_sync(0xFFFFFFFFu, ok && !*fail_flag);
+        for (int item = GEMV_DBG(16) ? n_items : twarp; item < n_items; item += tcw) {
+            // the common case is a slot that is already full: one probe, and the abort flag is only looked at
+            // when the warp has to wait
+            bool ok = GEMV_DBG(2) || mbar_test_wait(fbar + 8 * slot, phase);
+            if (!__all_sync(0xFFFFFFFFu, ok)) {
+                ok = mbar_wait_bounded(fbar + 8 * slot, phase);
+                ok = __all_sync(0xFFFFFFFFu, ok && !*fail_flag);
+            }
             if (!ok) {
                 if (lane == 0) {
                     atomicMax(p.status, DEV_ERR_PIPE_TIMEOUT);
@@ -577,7 +619,7 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1) stream_kernel(const S
                 break;
             }
             int sg, lg;
-            locate_group(J, gb + g, sg, lg);
+            locate_group(J, gb + g, sg, lg, glu);
             const int nr = group_rows(lg, J.seg[sg].n);
             const int cb = (c == nchunks - 1) ? (int)J.bytes_tail : (int)J.bytes_full;   // bytes per tile row
             const int sb0 = c * KC;
@@ -589,9 +631,9 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1) stream_kernel(const S
 
             // the pending sum uses full-warp shuffles, so it may sit inside the branch below only
             // when every lane takes that branch (a chunk of 8 whole records)
-            const bool whole = (sb0 + KC <= nsb) && !(p.debug & 1);
+            const bool whole = (sb0 + KC <= nsb) && !GEMV_DBG(1);
             if (!whole) flush_pending();
-            if (sb0 + lsb < nsb && !(p.debug & 1)) {
+            if (sb0 + lsb < nsb && !GEMV_DBG(1)) {
                 const uint32_t sl = ring_sa + slot * slot_bytes;
                 if ((TYPES & TY_Q4K) && (TYPES == TY_Q4K || qt == QT_Q4_K))
                     item_dot<QT_Q4_K, MT>(nsb, sl, cb, sb0, lsb, j, nr, xv, units16, whole, acc, flush_pending);
@@ -611,7 +653,7 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1) stream_kernel(const S
             for (int r = 0; r < R; ++r)
 #pragma unroll
                 for (int m = 0; m < MT; ++m) pend[r][m] = acc[r][m];
-            pend_cell = (p.debug & 32) ? -1 : (g * R) * nchunks + c;
+            pend_cell = GEMV_DBG(32) ? -1 : (g * R) * nchunks + c;
             pend_nr = nr;
             if constexpr (MT > 1) flush_pending();   // several activation rows: registers are scarce, sum at once
             g += step_g;
@@ -630,7 +672,7 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1) stream_kernel(const S
             }
         }
         have_raw = false;
-        if (MT == 1 && !(p.debug & 4)) {
+        if (MT == 1 && !GEMV_DBG(4)) {
             int jn = jb + 1;
             while (jn < p.njobs && p.teams == 2 && jobs_s[jn].team != team) ++jn;
             if (jn < p.njobs) {
@@ -675,11 +717,39 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1) stream_kernel(const S
             }
             ++xe;
         }
-        const int cells = (p.debug & 8) ? 0 : (ge - gb) * R * MT;
+        const bool accum = FUSED && (J.flags & STREAM_JOB_ACCUM) != 0;
+        auto store_out = [&](const StreamSeg &S, long long idx, float v) {
+            if (J.y_is_bf16) {
+                __nv_bfloat16 *yp = reinterpret_cast<__nv_bfloat16 *>(S.y) + idx;
+                *yp = __float2bfloat16_rn(accum ? __bfloat162float(*yp) + v : v);
+            } else {
+                float *yp = reinterpret_cast<float *>(S.y) + idx;
+                *yp = accum ? *yp + v : v;
+            }
+        };
+        if (glu) {
+            // local groups alternate gate, up: output row = silu(gate row) * up row, to the first segment's y
+            const int outs = GEMV_DBG(8) ? 0 : ((ge - gb) >> 1) * R * MT;
+            for (int t = tid; t < outs; t += T) {
+                const int ro = t / MT, m = t - ro * MT;          // ro = local pair * 4 + row in group
+                const int pair = ro / R, r = ro & (R - 1);
+                const int row = ((gb >> 1) + pair) * R + r;
+                if (row < J.seg[0].n && m < p.M) {
+                    float gv = 0.f, uv = 0.f;
+                    const int cg = ((2 * pair) * R + r) * nchunks, cu = ((2 * pair + 1) * R + r) * nchunks;
+                    for (int cc = 0; cc < nchunks; ++cc) {
+                        gv += partial[(cg + cc) * MT + m];
+                        uv += partial[(cu + cc) * MT + m];
+                    }
+                    store_out(J.seg[0], (long long)m * J.seg[0].ldy + row, gv / (1.f + __expf(-gv)) * uv);
+                }
+            }
+        }
+        const int cells = (GEMV_DBG(8) || glu) ? 0 : (ge - gb) * R * MT;
         for (int t = tid; t < cells; t += T) {
             const int rl = t / MT, m = t - rl * MT;      // rl = local group * 4 + row in group
             int sg, lg;
-            locate_group(J, gb + rl / R, sg, lg);
+            locate_group(J, gb + rl / R, sg, lg, false);
             const int row = lg * R + (rl & (R - 1));
             if (row < J.seg[sg].n && m < p.M) {
                 float v = 0.f;
@@ -690,11 +760,7 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1) stream_kernel(const S
                         st_pair(reinterpret_cast<unsigned long long *>(p.peer_base[r] + kPeerFusedSlotOff) + si, v, xe);
                     continue;
                 }
-                const long long idx = (long long)m * J.seg[sg].ldy + row;
-                if (J.y_is_bf16)
-                    reinterpret_cast<__nv_bfloat16 *>(J.seg[sg].y)[idx] = __float2bfloat16_rn(v);
-                else
-                    reinterpret_cast<float *>(J.seg[sg].y)[idx] = v;
+                store_out(J.seg[sg], (long long)m * J.seg[sg].ldy + row, v);
             }
         }
         if (xsum) {
@@ -765,7 +831,7 @@ cudaError_t stream_xprep_launch(const StreamJob *jobs_dev, int njobs, int M, cud
 
 namespace {
 
-template <int MT, int TYPES>
+template <int MT, int TYPES, bool FUSED = false>
 cudaError_t launch_t(const StreamLaunch &a, StreamParams &p, int grid, cudaStream_t st) {
     int warps = a.warps > 0 ? a.warps : kMaxWarps;
     if (warps > kMaxWarps) warps = kMaxWarps;
@@ -777,7 +843,8 @@ cudaError_t launch_t(const StreamLaunch &a, StreamParams &p, int grid, cudaStrea
         const size_t n_isum = J.qt == QT_Q6_K ? J.Kpad / 16 : J.Kpad / 32;
         const size_t per_m = 2 * (size_t)J.Kpad + (J.Kpad / 32) * 4 + n_isum * 4;
         x_bytes = std::max(x_bytes, (MT * per_m + 127) & ~size_t(127));
-        const int groups = (J.total_groups + grid - 1) / grid;
+        int groups = (J.total_groups + grid - 1) / grid;
+        if (J.flags & STREAM_JOB_SWIGLU) groups = 2 * ((J.total_groups / 2 + grid - 1) / grid);
         partial = std::max(partial, (((size_t)groups * R * J.nchunks * MT * 4) + 127) & ~size_t(127));
         stride = std::max(stride, chunk_bytes(J.qt));
     }
@@ -799,7 +866,10 @@ cudaError_t launch_t(const StreamLaunch &a, StreamParams &p, int grid, cudaStrea
     p.depth = depth;
     const size_t smem = fixed + (size_t)warps * depth * R * stride;
 
-    auto kern = stream_kernel<MT, TYPES>;
+    bool fused = false;
+    for (int i = 0; i < a.njobs; ++i) fused = fused || (a.jobs_host[i].flags & (STREAM_JOB_SWIGLU | STREAM_JOB_ACCUM)) != 0;
+    if (fused != FUSED) return launch_t<MT, TYPES, !FUSED>(a, p, grid, st);
+    auto kern = stream_kernel<MT, TYPES, FUSED>;
     static std::atomic<size_t> configured{0};   // per instantiation; a context on another device re-sets it
     static std::atomic<int> configured_dev{-1};  // (contexts on several threads may launch at once)
     int dev = 0;

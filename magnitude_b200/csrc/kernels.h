@@ -30,6 +30,8 @@ constexpr int kStreamMaxSeg = 4;
 enum : int {
     STREAM_JOB_WAITS = 1,       // the job reads what earlier jobs of the launch wrote
     STREAM_JOB_SUM_RANKS = 2,   // the job's outputs are summed over the attached peer ranks inside the launch
+    STREAM_JOB_SWIGLU = 4,      // two segments (gate, up) of equal rows: seg[0].y receives silu(gate x) * (up x)
+    STREAM_JOB_ACCUM = 8,       // the results are added to what the output holds (residual connection)
 };
 
 struct StreamSeg {

@@ -221,11 +221,14 @@ class Backend:
         )
         return outs
 
-    def plan(self, jobs, waits: Sequence[bool] | None = None, sum_ranks: Sequence[bool] | None = None) -> Plan:
+    def plan(self, jobs, waits: Sequence[bool] | None = None, sum_ranks: Sequence[bool] | None = None,
+             swiglu: Sequence[bool] | None = None, accumulate: Sequence[bool] | None = None) -> Plan:
         """jobs: sequence of (weights, x, outs) with weights/outs sequences of equal length (1..4),
-        x a CUDA tensor [M, K] (M <= 4, the same for every job).  waits[i] marks job i as reading
+        x a CUDA tensor [M, K] (M <= 16, the same for every job).  waits[i] marks job i as reading
         what earlier jobs of the plan write; sum_ranks[i] marks job i's outputs as partial sums that
-        the launch adds up over the attached peer ranks (row-parallel projection)."""
+        the launch adds up over the attached peer ranks (row-parallel projection); swiglu[i] marks a
+        job of two weights (gate, up) and ONE output that receives silu(gate x) * (up x);
+        accumulate[i] makes job i add to its outputs (residual connection)."""
         torch = _torch()
         n = len(jobs)
         arr = (B.Job * n)()
@@ -240,6 +243,9 @@ class Backend:
                 m = x.shape[0]
             elif m != x.shape[0]:
                 raise B.B200QError(B.ERR_INVALID_CONFIG, "every job of a plan takes the same number of rows")
+            glu = bool(swiglu and swiglu[i])
+            if glu and len(ws) == 2 and len(outs) == 1:
+                outs = [outs[0], outs[0]]
             if len(ws) != len(outs) or not 1 <= len(ws) <= 4:
                 raise B.B200QError(B.ERR_INVALID_CONFIG, "a job takes 1..4 weights and as many outputs")
             j = arr[i]
@@ -248,7 +254,8 @@ class Backend:
             j.x_dev = x.data_ptr()
             j.ldx = x.stride(0) if m > 1 else max(x.shape[1], 1)
             j.y_dtype = _TORCH_DTYPE[outs[0].dtype]
-            j.flags = (B.JOB_WAITS_FOR_EARLIER if (waits and waits[i]) else 0) | (B.JOB_SUM_RANKS if (sum_ranks and sum_ranks[i]) else 0)
+            j.flags = ((B.JOB_WAITS_FOR_EARLIER if (waits and waits[i]) else 0) | (B.JOB_SUM_RANKS if (sum_ranks and sum_ranks[i]) else 0) |
+                       (B.JOB_SWIGLU if glu else 0) | (B.JOB_ACCUMULATE if (accumulate and accumulate[i]) else 0))
             for k, (w, o) in enumerate(zip(ws, outs)):
                 if o.dim() == 1:
                     o = o.unsqueeze(0)
