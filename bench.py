@@ -467,6 +467,59 @@ def run_b200(args):
         dependent = {"ms_per_step": ms_dep, "value": LAYERS * (2 * algorithmic_bytes(INTER, HIDDEN) + algorithmic_bytes(HIDDEN, INTER)) / (ms_dep * 1e-3) / 1e9,
                      "unit": UNIT, "note": "same step, every down projection flagged as reading what gate/up wrote (one consumer team, grid counter between jobs)"}
         dep_plan.close()
+        # The MLP block as a model runs it: h = silu(gate x) * (up x) in the gate/up job's epilogue, down
+        # reads h and adds into the residual stream x, the next layer's gate/up reads that stream.
+        x_res = torch.empty((1, HIDDEN), dtype=torch.float32, device=dev)
+        h_mid = torch.empty((1, INTER), dtype=torch.float32, device=dev)
+        x0_res = x_h.float()
+
+        def fused_plan(n_layers):
+            fj, fw, fg, fa = [], [], [], []
+            for l in range(n_layers):
+                fj += [([gates[l], ups[l]], x_res, [h_mid]), ([downs[l]], h_mid, [x_res])]
+                fw += [l > 0, True]
+                fg += [True, False]
+                fa += [False, True]
+            return be.plan(fj, waits=fw, swiglu=fg, accumulate=fa)
+
+        fcheck = None
+        if not args.no_check:
+            two = fused_plan(2)
+            x_res.copy_(x0_res)
+            two.run(stream=torch.cuda.current_stream())
+            torch.cuda.synchronize()
+            be.sync()
+            wg_f = gq.dequantize_q4_k(gate_h, HIDDEN).astype(np.float64)
+            wu_f = gq.dequantize_q4_k(up_h, HIDDEN).astype(np.float64)
+            wd_f = gq.dequantize_q4_k(down_h, INTER).astype(np.float64)
+            xr = x0_res.cpu().numpy().astype(np.float64)[0]
+            for _ in range(2):
+                gv, uv = wg_f @ xr, wu_f @ xr
+                xr = xr + wd_f @ (gv / (1.0 + np.exp(-gv)) * uv)
+            del wg_f, wu_f, wd_f
+            got = x_res.cpu().numpy().astype(np.float64)[0]
+            rms = float(np.sqrt(np.mean(xr * xr)))
+            werr = float(np.max(np.abs(got - xr) / (5e-3 * np.maximum(np.abs(xr), rms))))
+            fcheck = {"max_err_over_tol": werr, "ok": bool(werr <= 1.0), "what": "residual stream after two fused layers", "tolerance": "5e-3 (two chained layers)"}
+            two.close()
+        fplan = fused_plan(LAYERS)
+        with torch.cuda.stream(stream):
+            for _ in range(3):
+                fplan.run(stream=stream)
+        stream.synchronize()
+        with torch.cuda.stream(stream):
+            e0.record(stream)
+            for _ in range(reps):
+                fplan.run(stream=stream)
+            e1.record(stream)
+        stream.synchronize()
+        be.sync(stream)
+        ms_f = e0.elapsed_time(e1) / reps
+        dependent["fused_layer"] = {"ms_per_step": ms_f, "value": LAYERS * (2 * algorithmic_bytes(INTER, HIDDEN) + algorithmic_bytes(HIDDEN, INTER)) / (ms_f * 1e-3) / 1e9,
+                                    "unit": UNIT, "check": fcheck,
+                                    "note": "32 chained MLP blocks: SwiGLU in the gate/up job's epilogue, down adds into the residual stream, every job waits for the one before "
+                                            "(timing only beyond the two checked layers: with random weights and no norm the stream's values grow without bound)"}
+        fplan.close()
         with ClockSampler(local_rank) as long_clocks:
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             n_long = 0

@@ -44,6 +44,13 @@ __device__ long long g_gemm_trace[16384];
 
 namespace {
 
+// timing experiments (parts of the pipeline switched off; results invalid) exist only in builds that ask for them
+#ifdef B200Q_TIMING_EXPERIMENTS
+#define PAIR_DBG(bit) (p.debug & (bit))
+#else
+#define PAIR_DBG(bit) (false)
+#endif
+
 constexpr int BM = 128;          // weight rows per tile (MMA M)
 constexpr int BK = 64;           // weights per K-step (one 128-byte swizzle row of fp16)
 constexpr int kAStages = 4;       // dequantized-weight stages: one per unit group, so each group meets every phase of its stage
@@ -442,7 +449,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const GemmParams p
                     const int stage = it % SB_;
                     ok = wait_or_abort<true>(bempty_s + 8 * stage, ((it / SB_) & 1) ^ 1, sm, p.status);
                     if (!ok) break;
-                    if (p.debug & 1) {
+                    if (PAIR_DBG(1)) {
                         mbar_arrive(bfull_s + 8 * stage);
                         continue;
                     }
@@ -464,7 +471,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const GemmParams p
                     const int wb = rs % kWBufs;
                     ok = wait_or_abort<true>(wempty_s + 8 * wb, ((rs / kWBufs) & 1) ^ 1, sm, p.status);
                     if (!ok) break;
-                    if (p.debug & 4) {
+                    if (PAIR_DBG(4)) {
                         mbar_arrive(wfull_s + 8 * wb);
                         continue;
                     }
@@ -515,7 +522,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const GemmParams p
                     }
                     const uint64_t adesc = make_desc_sw128(a_s + sa * kStageABytes);
                     const uint64_t bdesc = make_desc_sw128(b_s + sb * kStageBBytes);
-                    if (!(p.debug & 8))
+                    if (!PAIR_DBG(8))
 #pragma unroll
                         for (int kk = 0; kk < BK / 16; ++kk)   // 16 fp16 = 32 bytes = +2 in the address field
                             umma_f16(d_tmem, adesc + 2 * kk, bdesc + 2 * kk, idesc, (ks | kk) != 0);
@@ -576,13 +583,13 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const GemmParams p
             // the arithmetic happens while the tensor core still reads the stage's previous contents:
             // once the stage is free only the eight stores remain before it can be handed over
             uint32_t o[32];
-            if (!(p.debug & 2)) cur.convert(j, o);
+            if (!PAIR_DBG(2)) cur.convert(j, o);
             const int stage = j;       // K-step 4 rs + j: kAStages == 4, so the group owns this stage
             if (lane == 0) ok = wait_or_abort<true>(aempty_s + 8 * stage, (rs & 1) ^ 1, sm, p.status);
             ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
             if (!ok) break;
-            if (!(p.debug & 2)) store_row(o, a_s + stage * kStageABytes + row_off, r7);
-            if (!(p.debug & 32)) fence_proxy_async();       // generic-proxy stores -> visible to the tensor core's reads
+            if (!PAIR_DBG(2)) store_row(o, a_s + stage * kStageABytes + row_off, r7);
+            if (!PAIR_DBG(32)) fence_proxy_async();       // generic-proxy stores -> visible to the tensor core's reads
             __syncwarp();
             if (lane == 0) mbar_arrive(afull_s + 8 * stage);
             cur = nxt;
@@ -602,7 +609,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const GemmParams p
             const int n = t.tn * BM + q * 32 + lane;
             const int m0 = t.tm * p.bn;
             float *part = p.ksplit > 1 ? p.part + (size_t)(unit % p.ksplit) * p.M * p.N : nullptr;
-            for (int c0 = 0; c0 < ((p.debug & 16) ? 0 : p.bn); c0 += 32) {
+            for (int c0 = 0; c0 < (PAIR_DBG(16) ? 0 : p.bn); c0 += 32) {
                 uint32_t v[32];
                 tmem_ld32(tmem_base + buf * 256 + ((uint32_t)(q * 32) << 16) + c0, v);
                 tmem_ld_wait();
@@ -690,12 +697,6 @@ constexpr int kTsACol0 = 2 * kTsAccCols;            // first A-stage column in T
 // larger packed-record buffers of Q6_K and Q8_0 and the TS form's tensor-memory budget leave four
 // weight stages.  B200Q_PAIR_SA / B200Q_PAIR_SB override Q4_K's split at compile time.
 constexpr int kMaxPairAStages = 8;
-// timing experiments (parts of the pipeline switched off; results invalid) exist only in builds that ask for them
-#ifdef B200Q_TIMING_EXPERIMENTS
-#define PAIR_DBG(bit) (p.debug & (bit))
-#else
-#define PAIR_DBG(bit) (false)
-#endif
 #ifndef B200Q_PAIR_SA
 #define B200Q_PAIR_SA 6
 #define B200Q_PAIR_SB 4
