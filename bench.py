@@ -688,6 +688,15 @@ def run_b200(args):
         cal = line["secondary"].get("calibration")
         if isinstance(cal, dict) and "rows" in cal:
             line["calibration"] = cal["rows"]
+        # a second GPU baseline: the same projections through the vllm package's GGUF mat-vec kernel, in a
+        # process of its own (the package's import is heavy and must not disturb this one)
+        try:
+            out = subprocess.run([sys.executable, os.path.abspath(__file__), "--workload", "library", "--steps", "10", "--warmup", "3"],
+                                 capture_output=True, text=True, timeout=240)
+            rows = [json.loads(l) for l in out.stdout.splitlines() if l.startswith("{")]
+            line["secondary"]["library_arm"] = rows[-1] if rows else {"unavailable": (out.stderr or "no output")[-300:]}
+        except Exception as exc:  # pragma: no cover
+            line["secondary"]["library_arm"] = {"unavailable": f"{type(exc).__name__}: {exc}"[:300]}
     print(json.dumps(mark_diagnostic(line, args)))
     sys.stdout.flush()
     if dist is not None:
@@ -1164,6 +1173,96 @@ def run_layer32b(args, emit=True):
 
 
 # ------------------------------------------------------------------------------------------------
+# library arm: the same decode projections through the GGUF mat-vec kernel of the vllm package in the
+# image (its port of llama.cpp's mmvq kernel: activation re-quantized to Q8_1, integer block dots).
+# Not this repository's code and not the product path: a second GPU baseline beside the CPU arm.
+# ------------------------------------------------------------------------------------------------
+
+def run_library_arm(args, emit=True):
+    import torch
+
+    rank, local_rank, world = dist_env()
+    if world > 1:
+        if rank == 0 and emit:
+            print(json.dumps({"metric": METRIC, "impl": "library", "unavailable": "the library arm is single-GPU"}))
+        return None
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device")
+    try:
+        from vllm import _custom_ops as ops
+        ops.ggml_mul_mat_vec_a8  # noqa: B018
+    except Exception as exc:
+        line = {"metric": METRIC, "impl": "library", "unavailable": f"vllm GGUF ops not usable: {type(exc).__name__}: {exc}"[:300]}
+        if emit:
+            print(json.dumps(line))
+        return line
+    import magnitude_b200 as mb
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    gate_h, up_h, down_h = make_host_layer(encoder=mb.quantize)
+    copies = 8          # 8 x 99 MB of packed weights: more than L2
+
+    def dev_bytes(a):
+        return torch.from_numpy(np.ascontiguousarray(a).view(np.uint8).reshape(a.shape[0], -1)).to(dev)
+
+    layers = [(dev_bytes(gate_h), dev_bytes(up_h), dev_bytes(down_h)) for _ in range(copies)]
+    rng = np.random.default_rng(1)
+    x_h = torch.from_numpy(rng.standard_normal((1, HIDDEN), dtype=np.float32)).to(dev).to(torch.float16)
+    x_i = torch.from_numpy(rng.standard_normal((1, INTER), dtype=np.float32)).to(dev).to(torch.float16)
+    stream = torch.cuda.Stream(device=dev)
+
+    def step():
+        outs = None
+        for g, u, d in layers:
+            outs = (ops.ggml_mul_mat_vec_a8(g, x_h, Q4_K, INTER), ops.ggml_mul_mat_vec_a8(u, x_h, Q4_K, INTER),
+                    ops.ggml_mul_mat_vec_a8(d, x_i, Q4_K, HIDDEN))
+        return outs
+
+    with torch.cuda.stream(stream):
+        for _ in range(max(args.warmup, 3)):
+            outs = step()
+    stream.synchronize()
+    # agreement with the product's own result on one projection, within the 8-bit activation's noise
+    be = mb.Backend(local_rank)
+    w = be.upload(Q4_K, down_h, HIDDEN, INTER)
+    ours = be.project(w, x_i.float())
+    be.sync()
+    a, b = ours.float().cpu().numpy().reshape(-1).astype(np.float64), outs[2].float().cpu().numpy().reshape(-1).astype(np.float64)
+    agree = float(np.sqrt(np.mean((a - b) ** 2)) / np.sqrt(np.mean(a * a)))
+    be.close()
+    graph = torch.cuda.CUDAGraph()
+    try:
+        with torch.cuda.graph(graph, stream=stream):
+            step()
+    except Exception:
+        graph = None
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local_rank) as clocks:
+        with torch.cuda.stream(stream):
+            ev0.record(stream)
+            for _ in range(args.steps):
+                if graph is not None:
+                    graph.replay()
+                else:
+                    step()
+            ev1.record(stream)
+        stream.synchronize()
+    ms = ev0.elapsed_time(ev1) / args.steps
+    bytes_step = copies * (2 * algorithmic_bytes(INTER, HIDDEN, x_bytes=2, y_bytes=2) + algorithmic_bytes(HIDDEN, INTER, x_bytes=2, y_bytes=2))
+    peak, src = peaks()
+    line = {"metric": METRIC, "impl": "library", "value": bytes_step / (ms * 1e-3) / 1e9, "unit": UNIT, "n_gpus": 1, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+            "kernel": "vllm _custom_ops.ggml_mul_mat_vec_a8 (llama.cpp mmvq port; activation re-quantized to Q8_1, fp16 in and out)",
+            "config": {"workload": f"configs[1] shapes, {copies} layer copies per step (gate, up, down), one library call per projection", "cuda_graph": graph is not None},
+            "frac_of_hbm_peak": bytes_step / (ms * 1e-3) / 1e9 / peak, "peak_source": f"of {src}",
+            "rms_difference_to_this_library": agree, "clocks": clocks.summary()}
+    if emit:
+        print(json.dumps(line))
+    return line
+
+
+# ------------------------------------------------------------------------------------------------
 # calibration rows: sustained mat-vec bytes per second and launch cost per block type
 # ------------------------------------------------------------------------------------------------
 
@@ -1253,7 +1352,7 @@ def main():
                     help="skinny workload: smallest M sent to the skinny kernel (default: the library's, 5)")
     ap.add_argument("--quick", action="store_true", help="headline figure only: no dependent / sustained / secondary measurements")
     ap.add_argument("--no-check", action="store_true", help="skip the host check of the step's results")
-    ap.add_argument("--workload", choices=["decode", "prefill", "skinny", "calibration", "layer32b"], default="decode",
+    ap.add_argument("--workload", choices=["decode", "prefill", "skinny", "calibration", "layer32b", "library"], default="decode",
                     help="decode = the headline Q4_K GEMV step; prefill = the M=2048 Q4_K GEMM (secondary line, TFLOP/s)")
     args = ap.parse_args()
     # last resort against a stuck collective or teardown: never hold a GPU box for more than 20 minutes
@@ -1270,6 +1369,8 @@ def main():
         run_calibration(args)
     elif args.workload == "layer32b":
         run_layer32b(args)
+    elif args.workload == "library":
+        run_library_arm(args)
     elif args.impl == "reference":
         run_reference(args)
     else:
