@@ -1257,6 +1257,25 @@ def run_library_arm(args, emit=True):
             "config": {"workload": f"configs[1] shapes, {copies} layer copies per step (gate, up, down), one library call per projection", "cuda_graph": graph is not None},
             "frac_of_hbm_peak": bytes_step / (ms * 1e-3) / 1e9 / peak, "peak_source": f"of {src}",
             "rms_difference_to_this_library": agree, "clocks": clocks.summary()}
+    # the prefill half through the package's mat-mat kernel (llama.cpp's mmq: int8 mma.sync, Q8_1 activations)
+    try:
+        M = 2048
+        xp = torch.from_numpy(np.random.default_rng(2).standard_normal((M, HIDDEN), dtype=np.float32)).to(dev).to(torch.float16)
+        with torch.cuda.stream(stream):
+            for g, _, _ in layers[:3]:
+                ops.ggml_mul_mat_a8(g, xp, Q4_K, INTER)
+            ev0.record(stream)
+            for _ in range(max(2, args.steps // 2)):
+                for g, _, _ in layers:
+                    ops.ggml_mul_mat_a8(g, xp, Q4_K, INTER)
+            ev1.record(stream)
+        stream.synchronize()
+        us = ev0.elapsed_time(ev1) * 1e3 / (max(2, args.steps // 2) * copies)
+        tf = 2.0 * M * INTER * HIDDEN / (us * 1e-6) / 1e12
+        line["prefill"] = {"kernel": "vllm _custom_ops.ggml_mul_mat_a8 (llama.cpp mmq port), Q4_K 14336x4096 x M=2048, fp16 in and out",
+                           "us_per_product": us, "value": tf, "unit": "TFLOP/s"}
+    except Exception as exc:  # pragma: no cover
+        line["prefill"] = {"unavailable": f"{type(exc).__name__}: {exc}"[:200]}
     if emit:
         print(json.dumps(line))
     return line
