@@ -472,15 +472,18 @@ def run_b200(args):
         x_res = torch.empty((1, HIDDEN), dtype=torch.float32, device=dev)
         h_mid = torch.empty((1, INTER), dtype=torch.float32, device=dev)
         x0_res = x_h.float()
+        gamma = torch.from_numpy(np.random.default_rng(7).uniform(0.5, 1.5, HIDDEN).astype(np.float32)).to(dev)
+        norm_eps = 1e-5
 
         def fused_plan(n_layers):
-            fj, fw, fg, fa = [], [], [], []
+            fj, fw, fg, fa, fn = [], [], [], [], []
             for l in range(n_layers):
                 fj += [([gates[l], ups[l]], x_res, [h_mid]), ([downs[l]], h_mid, [x_res])]
                 fw += [l > 0, True]
                 fg += [True, False]
                 fa += [False, True]
-            return be.plan(fj, waits=fw, swiglu=fg, accumulate=fa)
+                fn += [gamma, None]                       # RMSNorm of the stream on the gate/up job's load
+            return be.plan(fj, waits=fw, swiglu=fg, accumulate=fa, norms=fn, norm_eps=norm_eps)
 
         fcheck = None
         if not args.no_check:
@@ -493,8 +496,10 @@ def run_b200(args):
             wu_f = gq.dequantize_q4_k(up_h, HIDDEN).astype(np.float64)
             wd_f = gq.dequantize_q4_k(down_h, INTER).astype(np.float64)
             xr = x0_res.cpu().numpy().astype(np.float64)[0]
+            gam = gamma.cpu().numpy().astype(np.float64)
             for _ in range(2):
-                gv, uv = wg_f @ xr, wu_f @ xr
+                xn = xr / np.sqrt(np.mean(xr * xr) + norm_eps) * gam
+                gv, uv = wg_f @ xn, wu_f @ xn
                 xr = xr + wd_f @ (gv / (1.0 + np.exp(-gv)) * uv)
             del wg_f, wu_f, wd_f
             got = x_res.cpu().numpy().astype(np.float64)[0]
@@ -517,8 +522,8 @@ def run_b200(args):
         ms_f = e0.elapsed_time(e1) / reps
         dependent["fused_layer"] = {"ms_per_step": ms_f, "value": LAYERS * (2 * algorithmic_bytes(INTER, HIDDEN) + algorithmic_bytes(HIDDEN, INTER)) / (ms_f * 1e-3) / 1e9,
                                     "unit": UNIT, "check": fcheck,
-                                    "note": "32 chained MLP blocks: SwiGLU in the gate/up job's epilogue, down adds into the residual stream, every job waits for the one before "
-                                            "(timing only beyond the two checked layers: with random weights and no norm the stream's values grow without bound)"}
+                                    "note": "32 chained MLP blocks: RMSNorm on the gate/up job's activation load, SwiGLU in its epilogue, down adds into the "
+                                            "residual stream, every job waits for the one before"}
         fplan.close()
         with ClockSampler(local_rank) as long_clocks:
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)

@@ -331,6 +331,13 @@ typedef struct b200q_job {
     int64_t ldy[4];
     int32_t y_dtype;          /* B200Q_TYPE_F32 or B200Q_TYPE_BF16 */
     int32_t flags;            /* B200Q_JOB_* */
+    /* RMSNorm fused into the activation load: when norm_weight is not NULL the job multiplies
+     * x_norm[m][k] = x[m][k] * rsqrt(mean_k(x[m][k]^2) + norm_eps) * norm_weight[k] (fp32 arithmetic;
+     * norm_weight = K floats in device memory) instead of x: the normalisation llama-style models
+     * apply before QKV and before gate/up.  Streaming plans only (M <= 4). */
+    const float *norm_weight;
+    float norm_eps;
+    int32_t reserved;         /* 0 */
 } b200q_job;
 
 b200q_status b200q_plan_create(b200q_ctx *ctx, const b200q_job *jobs, int32_t n_jobs, int64_t M,

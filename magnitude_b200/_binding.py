@@ -50,6 +50,9 @@ class Job(ctypes.Structure):
         ("ldy", c_int64 * 4),
         ("y_dtype", c_int32),
         ("flags", c_int32),
+        ("norm_weight", c_void_p),
+        ("norm_eps", ctypes.c_float),
+        ("reserved", c_int32),
     ]
 
 

@@ -957,13 +957,13 @@ b200q_status b200q_plan_create(b200q_ctx *ctx, const b200q_job *jobs, int32_t n_
     pl->M = (int)M;
     bool rank_sums = false;      // ... or another epilogue only the streaming kernel has
     for (int i = 0; i < n_jobs; ++i)
-        rank_sums |= (jobs[i].flags & (B200Q_JOB_SUM_RANKS | B200Q_JOB_SWIGLU | B200Q_JOB_ACCUMULATE)) != 0;
+        rank_sums |= (jobs[i].flags & (B200Q_JOB_SUM_RANKS | B200Q_JOB_SWIGLU | B200Q_JOB_ACCUMULATE)) != 0 || jobs[i].norm_weight != nullptr;
     // 3 or more rows run on the skinny kernel, like single calls; plans that add partial sums over
     // ranks inside the launch stay on the streaming kernel (up to 4 rows)
     if (M > gemv_max_m() || (M >= ctx->skinny_min_m && !rank_sums)) {
         if (rank_sums) {
             delete pl;
-            return fail(ctx, B200Q_ERR_INVALID_CONFIG, "rank sums, SWIGLU and ACCUMULATE jobs need a streaming plan (M <= %d)", gemv_max_m());
+            return fail(ctx, B200Q_ERR_INVALID_CONFIG, "rank sums, SWIGLU, ACCUMULATE and fused-norm jobs need a streaming plan (M <= %d)", gemv_max_m());
         }
         s = plan_create_skinny(ctx, pl, jobs, n_jobs, (int)M);
         if (s != B200Q_OK) {
@@ -1014,6 +1014,14 @@ b200q_status b200q_plan_create(b200q_ctx *ctx, const b200q_job *jobs, int32_t n_
         if (j.flags & B200Q_JOB_ACCUMULATE) jflags |= STREAM_JOB_ACCUM;
         StreamJob J;
         fill_job(J, j.w, j.n_weights, j.x_dev, j.x_dtype, j.ldx, j.y_dev, j.y_dtype, j.ldy, jflags);
+        if (j.norm_weight) {
+            if (!(j.norm_eps >= 0.f) || (reinterpret_cast<uintptr_t>(j.norm_weight) & 3)) {
+                delete pl;
+                return fail(ctx, B200Q_ERR_INVALID_CONFIG, "job %d: norm_weight must be 4-byte aligned and norm_eps >= 0", i);
+            }
+            J.gamma = j.norm_weight;
+            J.norm_eps = j.norm_eps;
+        }
         pl->jobs.push_back(J);
     }
     if (pl->jobs.size() >= 2 && ctx->gemv_xprep) {

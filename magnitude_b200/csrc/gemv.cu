@@ -430,6 +430,8 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1) stream_kernel(const S
         XSrc xs;
         xs.x = Jx.x; xs.ldx = Jx.ldx; xs.x_is_bf16 = Jx.x_is_bf16; xs.x_vec_ok = Jx.x_vec_ok;
         xs.K = Jx.K; xs.Kpad = Jx.Kpad;
+        xs.gamma = FUSED ? Jx.gamma : nullptr;
+        xs.rs = 1.f;
         return xs;
     };
 
@@ -536,9 +538,23 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1) stream_kernel(const S
         const bool pre_x = J.xq != nullptr && !GEMV_DBG(2);
         XView xv[MT];
         {
-            const XSrc xs = job_xsrc(J);
+            XSrc xs = job_xsrc(J);
+            const bool norm = FUSED && xs.gamma != nullptr && !pre_x;
 #pragma unroll
             for (int m = 0; m < MT; ++m) {
+                if (norm && m < p.M) {
+                    // RMSNorm on the load: the team adds up the row's squares first (partials through the
+                    // partial-sum table, which no item of this job has touched yet)
+                    float ss = row_square_share(xs, m, tid, T);
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o);
+                    team_sync(team, T);
+                    if (lane == 0) partial[twarp] = ss;
+                    team_sync(team, T);
+                    float tot = 0.f;
+                    for (int w = 0; w < tcw; ++w) tot += partial[w];
+                    xs.rs = rsqrtf(tot / (float)xs.K + J.norm_eps);
+                }
                 uint8_t *b = xbase + m * per_m;
                 float *sxp = reinterpret_cast<float *>(b + 2 * plane);
                 int *isp = reinterpret_cast<int *>(b + 2 * plane + (J.Kpad >> 5) * 4);
@@ -548,12 +564,12 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1) stream_kernel(const S
                 xv[m].isum = smem_u32(isp);
                 if (m < p.M && !GEMV_DBG(4) && !pre_x) {
                     const bool q6 = (TYPES & TY_Q6K) && (TYPES == TY_Q6K || qt == QT_Q6_K);
-                    if (MT == 1 && have_raw) {
+                    if (MT == 1 && have_raw && !norm) {
                         if (q6) prep_from_raw<QT_Q6_K>(xs, tid, T, xraw, b, b + plane, sxp, isp, units16);
                         else if (TYPES & ~TY_Q6K) prep_from_raw<QT_Q4_K>(xs, tid, T, xraw, b, b + plane, sxp, isp, units16);
                     } else {
-                        if (q6) prep_row<QT_Q6_K>(xs, m, tid, T, b, b + plane, sxp, isp, units16);
-                        else if (TYPES & ~TY_Q6K) prep_row<QT_Q4_K>(xs, m, tid, T, b, b + plane, sxp, isp, units16);
+                        if (q6) prep_row<QT_Q6_K, FUSED>(xs, m, tid, T, b, b + plane, sxp, isp, units16);
+                        else if (TYPES & ~TY_Q6K) prep_row<QT_Q4_K, FUSED>(xs, m, tid, T, b, b + plane, sxp, isp, units16);
                     }
                 }
             }
@@ -678,7 +694,7 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1) stream_kernel(const S
             if (jn < p.njobs) {
                 const StreamJob &Jn = jobs_s[jn];
                 const XSrc xn = job_xsrc(Jn);
-                if (!(Jn.flags & STREAM_JOB_WAITS) && !Jn.xq && prep_can_prefetch(xn, T)) {
+                if (!(Jn.flags & STREAM_JOB_WAITS) && !Jn.xq && !xn.gamma && prep_can_prefetch(xn, T)) {
                     prep_prefetch(xn, tid, T, xraw);
                     have_raw = true;
                 }
@@ -802,6 +818,9 @@ __global__ void __launch_bounds__(256) xprep_kernel(const StreamJob *jobs, int M
     XSrc xs;
     xs.x = J.x; xs.ldx = J.ldx; xs.x_is_bf16 = J.x_is_bf16; xs.x_vec_ok = J.x_vec_ok;
     xs.K = J.K; xs.Kpad = J.Kpad;
+    xs.gamma = J.gamma;
+    xs.rs = 1.f;
+    __shared__ float warp_ss[8];
     const int units16 = (J.Kpad >> 6) * 16, plane = J.Kpad;
     const int n_isum = (J.qt == QT_Q6_K) ? (J.Kpad >> 4) : (J.Kpad >> 5);
     const int per_m = 2 * plane + (J.Kpad >> 5) * 4 + n_isum * 4;
@@ -810,8 +829,20 @@ __global__ void __launch_bounds__(256) xprep_kernel(const StreamJob *jobs, int M
         uint8_t *b = const_cast<uint8_t *>(J.xq) + (size_t)m * per_m;
         float *sxp = reinterpret_cast<float *>(b + 2 * plane);
         int *isp = reinterpret_cast<int *>(b + 2 * plane + (J.Kpad >> 5) * 4);
-        if (J.qt == QT_Q6_K) prep_row<QT_Q6_K>(xs, m, tid, T, b, b + plane, sxp, isp, units16);
-        else prep_row<QT_Q4_K>(xs, m, tid, T, b, b + plane, sxp, isp, units16);
+        if (xs.gamma) {
+            // RMSNorm on the load: every block of the job adds up the whole row's squares itself
+            float ss = row_square_share(xs, m, threadIdx.x, blockDim.x);
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o);
+            __syncthreads();
+            if ((threadIdx.x & 31) == 0) warp_ss[threadIdx.x >> 5] = ss;
+            __syncthreads();
+            float tot = 0.f;
+            for (int w = 0; w < (int)(blockDim.x >> 5); ++w) tot += warp_ss[w];
+            xs.rs = rsqrtf(tot / (float)xs.K + J.norm_eps);
+        }
+        if (J.qt == QT_Q6_K) prep_row<QT_Q6_K, true>(xs, m, tid, T, b, b + plane, sxp, isp, units16);
+        else prep_row<QT_Q4_K, true>(xs, m, tid, T, b, b + plane, sxp, isp, units16);
     }
 }
 
@@ -867,7 +898,8 @@ cudaError_t launch_t(const StreamLaunch &a, StreamParams &p, int grid, cudaStrea
     const size_t smem = fixed + (size_t)warps * depth * R * stride;
 
     bool fused = false;
-    for (int i = 0; i < a.njobs; ++i) fused = fused || (a.jobs_host[i].flags & (STREAM_JOB_SWIGLU | STREAM_JOB_ACCUM)) != 0;
+    for (int i = 0; i < a.njobs; ++i)
+        fused = fused || (a.jobs_host[i].flags & (STREAM_JOB_SWIGLU | STREAM_JOB_ACCUM)) != 0 || a.jobs_host[i].gamma != nullptr;
     if (fused != FUSED) return launch_t<MT, TYPES, !FUSED>(a, p, grid, st);
     auto kern = stream_kernel<MT, TYPES, FUSED>;
     static std::atomic<size_t> configured{0};   // per instantiation; a context on another device re-sets it

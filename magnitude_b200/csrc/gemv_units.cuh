@@ -13,7 +13,27 @@ struct XSrc {
     int x_is_bf16;
     int x_vec_ok;       // rows are 16-byte aligned: vector loads allowed
     int K, Kpad;
+    const float *gamma; // RMSNorm weight [K] applied on the load (with `rs`), or null
+    float rs;           // 1 / sqrt(mean(x^2) + eps) of the row being converted
 };
+
+// sum of squares of this thread's share of activation row m (threads tid of T take 8 elements in turn)
+__device__ __forceinline__ void load_x8(const XSrc &p, int m, int k0, float (&v)[8]);
+__device__ __forceinline__ float row_square_share(const XSrc &p, int m, int tid, int T) {
+    float ss = 0.f;
+    for (int k0 = tid * 8; k0 < p.K; k0 += T * 8) {
+        float v[8];
+        load_x8(p, m, k0, v);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) ss = fmaf(v[i], v[i], ss);       // elements beyond K load as zero
+    }
+    return ss;
+}
+// x * rs * gamma for 8 loaded elements starting at k0
+__device__ __forceinline__ void norm_x8(const XSrc &p, int k0, float (&v)[8]) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = (k0 + i < p.K) ? v[i] * p.rs * p.gamma[k0 + i] : 0.f;
+}
 
 // byte offset, inside one byte plane of the fixed-point activation, of the 16-byte group that
 // holds element k.  Groups are stored [c][unit][16] so a lane's four 16-byte reads of one
@@ -285,7 +305,7 @@ __device__ __forceinline__ void prep_store8(const float (&v)[8], int k0, uint8_t
 
 // Threads tid = 0 .. T-1 (whole warps) convert activation row m.  Loads are issued four deep before any is used so a
 // long row costs one trip to L2, not one per 8 * T elements.
-template <int QT>
+template <int QT, bool NORM = false>
 __device__ __forceinline__ void prep_row(const XSrc &p, int m, int tid, int T, uint8_t *xh, uint8_t *xl,
                                          float *sx, int *isum, int units16) {
     constexpr int PB = 4;
@@ -297,7 +317,10 @@ __device__ __forceinline__ void prep_row(const XSrc &p, int m, int tid, int T, u
             if (base + b * stride < p.Kpad) load_x8(p, m, base + b * stride, v[b]);
 #pragma unroll
         for (int b = 0; b < PB; ++b)
-            if (base + b * stride < p.Kpad) prep_store8<QT>(v[b], base + b * stride, xh, xl, sx, isum, units16);
+            if (base + b * stride < p.Kpad) {
+                if (NORM && p.gamma) norm_x8(p, base + b * stride, v[b]);
+                prep_store8<QT>(v[b], base + b * stride, xh, xl, sx, isum, units16);
+            }
     }
 }
 

@@ -56,6 +56,8 @@ struct StreamJob {
     int x_is_bf16, x_vec_ok, y_is_bf16;
     int flags;                         // STREAM_JOB_*
     int team;                          // which half of the consumer warps runs the job (see stream_assign_teams)
+    const float *gamma;                // RMSNorm weight [K]: the activation is normalised on the load (null = none)
+    float norm_eps;
     const uint8_t *xq;                 // device buffer for the activation in fixed point, filled by stream_xprep_launch
                                        // before the streaming launch (stream_xq_bytes); null = converted inside the kernel
 };

@@ -222,13 +222,15 @@ class Backend:
         return outs
 
     def plan(self, jobs, waits: Sequence[bool] | None = None, sum_ranks: Sequence[bool] | None = None,
-             swiglu: Sequence[bool] | None = None, accumulate: Sequence[bool] | None = None) -> Plan:
+             swiglu: Sequence[bool] | None = None, accumulate: Sequence[bool] | None = None,
+             norms: Sequence | None = None, norm_eps: float = 1e-5) -> Plan:
         """jobs: sequence of (weights, x, outs) with weights/outs sequences of equal length (1..4),
         x a CUDA tensor [M, K] (M <= 16, the same for every job).  waits[i] marks job i as reading
         what earlier jobs of the plan write; sum_ranks[i] marks job i's outputs as partial sums that
         the launch adds up over the attached peer ranks (row-parallel projection); swiglu[i] marks a
         job of two weights (gate, up) and ONE output that receives silu(gate x) * (up x);
-        accumulate[i] makes job i add to its outputs (residual connection)."""
+        accumulate[i] makes job i add to its outputs (residual connection); norms[i], when not None,
+        is a float32 CUDA tensor [K]: job i multiplies RMSNorm(x) * norms[i] instead of x."""
         torch = _torch()
         n = len(jobs)
         arr = (B.Job * n)()
@@ -262,7 +264,13 @@ class Backend:
                 j.w[k] = w._h.value
                 j.y_dev[k] = o.data_ptr()
                 j.ldy[k] = o.stride(0) if m > 1 else max(o.shape[1], 1)
-            keep.append((list(ws), x, list(outs)))
+            gamma = norms[i] if norms else None
+            if gamma is not None:
+                if gamma.dtype != torch.float32 or gamma.numel() != x.shape[1] or not gamma.is_contiguous():
+                    raise B.B200QError(B.ERR_INVALID_CONFIG, "a norm weight is a contiguous float32 tensor of K elements")
+                j.norm_weight = gamma.data_ptr()
+                j.norm_eps = norm_eps
+            keep.append((list(ws), x, list(outs), gamma))
         out = c_void_p()
         self._check(B.lib().b200q_plan_create(self._h, arr, n, m or 1, byref(out)))
         return Plan(self, out.value, keep)

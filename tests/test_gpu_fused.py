@@ -72,6 +72,32 @@ def test_accumulate_job(backend, orc, m):
         assert np.all(np.abs(y.cpu().numpy() - want) <= _bound(y0.cpu().numpy().astype(np.float64), 1e-3))
 
 
+def _rmsnorm(x, gamma, eps):
+    x = x.astype(np.float64)
+    return x / np.sqrt(np.mean(x * x, axis=-1, keepdims=True) + eps) * gamma.astype(np.float64)
+
+
+@pytest.mark.parametrize("qt", [mb.TYPE_Q4_K, mb.TYPE_Q6_K, mb.TYPE_Q8_0])
+@pytest.mark.parametrize("m,n,k,x_dtype", [(1, 512, 4096, torch.bfloat16), (2, 300, 2304, torch.float32), (4, 64, 256, torch.bfloat16)])
+def test_rmsnorm_on_the_activation_load(backend, orc, qt, m, n, k, x_dtype):
+    p = _weights(orc, qt, n, k, seed=n)
+    w = backend.upload(qt, p, n, k)
+    rng = np.random.default_rng(k + m)
+    x = (torch.from_numpy(rng.standard_normal((m, k), dtype=np.float32)) * 3.0).cuda().to(x_dtype)
+    gamma = torch.from_numpy(rng.uniform(0.5, 1.5, k).astype(np.float32)).cuda()
+    eps = 1e-5
+    ref = orc.matmul_exact(qt, p, n, k, _rmsnorm(x.float().cpu().numpy(), gamma.cpu().numpy(), eps).astype(np.float32))
+    y_img, y_in, mid, other = (torch.empty((m, n), device="cuda") for _ in range(4))
+    # two independent jobs: the activation prep launch normalises; a job that waits converts inside the kernel
+    backend.plan([([w], x, [y_img]), ([w], x, [other])], norms=[gamma, None], norm_eps=eps).run()
+    backend.plan([([w], x, [mid]), ([w], x, [y_in])], waits=[False, True], norms=[None, gamma], norm_eps=eps).run()
+    backend.sync()
+    for got in (y_img, y_in):
+        g = got.cpu().numpy().astype(np.float64)
+        assert np.all(np.abs(g - ref) <= _bound(ref, 1e-3))
+    assert torch.equal(other, mid)            # the job without a norm weight is untouched by its neighbour's
+
+
 @pytest.mark.parametrize("m", [1, 2])
 def test_dependent_mlp_layer(backend, orc, m):
     """gate/up -> silu * -> down -> residual, two layers chained through the residual stream."""
@@ -91,12 +117,14 @@ def test_dependent_mlp_layer(backend, orc, m):
         waits += [len(jobs) > 2, True]          # the next layer reads the stream the previous down wrote
         glu += [True, False]
         acc += [False, True]
-    plan = backend.plan(jobs, waits=waits, swiglu=glu, accumulate=acc)
+    gammas = [torch.from_numpy(np.random.default_rng(40 + l).uniform(0.5, 1.5, hdim).astype(np.float32)).cuda() for l in range(2)]
+    norms = [gammas[i // 2] if i % 2 == 0 else None for i in range(len(jobs))]      # pre-norm before gate/up
+    plan = backend.plan(jobs, waits=waits, swiglu=glu, accumulate=acc, norms=norms, norm_eps=1e-6)
     plan.run()
     backend.sync()
     ref = x0.astype(np.float64)
-    for g, u, d in layers:
-        xin = ref.astype(np.float32)
+    for l, (g, u, d) in enumerate(layers):
+        xin = _rmsnorm(ref, gammas[l].cpu().numpy(), 1e-6).astype(np.float32)
         h = _silu_mul(orc.matmul_exact(mb.TYPE_Q4_K, g, idim, hdim, xin), orc.matmul_exact(mb.TYPE_Q4_K, u, idim, hdim, xin))
         ref = ref + orc.matmul_exact(mb.TYPE_Q6_K, d, hdim, idim, h.astype(np.float32))
     got = xs.cpu().numpy().astype(np.float64)
