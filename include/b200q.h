@@ -62,6 +62,7 @@ enum {
     B200Q_TYPE_F32 = 0,
     B200Q_TYPE_Q8_0 = 8,
     B200Q_TYPE_Q4_K = 12,
+    B200Q_TYPE_Q5_K = 13,
     B200Q_TYPE_Q6_K = 14,
     B200Q_TYPE_BF16 = 30
 };

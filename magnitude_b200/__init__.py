@@ -16,6 +16,7 @@ from ._binding import (  # noqa: F401
     TYPE_BF16,
     TYPE_F32,
     TYPE_Q4_K,
+    TYPE_Q5_K,
     TYPE_Q6_K,
     TYPE_Q8_0,
 )

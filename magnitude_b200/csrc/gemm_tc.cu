@@ -259,6 +259,42 @@ template <> struct Unit<QT_Q4_K> {
     }
 };
 
+// Q5_K: the device record is the Q4_K record followed by the 32 bytes of fifth bits (bit s of byte l =
+// weight l of sub-block s); a level 0..31 still fits the byte trick, so both halves of the unit go
+// through the 0x64 form.
+template <> struct Unit<QT_Q5_K> {
+    uint4 hdr, q0, q1, h0, h1;
+    __device__ __forceinline__ void load(uint32_t rec, uint32_t, int j) {
+        hdr = lds128(rec);
+        q0 = lds128(rec + 16 + 32 * j);
+        q1 = lds128(rec + 32 + 32 * j);
+        h0 = lds128(rec + 144);
+        h1 = lds128(rec + 160);
+    }
+    __device__ __forceinline__ void convert(int j, uint32_t (&o)[32]) const {
+        int sa, ma, sb, mb;
+        q4k_scale_min(hdr.y, hdr.z, hdr.w, 2 * j, sa, ma);
+        q4k_scale_min(hdr.y, hdr.z, hdr.w, 2 * j + 1, sb, mb);
+        const float d = half_bits_to_float(hdr.x), dmin = half_bits_to_float(hdr.x >> 16);
+        __half2 o_lo, s_lo, c_lo, o_hi, s_hi, c_hi;
+        centered(d * (float)sa, dmin * (float)ma, as_h2(0x64006400u), o_lo, s_lo, c_lo);
+        centered(d * (float)sb, dmin * (float)mb, as_h2(0x64006400u), o_hi, s_hi, c_hi);
+        const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+        const uint32_t f[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
+#pragma unroll
+        for (int n = 0; n < 4; ++n) {     // chunk n = weights 8n..8n+7 of sub-block 2j; chunk 4 + n = those of sub-block 2j + 1
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const uint32_t fb = f[2 * n + i] >> (2 * j);
+                const uint32_t lo = (w[2 * n + i] & 0x0F0F0F0Fu) | ((fb & 0x01010101u) << 4);
+                const uint32_t hi = ((w[2 * n + i] >> 4) & 0x0F0F0F0Fu) | ((fb & 0x02020202u) << 3);
+                word_affine<0x64>(lo, o_lo, s_lo, c_lo, o[4 * n + 2 * i], o[4 * n + 2 * i + 1]);
+                word_affine<0x64>(hi, o_hi, s_hi, c_hi, o[16 + 4 * n + 2 * i], o[16 + 4 * n + 2 * i + 1]);
+            }
+        }
+    }
+};
+
 template <> struct Unit<QT_Q8_0> {
     uint4 q[4];
     uint32_t dd;
@@ -701,7 +737,7 @@ constexpr int kMaxPairAStages = 8;
 #define B200Q_PAIR_SA 6
 #define B200Q_PAIR_SB 4
 #endif
-__host__ __device__ constexpr int pair_a_stages(int qt, bool ts) { return (!ts && qt == QT_Q4_K) ? B200Q_PAIR_SA : 4; }
+__host__ __device__ constexpr int pair_a_stages(int qt, bool ts) { return (!ts && (qt == QT_Q4_K || qt == QT_Q5_K)) ? B200Q_PAIR_SA : 4; }
 __host__ __device__ constexpr int pair_b_rows(bool ts) { return ts ? 96 : 128; }       // tokens each CTA stages per K-step
 __host__ __device__ constexpr int pair_b_stage_bytes(bool ts = false) { return ((pair_b_rows(ts) * BK * 2 + 1023) / 1024) * 1024; }
 __host__ __device__ constexpr int pair_b_stages(int qt, bool ts = false) { return ts ? 8 : qt == QT_Q8_0 ? 5 : qt == QT_Q6_K ? 6 : B200Q_PAIR_SB; }
@@ -1445,6 +1481,7 @@ cudaError_t gemm_launch(const GemmLaunch &a, cudaStream_t st) {
         const int grid2 = 2 * std::min(p.pair_tiles, a.sm_count / 2);
         switch (a.qt) {
         case QT_Q4_K: return use_ts ? launch_gemm_pair<QT_Q4_K, true>(p, maps, grid2, st) : launch_gemm_pair<QT_Q4_K, false>(p, maps, grid2, st);
+        case QT_Q5_K: return use_ts ? launch_gemm_pair<QT_Q5_K, true>(p, maps, grid2, st) : launch_gemm_pair<QT_Q5_K, false>(p, maps, grid2, st);
         case QT_Q6_K: return use_ts ? launch_gemm_pair<QT_Q6_K, true>(p, maps, grid2, st) : launch_gemm_pair<QT_Q6_K, false>(p, maps, grid2, st);
         case QT_Q8_0: return use_ts ? launch_gemm_pair<QT_Q8_0, true>(p, maps, grid2, st) : launch_gemm_pair<QT_Q8_0, false>(p, maps, grid2, st);
         default: return cudaErrorInvalidValue;
@@ -1454,6 +1491,7 @@ cudaError_t gemm_launch(const GemmLaunch &a, cudaStream_t st) {
     cudaError_t e;
     switch (a.qt) {
     case QT_Q4_K: e = launch_gemm<QT_Q4_K>(p, maps, grid, st); break;
+    case QT_Q5_K: e = launch_gemm<QT_Q5_K>(p, maps, grid, st); break;
     case QT_Q6_K: e = launch_gemm<QT_Q6_K>(p, maps, grid, st); break;
     case QT_Q8_0: e = launch_gemm<QT_Q8_0>(p, maps, grid, st); break;
     default: return cudaErrorInvalidValue;

@@ -83,7 +83,7 @@ template <int QT> struct XRegs {
         } else {
             const uint2 s = lds64(xv.sx + gu * 8);
             sx[0] = __uint_as_float(s.x); sx[1] = __uint_as_float(s.y);
-            if (QT == QT_Q4_K) {
+            if (QT == QT_Q4_K || QT == QT_Q5_K) {
                 const uint2 i = lds64(xv.isum + gu * 8);
                 is[0] = (int)i.x; is[1] = (int)i.y;
             }
@@ -140,6 +140,61 @@ template <> struct WRegs<QT_Q4_K> {
         }
         const float fa = (float)((hA * 256 + lA) * scA);
         const float fb = (float)(((hB * 256 + lB) >> 4) * scB);   // hi held 16 * nibble: exact shift
+        const float ua = (float)(mnA * xr.is[0]);
+        const float ub = (float)(mnB * xr.is[1]);
+        return xr.sx[0] * (d * fa - dmin * ua) + xr.sx[1] * (d * fb - dmin * ub);
+    }
+};
+
+// Q5_K record on the device: the Q4_K fields, then the 32 bytes of fifth bits (bit s of byte l belongs
+// to weight l of sub-block s).  Levels 0..31 sit one per byte, so both sub-blocks use plain dp4a.
+template <> struct WRegs<QT_Q5_K> {
+    uint32_t lo[8], hi[8];
+    int scA, mnA, scB, mnB;
+    float d, dmin;
+    __device__ __forceinline__ void load(uint32_t rec, int j) {
+        const uint4 hdr = lds128(rec);
+        const uint4 qa = lds128(rec + 16 + 32 * j);
+        const uint4 qb = lds128(rec + 32 + 32 * j);
+        const uint4 ha = lds128(rec + 144);
+        const uint4 hb = lds128(rec + 160);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint32_t a = word_of(qa, i), b = word_of(qb, i);
+            const uint32_t fa = word_of(ha, i) >> (2 * j), fb = word_of(hb, i) >> (2 * j);
+            lo[i] = (a & 0x0F0F0F0Fu) | ((fa & 0x01010101u) << 4);
+            hi[i] = ((a >> 4) & 0x0F0F0F0Fu) | ((fa & 0x02020202u) << 3);
+            lo[4 + i] = (b & 0x0F0F0F0Fu) | ((fb & 0x01010101u) << 4);
+            hi[4 + i] = ((b >> 4) & 0x0F0F0F0Fu) | ((fb & 0x02020202u) << 3);
+        }
+        const int sh = 16 * (j & 1);
+        const uint32_t y2 = (hdr.y >> sh) & 0xFFFFu, z2 = (hdr.z >> sh) & 0xFFFFu, w2 = (hdr.w >> sh) & 0xFFFFu;
+        const uint32_t sc_lo = y2 & 0x3F3Fu, mn_lo = z2 & 0x3F3Fu;
+        const uint32_t sc_hi = (w2 & 0x0F0Fu) | ((y2 >> 2) & 0x3030u);
+        const uint32_t mn_hi = ((w2 >> 4) & 0x0F0Fu) | ((z2 >> 2) & 0x3030u);
+        const uint32_t sc2 = (j >= 2) ? sc_hi : sc_lo, mn2 = (j >= 2) ? mn_hi : mn_lo;
+        scA = sc2 & 0xFF;
+        scB = sc2 >> 8;
+        mnA = mn2 & 0xFF;
+        mnB = mn2 >> 8;
+        d = half_bits_to_float(hdr.x);
+        dmin = half_bits_to_float(hdr.x >> 16);
+    }
+    __device__ __forceinline__ float dot(const XRegs<QT_Q5_K> &xr) const {
+        int hA = 0, lA = 0, hB = 0, lB = 0;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            hA = dp4a_us(lo[i], word_of(xr.h[0], i), hA);
+            lA = dp4a_us(lo[i], word_of(xr.l[0], i), lA);
+            hA = dp4a_us(lo[4 + i], word_of(xr.h[1], i), hA);
+            lA = dp4a_us(lo[4 + i], word_of(xr.l[1], i), lA);
+            hB = dp4a_us(hi[i], word_of(xr.h[2], i), hB);
+            lB = dp4a_us(hi[i], word_of(xr.l[2], i), lB);
+            hB = dp4a_us(hi[4 + i], word_of(xr.h[3], i), hB);
+            lB = dp4a_us(hi[4 + i], word_of(xr.l[3], i), lB);
+        }
+        const float fa = (float)((hA * 256 + lA) * scA);
+        const float fb = (float)((hB * 256 + lB) * scB);
         const float ua = (float)(mnA * xr.is[0]);
         const float ub = (float)(mnB * xr.is[1]);
         return xr.sx[0] * (d * fa - dmin * ua) + xr.sx[1] * (d * fb - dmin * ub);

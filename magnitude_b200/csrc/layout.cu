@@ -16,6 +16,12 @@ void repack_host(int qt, int64_t K, const uint8_t *gguf, int64_t r0, int64_t n, 
             uint8_t *rec = dst + record_off(qt, r, sb, n, nsb);
             if (qt == QT_Q4_K) {
                 memcpy(rec, s + (sb0 + sb) * 144, 144);
+            } else if (qt == QT_Q5_K) {
+                // [d dmin scales | nibbles | fifth bits]: the first 144 bytes read like a Q4_K record
+                const uint8_t *blk = s + (sb0 + sb) * 176;
+                memcpy(rec, blk, 16);
+                memcpy(rec + 16, blk + 48, 128);
+                memcpy(rec + 144, blk + 16, 32);
             } else if (qt == QT_Q8_0) {
                 const int64_t nblk = K / 32;
                 for (int b = 0; b < 8; ++b) {
@@ -49,14 +55,15 @@ __global__ void __launch_bounds__(256) dequant_kernel(const uint8_t *__restrict_
     const int64_t k = (int64_t)sb * 256 + t;
     if (k >= K) return;
     float v;
-    if (QT == QT_Q4_K) {
+    if (QT == QT_Q4_K || QT == QT_Q5_K) {
         const uint8_t *rec = w + record_off(QT, row, sb, N, nsb);
         const uint32_t *hw = reinterpret_cast<const uint32_t *>(rec);
         const float d = half_bits_to_float(hw[0]), dmin = half_bits_to_float(hw[0] >> 16);
         int sc, mn;
         q4k_scale_min(hw[1], hw[2], hw[3], t >> 5, sc, mn);
         const uint8_t byte = rec[16 + 32 * (t >> 6) + (t & 31)];
-        const int q = (t & 32) ? (byte >> 4) : (byte & 0xF);
+        int q = (t & 32) ? (byte >> 4) : (byte & 0xF);
+        if (QT == QT_Q5_K) q += ((rec[144 + (t & 31)] >> (t >> 5)) & 1) << 4;      // bit j of byte l: sub-block j, weight l
         const float d1 = __fmul_rn(d, (float)sc);
         const float m1 = __fmul_rn(dmin, (float)mn);
         v = __fsub_rn(__fmul_rn(d1, (float)q), m1);
@@ -88,6 +95,7 @@ cudaError_t dequant_launch(int qt, const uint8_t *w, int64_t N, int64_t K, int64
     if (blocks > 0x7FFFFFFF) return cudaErrorInvalidValue;
     switch (qt) {
     case QT_Q4_K: dequant_kernel<QT_Q4_K><<<(unsigned)blocks, 256, 0, st>>>(w, N, K, nsb, out); break;
+    case QT_Q5_K: dequant_kernel<QT_Q5_K><<<(unsigned)blocks, 256, 0, st>>>(w, N, K, nsb, out); break;
     case QT_Q8_0: dequant_kernel<QT_Q8_0><<<(unsigned)blocks, 256, 0, st>>>(w, N, K, nsb, out); break;
     case QT_Q6_K: dequant_kernel<QT_Q6_K><<<(unsigned)blocks, 256, 0, st>>>(w, N, K, nsb, out); break;
     default: return cudaErrorInvalidValue;

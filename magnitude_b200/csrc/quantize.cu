@@ -1,4 +1,4 @@
-// The format's reference quantizer, fp32 -> Q8_0 / Q4_K / Q6_K (host code, threads over rows):
+// The format's reference quantizer, fp32 -> Q8_0 / Q4_K / Q5_K / Q6_K (host code, threads over rows):
 // what a model converter runs once per tensor (reference row "quantizer fp32 -> blocks", upstream of
 // LlamaModel::load_from_file, inference/crates/icn-engine/src/lib.rs:972).  Restated from the
 // published algorithm of the GGUF reference implementation: Q8_0 takes d = max|w| / 127; Q4_K fits
@@ -91,7 +91,8 @@ void row_q8_0(const float *x, uint8_t *y, int64_t k) {
 // ---- Q4_K: [fp16 d][fp16 dmin][12 bytes of 6-bit scales and minima][128 bytes of nibbles] ---------
 // weighted fit of x ~ scale * L + min over levels L in 0..nmax with min <= 0; returns the scale,
 // *neg_min = -min
-float fit_affine(int n, int nmax, const float *x, const float *wt, uint8_t *L, float *neg_min, uint8_t *Ltry) {
+float fit_affine(int n, int nmax, const float *x, const float *wt, uint8_t *L, float *neg_min, uint8_t *Ltry,
+                 float rmin = -1.f, float rdelta = 0.1f, int nstep = 20) {
     float lo = x[0], hi = x[0], sw = wt[0], sx = wt[0] * x[0];
     for (int i = 1; i < n; ++i) {
         lo = std::min(lo, x[i]);
@@ -112,8 +113,8 @@ float fit_affine(int n, int nmax, const float *x, const float *wt, uint8_t *L, f
         const float diff = scale * L[i] + lo - x[i];
         best += wt[i] * (diff * diff);
     }
-    for (int step = 0; step <= 20; ++step) {
-        iscale = (-1.f + 0.1f * step + nmax) / (hi - lo);
+    for (int step = 0; step <= nstep; ++step) {
+        iscale = (rmin + rdelta * step + nmax) / (hi - lo);
         float sl = 0, sl2 = 0, sxl = 0;
         for (int i = 0; i < n; ++i) {
             const int l = std::min(nmax, std::max(0, nearest_int(iscale * (x[i] - lo))));
@@ -156,17 +157,22 @@ void scale_min_6bit(int j, const uint8_t *q, int *sc, int *mn) {
     }
 }
 
-void row_q4_k(const float *x, uint8_t *y, int64_t k) {
+// Q5_K is the same scheme with 32 levels: [d][dmin][scales 12][32 bytes of fifth bits][128 bytes of nibbles];
+// its sub-block search runs over iscale = (-0.5 + 0.1 step + 31) / range, step 0..15.
+template <int NMAX>
+void row_q45_k(const float *x, uint8_t *y, int64_t k) {
+    constexpr int kBlock = NMAX == 15 ? 144 : 176;
     uint8_t L[256], Ltry[32];
     float wt[32], mins[8], scales[8];
-    for (int64_t b = 0; b < k / 256; ++b, x += 256, y += 144) {
+    for (int64_t b = 0; b < k / 256; ++b, x += 256, y += kBlock) {
         float max_scale = 0, max_min = 0;
         for (int j = 0; j < 8; ++j) {
             float sum2 = 0;
             for (int l = 0; l < 32; ++l) sum2 += x[32 * j + l] * x[32 * j + l];
             const float av = sqrtf(sum2 / 32);
             for (int l = 0; l < 32; ++l) wt[l] = av + fabsf(x[32 * j + l]);
-            scales[j] = fit_affine(32, 15, x + 32 * j, wt, L + 32 * j, &mins[j], Ltry);
+            scales[j] = NMAX == 15 ? fit_affine(32, 15, x + 32 * j, wt, L + 32 * j, &mins[j], Ltry)
+                                   : fit_affine(32, 31, x + 32 * j, wt, L + 32 * j, &mins[j], Ltry, -0.5f, 0.1f, 15);
             max_scale = std::max(max_scale, scales[j]);
             max_min = std::max(max_min, mins[j]);
         }
@@ -196,13 +202,26 @@ void row_q4_k(const float *x, uint8_t *y, int64_t k) {
             const float d = fd * sc;
             if (!d) continue;      // keeps the levels of the per-sub-block search
             const float dm = fm * mn;
-            for (int i = 0; i < 32; ++i) L[32 * j + i] = (uint8_t)std::min(15, std::max(0, nearest_int((x[32 * j + i] + dm) / d)));
+            for (int i = 0; i < 32; ++i) L[32 * j + i] = (uint8_t)std::min(NMAX, std::max(0, nearest_int((x[32 * j + i] + dm) / d)));
         }
-        uint8_t *q = y + 16;
-        for (int j = 0; j < 256; j += 64, q += 32)
-            for (int l = 0; l < 32; ++l) q[l] = (uint8_t)(L[j + l] | (L[j + l + 32] << 4));
+        if (NMAX == 15) {
+            uint8_t *q = y + 16;
+            for (int j = 0; j < 256; j += 64, q += 32)
+                for (int l = 0; l < 32; ++l) q[l] = (uint8_t)(L[j + l] | (L[j + l + 32] << 4));
+        } else {
+            uint8_t *qh = y + 16, *q = y + 48;
+            memset(qh, 0, 32);
+            for (int j = 0, bit = 0; j < 256; j += 64, q += 32, bit += 2)
+                for (int l = 0; l < 32; ++l) {
+                    const int l1 = L[j + l], l2 = L[j + l + 32];
+                    qh[l] |= (uint8_t)(((l1 >> 4) << bit) | ((l2 >> 4) << (bit + 1)));
+                    q[l] = (uint8_t)((l1 & 15) | ((l2 & 15) << 4));
+                }
+        }
     }
 }
+void row_q4_k(const float *x, uint8_t *y, int64_t k) { row_q45_k<15>(x, y, k); }
+void row_q5_k(const float *x, uint8_t *y, int64_t k) { row_q45_k<31>(x, y, k); }
 
 // ---- Q6_K: [128 low nibbles][64 bytes of high bit pairs][16 int8 scales][fp16 d] ---------------------
 // symmetric fit x ~ scale * l, l in -nmax..nmax-1, weights x^2; stores l + nmax
@@ -285,8 +304,8 @@ void row_q6_k(const float *x, uint8_t *y, int64_t k) {
 extern "C" b200q_status b200q_quantize(int32_t type, const float *weights, int64_t N, int64_t K, void *packed_out, size_t out_bytes,
                                        int32_t threads) {
     const int64_t want = b200q_tensor_storage_bytes(type, N < 0 || K < 0 ? -1 : N * K);
-    if ((type != B200Q_TYPE_Q8_0 && type != B200Q_TYPE_Q4_K && type != B200Q_TYPE_Q6_K) || N < 0 || K < 0) return B200Q_ERR_INVALID_CONFIG;
-    const int64_t blk = type == B200Q_TYPE_Q8_0 ? 32 : 256, bb = type == B200Q_TYPE_Q8_0 ? 34 : type == B200Q_TYPE_Q4_K ? 144 : 210;
+    if ((type != B200Q_TYPE_Q8_0 && type != B200Q_TYPE_Q4_K && type != B200Q_TYPE_Q5_K && type != B200Q_TYPE_Q6_K) || N < 0 || K < 0) return B200Q_ERR_INVALID_CONFIG;
+    const int64_t blk = type == B200Q_TYPE_Q8_0 ? 32 : 256, bb = type == B200Q_TYPE_Q8_0 ? 34 : type == B200Q_TYPE_Q4_K ? 144 : type == B200Q_TYPE_Q5_K ? 176 : 210;
     if (K % blk || want < 0 || (int64_t)out_bytes != want) return B200Q_ERR_INVALID_CONFIG;
     if (N * K == 0) return B200Q_OK;
     if (!weights || !packed_out) return B200Q_ERR_INVALID_CONFIG;
@@ -299,6 +318,7 @@ extern "C" b200q_status b200q_quantize(int32_t type, const float *weights, int64
             uint8_t *y = reinterpret_cast<uint8_t *>(packed_out) + r * rb;
             if (type == B200Q_TYPE_Q8_0) row_q8_0(x, y, K);
             else if (type == B200Q_TYPE_Q4_K) row_q4_k(x, y, K);
+            else if (type == B200Q_TYPE_Q5_K) row_q5_k(x, y, K);
             else row_q6_k(x, y, K);
         }
     };

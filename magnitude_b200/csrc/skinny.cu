@@ -63,7 +63,7 @@ constexpr int kRedDepth = 4;                      // partial-tile sets in flight
 // shared-memory distance between the rows of a stage: the chunk's bytes per row, padded so that the
 // 8 rows a fragment load touches start 32 bytes apart modulo 128 (Q6_K reads 4-byte words and is
 // conflict-free at its natural 1680)
-__host__ __device__ constexpr int sk_row_stride(int qt) { return qt == QT_Q4_K ? 1184 : qt == QT_Q8_0 ? 2208 : 1680; }
+__host__ __device__ constexpr int sk_row_stride(int qt) { return qt == QT_Q4_K ? 1184 : qt == QT_Q5_K ? 1440 : qt == QT_Q8_0 ? 2208 : 1680; }
 __host__ __device__ constexpr int sk_subblocks(int qt) { return qt == QT_Q6_K ? 16 : 8; }   // scale blocks per record
 
 struct SkJob {
@@ -214,6 +214,67 @@ template <int NT> struct SkRecord<QT_Q4_K, NT> {
                     if (h) ra >>= 4, rb >>= 4;
                     const uint32_t a0 = pair02<0x43004300u>(ra), a2 = pair02<0x43004300u>(ra >> 8);
                     const uint32_t a1 = pair02<0x43004300u>(rb), a3 = pair02<0x43004300u>(rb >> 8);
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt) {
+                        const int bi = ((nt * 8 + sb) * 2 + s) * 2;
+                        if (s == 0) mma_first(c[q][nt], a0, a1, a2, a3, B[bi], B[bi + 1]);
+                        else mma_more(c[q][nt], a0, a1, a2, a3, B[bi], B[bi + 1]);
+                    }
+                }
+            }
+#pragma unroll
+            for (int q = 0; q < QB; ++q) {
+                const int sb = b0 + q;
+                const float2 pa = ldsn_f2(sct + (sb * kSkRows + g) * 8), pb = ldsn_f2(sct + (sb * kSkRows + g + 8) * 8);
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) fold(acc[nt], c[q][nt], pa, pb, ldsn_f2(xst + ((sb * NT + nt) * 8 + 2 * t) * 4));
+            }
+        }
+    }
+};
+
+// Q5_K: the Q4_K record followed by 32 bytes of fifth bits; levels 0..31 still sit exactly in the bf16 form 128 + q
+template <int NT> struct SkRecord<QT_Q5_K, NT> {
+    static constexpr int QB = 8 / NT;
+    // lane L prepares row L >> 1, sub-blocks 4 (L & 1) .. + 3: p = d sc, q = 128 p + dmin m
+    static __device__ __forceinline__ void scales(uint32_t rec_row, uint32_t, int lane, uint32_t sct) {
+        const int row = lane >> 1, half = lane & 1;
+        const uint4 hdr = ldsn128(rec_row);
+        const float d = half_bits_to_float(hdr.x), dmin = half_bits_to_float(hdr.x >> 16);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int sb = 4 * half + i;
+            int sc, mn;
+            q4k_scale_min(hdr.y, hdr.z, hdr.w, sb, sc, mn);
+            const float p = d * (float)sc;
+            sts_f2(sct + (sb * kSkRows + row) * 8, p, -fmaf(128.f, p, dmin * (float)mn));
+        }
+    }
+    static __device__ __forceinline__ void run(uint32_t recA, uint32_t recB, int g, int t, const uint32_t (&B)[32 * NT],
+                                               uint32_t sct, uint32_t xst, float (&acc)[NT][4]) {
+        uint2 wa[4], wb[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            wa[j] = ldsn64(recA + 16 + 32 * j + 8 * t);
+            wb[j] = ldsn64(recB + 16 + 32 * j + 8 * t);
+        }
+        // fifth bits of this lane's eight positions: bit sb of a byte belongs to sub-block sb
+        const uint2 fa = ldsn64(recA + 144 + 8 * t), fb = ldsn64(recB + 144 + 8 * t);
+#pragma unroll
+        for (int b0 = 0; b0 < 8; b0 += QB) {
+            float c[QB][NT][4];
+#pragma unroll
+            for (int s = 0; s < 2; ++s) {
+#pragma unroll
+                for (int q = 0; q < QB; ++q) {
+                    const int sb = b0 + q, j = sb >> 1, h = sb & 1;
+                    uint32_t ra = s ? wa[j].y : wa[j].x, rb = s ? wb[j].y : wb[j].x;
+                    if (h) ra >>= 4, rb >>= 4;
+                    const uint32_t ha = (s ? fa.y : fa.x) >> sb, hb = (s ? fb.y : fb.x) >> sb;
+                    const uint32_t a0 = pair02<0x43004300u>(ra) | ((ha & 0x00010001u) << 4);
+                    const uint32_t a2 = pair02<0x43004300u>(ra >> 8) | (((ha >> 8) & 0x00010001u) << 4);
+                    const uint32_t a1 = pair02<0x43004300u>(rb) | ((hb & 0x00010001u) << 4);
+                    const uint32_t a3 = pair02<0x43004300u>(rb >> 8) | (((hb >> 8) & 0x00010001u) << 4);
 #pragma unroll
                     for (int nt = 0; nt < NT; ++nt) {
                         const int bi = ((nt * 8 + sb) * 2 + s) * 2;
@@ -866,6 +927,8 @@ cudaError_t skinny_set_launch(const SkinnySet *set, cudaStream_t st) {
     switch (set->qt * 4 + set->NT) {
     case QT_Q4_K * 4 + 1: e = sk_launch_t<QT_Q4_K, 1>(set->p, set->grid, set->smem_limit, st); break;
     case QT_Q4_K * 4 + 2: e = sk_launch_t<QT_Q4_K, 2>(set->p, set->grid, set->smem_limit, st); break;
+    case QT_Q5_K * 4 + 1: e = sk_launch_t<QT_Q5_K, 1>(set->p, set->grid, set->smem_limit, st); break;
+    case QT_Q5_K * 4 + 2: e = sk_launch_t<QT_Q5_K, 2>(set->p, set->grid, set->smem_limit, st); break;
     case QT_Q6_K * 4 + 1: e = sk_launch_t<QT_Q6_K, 1>(set->p, set->grid, set->smem_limit, st); break;
     case QT_Q6_K * 4 + 2: e = sk_launch_t<QT_Q6_K, 2>(set->p, set->grid, set->smem_limit, st); break;
     case QT_Q8_0 * 4 + 1: e = sk_launch_t<QT_Q8_0, 1>(set->p, set->grid, set->smem_limit, st); break;

@@ -11,8 +11,8 @@ from __future__ import annotations
 
 import numpy as np
 
-Q8_0, Q4_K, Q6_K = 8, 12, 14
-BLOCK = {Q8_0: (32, 34), Q4_K: (256, 144), Q6_K: (256, 210)}
+Q8_0, Q4_K, Q5_K, Q6_K = 8, 12, 13, 14
+BLOCK = {Q8_0: (32, 34), Q4_K: (256, 144), Q5_K: (256, 176), Q6_K: (256, 210)}
 
 
 def _check(w: np.ndarray, blk: int) -> np.ndarray:
@@ -121,6 +121,29 @@ def dequantize_q4_k(packed: np.ndarray, k: int) -> np.ndarray:
     return ((dl[..., None] * q).astype(np.float32) - ml[..., None]).astype(np.float32).reshape(n, k)
 
 
+def dequantize_q5_k(packed: np.ndarray, k: int) -> np.ndarray:
+    """fp32 [N, K] of Q5_K blocks: the Q4_K rule with levels nibble + 16 * (bit s of qh[l]) for sub-block s."""
+    rows = np.ascontiguousarray(packed, dtype=np.uint8).reshape(-1, k // 256, 176)
+    n, nb = rows.shape[:2]
+    d = rows[..., 0:2].copy().view(np.float16).astype(np.float32)[..., 0]
+    dmin = rows[..., 2:4].copy().view(np.float16).astype(np.float32)[..., 0]
+    sc = rows[..., 4:16]
+    ls = np.empty((n, nb, 8), np.uint8)
+    lm = np.empty((n, nb, 8), np.uint8)
+    ls[..., 0:4] = sc[..., 0:4] & 63
+    lm[..., 0:4] = sc[..., 4:8] & 63
+    ls[..., 4:8] = (sc[..., 8:12] & 0xF) | ((sc[..., 0:4] >> 6) << 4)
+    lm[..., 4:8] = (sc[..., 8:12] >> 4) | ((sc[..., 4:8] >> 6) << 4)
+    qh = rows[..., 16:48]                                       # [n, nb, 32]
+    qs = rows[..., 48:].reshape(n, nb, 4, 32)
+    nib = np.stack([qs & 0xF, qs >> 4], axis=3).reshape(n, nb, 8, 32)
+    hb = (qh[:, :, None, :] >> np.arange(8, dtype=np.uint8)[None, None, :, None]) & 1
+    q = (nib + 16 * hb).astype(np.float32)
+    dl = (d[..., None] * ls.astype(np.float32)).astype(np.float32)
+    ml = (dmin[..., None] * lm.astype(np.float32)).astype(np.float32)
+    return ((dl[..., None] * q).astype(np.float32) - ml[..., None]).astype(np.float32).reshape(n, k)
+
+
 def dequantize_q6_k(packed: np.ndarray, k: int) -> np.ndarray:
     """fp32 [N, K] of Q6_K blocks: w = (d * sc) * (q - 32), the product d * sc rounded to fp32 first."""
     rows = np.ascontiguousarray(packed, dtype=np.uint8).reshape(-1, k // 256, 210)
@@ -142,6 +165,8 @@ def dequantize_q6_k(packed: np.ndarray, k: int) -> np.ndarray:
 def dequantize(qtype: int, packed: np.ndarray, k: int) -> np.ndarray:
     if qtype == Q4_K:
         return dequantize_q4_k(packed, k)
+    if qtype == Q5_K:
+        return dequantize_q5_k(packed, k)
     if qtype == Q6_K:
         return dequantize_q6_k(packed, k)
     raise ValueError(f"no numpy decoder for ggml type id {qtype}")

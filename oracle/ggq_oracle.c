@@ -1,5 +1,5 @@
 /*
- * CPU oracle for the GGUF block-quantized projection matmul (Q8_0 / Q4_K / Q6_K).
+ * CPU oracle for the GGUF block-quantized projection matmul (Q8_0 / Q4_K / Q5_K / Q6_K).
  *
  * TEST INFRASTRUCTURE ONLY.  Nothing in the shipped library links, loads or calls this
  * file; it exists so the tests, the smoke check and the bench's CPU-baseline leg have an
@@ -11,20 +11,21 @@
  * (pinned in inference/native-pin.toml:3-14).  That source tree is an un-vendored submodule
  * and is not available, and the reference holds no golden vector for a quantized matmul.
  * What this file restates is the published ggml block-format algorithm of that dependency:
- *   - block layouts block_q8_0 / block_q4_K / block_q6_K / block_q8_K,
- *   - dequantize_row_{q8_0,q4_K,q6_K},
- *   - the reference quantizers quantize_row_{q8_0,q4_K,q6_K}_ref and their helpers
+ *   - block layouts block_q8_0 / block_q4_K / block_q5_K / block_q6_K / block_q8_K,
+ *   - dequantize_row_{q8_0,q4_K,q5_K,q6_K},
+ *   - the reference quantizers quantize_row_{q8_0,q4_K,q5_K,q6_K}_ref and their helpers
  *     make_qkx2_quants / make_qx_quants,
  *   - the CPU backend's MUL_MAT strategy: quantize the activation row to Q8_0 (for Q8_0
  *     weights) or Q8_K (for K-quants), integer block dots, fp32 scale-and-accumulate.
  * It is pinned instead against the independent `gguf` Python package (dequantize for all
- * three types, quantize for Q8_0) through the fixtures under tests/golden/.
+ * four types, quantize for Q8_0) through the fixtures under tests/golden/.
  *
  * Floating-point contract for dequantization (bit-exact target of the CUDA path):
  *   fp16 -> fp32 exact; every product and difference is a separately rounded fp32
  *   operation, no fused multiply-add (build with -ffp-contract=off):
  *     Q8_0:  w = d * q
  *     Q4_K:  w = (d * sc) * q - (dmin * m)
+ *     Q5_K:  w = (d * sc) * q - (dmin * m)   with q = nibble + 16 * high bit
  *     Q6_K:  w = (d * sc) * q         with q in [-32, 31]
  *
  * Build: see oracle/Makefile (gcc -O3 -ffp-contract=off -fopenmp).
@@ -43,12 +44,14 @@
 #define K_SCALE_SIZE 12
 #define GROUP_MAX_EPS 1e-15f
 
-enum { GGQ_TYPE_Q8_0 = 8, GGQ_TYPE_Q4_K = 12, GGQ_TYPE_Q6_K = 14 };
+enum { GGQ_TYPE_Q8_0 = 8, GGQ_TYPE_Q4_K = 12, GGQ_TYPE_Q5_K = 13, GGQ_TYPE_Q6_K = 14 };
 
 #pragma pack(push, 1)
 typedef struct { uint16_t d; int8_t qs[QK8_0]; } blk_q8_0;                 /* 34 B  */
 typedef struct { uint16_t d; uint16_t dmin; uint8_t scales[K_SCALE_SIZE];
                  uint8_t qs[QK_K / 2]; } blk_q4_K;                          /* 144 B */
+typedef struct { uint16_t d; uint16_t dmin; uint8_t scales[K_SCALE_SIZE];
+                 uint8_t qh[QK_K / 8]; uint8_t qs[QK_K / 2]; } blk_q5_K;           /* 176 B */
 typedef struct { uint8_t ql[QK_K / 2]; uint8_t qh[QK_K / 4];
                  int8_t scales[QK_K / 16]; uint16_t d; } blk_q6_K;          /* 210 B */
 typedef struct { float d; int8_t qs[QK_K]; int16_t bsums[QK_K / 16]; } blk_q8_K; /* activation */
@@ -56,6 +59,7 @@ typedef struct { float d; int8_t qs[QK_K]; int16_t bsums[QK_K / 16]; } blk_q8_K;
 
 _Static_assert(sizeof(blk_q8_0) == 34, "q8_0 size");
 _Static_assert(sizeof(blk_q4_K) == 144, "q4_K size");
+_Static_assert(sizeof(blk_q5_K) == 176, "q5_K size");
 _Static_assert(sizeof(blk_q6_K) == 210, "q6_K size");
 _Static_assert(sizeof(blk_q8_K) == 4 + 256 + 32, "q8_K size");
 
@@ -147,12 +151,13 @@ void ggq_f16_to_f32(const uint16_t *src, float *dst, int64_t n) {
 /* ------------------------------------------------------------------ sizes */
 
 int64_t ggq_block_elems(int type) {
-    return type == GGQ_TYPE_Q8_0 ? QK8_0 : (type == GGQ_TYPE_Q4_K || type == GGQ_TYPE_Q6_K) ? QK_K : 0;
+    return type == GGQ_TYPE_Q8_0 ? QK8_0 : (type == GGQ_TYPE_Q4_K || type == GGQ_TYPE_Q5_K || type == GGQ_TYPE_Q6_K) ? QK_K : 0;
 }
 int64_t ggq_block_bytes(int type) {
     switch (type) {
     case GGQ_TYPE_Q8_0: return sizeof(blk_q8_0);
     case GGQ_TYPE_Q4_K: return sizeof(blk_q4_K);
+    case GGQ_TYPE_Q5_K: return sizeof(blk_q5_K);
     case GGQ_TYPE_Q6_K: return sizeof(blk_q6_K);
     default: return 0;
     }
@@ -218,6 +223,34 @@ static void dequant_row_q4_K(const blk_q4_K *x, float *y, int64_t k) {
     }
 }
 
+/* ggml dequantize_row_q5_K: the fifth bit of sub-block j's weight l is bit j of qh[l] */
+static void dequant_row_q5_K(const blk_q5_K *x, float *y, int64_t k) {
+    int64_t nb = k / QK_K;
+    for (int64_t i = 0; i < nb; ++i) {
+        const uint8_t *ql = x[i].qs;
+        const uint8_t *qh = x[i].qh;
+        float d = f16_to_f32(x[i].d);
+        float dmin = f16_to_f32(x[i].dmin);
+        int is = 0;
+        uint8_t sc, m;
+        uint8_t u1 = 1, u2 = 2;
+        for (int j = 0; j < QK_K; j += 64) {
+            get_scale_min_k4(is + 0, x[i].scales, &sc, &m);
+            float d1 = d * (float)sc;
+            float m1 = dmin * (float)m;
+            get_scale_min_k4(is + 1, x[i].scales, &sc, &m);
+            float d2 = d * (float)sc;
+            float m2 = dmin * (float)m;
+            for (int l = 0; l < 32; ++l) *y++ = d1 * (float)((ql[l] & 0xF) + ((qh[l] & u1) ? 16 : 0)) - m1;
+            for (int l = 0; l < 32; ++l) *y++ = d2 * (float)((ql[l] >> 4) + ((qh[l] & u2) ? 16 : 0)) - m2;
+            ql += 32;
+            is += 2;
+            u1 <<= 2;
+            u2 <<= 2;
+        }
+    }
+}
+
 static void dequant_row_q6_K(const blk_q6_K *x, float *y, int64_t k) {
     int64_t nb = k / QK_K;
     for (int64_t i = 0; i < nb; ++i) {
@@ -260,6 +293,7 @@ int ggq_dequantize(int type, const void *packed, float *out, int64_t n_rows, int
         float *y = out + r * k;
         if (type == GGQ_TYPE_Q8_0) dequant_row_q8_0((const blk_q8_0 *)row, y, k);
         else if (type == GGQ_TYPE_Q4_K) dequant_row_q4_K((const blk_q4_K *)row, y, k);
+        else if (type == GGQ_TYPE_Q5_K) dequant_row_q5_K((const blk_q5_K *)row, y, k);
         else dequant_row_q6_K((const blk_q6_K *)row, y, k);
     }
     return 0;
@@ -412,6 +446,77 @@ static void quant_row_q4_K(const float *x, blk_q4_K *y, int64_t k) {
     }
 }
 
+/* ggml quantize_row_q5_K_ref: the Q4_K scheme with 32 levels (search make_qkx2_quants(32, 31, ..., -0.5, 0.1, 15)) */
+static void quant_row_q5_K(const float *x, blk_q5_K *y, int64_t k) {
+    int64_t nb = k / QK_K;
+    uint8_t L[QK_K];
+    uint8_t Laux[32];
+    float weights[32];
+    float mins[QK_K / 32];
+    float scales[QK_K / 32];
+    for (int64_t i = 0; i < nb; ++i) {
+        float max_scale = 0, max_min = 0;
+        for (int j = 0; j < QK_K / 32; ++j) {
+            float sum_x2 = 0;
+            for (int l = 0; l < 32; ++l) sum_x2 += x[32 * j + l] * x[32 * j + l];
+            float av_x = sqrtf(sum_x2 / 32);
+            for (int l = 0; l < 32; ++l) weights[l] = av_x + fabsf(x[32 * j + l]);
+            scales[j] = make_qkx2_quants(32, 31, x + 32 * j, weights, L + 32 * j, &mins[j], Laux,
+                                         -0.5f, 0.1f, 15, 0);
+            if (scales[j] > max_scale) max_scale = scales[j];
+            if (mins[j] > max_min) max_min = mins[j];
+        }
+        float inv_scale = max_scale > 0 ? 63.f / max_scale : 0.f;
+        float inv_min = max_min > 0 ? 63.f / max_min : 0.f;
+        memset(y[i].scales, 0, K_SCALE_SIZE);
+        for (int j = 0; j < QK_K / 32; ++j) {
+            int ls = nearest_int(inv_scale * scales[j]);
+            int lm = nearest_int(inv_min * mins[j]);
+            ls = ls > 63 ? 63 : ls;
+            lm = lm > 63 ? 63 : lm;
+            if (j < 4) {
+                y[i].scales[j] = (uint8_t)ls;
+                y[i].scales[j + 4] = (uint8_t)lm;
+            } else {
+                y[i].scales[j + 4] = (uint8_t)((ls & 0xF) | ((lm & 0xF) << 4));
+                y[i].scales[j - 4] |= (uint8_t)((ls >> 4) << 6);
+                y[i].scales[j - 0] |= (uint8_t)((lm >> 4) << 6);
+            }
+        }
+        y[i].d = f32_to_f16(max_scale / 63.f);
+        y[i].dmin = f32_to_f16(max_min / 63.f);
+        uint8_t sc, m;
+        for (int j = 0; j < QK_K / 32; ++j) {
+            get_scale_min_k4(j, y[i].scales, &sc, &m);
+            float d = f16_to_f32(y[i].d) * sc;
+            if (!d) continue;
+            float dm = f16_to_f32(y[i].dmin) * m;
+            for (int ii = 0; ii < 32; ++ii) {
+                int l = nearest_int((x[32 * j + ii] + dm) / d);
+                l = l < 0 ? 0 : l > 31 ? 31 : l;
+                L[32 * j + ii] = (uint8_t)l;
+            }
+        }
+        uint8_t *qh = y[i].qh;
+        uint8_t *ql = y[i].qs;
+        memset(qh, 0, QK_K / 8);
+        uint8_t m1 = 1, m2 = 2;
+        for (int n = 0; n < QK_K; n += 64) {
+            for (int j = 0; j < 32; ++j) {
+                int l1 = L[n + j];
+                if (l1 > 15) { l1 -= 16; qh[j] |= m1; }
+                int l2 = L[n + j + 32];
+                if (l2 > 15) { l2 -= 16; qh[j] |= m2; }
+                ql[j] = (uint8_t)(l1 | (l2 << 4));
+            }
+            m1 <<= 2;
+            m2 <<= 2;
+            ql += 32;
+        }
+        x += QK_K;
+    }
+}
+
 static float make_qx_quants(int n, int nmax, const float *x, int8_t *L, int rmse_type) {
     float max = 0, amax = 0;
     for (int i = 0; i < n; ++i) {
@@ -524,6 +629,7 @@ int ggq_quantize(int type, const float *src, void *packed, int64_t n_rows, int64
         const float *x = src + r * k;
         if (type == GGQ_TYPE_Q8_0) quant_row_q8_0(x, (blk_q8_0 *)row, k);
         else if (type == GGQ_TYPE_Q4_K) quant_row_q4_K(x, (blk_q4_K *)row, k);
+        else if (type == GGQ_TYPE_Q5_K) quant_row_q5_K(x, (blk_q5_K *)row, k);
         else quant_row_q6_K(x, (blk_q6_K *)row, k);
     }
     return 0;
@@ -546,6 +652,7 @@ int ggq_matmul_exact(int type, const void *packed, int64_t n, int64_t k, const f
             const void *row = p + r * rb;
             if (type == GGQ_TYPE_Q8_0) dequant_row_q8_0((const blk_q8_0 *)row, wf, k);
             else if (type == GGQ_TYPE_Q4_K) dequant_row_q4_K((const blk_q4_K *)row, wf, k);
+            else if (type == GGQ_TYPE_Q5_K) dequant_row_q5_K((const blk_q5_K *)row, wf, k);
             else dequant_row_q6_K((const blk_q6_K *)row, wf, k);
             for (int64_t t = 0; t < m; ++t) {
                 const float *xr = x + t * ldx;
@@ -653,6 +760,50 @@ static float vec_dot_q4_K_q8_K(int64_t k, const blk_q4_K *x, const blk_q8_K *y) 
     return sumf;
 }
 
+/* ggml_vec_dot_q5_K_q8_K (generic path): as Q4_K with the fifth bit added to the unpacked levels */
+static float vec_dot_q5_K_q8_K(int64_t k, const blk_q5_K *x, const blk_q8_K *y) {
+    int64_t nb = k / QK_K;
+    float sums[8] = {0};
+    float sumf = 0;
+    int8_t aux8[QK_K];
+    for (int64_t i = 0; i < nb; ++i) {
+        const uint8_t *q4 = x[i].qs;
+        const uint8_t *hm = x[i].qh;
+        const int8_t *q8 = y[i].qs;
+        int8_t *a = aux8;
+        uint8_t m = 1;
+        for (int j = 0; j < QK_K / 64; ++j) {
+            for (int l = 0; l < 32; ++l) a[l] = (int8_t)((q4[l] & 0xF) + ((hm[l] & m) ? 16 : 0));
+            a += 32;
+            m <<= 1;
+            for (int l = 0; l < 32; ++l) a[l] = (int8_t)((q4[l] >> 4) + ((hm[l] & m) ? 16 : 0));
+            a += 32;
+            m <<= 1;
+            q4 += 32;
+        }
+        uint8_t sc[8], mn[8];
+        for (int j = 0; j < 8; ++j) get_scale_min_k4(j, x[i].scales, &sc[j], &mn[j]);
+        int sumi = 0;
+        for (int j = 0; j < QK_K / 16; ++j) sumi += y[i].bsums[j] * mn[j / 2];
+        int32_t aux32[8] = {0};
+        a = aux8;
+        for (int j = 0; j < QK_K / 32; ++j) {
+            int32_t scale = sc[j];
+            for (int c = 0; c < 4; ++c) {
+                for (int l = 0; l < 8; ++l) aux32[l] += scale * ((int)q8[l] * (int)a[l]);
+                q8 += 8;
+                a += 8;
+            }
+        }
+        float d = f16_to_f32(x[i].d) * y[i].d;
+        for (int l = 0; l < 8; ++l) sums[l] += d * aux32[l];
+        float dmin = f16_to_f32(x[i].dmin) * y[i].d;
+        sumf -= dmin * sumi;
+    }
+    for (int l = 0; l < 8; ++l) sumf += sums[l];
+    return sumf;
+}
+
 static float vec_dot_q6_K_q8_K(int64_t k, const blk_q6_K *x, const blk_q8_K *y) {
     int64_t nb = k / QK_K;
     float sums[8] = {0};
@@ -728,6 +879,7 @@ int ggq_matmul_cpu(int type, const void *packed, int64_t n, int64_t k, const flo
             float v;
             if (type == GGQ_TYPE_Q8_0) v = vec_dot_q8_0_q8_0(k, (const blk_q8_0 *)row, (const blk_q8_0 *)a);
             else if (type == GGQ_TYPE_Q4_K) v = vec_dot_q4_K_q8_K(k, (const blk_q4_K *)row, (const blk_q8_K *)a);
+            else if (type == GGQ_TYPE_Q5_K) v = vec_dot_q5_K_q8_K(k, (const blk_q5_K *)row, (const blk_q8_K *)a);
             else v = vec_dot_q6_K_q8_K(k, (const blk_q6_K *)row, (const blk_q8_K *)a);
             y[t * ldy + r] = v;
         }

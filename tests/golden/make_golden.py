@@ -12,10 +12,11 @@ import numpy as np
 from gguf import quants
 
 OUT = Path(__file__).resolve().parent / "ggml_blocks.npz"
-T = {8: gguf.GGMLQuantizationType.Q8_0, 12: gguf.GGMLQuantizationType.Q4_K, 14: gguf.GGMLQuantizationType.Q6_K}
-BLK = {8: (32, 34), 12: (256, 144), 14: (256, 210)}
+T = {8: gguf.GGMLQuantizationType.Q8_0, 12: gguf.GGMLQuantizationType.Q4_K, 13: gguf.GGMLQuantizationType.Q5_K,
+     14: gguf.GGMLQuantizationType.Q6_K}
+BLK = {8: (32, 34), 12: (256, 144), 13: (256, 176), 14: (256, 210)}
 # byte offsets of the fp16 fields inside a block (kept finite so decoded values are comparable)
-F16_AT = {8: [0], 12: [0, 2], 14: [208]}
+F16_AT = {8: [0], 12: [0, 2], 13: [0, 2], 14: [208]}
 
 
 def random_blocks(rng, qt, rows, k):
@@ -34,16 +35,20 @@ def random_blocks(rng, qt, rows, k):
 def main():
     rng = np.random.default_rng(1234)
     out = {}
-    for qt in (8, 12, 14):
+    def case(qt):
         rows, k = 6, 768
         packed = random_blocks(rng, qt, rows, k)
         out[f"packed_{qt}"] = packed
         out[f"dequant_{qt}"] = quants.dequantize(packed, T[qt]).astype(np.float32)
+
+    for qt in (8, 12, 14):
+        case(qt)
     w = (rng.standard_normal((4, 512)) * 0.02).astype(np.float32)
     w[0, :32] = 0.0          # an all-zero block
     w[1, 5] = 0.5            # an outlier
     out["q8_0_src"] = w
     out["q8_0_packed"] = quants.quantize(w, T[8])
+    case(13)      # drawn last: the cases above keep the bytes they had before Q5_K was added
     np.savez_compressed(OUT, **out)
     print("wrote", OUT, OUT.stat().st_size, "bytes")
 
