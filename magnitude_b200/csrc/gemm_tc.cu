@@ -729,18 +729,19 @@ constexpr int kTsACol0 = 2 * kTsAccCols;            // first A-stage column in T
 // released (stores, proxy fence, arrival across the pair: more than a thousand cycles) is off the
 // tensor cores' path.  Activation stages hide the latency of the TMA loads.  Q4_K's small records
 // leave room for 11 stages of 16 KB; 6 + 4 (both in two-stage hand-over units, see the kernel)
-// measured fastest: 1026 TFLOP/s on 2048 x 4096 x 14336 against 956 for 6 + 5 and 833 for 4 + 6.  The
-// larger packed-record buffers of Q6_K and Q8_0 and the TS form's tensor-memory budget leave four
-// weight stages.  B200Q_PAIR_SA / B200Q_PAIR_SB override Q4_K's split at compile time.
+// measured fastest: 1026 TFLOP/s on 2048 x 4096 x 14336 against 956 for 6 + 5 and 833 for 4 + 6; the
+// same split serves Q5_K and Q6_K (Q6_K: 896 TFLOP/s against 792 with 4 + 6).  Q8_0's packed-record
+// buffers (2 x 34 KB) and the TS form's tensor-memory budget leave four weight stages.
+// B200Q_PAIR_SA / B200Q_PAIR_SB override the split at compile time.
 constexpr int kMaxPairAStages = 8;
 #ifndef B200Q_PAIR_SA
 #define B200Q_PAIR_SA 6
 #define B200Q_PAIR_SB 4
 #endif
-__host__ __device__ constexpr int pair_a_stages(int qt, bool ts) { return (!ts && (qt == QT_Q4_K || qt == QT_Q5_K)) ? B200Q_PAIR_SA : 4; }
+__host__ __device__ constexpr int pair_a_stages(int qt, bool ts) { return (!ts && qt != QT_Q8_0) ? B200Q_PAIR_SA : 4; }
 __host__ __device__ constexpr int pair_b_rows(bool ts) { return ts ? 96 : 128; }       // tokens each CTA stages per K-step
 __host__ __device__ constexpr int pair_b_stage_bytes(bool ts = false) { return ((pair_b_rows(ts) * BK * 2 + 1023) / 1024) * 1024; }
-__host__ __device__ constexpr int pair_b_stages(int qt, bool ts = false) { return ts ? 8 : qt == QT_Q8_0 ? 5 : qt == QT_Q6_K ? 6 : B200Q_PAIR_SB; }
+__host__ __device__ constexpr int pair_b_stages(int qt, bool ts = false) { return ts ? 8 : qt == QT_Q8_0 ? 5 : B200Q_PAIR_SB; }
 // activation stages per hand-over unit: two when the stages pair up
 __host__ __device__ constexpr int pair_b_group(int qt, bool ts = false) { return pair_b_stages(qt, ts) % 2 == 0 ? 2 : 1; }
 constexpr int kMaxPairBStages = 8;
