@@ -60,6 +60,7 @@ enum {
 /* ggml tensor type ids, the values GGUF files carry (gguf.rs:126 reads them as u32). */
 enum {
     B200Q_TYPE_F32 = 0,
+    B200Q_TYPE_Q4_0 = 2,
     B200Q_TYPE_Q8_0 = 8,
     B200Q_TYPE_Q4_K = 12,
     B200Q_TYPE_Q5_K = 13,

@@ -34,16 +34,16 @@ namespace b200q {
 // The byte count equals GGUF's except for the Q8_0 K padding and at most 14 bytes per Q6_K row.
 // ---------------------------------------------------------------------------------------------
 
-enum : int { QT_Q8_0 = B200Q_TYPE_Q8_0, QT_Q4_K = B200Q_TYPE_Q4_K, QT_Q5_K = B200Q_TYPE_Q5_K, QT_Q6_K = B200Q_TYPE_Q6_K };
+enum : int { QT_Q4_0 = B200Q_TYPE_Q4_0, QT_Q8_0 = B200Q_TYPE_Q8_0, QT_Q4_K = B200Q_TYPE_Q4_K, QT_Q5_K = B200Q_TYPE_Q5_K, QT_Q6_K = B200Q_TYPE_Q6_K };
 
 constexpr int SB = 256;  // weights per superblock record
 
 __host__ __device__ constexpr int rec_bytes(int qt) {
-    return qt == QT_Q4_K ? 144 : qt == QT_Q5_K ? 176 : qt == QT_Q8_0 ? 272 : 208;
+    return (qt == QT_Q4_K || qt == QT_Q4_0) ? 144 : qt == QT_Q5_K ? 176 : qt == QT_Q8_0 ? 272 : 208;
 }
-__host__ __device__ constexpr int gguf_block_elems(int qt) { return qt == QT_Q8_0 ? 32 : 256; }
+__host__ __device__ constexpr int gguf_block_elems(int qt) { return (qt == QT_Q8_0 || qt == QT_Q4_0) ? 32 : 256; }
 __host__ __device__ constexpr int gguf_block_bytes(int qt) {
-    return qt == QT_Q4_K ? 144 : qt == QT_Q5_K ? 176 : qt == QT_Q8_0 ? 34 : 210;
+    return qt == QT_Q4_K ? 144 : qt == QT_Q5_K ? 176 : qt == QT_Q8_0 ? 34 : qt == QT_Q4_0 ? 18 : 210;
 }
 
 // byte offset of superblock record `sb` inside a row

@@ -68,7 +68,7 @@ constexpr int kMaxBStages = 4;
 // per-type shared-memory plan: the packed-record buffers differ in size, the activation ring takes
 // what is left of the 227 KB
 __host__ __device__ constexpr int wbuf_bytes(int qt) { return ((BM * rec_bytes(qt) + 1023) / 1024) * 1024; }
-__host__ __device__ constexpr int b_stages(int qt) { return qt == QT_Q4_K ? 4 : 3; }
+__host__ __device__ constexpr int b_stages(int qt) { return (qt == QT_Q4_K || qt == QT_Q4_0) ? 4 : 3; }
 __host__ __device__ constexpr int bn_max(int qt) { return qt == QT_Q6_K ? 256 : 240; }     // widest token tile
 __host__ __device__ constexpr int b_stage_bytes(int qt) { return bn_max(qt) * BK * 2; }
 __host__ __device__ constexpr int smem_data_bytes(int qt) {
@@ -291,6 +291,35 @@ template <> struct Unit<QT_Q5_K> {
                 word_affine<0x64>(lo, o_lo, s_lo, c_lo, o[4 * n + 2 * i], o[4 * n + 2 * i + 1]);
                 word_affine<0x64>(hi, o_hi, s_hi, c_hi, o[16 + 4 * n + 2 * i], o[16 + 4 * n + 2 * i + 1]);
             }
+        }
+    }
+};
+
+// Q4_0: [8 x fp16 d][nibbles in the Q4_K arrangement]; weight = d q - 8 d, centred at q0 = 8 exactly
+template <> struct Unit<QT_Q4_0> {
+    uint4 hdr, q0, q1;
+    __device__ __forceinline__ void load(uint32_t rec, uint32_t, int j) {
+        hdr = lds128(rec);
+        q0 = lds128(rec + 16 + 32 * j);
+        q1 = lds128(rec + 32 + 32 * j);
+    }
+    __device__ __forceinline__ void convert(int j, uint32_t (&o)[32]) const {
+        const uint32_t dw[4] = {hdr.x, hdr.y, hdr.z, hdr.w};
+        uint32_t dd = dw[0];
+#pragma unroll
+        for (int i = 1; i < 4; ++i)
+            if (i == j) dd = dw[i];
+        const float da = half_bits_to_float(dd), db = half_bits_to_float(dd >> 16);
+        __half2 o_lo, s_lo, c_lo, o_hi, s_hi, c_hi;
+        centered(da, 8.f * da, as_h2(0x64006400u), o_lo, s_lo, c_lo);
+        centered(db, 8.f * db, as_h2(0x54005400u), o_hi, s_hi, c_hi);
+        const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+#pragma unroll
+        for (int n = 0; n < 4; ++n) {
+            word_affine<0x64>(w[2 * n] & 0x0F0F0F0Fu, o_lo, s_lo, c_lo, o[4 * n], o[4 * n + 1]);
+            word_affine<0x64>(w[2 * n + 1] & 0x0F0F0F0Fu, o_lo, s_lo, c_lo, o[4 * n + 2], o[4 * n + 3]);
+            word_affine<0x54>(w[2 * n] & 0xF0F0F0F0u, o_hi, s_hi, c_hi, o[16 + 4 * n], o[16 + 4 * n + 1]);
+            word_affine<0x54>(w[2 * n + 1] & 0xF0F0F0F0u, o_hi, s_hi, c_hi, o[16 + 4 * n + 2], o[16 + 4 * n + 3]);
         }
     }
 };
@@ -1483,6 +1512,7 @@ cudaError_t gemm_launch(const GemmLaunch &a, cudaStream_t st) {
         switch (a.qt) {
         case QT_Q4_K: return use_ts ? launch_gemm_pair<QT_Q4_K, true>(p, maps, grid2, st) : launch_gemm_pair<QT_Q4_K, false>(p, maps, grid2, st);
         case QT_Q5_K: return use_ts ? launch_gemm_pair<QT_Q5_K, true>(p, maps, grid2, st) : launch_gemm_pair<QT_Q5_K, false>(p, maps, grid2, st);
+        case QT_Q4_0: return use_ts ? launch_gemm_pair<QT_Q4_0, true>(p, maps, grid2, st) : launch_gemm_pair<QT_Q4_0, false>(p, maps, grid2, st);
         case QT_Q6_K: return use_ts ? launch_gemm_pair<QT_Q6_K, true>(p, maps, grid2, st) : launch_gemm_pair<QT_Q6_K, false>(p, maps, grid2, st);
         case QT_Q8_0: return use_ts ? launch_gemm_pair<QT_Q8_0, true>(p, maps, grid2, st) : launch_gemm_pair<QT_Q8_0, false>(p, maps, grid2, st);
         default: return cudaErrorInvalidValue;
@@ -1493,6 +1523,7 @@ cudaError_t gemm_launch(const GemmLaunch &a, cudaStream_t st) {
     switch (a.qt) {
     case QT_Q4_K: e = launch_gemm<QT_Q4_K>(p, maps, grid, st); break;
     case QT_Q5_K: e = launch_gemm<QT_Q5_K>(p, maps, grid, st); break;
+    case QT_Q4_0: e = launch_gemm<QT_Q4_0>(p, maps, grid, st); break;
     case QT_Q6_K: e = launch_gemm<QT_Q6_K>(p, maps, grid, st); break;
     case QT_Q8_0: e = launch_gemm<QT_Q8_0>(p, maps, grid, st); break;
     default: return cudaErrorInvalidValue;

@@ -83,7 +83,7 @@ template <int QT> struct XRegs {
         } else {
             const uint2 s = lds64(xv.sx + gu * 8);
             sx[0] = __uint_as_float(s.x); sx[1] = __uint_as_float(s.y);
-            if (QT == QT_Q4_K || QT == QT_Q5_K) {
+            if (QT == QT_Q4_K || QT == QT_Q5_K || QT == QT_Q4_0) {
                 const uint2 i = lds64(xv.isum + gu * 8);
                 is[0] = (int)i.x; is[1] = (int)i.y;
             }
@@ -198,6 +198,45 @@ template <> struct WRegs<QT_Q5_K> {
         const float ua = (float)(mnA * xr.is[0]);
         const float ub = (float)(mnB * xr.is[1]);
         return xr.sx[0] * (d * fa - dmin * ua) + xr.sx[1] * (d * fb - dmin * ub);
+    }
+};
+
+// Q4_0 record on the device: the eight fp16 d of its native blocks, then the nibbles in the Q4_K
+// arrangement; w = d (q - 8), so a block's dot is d (sum q x - 8 sum x) with both sums integers.
+template <> struct WRegs<QT_Q4_0> {
+    uint32_t lo[8], hi[8];   // low nibbles = block 2j; hi keeps 16 * nibble of block 2j + 1
+    float dA, dB;
+    __device__ __forceinline__ void load(uint32_t rec, int j) {
+        const uint4 qa = lds128(rec + 16 + 32 * j);
+        const uint4 qb = lds128(rec + 32 + 32 * j);
+        const uint32_t dd = lds32(rec + 4 * j);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint32_t a = word_of(qa, i), b = word_of(qb, i);
+            lo[i] = a & 0x0F0F0F0Fu;
+            hi[i] = a & 0xF0F0F0F0u;
+            lo[4 + i] = b & 0x0F0F0F0Fu;
+            hi[4 + i] = b & 0xF0F0F0F0u;
+        }
+        dA = half_bits_to_float(dd);
+        dB = half_bits_to_float(dd >> 16);
+    }
+    __device__ __forceinline__ float dot(const XRegs<QT_Q4_0> &xr) const {
+        int hA = 0, lA = 0, hB = 0, lB = 0;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            hA = dp4a_us(lo[i], word_of(xr.h[0], i), hA);
+            lA = dp4a_us(lo[i], word_of(xr.l[0], i), lA);
+            hA = dp4a_us(lo[4 + i], word_of(xr.h[1], i), hA);
+            lA = dp4a_us(lo[4 + i], word_of(xr.l[1], i), lA);
+            hB = dp4a_us(hi[i], word_of(xr.h[2], i), hB);
+            lB = dp4a_us(hi[i], word_of(xr.l[2], i), lB);
+            hB = dp4a_us(hi[4 + i], word_of(xr.h[3], i), hB);
+            lB = dp4a_us(hi[4 + i], word_of(xr.l[3], i), lB);
+        }
+        const float fa = (float)((hA * 256 + lA) - 8 * xr.is[0]);
+        const float fb = (float)(((hB * 256 + lB) >> 4) - 8 * xr.is[1]);     // hi held 16 * nibble: exact shift
+        return xr.sx[0] * (dA * fa) + xr.sx[1] * (dB * fb);
     }
 };
 

@@ -22,6 +22,22 @@ void repack_host(int qt, int64_t K, const uint8_t *gguf, int64_t r0, int64_t n, 
                 memcpy(rec, blk, 16);
                 memcpy(rec + 16, blk + 48, 128);
                 memcpy(rec + 144, blk + 16, 32);
+            } else if (qt == QT_Q4_0) {
+                // eight native blocks -> [8 x fp16 d][128 bytes of nibbles in the Q4_K arrangement: block 2j in the
+                // low nibbles of bytes 32j .. 32j + 31, block 2j + 1 in their high nibbles]; K padding: zero blocks
+                const int64_t nblk = K / 32;
+                memset(rec, 0, 144);
+                for (int b = 0; b < 8; ++b) {
+                    const int64_t blk = (sb0 + sb) * 8 + b;
+                    if (blk >= nblk) continue;
+                    const uint8_t *src = s + blk * 18;
+                    memcpy(rec + 2 * b, src, 2);
+                    uint8_t *q = rec + 16 + 32 * (b >> 1);
+                    for (int l = 0; l < 32; ++l) {
+                        const uint8_t v = l < 16 ? (src[2 + l] & 0xF) : (src[2 + l - 16] >> 4);
+                        q[l] |= (b & 1) ? (uint8_t)(v << 4) : v;
+                    }
+                }
             } else if (qt == QT_Q8_0) {
                 const int64_t nblk = K / 32;
                 for (int b = 0; b < 8; ++b) {
@@ -67,6 +83,13 @@ __global__ void __launch_bounds__(256) dequant_kernel(const uint8_t *__restrict_
         const float d1 = __fmul_rn(d, (float)sc);
         const float m1 = __fmul_rn(dmin, (float)mn);
         v = __fsub_rn(__fmul_rn(d1, (float)q), m1);
+    } else if (QT == QT_Q4_0) {
+        const uint8_t *rec = w + record_off(QT, row, sb, N, nsb);
+        const int b = t >> 5;
+        const float d = half_bits_to_float(*reinterpret_cast<const uint16_t *>(rec + 2 * b));
+        const uint8_t byte = rec[16 + 32 * (b >> 1) + (t & 31)];
+        const int q = (b & 1) ? (byte >> 4) : (byte & 0xF);
+        v = __fmul_rn((float)(q - 8), d);
     } else if (QT == QT_Q8_0) {
         const uint8_t *rec = w + record_off(QT, row, sb, N, nsb);
         const float d = half_bits_to_float(*reinterpret_cast<const uint16_t *>(rec + 256 + 2 * (t >> 5)));
@@ -97,6 +120,7 @@ cudaError_t dequant_launch(int qt, const uint8_t *w, int64_t N, int64_t K, int64
     case QT_Q4_K: dequant_kernel<QT_Q4_K><<<(unsigned)blocks, 256, 0, st>>>(w, N, K, nsb, out); break;
     case QT_Q5_K: dequant_kernel<QT_Q5_K><<<(unsigned)blocks, 256, 0, st>>>(w, N, K, nsb, out); break;
     case QT_Q8_0: dequant_kernel<QT_Q8_0><<<(unsigned)blocks, 256, 0, st>>>(w, N, K, nsb, out); break;
+    case QT_Q4_0: dequant_kernel<QT_Q4_0><<<(unsigned)blocks, 256, 0, st>>>(w, N, K, nsb, out); break;
     case QT_Q6_K: dequant_kernel<QT_Q6_K><<<(unsigned)blocks, 256, 0, st>>>(w, N, K, nsb, out); break;
     default: return cudaErrorInvalidValue;
     }

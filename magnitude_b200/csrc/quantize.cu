@@ -1,4 +1,4 @@
-// The format's reference quantizer, fp32 -> Q8_0 / Q4_K / Q5_K / Q6_K (host code, threads over rows):
+// The format's reference quantizer, fp32 -> Q4_0 / Q8_0 / Q4_K / Q5_K / Q6_K (host code, threads over rows):
 // what a model converter runs once per tensor (reference row "quantizer fp32 -> blocks", upstream of
 // LlamaModel::load_from_file, inference/crates/icn-engine/src/lib.rs:972).  Restated from the
 // published algorithm of the GGUF reference implementation: Q8_0 takes d = max|w| / 127; Q4_K fits
@@ -85,6 +85,23 @@ void row_q8_0(const float *x, uint8_t *y, int64_t k) {
         const float d = amax / 127.f, id = d ? 1.f / d : 0.f;
         put_half(y, d);
         for (int j = 0; j < 32; ++j) y[2 + j] = (uint8_t)(int8_t)roundf(x[j] * id);
+    }
+}
+
+// ---- Q4_0: [fp16 d][16 bytes: weights 0..15 in the low nibbles, 16..31 in the high nibbles] -----------
+// d = (the value of largest magnitude) / -8, level = min(15, trunc(x / d + 8.5))
+void row_q4_0(const float *x, uint8_t *y, int64_t k) {
+    for (int64_t b = 0; b < k / 32; ++b, x += 32, y += 18) {
+        float amax = 0, max = 0;
+        for (int j = 0; j < 32; ++j)
+            if (amax < fabsf(x[j])) amax = fabsf(x[j]), max = x[j];
+        const float d = max / -8, id = d ? 1.0f / d : 0.0f;
+        put_half(y, d);
+        for (int j = 0; j < 16; ++j) {
+            const uint8_t a = (uint8_t)std::min(15, (int)(uint8_t)(int8_t)(x[j] * id + 8.5f));
+            const uint8_t c = (uint8_t)std::min(15, (int)(uint8_t)(int8_t)(x[16 + j] * id + 8.5f));
+            y[2 + j] = (uint8_t)(a | (c << 4));
+        }
     }
 }
 
@@ -304,8 +321,8 @@ void row_q6_k(const float *x, uint8_t *y, int64_t k) {
 extern "C" b200q_status b200q_quantize(int32_t type, const float *weights, int64_t N, int64_t K, void *packed_out, size_t out_bytes,
                                        int32_t threads) {
     const int64_t want = b200q_tensor_storage_bytes(type, N < 0 || K < 0 ? -1 : N * K);
-    if ((type != B200Q_TYPE_Q8_0 && type != B200Q_TYPE_Q4_K && type != B200Q_TYPE_Q5_K && type != B200Q_TYPE_Q6_K) || N < 0 || K < 0) return B200Q_ERR_INVALID_CONFIG;
-    const int64_t blk = type == B200Q_TYPE_Q8_0 ? 32 : 256, bb = type == B200Q_TYPE_Q8_0 ? 34 : type == B200Q_TYPE_Q4_K ? 144 : type == B200Q_TYPE_Q5_K ? 176 : 210;
+    if ((type != B200Q_TYPE_Q4_0 && type != B200Q_TYPE_Q8_0 && type != B200Q_TYPE_Q4_K && type != B200Q_TYPE_Q5_K && type != B200Q_TYPE_Q6_K) || N < 0 || K < 0) return B200Q_ERR_INVALID_CONFIG;
+    const int64_t blk = (type == B200Q_TYPE_Q8_0 || type == B200Q_TYPE_Q4_0) ? 32 : 256, bb = type == B200Q_TYPE_Q4_0 ? 18 : type == B200Q_TYPE_Q8_0 ? 34 : type == B200Q_TYPE_Q4_K ? 144 : type == B200Q_TYPE_Q5_K ? 176 : 210;
     if (K % blk || want < 0 || (int64_t)out_bytes != want) return B200Q_ERR_INVALID_CONFIG;
     if (N * K == 0) return B200Q_OK;
     if (!weights || !packed_out) return B200Q_ERR_INVALID_CONFIG;
@@ -317,6 +334,7 @@ extern "C" b200q_status b200q_quantize(int32_t type, const float *weights, int64
             const float *x = weights + r * K;
             uint8_t *y = reinterpret_cast<uint8_t *>(packed_out) + r * rb;
             if (type == B200Q_TYPE_Q8_0) row_q8_0(x, y, K);
+            else if (type == B200Q_TYPE_Q4_0) row_q4_0(x, y, K);
             else if (type == B200Q_TYPE_Q4_K) row_q4_k(x, y, K);
             else if (type == B200Q_TYPE_Q5_K) row_q5_k(x, y, K);
             else row_q6_k(x, y, K);

@@ -63,7 +63,7 @@ constexpr int kRedDepth = 4;                      // partial-tile sets in flight
 // shared-memory distance between the rows of a stage: the chunk's bytes per row, padded so that the
 // 8 rows a fragment load touches start 32 bytes apart modulo 128 (Q6_K reads 4-byte words and is
 // conflict-free at its natural 1680)
-__host__ __device__ constexpr int sk_row_stride(int qt) { return qt == QT_Q4_K ? 1184 : qt == QT_Q5_K ? 1440 : qt == QT_Q8_0 ? 2208 : 1680; }
+__host__ __device__ constexpr int sk_row_stride(int qt) { return (qt == QT_Q4_K || qt == QT_Q4_0) ? 1184 : qt == QT_Q5_K ? 1440 : qt == QT_Q8_0 ? 2208 : 1680; }
 __host__ __device__ constexpr int sk_subblocks(int qt) { return qt == QT_Q6_K ? 16 : 8; }   // scale blocks per record
 
 struct SkJob {
@@ -291,6 +291,24 @@ template <int NT> struct SkRecord<QT_Q5_K, NT> {
                 for (int nt = 0; nt < NT; ++nt) fold(acc[nt], c[q][nt], pa, pb, ldsn_f2(xst + ((sb * NT + nt) * 8 + 2 * t) * 4));
             }
         }
+    }
+};
+
+// Q4_0: [8 x fp16 d][nibbles in the Q4_K arrangement]; w = d (q - 8): p = d, the X term carries 128 + 8
+template <int NT> struct SkRecord<QT_Q4_0, NT> {
+    static __device__ __forceinline__ void scales(uint32_t rec_row, uint32_t, int lane, uint32_t sct) {
+        const int row = lane >> 1, half = lane & 1;
+        const uint2 dd = ldsn64(rec_row + 8 * half);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint32_t wv = i < 2 ? dd.x : dd.y;
+            const float d = half_bits_to_float(wv >> (16 * (i & 1)));
+            sts_f2(sct + ((4 * half + i) * kSkRows + row) * 8, d, -136.f * d);
+        }
+    }
+    static __device__ __forceinline__ void run(uint32_t recA, uint32_t recB, int g, int t, const uint32_t (&B)[32 * NT],
+                                               uint32_t sct, uint32_t xst, float (&acc)[NT][4]) {
+        SkRecord<QT_Q4_K, NT>::run(recA, recB, g, t, B, sct, xst, acc);
     }
 };
 
@@ -927,6 +945,8 @@ cudaError_t skinny_set_launch(const SkinnySet *set, cudaStream_t st) {
     switch (set->qt * 4 + set->NT) {
     case QT_Q4_K * 4 + 1: e = sk_launch_t<QT_Q4_K, 1>(set->p, set->grid, set->smem_limit, st); break;
     case QT_Q4_K * 4 + 2: e = sk_launch_t<QT_Q4_K, 2>(set->p, set->grid, set->smem_limit, st); break;
+    case QT_Q4_0 * 4 + 1: e = sk_launch_t<QT_Q4_0, 1>(set->p, set->grid, set->smem_limit, st); break;
+    case QT_Q4_0 * 4 + 2: e = sk_launch_t<QT_Q4_0, 2>(set->p, set->grid, set->smem_limit, st); break;
     case QT_Q5_K * 4 + 1: e = sk_launch_t<QT_Q5_K, 1>(set->p, set->grid, set->smem_limit, st); break;
     case QT_Q5_K * 4 + 2: e = sk_launch_t<QT_Q5_K, 2>(set->p, set->grid, set->smem_limit, st); break;
     case QT_Q6_K * 4 + 1: e = sk_launch_t<QT_Q6_K, 1>(set->p, set->grid, set->smem_limit, st); break;

@@ -11,8 +11,8 @@ from __future__ import annotations
 
 import numpy as np
 
-Q8_0, Q4_K, Q5_K, Q6_K = 8, 12, 13, 14
-BLOCK = {Q8_0: (32, 34), Q4_K: (256, 144), Q5_K: (256, 176), Q6_K: (256, 210)}
+Q4_0, Q8_0, Q4_K, Q5_K, Q6_K = 2, 8, 12, 13, 14
+BLOCK = {Q4_0: (32, 18), Q8_0: (32, 34), Q4_K: (256, 144), Q5_K: (256, 176), Q6_K: (256, 210)}
 
 
 def _check(w: np.ndarray, blk: int) -> np.ndarray:
@@ -121,6 +121,15 @@ def dequantize_q4_k(packed: np.ndarray, k: int) -> np.ndarray:
     return ((dl[..., None] * q).astype(np.float32) - ml[..., None]).astype(np.float32).reshape(n, k)
 
 
+def dequantize_q4_0(packed: np.ndarray, k: int) -> np.ndarray:
+    """fp32 [N, K] of Q4_0 blocks: w = (q - 8) * d, weights 0..15 in the low nibbles, 16..31 in the high ones."""
+    rows = np.ascontiguousarray(packed, dtype=np.uint8).reshape(-1, k // 32, 18)
+    d = rows[..., 0:2].copy().view(np.float16).astype(np.float32)
+    qs = rows[..., 2:]
+    q = np.concatenate([qs & 0xF, qs >> 4], axis=-1).astype(np.float32) - np.float32(8)
+    return (q * d).astype(np.float32).reshape(rows.shape[0], k)
+
+
 def dequantize_q5_k(packed: np.ndarray, k: int) -> np.ndarray:
     """fp32 [N, K] of Q5_K blocks: the Q4_K rule with levels nibble + 16 * (bit s of qh[l]) for sub-block s."""
     rows = np.ascontiguousarray(packed, dtype=np.uint8).reshape(-1, k // 256, 176)
@@ -165,6 +174,8 @@ def dequantize_q6_k(packed: np.ndarray, k: int) -> np.ndarray:
 def dequantize(qtype: int, packed: np.ndarray, k: int) -> np.ndarray:
     if qtype == Q4_K:
         return dequantize_q4_k(packed, k)
+    if qtype == Q4_0:
+        return dequantize_q4_0(packed, k)
     if qtype == Q5_K:
         return dequantize_q5_k(packed, k)
     if qtype == Q6_K:

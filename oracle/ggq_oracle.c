@@ -1,5 +1,5 @@
 /*
- * CPU oracle for the GGUF block-quantized projection matmul (Q8_0 / Q4_K / Q5_K / Q6_K).
+ * CPU oracle for the GGUF block-quantized projection matmul (Q4_0 / Q8_0 / Q4_K / Q5_K / Q6_K).
  *
  * TEST INFRASTRUCTURE ONLY.  Nothing in the shipped library links, loads or calls this
  * file; it exists so the tests, the smoke check and the bench's CPU-baseline leg have an
@@ -24,6 +24,7 @@
  *   fp16 -> fp32 exact; every product and difference is a separately rounded fp32
  *   operation, no fused multiply-add (build with -ffp-contract=off):
  *     Q8_0:  w = d * q
+ *     Q4_0:  w = (q - 8) * d
  *     Q4_K:  w = (d * sc) * q - (dmin * m)
  *     Q5_K:  w = (d * sc) * q - (dmin * m)   with q = nibble + 16 * high bit
  *     Q6_K:  w = (d * sc) * q         with q in [-32, 31]
@@ -44,10 +45,11 @@
 #define K_SCALE_SIZE 12
 #define GROUP_MAX_EPS 1e-15f
 
-enum { GGQ_TYPE_Q8_0 = 8, GGQ_TYPE_Q4_K = 12, GGQ_TYPE_Q5_K = 13, GGQ_TYPE_Q6_K = 14 };
+enum { GGQ_TYPE_Q4_0 = 2, GGQ_TYPE_Q8_0 = 8, GGQ_TYPE_Q4_K = 12, GGQ_TYPE_Q5_K = 13, GGQ_TYPE_Q6_K = 14 };
 
 #pragma pack(push, 1)
 typedef struct { uint16_t d; int8_t qs[QK8_0]; } blk_q8_0;                 /* 34 B  */
+typedef struct { uint16_t d; uint8_t qs[QK8_0 / 2]; } blk_q4_0;            /* 18 B  */
 typedef struct { uint16_t d; uint16_t dmin; uint8_t scales[K_SCALE_SIZE];
                  uint8_t qs[QK_K / 2]; } blk_q4_K;                          /* 144 B */
 typedef struct { uint16_t d; uint16_t dmin; uint8_t scales[K_SCALE_SIZE];
@@ -58,6 +60,7 @@ typedef struct { float d; int8_t qs[QK_K]; int16_t bsums[QK_K / 16]; } blk_q8_K;
 #pragma pack(pop)
 
 _Static_assert(sizeof(blk_q8_0) == 34, "q8_0 size");
+_Static_assert(sizeof(blk_q4_0) == 18, "q4_0 size");
 _Static_assert(sizeof(blk_q4_K) == 144, "q4_K size");
 _Static_assert(sizeof(blk_q5_K) == 176, "q5_K size");
 _Static_assert(sizeof(blk_q6_K) == 210, "q6_K size");
@@ -151,11 +154,12 @@ void ggq_f16_to_f32(const uint16_t *src, float *dst, int64_t n) {
 /* ------------------------------------------------------------------ sizes */
 
 int64_t ggq_block_elems(int type) {
-    return type == GGQ_TYPE_Q8_0 ? QK8_0 : (type == GGQ_TYPE_Q4_K || type == GGQ_TYPE_Q5_K || type == GGQ_TYPE_Q6_K) ? QK_K : 0;
+    return (type == GGQ_TYPE_Q8_0 || type == GGQ_TYPE_Q4_0) ? QK8_0 : (type == GGQ_TYPE_Q4_K || type == GGQ_TYPE_Q5_K || type == GGQ_TYPE_Q6_K) ? QK_K : 0;
 }
 int64_t ggq_block_bytes(int type) {
     switch (type) {
     case GGQ_TYPE_Q8_0: return sizeof(blk_q8_0);
+    case GGQ_TYPE_Q4_0: return sizeof(blk_q4_0);
     case GGQ_TYPE_Q4_K: return sizeof(blk_q4_K);
     case GGQ_TYPE_Q5_K: return sizeof(blk_q5_K);
     case GGQ_TYPE_Q6_K: return sizeof(blk_q6_K);
@@ -197,6 +201,20 @@ static void dequant_row_q8_0(const blk_q8_0 *x, float *y, int64_t k) {
     for (int64_t i = 0; i < nb; ++i) {
         float d = f16_to_f32(x[i].d);
         for (int j = 0; j < QK8_0; ++j) y[i * QK8_0 + j] = d * (float)x[i].qs[j];
+    }
+}
+
+/* ggml dequantize_row_q4_0: weights 0..15 are the low nibbles, 16..31 the high nibbles; w = (q - 8) * d */
+static void dequant_row_q4_0(const blk_q4_0 *x, float *y, int64_t k) {
+    int64_t nb = k / QK8_0;
+    for (int64_t i = 0; i < nb; ++i) {
+        float d = f16_to_f32(x[i].d);
+        for (int j = 0; j < QK8_0 / 2; ++j) {
+            int x0 = (x[i].qs[j] & 0x0F) - 8;
+            int x1 = (x[i].qs[j] >> 4) - 8;
+            y[i * QK8_0 + j] = (float)x0 * d;
+            y[i * QK8_0 + j + QK8_0 / 2] = (float)x1 * d;
+        }
     }
 }
 
@@ -292,6 +310,7 @@ int ggq_dequantize(int type, const void *packed, float *out, int64_t n_rows, int
         const void *row = p + r * rb;
         float *y = out + r * k;
         if (type == GGQ_TYPE_Q8_0) dequant_row_q8_0((const blk_q8_0 *)row, y, k);
+        else if (type == GGQ_TYPE_Q4_0) dequant_row_q4_0((const blk_q4_0 *)row, y, k);
         else if (type == GGQ_TYPE_Q4_K) dequant_row_q4_K((const blk_q4_K *)row, y, k);
         else if (type == GGQ_TYPE_Q5_K) dequant_row_q5_K((const blk_q5_K *)row, y, k);
         else dequant_row_q6_K((const blk_q6_K *)row, y, k);
@@ -313,6 +332,33 @@ static void quant_row_q8_0(const float *x, blk_q8_0 *y, int64_t k) {
         float id = d ? 1.0f / d : 0.0f;
         y[i].d = f32_to_f16(d);
         for (int j = 0; j < QK8_0; ++j) y[i].qs[j] = (int8_t)roundf(x[i * QK8_0 + j] * id);
+    }
+}
+
+/* ggml quantize_row_q4_0_ref: d = (the value of largest magnitude) / -8, q = min(15, trunc(x / d + 8.5)) */
+static void quant_row_q4_0(const float *x, blk_q4_0 *y, int64_t k) {
+    int64_t nb = k / QK8_0;
+    for (int64_t i = 0; i < nb; ++i) {
+        float amax = 0.0f, max = 0.0f;
+        for (int j = 0; j < QK8_0; ++j) {
+            float v = x[i * QK8_0 + j];
+            if (amax < fabsf(v)) {
+                amax = fabsf(v);
+                max = v;
+            }
+        }
+        float d = max / -8;
+        float id = d ? 1.0f / d : 0.0f;
+        y[i].d = f32_to_f16(d);
+        for (int j = 0; j < QK8_0 / 2; ++j) {
+            float x0 = x[i * QK8_0 + 0 + j] * id;
+            float x1 = x[i * QK8_0 + QK8_0 / 2 + j] * id;
+            uint8_t xi0 = (uint8_t)((int8_t)(x0 + 8.5f));
+            uint8_t xi1 = (uint8_t)((int8_t)(x1 + 8.5f));
+            xi0 = xi0 > 15 ? 15 : xi0;
+            xi1 = xi1 > 15 ? 15 : xi1;
+            y[i].qs[j] = (uint8_t)(xi0 | (xi1 << 4));
+        }
     }
 }
 
@@ -628,6 +674,7 @@ int ggq_quantize(int type, const float *src, void *packed, int64_t n_rows, int64
         void *row = p + r * rb;
         const float *x = src + r * k;
         if (type == GGQ_TYPE_Q8_0) quant_row_q8_0(x, (blk_q8_0 *)row, k);
+        else if (type == GGQ_TYPE_Q4_0) quant_row_q4_0(x, (blk_q4_0 *)row, k);
         else if (type == GGQ_TYPE_Q4_K) quant_row_q4_K(x, (blk_q4_K *)row, k);
         else if (type == GGQ_TYPE_Q5_K) quant_row_q5_K(x, (blk_q5_K *)row, k);
         else quant_row_q6_K(x, (blk_q6_K *)row, k);
@@ -651,6 +698,7 @@ int ggq_matmul_exact(int type, const void *packed, int64_t n, int64_t k, const f
         for (int64_t r = 0; r < n; ++r) {
             const void *row = p + r * rb;
             if (type == GGQ_TYPE_Q8_0) dequant_row_q8_0((const blk_q8_0 *)row, wf, k);
+            else if (type == GGQ_TYPE_Q4_0) dequant_row_q4_0((const blk_q4_0 *)row, wf, k);
             else if (type == GGQ_TYPE_Q4_K) dequant_row_q4_K((const blk_q4_K *)row, wf, k);
             else if (type == GGQ_TYPE_Q5_K) dequant_row_q5_K((const blk_q5_K *)row, wf, k);
             else dequant_row_q6_K((const blk_q6_K *)row, wf, k);
@@ -717,6 +765,23 @@ static float vec_dot_q8_0_q8_0(int64_t k, const blk_q8_0 *x, const blk_q8_0 *y) 
         int sumi = 0;
         for (int j = 0; j < QK8_0; ++j) sumi += x[ib].qs[j] * y[ib].qs[j];
         sumf += sumi * (f16_to_f32(x[ib].d) * f16_to_f32(y[ib].d));
+    }
+    return sumf;
+}
+
+/* ggml_vec_dot_q4_0_q8_0 (generic path) */
+static float vec_dot_q4_0_q8_0(int64_t k, const blk_q4_0 *x, const blk_q8_0 *y) {
+    int64_t nb = k / QK8_0;
+    float sumf = 0;
+    for (int64_t i = 0; i < nb; ++i) {
+        int sumi0 = 0, sumi1 = 0;
+        for (int j = 0; j < QK8_0 / 2; ++j) {
+            int v0 = (x[i].qs[j] & 0x0F) - 8;
+            int v1 = (x[i].qs[j] >> 4) - 8;
+            sumi0 += v0 * y[i].qs[j];
+            sumi1 += v1 * y[i].qs[j + QK8_0 / 2];
+        }
+        sumf += (float)(sumi0 + sumi1) * f16_to_f32(x[i].d) * f16_to_f32(y[i].d);
     }
     return sumf;
 }
@@ -856,7 +921,8 @@ int ggq_matmul_cpu(int type, const void *packed, int64_t n, int64_t k, const flo
     int64_t rb = ggq_row_bytes(type, k);
     if (rb < 0) return -1;
     const uint8_t *p = (const uint8_t *)packed;
-    size_t act_row = (type == GGQ_TYPE_Q8_0) ? (size_t)(k / QK8_0) * sizeof(blk_q8_0)
+    const int act8_0 = type == GGQ_TYPE_Q8_0 || type == GGQ_TYPE_Q4_0;      /* these pair with Q8_0 activations */
+    size_t act_row = act8_0 ? (size_t)(k / QK8_0) * sizeof(blk_q8_0)
                                               : (size_t)(k / QK_K) * sizeof(blk_q8_K);
     uint8_t *act = (uint8_t *)malloc(act_row * (size_t)m);
     if (!act) return -2;
@@ -868,7 +934,7 @@ int ggq_matmul_cpu(int type, const void *packed, int64_t n, int64_t k, const flo
 #endif
 #pragma omp parallel for schedule(static) num_threads(nt)
     for (int64_t t = 0; t < m; ++t) {
-        if (type == GGQ_TYPE_Q8_0) quant_act_q8_0(x + t * ldx, (blk_q8_0 *)(act + t * act_row), k);
+        if (act8_0) quant_act_q8_0(x + t * ldx, (blk_q8_0 *)(act + t * act_row), k);
         else quant_act_q8_K(x + t * ldx, (blk_q8_K *)(act + t * act_row), k);
     }
 #pragma omp parallel for schedule(static) num_threads(nt)
@@ -878,6 +944,7 @@ int ggq_matmul_cpu(int type, const void *packed, int64_t n, int64_t k, const flo
             const void *a = act + t * act_row;
             float v;
             if (type == GGQ_TYPE_Q8_0) v = vec_dot_q8_0_q8_0(k, (const blk_q8_0 *)row, (const blk_q8_0 *)a);
+            else if (type == GGQ_TYPE_Q4_0) v = vec_dot_q4_0_q8_0(k, (const blk_q4_0 *)row, (const blk_q8_0 *)a);
             else if (type == GGQ_TYPE_Q4_K) v = vec_dot_q4_K_q8_K(k, (const blk_q4_K *)row, (const blk_q8_K *)a);
             else if (type == GGQ_TYPE_Q5_K) v = vec_dot_q5_K_q8_K(k, (const blk_q5_K *)row, (const blk_q8_K *)a);
             else v = vec_dot_q6_K_q8_K(k, (const blk_q6_K *)row, (const blk_q8_K *)a);

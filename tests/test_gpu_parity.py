@@ -16,7 +16,7 @@ import magnitude_b200 as mb  # noqa: E402
 from magnitude_b200 import ggml_quant as gq  # noqa: E402
 
 GOLD = Path(__file__).resolve().parent / "golden" / "ggml_blocks.npz"
-TYPES = [mb.TYPE_Q4_K, mb.TYPE_Q6_K, mb.TYPE_Q8_0, mb.TYPE_Q5_K]
+TYPES = [mb.TYPE_Q4_K, mb.TYPE_Q6_K, mb.TYPE_Q8_0, mb.TYPE_Q5_K, mb.TYPE_Q4_0]
 REL_DECODE = 1e-3
 REL_BF16 = 5e-3
 
@@ -194,7 +194,7 @@ def test_edge_cases_and_errors(backend, orc):
     assert not torch.isfinite(yb).all()
     # errors: bad type, K not a block multiple, wrong byte count, wrong dtype
     with pytest.raises(mb.B200QError) as e:
-        backend.upload(2, packed, 8, k)
+        backend.upload(3, packed, 8, k)      # Q4_1: a ggml type this library does not multiply
     assert e.value.status == 1
     with pytest.raises(mb.B200QError):
         backend.upload(mb.TYPE_Q4_K, packed, 8, k + 32)
