@@ -1331,7 +1331,7 @@ def run_calibration(args, emit=True):
     for _ in range(3):
         be.project(tiny, xt, out=yt, stream=stream)
     launch_us = float(np.median(timed(lambda: be.project(tiny, xt, out=yt, stream=stream), 20))) * 1e3
-    for qt, name, blk_e, blk_b in ((Q4_K, "Q4_K", 256, 144), (13, "Q5_K", 256, 176), (14, "Q6_K", 256, 210), (8, "Q8_0", 32, 34), (2, "Q4_0", 32, 18)):
+    for qt, name, blk_e, blk_b in ((Q4_K, "Q4_K", 256, 144), (13, "Q5_K", 256, 176), (14, "Q6_K", 256, 210), (8, "Q8_0", 32, 34), (2, "Q4_0", 32, 18), (39, "MXFP4", 32, 17)):
         w0 = be.upload(qt, gq.synth_weights(qt, n, k, 0, encoder=mb.quantize), n, k)
         ws = [w0] + [w0.clone() for _ in range(copies - 1)]
         plan = be.plan([([w], x, [y]) for w in ws])

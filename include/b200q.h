@@ -65,7 +65,8 @@ enum {
     B200Q_TYPE_Q4_K = 12,
     B200Q_TYPE_Q5_K = 13,
     B200Q_TYPE_Q6_K = 14,
-    B200Q_TYPE_BF16 = 30
+    B200Q_TYPE_BF16 = 30,
+    B200Q_TYPE_MXFP4 = 39   /* on the tensor-core GEMM route the block scales must lie in 2^-24 .. 2^11 (fp16 operands) */
 };
 
 /* How a weight is cut for tensor parallelism (the reference only names the modes:

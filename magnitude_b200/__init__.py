@@ -15,6 +15,7 @@ from ._binding import (  # noqa: F401
     SPLIT_ROW,
     TYPE_BF16,
     TYPE_F32,
+    TYPE_MXFP4,
     TYPE_Q4_0,
     TYPE_Q4_K,
     TYPE_Q5_K,

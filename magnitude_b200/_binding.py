@@ -25,7 +25,7 @@ STATUS_NAMES = {
     7: "Timeout",
 }
 
-TYPE_F32, TYPE_Q4_0, TYPE_Q8_0, TYPE_Q4_K, TYPE_Q5_K, TYPE_Q6_K, TYPE_BF16 = 0, 2, 8, 12, 13, 14, 30
+TYPE_F32, TYPE_Q4_0, TYPE_Q8_0, TYPE_Q4_K, TYPE_Q5_K, TYPE_Q6_K, TYPE_BF16, TYPE_MXFP4 = 0, 2, 8, 12, 13, 14, 30, 39
 SPLIT_COLUMN, SPLIT_ROW = 0, 1
 ROUTE_NONE, ROUTE_GEMV, ROUTE_SKINNY, ROUTE_GEMM = 0, 1, 2, 3
 

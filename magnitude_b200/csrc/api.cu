@@ -157,7 +157,7 @@ b200q_status cuda_fail(b200q_ctx *ctx, cudaError_t e, const char *what) {
         if (e__ != cudaSuccess) return cuda_fail(ctx, e__, #expr); \
     } while (0)
 
-bool known_type(int t) { return t == QT_Q4_0 || t == QT_Q8_0 || t == QT_Q4_K || t == QT_Q5_K || t == QT_Q6_K; }
+bool known_type(int t) { return t == QT_MXFP4 || t == QT_Q4_0 || t == QT_Q8_0 || t == QT_Q4_K || t == QT_Q5_K || t == QT_Q6_K; }
 bool act_type(int t) { return t == B200Q_TYPE_F32 || t == B200Q_TYPE_BF16; }
 size_t act_size(int t) { return t == B200Q_TYPE_BF16 ? 2 : 4; }
 

@@ -34,16 +34,16 @@ namespace b200q {
 // The byte count equals GGUF's except for the Q8_0 K padding and at most 14 bytes per Q6_K row.
 // ---------------------------------------------------------------------------------------------
 
-enum : int { QT_Q4_0 = B200Q_TYPE_Q4_0, QT_Q8_0 = B200Q_TYPE_Q8_0, QT_Q4_K = B200Q_TYPE_Q4_K, QT_Q5_K = B200Q_TYPE_Q5_K, QT_Q6_K = B200Q_TYPE_Q6_K };
+enum : int { QT_Q4_0 = B200Q_TYPE_Q4_0, QT_Q8_0 = B200Q_TYPE_Q8_0, QT_Q4_K = B200Q_TYPE_Q4_K, QT_Q5_K = B200Q_TYPE_Q5_K, QT_Q6_K = B200Q_TYPE_Q6_K, QT_MXFP4 = B200Q_TYPE_MXFP4 };
 
 constexpr int SB = 256;  // weights per superblock record
 
 __host__ __device__ constexpr int rec_bytes(int qt) {
-    return (qt == QT_Q4_K || qt == QT_Q4_0) ? 144 : qt == QT_Q5_K ? 176 : qt == QT_Q8_0 ? 272 : 208;
+    return (qt == QT_Q4_K || qt == QT_Q4_0 || qt == QT_MXFP4) ? 144 : qt == QT_Q5_K ? 176 : qt == QT_Q8_0 ? 272 : 208;
 }
-__host__ __device__ constexpr int gguf_block_elems(int qt) { return (qt == QT_Q8_0 || qt == QT_Q4_0) ? 32 : 256; }
+__host__ __device__ constexpr int gguf_block_elems(int qt) { return (qt == QT_Q8_0 || qt == QT_Q4_0 || qt == QT_MXFP4) ? 32 : 256; }
 __host__ __device__ constexpr int gguf_block_bytes(int qt) {
-    return qt == QT_Q4_K ? 144 : qt == QT_Q5_K ? 176 : qt == QT_Q8_0 ? 34 : qt == QT_Q4_0 ? 18 : 210;
+    return qt == QT_Q4_K ? 144 : qt == QT_Q5_K ? 176 : qt == QT_Q8_0 ? 34 : qt == QT_Q4_0 ? 18 : qt == QT_MXFP4 ? 17 : 210;
 }
 
 // byte offset of superblock record `sb` inside a row
@@ -99,6 +99,21 @@ __host__ __device__ inline int64_t q6k_d_record_off(int64_t row, int64_t sb, int
     return tile_off(QT_Q6_K, g, c, N, nsb) + (row - g * kRowGroup) * chunk_row_bytes(QT_Q6_K, c, nsb) +
            (q6k_d_off(sb, nsb) - rec_off(QT_Q6_K, c * kChunkRecs));
 }
+
+// MXFP4 helpers.  Scale byte e (e8m0) -> 2^(e - 128), the halved scale ggml pairs with its doubled e2m1
+// values {0, 1, 2, 3, 4, 6, 8, 12} and their negatives (codes 8..15).
+__host__ __device__ inline uint32_t e8m0_half_bits(uint32_t e) { return e < 2 ? (0x00200000u << e) : ((e - 1) << 23); }
+#ifdef __CUDACC__
+// four e2m1 codes (the four nibbles of sel's low 16 bits) -> four bytes 64 + value, by table look-up:
+// prmt copies a table byte, or, when the selector nibble's bit 3 is set, replicates that byte's top
+// bit (0 here): non-negative codes hit the first table, negative ones (sign bit flipped) the second.
+__device__ __forceinline__ uint32_t mxfp4_bytes(uint32_t sel) {
+    uint32_t pos, neg;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(pos) : "r"(0x43424140u), "r"(0x4C484644u), "r"(sel));
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(neg) : "r"(0x3D3E3F40u), "r"(0x34383A3Cu), "r"(sel ^ 0x8888u));
+    return pos | neg;
+}
+#endif
 
 // Device status word values (atomicMax'ed, so larger = more severe).
 enum : int {

@@ -68,7 +68,7 @@ constexpr int kMaxBStages = 4;
 // per-type shared-memory plan: the packed-record buffers differ in size, the activation ring takes
 // what is left of the 227 KB
 __host__ __device__ constexpr int wbuf_bytes(int qt) { return ((BM * rec_bytes(qt) + 1023) / 1024) * 1024; }
-__host__ __device__ constexpr int b_stages(int qt) { return (qt == QT_Q4_K || qt == QT_Q4_0) ? 4 : 3; }
+__host__ __device__ constexpr int b_stages(int qt) { return (qt == QT_Q4_K || qt == QT_Q4_0 || qt == QT_MXFP4) ? 4 : 3; }
 __host__ __device__ constexpr int bn_max(int qt) { return qt == QT_Q6_K ? 256 : 240; }     // widest token tile
 __host__ __device__ constexpr int b_stage_bytes(int qt) { return bn_max(qt) * BK * 2; }
 __host__ __device__ constexpr int smem_data_bytes(int qt) {
@@ -320,6 +320,33 @@ template <> struct Unit<QT_Q4_0> {
             word_affine<0x64>(w[2 * n + 1] & 0x0F0F0F0Fu, o_lo, s_lo, c_lo, o[4 * n + 2], o[4 * n + 3]);
             word_affine<0x54>(w[2 * n] & 0xF0F0F0F0u, o_hi, s_hi, c_hi, o[16 + 4 * n], o[16 + 4 * n + 1]);
             word_affine<0x54>(w[2 * n + 1] & 0xF0F0F0F0u, o_hi, s_hi, c_hi, o[16 + 4 * n + 2], o[16 + 4 * n + 3]);
+        }
+    }
+};
+
+// MXFP4: [8 scale bytes, 8 of padding][per block four words of eight e2m1 codes in weight order]; a look-up
+// gives the bytes 64 + value, read as the halves 1024 + 64 + value; the scale 2^(e - 128) multiplies exactly
+// as long as it is an fp16 number (2^-24 .. 2^15; products beyond fp16's range saturate to inf like any fp16 product)
+template <> struct Unit<QT_MXFP4> {
+    uint4 hdr, q0, q1;
+    __device__ __forceinline__ void load(uint32_t rec, uint32_t, int j) {
+        hdr = lds128(rec);
+        q0 = lds128(rec + 16 + 32 * j);
+        q1 = lds128(rec + 32 + 32 * j);
+    }
+    __device__ __forceinline__ void convert(int j, uint32_t (&o)[32]) const {
+        const uint32_t ew = (j >> 1) ? hdr.y : hdr.x;
+        const uint32_t ee = ew >> (16 * (j & 1));
+        const __half2 da = __float2half2_rn(__uint_as_float(e8m0_half_bits(ee & 0xFF)));
+        const __half2 db = __float2half2_rn(__uint_as_float(e8m0_half_bits((ee >> 8) & 0xFF)));
+        const __half2 o1088 = as_h2(0x64406440u);      // 1024 + 64
+        const uint32_t wa[4] = {q0.x, q0.y, q0.z, q0.w}, wb[4] = {q1.x, q1.y, q1.z, q1.w};
+#pragma unroll
+        for (int n = 0; n < 4; ++n) {     // chunk n = weights 8n .. 8n + 7 of block 2j; chunk 4 + n = those of block 2j + 1
+            word_scale<0x64>(mxfp4_bytes(wa[n]), o1088, da, o[4 * n], o[4 * n + 1]);
+            word_scale<0x64>(mxfp4_bytes(wa[n] >> 16), o1088, da, o[4 * n + 2], o[4 * n + 3]);
+            word_scale<0x64>(mxfp4_bytes(wb[n]), o1088, db, o[16 + 4 * n], o[16 + 4 * n + 1]);
+            word_scale<0x64>(mxfp4_bytes(wb[n] >> 16), o1088, db, o[16 + 4 * n + 2], o[16 + 4 * n + 3]);
         }
     }
 };
@@ -1513,6 +1540,7 @@ cudaError_t gemm_launch(const GemmLaunch &a, cudaStream_t st) {
         case QT_Q4_K: return use_ts ? launch_gemm_pair<QT_Q4_K, true>(p, maps, grid2, st) : launch_gemm_pair<QT_Q4_K, false>(p, maps, grid2, st);
         case QT_Q5_K: return use_ts ? launch_gemm_pair<QT_Q5_K, true>(p, maps, grid2, st) : launch_gemm_pair<QT_Q5_K, false>(p, maps, grid2, st);
         case QT_Q4_0: return use_ts ? launch_gemm_pair<QT_Q4_0, true>(p, maps, grid2, st) : launch_gemm_pair<QT_Q4_0, false>(p, maps, grid2, st);
+        case QT_MXFP4: return use_ts ? launch_gemm_pair<QT_MXFP4, true>(p, maps, grid2, st) : launch_gemm_pair<QT_MXFP4, false>(p, maps, grid2, st);
         case QT_Q6_K: return use_ts ? launch_gemm_pair<QT_Q6_K, true>(p, maps, grid2, st) : launch_gemm_pair<QT_Q6_K, false>(p, maps, grid2, st);
         case QT_Q8_0: return use_ts ? launch_gemm_pair<QT_Q8_0, true>(p, maps, grid2, st) : launch_gemm_pair<QT_Q8_0, false>(p, maps, grid2, st);
         default: return cudaErrorInvalidValue;
@@ -1524,6 +1552,7 @@ cudaError_t gemm_launch(const GemmLaunch &a, cudaStream_t st) {
     case QT_Q4_K: e = launch_gemm<QT_Q4_K>(p, maps, grid, st); break;
     case QT_Q5_K: e = launch_gemm<QT_Q5_K>(p, maps, grid, st); break;
     case QT_Q4_0: e = launch_gemm<QT_Q4_0>(p, maps, grid, st); break;
+    case QT_MXFP4: e = launch_gemm<QT_MXFP4>(p, maps, grid, st); break;
     case QT_Q6_K: e = launch_gemm<QT_Q6_K>(p, maps, grid, st); break;
     case QT_Q8_0: e = launch_gemm<QT_Q8_0>(p, maps, grid, st); break;
     default: return cudaErrorInvalidValue;

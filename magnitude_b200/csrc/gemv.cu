@@ -52,7 +52,7 @@ constexpr int kMaxDepth = 8;
 constexpr int KC = kChunkRecs;   // superblock records per chunk: 32 units of 64 weights, one per lane
 constexpr int R = kRowGroup;     // rows per item
 
-constexpr int chunk_bytes(int qt) { return (qt == QT_Q4_K || qt == QT_Q4_0) ? KC * 144 : qt == QT_Q5_K ? KC * 176 : qt == QT_Q8_0 ? KC * 272 : 1680; }
+constexpr int chunk_bytes(int qt) { return (qt == QT_Q4_K || qt == QT_Q4_0 || qt == QT_MXFP4) ? KC * 144 : qt == QT_Q5_K ? KC * 176 : qt == QT_Q8_0 ? KC * 272 : 1680; }
 
 struct StreamParams {
     const StreamJob *jobs;   // device table, or nullptr when the single job is `inl`
@@ -217,7 +217,7 @@ __device__ __forceinline__ void item_dot(int nsb, uint32_t sl, int stride, int s
 
 // TYPES is the set of block types the launch's jobs use (bit 0 Q4_K, bit 1 Q6_K, bit 2 Q8_0): a
 // single-type launch compiles only that type's unpacking, which keeps it free of register spills.
-constexpr int TY_Q4K = 1, TY_Q6K = 2, TY_Q80 = 4, TY_Q5K = 8, TY_Q40 = 16;
+constexpr int TY_Q4K = 1, TY_Q6K = 2, TY_Q80 = 4, TY_Q5K = 8, TY_Q40 = 16, TY_MX4 = 32;
 
 // FUSED: some job of the launch has a fused epilogue (SWIGLU, ACCUM); launches without any run the
 // instantiation that carries none of that code.
@@ -659,6 +659,8 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1) stream_kernel(const S
                     item_dot<QT_Q5_K, MT>(nsb, sl, cb, sb0, lsb, j, nr, xv, units16, whole, acc, flush_pending);
                 else if ((TYPES & TY_Q40) && (TYPES == TY_Q40 || qt == QT_Q4_0))
                     item_dot<QT_Q4_0, MT>(nsb, sl, cb, sb0, lsb, j, nr, xv, units16, whole, acc, flush_pending);
+                else if ((TYPES & TY_MX4) && (TYPES == TY_MX4 || qt == QT_MXFP4))
+                    item_dot<QT_MXFP4, MT>(nsb, sl, cb, sb0, lsb, j, nr, xv, units16, whole, acc, flush_pending);
                 else if (TYPES & TY_Q80)
                     item_dot<QT_Q8_0, MT>(nsb, sl, cb, sb0, lsb, j, nr, xv, units16, whole, acc, flush_pending);
             }
@@ -989,18 +991,19 @@ cudaError_t stream_launch_one(const StreamLaunch &a, cudaStream_t st) {
     int types = 0;
     for (int i = 0; i < a.njobs; ++i) {
         const int qt = a.jobs_host[i].qt;
-        types |= qt == QT_Q4_K ? TY_Q4K : qt == QT_Q6_K ? TY_Q6K : qt == QT_Q8_0 ? TY_Q80 : qt == QT_Q5_K ? TY_Q5K : qt == QT_Q4_0 ? TY_Q40 : 32;
+        types |= qt == QT_Q4_K ? TY_Q4K : qt == QT_Q6_K ? TY_Q6K : qt == QT_Q8_0 ? TY_Q80 : qt == QT_Q5_K ? TY_Q5K : qt == QT_Q4_0 ? TY_Q40 : qt == QT_MXFP4 ? TY_MX4 : 64;
     }
-    if (types & 32) return cudaErrorInvalidValue;
+    if (types & 64) return cudaErrorInvalidValue;
     switch (types) {
     case TY_Q4K: return launch_m<TY_Q4K>(a, p, grid, st);
     case TY_Q6K: return launch_m<TY_Q6K>(a, p, grid, st);
     case TY_Q80: return launch_m<TY_Q80>(a, p, grid, st);
     case TY_Q5K: return launch_m<TY_Q5K>(a, p, grid, st);
     case TY_Q40: return launch_m<TY_Q40>(a, p, grid, st);
+    case TY_MX4: return launch_m<TY_MX4>(a, p, grid, st);
     default:
-        if (!(types & (TY_Q5K | TY_Q40))) return launch_m<TY_Q4K | TY_Q6K | TY_Q80>(a, p, grid, st);
-        return launch_m<TY_Q4K | TY_Q6K | TY_Q80 | TY_Q5K | TY_Q40>(a, p, grid, st);
+        if (!(types & (TY_Q5K | TY_Q40 | TY_MX4))) return launch_m<TY_Q4K | TY_Q6K | TY_Q80>(a, p, grid, st);
+        return launch_m<TY_Q4K | TY_Q6K | TY_Q80 | TY_Q5K | TY_Q40 | TY_MX4>(a, p, grid, st);
     }
 }
 

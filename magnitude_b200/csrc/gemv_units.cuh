@@ -83,7 +83,7 @@ template <int QT> struct XRegs {
         } else {
             const uint2 s = lds64(xv.sx + gu * 8);
             sx[0] = __uint_as_float(s.x); sx[1] = __uint_as_float(s.y);
-            if (QT == QT_Q4_K || QT == QT_Q5_K || QT == QT_Q4_0) {
+            if (QT == QT_Q4_K || QT == QT_Q5_K || QT == QT_Q4_0 || QT == QT_MXFP4) {
                 const uint2 i = lds64(xv.isum + gu * 8);
                 is[0] = (int)i.x; is[1] = (int)i.y;
             }
@@ -236,6 +236,45 @@ template <> struct WRegs<QT_Q4_0> {
         }
         const float fa = (float)((hA * 256 + lA) - 8 * xr.is[0]);
         const float fb = (float)(((hB * 256 + lB) >> 4) - 8 * xr.is[1]);     // hi held 16 * nibble: exact shift
+        return xr.sx[0] * (dA * fa) + xr.sx[1] * (dB * fb);
+    }
+};
+
+// MXFP4 record on the device: the eight scale bytes of its native blocks (16 bytes with padding), then per
+// block four words of eight e2m1 codes in weight order.  A look-up turns four codes into the bytes
+// 64 + value, so a block's dot is 2^(e - 128) (sum b x - 64 sum x) with both sums integers.
+template <> struct WRegs<QT_MXFP4> {
+    uint32_t a[8], b[8];     // bytes 64 + value of block 2j (a) and block 2j + 1 (b), four weights per word
+    float dA, dB;
+    __device__ __forceinline__ void load(uint32_t rec, int j) {
+        const uint4 qa = lds128(rec + 16 + 32 * j);
+        const uint4 qb = lds128(rec + 32 + 32 * j);
+        const uint32_t ee = lds32(rec + 4 * (j >> 1)) >> (16 * (j & 1));
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            a[2 * i] = mxfp4_bytes(word_of(qa, i));
+            a[2 * i + 1] = mxfp4_bytes(word_of(qa, i) >> 16);
+            b[2 * i] = mxfp4_bytes(word_of(qb, i));
+            b[2 * i + 1] = mxfp4_bytes(word_of(qb, i) >> 16);
+        }
+        dA = __uint_as_float(e8m0_half_bits(ee & 0xFF));
+        dB = __uint_as_float(e8m0_half_bits((ee >> 8) & 0xFF));
+    }
+    __device__ __forceinline__ float dot(const XRegs<QT_MXFP4> &xr) const {
+        int hA = 0, lA = 0, hB = 0, lB = 0;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            hA = dp4a_us(a[i], word_of(xr.h[0], i), hA);
+            lA = dp4a_us(a[i], word_of(xr.l[0], i), lA);
+            hA = dp4a_us(a[4 + i], word_of(xr.h[1], i), hA);
+            lA = dp4a_us(a[4 + i], word_of(xr.l[1], i), lA);
+            hB = dp4a_us(b[i], word_of(xr.h[2], i), hB);
+            lB = dp4a_us(b[i], word_of(xr.l[2], i), lB);
+            hB = dp4a_us(b[4 + i], word_of(xr.h[3], i), hB);
+            lB = dp4a_us(b[4 + i], word_of(xr.l[3], i), lB);
+        }
+        const float fa = (float)((hA * 256 + lA) - 64 * xr.is[0]);
+        const float fb = (float)((hB * 256 + lB) - 64 * xr.is[1]);
         return xr.sx[0] * (dA * fa) + xr.sx[1] * (dB * fb);
     }
 };

@@ -38,6 +38,22 @@ void repack_host(int qt, int64_t K, const uint8_t *gguf, int64_t r0, int64_t n, 
                         q[l] |= (b & 1) ? (uint8_t)(v << 4) : v;
                     }
                 }
+            } else if (qt == QT_MXFP4) {
+                // eight native blocks -> [8 scale bytes][8 zero bytes][per block four words of eight codes each, code n
+                // of word i = weight 8 i + n]: the order a table look-up by prmt wants; K padding: zero codes
+                const int64_t nblk = K / 32;
+                memset(rec, 0, 144);
+                for (int b = 0; b < 8; ++b) {
+                    const int64_t blk = (sb0 + sb) * 8 + b;
+                    if (blk >= nblk) continue;
+                    const uint8_t *src = s + blk * 17;
+                    rec[b] = src[0];
+                    uint8_t *q = rec + 16 + 16 * b;
+                    for (int l = 0; l < 32; ++l) {
+                        const uint8_t v = l < 16 ? (src[1 + l] & 0xF) : (src[1 + l - 16] >> 4);
+                        q[l >> 1] |= (l & 1) ? (uint8_t)(v << 4) : v;
+                    }
+                }
             } else if (qt == QT_Q8_0) {
                 const int64_t nblk = K / 32;
                 for (int b = 0; b < 8; ++b) {
@@ -90,6 +106,14 @@ __global__ void __launch_bounds__(256) dequant_kernel(const uint8_t *__restrict_
         const uint8_t byte = rec[16 + 32 * (b >> 1) + (t & 31)];
         const int q = (b & 1) ? (byte >> 4) : (byte & 0xF);
         v = __fmul_rn((float)(q - 8), d);
+    } else if (QT == QT_MXFP4) {
+        const uint8_t *rec = w + record_off(QT, row, sb, N, nsb);
+        const int b = t >> 5, l = t & 31;
+        const float d = __uint_as_float(e8m0_half_bits(rec[b]));
+        const uint8_t byte = rec[16 + 16 * b + (l >> 1)];
+        const int code = (l & 1) ? (byte >> 4) : (byte & 0xF);
+        const int mag = (0x0C08060403020100ull >> (8 * (code & 7))) & 0xFF;
+        v = __fmul_rn((float)((code & 8) ? -mag : mag), d);
     } else if (QT == QT_Q8_0) {
         const uint8_t *rec = w + record_off(QT, row, sb, N, nsb);
         const float d = half_bits_to_float(*reinterpret_cast<const uint16_t *>(rec + 256 + 2 * (t >> 5)));
@@ -121,6 +145,7 @@ cudaError_t dequant_launch(int qt, const uint8_t *w, int64_t N, int64_t K, int64
     case QT_Q5_K: dequant_kernel<QT_Q5_K><<<(unsigned)blocks, 256, 0, st>>>(w, N, K, nsb, out); break;
     case QT_Q8_0: dequant_kernel<QT_Q8_0><<<(unsigned)blocks, 256, 0, st>>>(w, N, K, nsb, out); break;
     case QT_Q4_0: dequant_kernel<QT_Q4_0><<<(unsigned)blocks, 256, 0, st>>>(w, N, K, nsb, out); break;
+    case QT_MXFP4: dequant_kernel<QT_MXFP4><<<(unsigned)blocks, 256, 0, st>>>(w, N, K, nsb, out); break;
     case QT_Q6_K: dequant_kernel<QT_Q6_K><<<(unsigned)blocks, 256, 0, st>>>(w, N, K, nsb, out); break;
     default: return cudaErrorInvalidValue;
     }

@@ -1,4 +1,4 @@
-// The format's reference quantizer, fp32 -> Q4_0 / Q8_0 / Q4_K / Q5_K / Q6_K (host code, threads over rows):
+// The format's reference quantizer, fp32 -> Q4_0 / Q8_0 / Q4_K / Q5_K / Q6_K / MXFP4 (host code, threads over rows):
 // what a model converter runs once per tensor (reference row "quantizer fp32 -> blocks", upstream of
 // LlamaModel::load_from_file, inference/crates/icn-engine/src/lib.rs:972).  Restated from the
 // published algorithm of the GGUF reference implementation: Q8_0 takes d = max|w| / 127; Q4_K fits
@@ -15,6 +15,7 @@
 #include <vector>
 
 #include "../../include/b200q.h"
+#include "common.cuh"
 
 namespace {
 
@@ -101,6 +102,41 @@ void row_q4_0(const float *x, uint8_t *y, int64_t k) {
             const uint8_t a = (uint8_t)std::min(15, (int)(uint8_t)(int8_t)(x[j] * id + 8.5f));
             const uint8_t c = (uint8_t)std::min(15, (int)(uint8_t)(int8_t)(x[16 + j] * id + 8.5f));
             y[2 + j] = (uint8_t)(a | (c << 4));
+        }
+    }
+}
+
+// ---- MXFP4: [e8m0 scale byte][16 bytes of e2m1 codes, weights 0..15 low nibbles, 16..31 high] ----------
+// e = floor(log2 max|x|) - 2 + 127 (from the float's exponent), each value to the nearest 2^(e - 128) * kvalue,
+// the first of equally near ones
+void row_mxfp4(const float *x, uint8_t *y, int64_t k) {
+    static const int8_t kv[16] = {0, 1, 2, 3, 4, 6, 8, 12, 0, -1, -2, -3, -4, -6, -8, -12};
+    for (int64_t b = 0; b < k / 32; ++b, x += 32, y += 17) {
+        float amax = 0;
+        for (int j = 0; j < 32; ++j) amax = std::max(amax, fabsf(x[j]));
+        uint8_t e = 0;
+        if (amax > 0) {
+            int ex;
+            frexpf(amax, &ex);
+            e = (uint8_t)std::min(255, std::max(0, ex - 1 - 2 + 127));
+        }
+        const uint32_t bits = b200q::e8m0_half_bits(e);
+        float d;
+        memcpy(&d, &bits, 4);
+        y[0] = e;
+        for (int j = 0; j < 16; ++j) {
+            int q[2];
+            for (int h = 0; h < 2; ++h) {
+                const float v = x[16 * h + j];
+                int best = 0;
+                float best_err = fabsf((float)kv[0] * d - v);
+                for (int c = 1; c < 16; ++c) {
+                    const float err = fabsf((float)kv[c] * d - v);
+                    if (err < best_err) best = c, best_err = err;
+                }
+                q[h] = best;
+            }
+            y[1 + j] = (uint8_t)(q[0] | (q[1] << 4));
         }
     }
 }
@@ -321,8 +357,8 @@ void row_q6_k(const float *x, uint8_t *y, int64_t k) {
 extern "C" b200q_status b200q_quantize(int32_t type, const float *weights, int64_t N, int64_t K, void *packed_out, size_t out_bytes,
                                        int32_t threads) {
     const int64_t want = b200q_tensor_storage_bytes(type, N < 0 || K < 0 ? -1 : N * K);
-    if ((type != B200Q_TYPE_Q4_0 && type != B200Q_TYPE_Q8_0 && type != B200Q_TYPE_Q4_K && type != B200Q_TYPE_Q5_K && type != B200Q_TYPE_Q6_K) || N < 0 || K < 0) return B200Q_ERR_INVALID_CONFIG;
-    const int64_t blk = (type == B200Q_TYPE_Q8_0 || type == B200Q_TYPE_Q4_0) ? 32 : 256, bb = type == B200Q_TYPE_Q4_0 ? 18 : type == B200Q_TYPE_Q8_0 ? 34 : type == B200Q_TYPE_Q4_K ? 144 : type == B200Q_TYPE_Q5_K ? 176 : 210;
+    if ((type != B200Q_TYPE_MXFP4 && type != B200Q_TYPE_Q4_0 && type != B200Q_TYPE_Q8_0 && type != B200Q_TYPE_Q4_K && type != B200Q_TYPE_Q5_K && type != B200Q_TYPE_Q6_K) || N < 0 || K < 0) return B200Q_ERR_INVALID_CONFIG;
+    const int64_t blk = (type == B200Q_TYPE_Q8_0 || type == B200Q_TYPE_Q4_0 || type == B200Q_TYPE_MXFP4) ? 32 : 256, bb = type == B200Q_TYPE_MXFP4 ? 17 : type == B200Q_TYPE_Q4_0 ? 18 : type == B200Q_TYPE_Q8_0 ? 34 : type == B200Q_TYPE_Q4_K ? 144 : type == B200Q_TYPE_Q5_K ? 176 : 210;
     if (K % blk || want < 0 || (int64_t)out_bytes != want) return B200Q_ERR_INVALID_CONFIG;
     if (N * K == 0) return B200Q_OK;
     if (!weights || !packed_out) return B200Q_ERR_INVALID_CONFIG;
@@ -335,6 +371,7 @@ extern "C" b200q_status b200q_quantize(int32_t type, const float *weights, int64
             uint8_t *y = reinterpret_cast<uint8_t *>(packed_out) + r * rb;
             if (type == B200Q_TYPE_Q8_0) row_q8_0(x, y, K);
             else if (type == B200Q_TYPE_Q4_0) row_q4_0(x, y, K);
+            else if (type == B200Q_TYPE_MXFP4) row_mxfp4(x, y, K);
             else if (type == B200Q_TYPE_Q4_K) row_q4_k(x, y, K);
             else if (type == B200Q_TYPE_Q5_K) row_q5_k(x, y, K);
             else row_q6_k(x, y, K);

@@ -63,7 +63,7 @@ constexpr int kRedDepth = 4;                      // partial-tile sets in flight
 // shared-memory distance between the rows of a stage: the chunk's bytes per row, padded so that the
 // 8 rows a fragment load touches start 32 bytes apart modulo 128 (Q6_K reads 4-byte words and is
 // conflict-free at its natural 1680)
-__host__ __device__ constexpr int sk_row_stride(int qt) { return (qt == QT_Q4_K || qt == QT_Q4_0) ? 1184 : qt == QT_Q5_K ? 1440 : qt == QT_Q8_0 ? 2208 : 1680; }
+__host__ __device__ constexpr int sk_row_stride(int qt) { return (qt == QT_Q4_K || qt == QT_Q4_0 || qt == QT_MXFP4) ? 1184 : qt == QT_Q5_K ? 1440 : qt == QT_Q8_0 ? 2208 : 1680; }
 __host__ __device__ constexpr int sk_subblocks(int qt) { return qt == QT_Q6_K ? 16 : 8; }   // scale blocks per record
 
 struct SkJob {
@@ -309,6 +309,58 @@ template <int NT> struct SkRecord<QT_Q4_0, NT> {
     static __device__ __forceinline__ void run(uint32_t recA, uint32_t recB, int g, int t, const uint32_t (&B)[32 * NT],
                                                uint32_t sct, uint32_t xst, float (&acc)[NT][4]) {
         SkRecord<QT_Q4_K, NT>::run(recA, recB, g, t, B, sct, xst, acc);
+    }
+};
+
+// MXFP4: [8 scale bytes, 8 of padding][per block four words of eight e2m1 codes in weight order].  A look-up
+// gives the bytes 64 + value, which sit exactly in the bf16 form 128 + b: p = 2^(e - 128), the X term carries 192.
+template <int NT> struct SkRecord<QT_MXFP4, NT> {
+    static constexpr int QB = 8 / NT;
+    static __device__ __forceinline__ void scales(uint32_t rec_row, uint32_t, int lane, uint32_t sct) {
+        const int row = lane >> 1, half = lane & 1;
+        const uint32_t ee = ldsn32(rec_row + 4 * half);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float d = __uint_as_float(e8m0_half_bits((ee >> (8 * i)) & 0xFF));
+            sts_f2(sct + ((4 * half + i) * kSkRows + row) * 8, d, -192.f * d);
+        }
+    }
+    static __device__ __forceinline__ void run(uint32_t recA, uint32_t recB, int g, int t, const uint32_t (&B)[32 * NT],
+                                               uint32_t sct, uint32_t xst, float (&acc)[NT][4]) {
+#pragma unroll
+        for (int b0 = 0; b0 < 8; b0 += QB) {
+            uint32_t wa[QB], wb[QB];     // lane t: the codes of weights 8t .. 8t + 7 of each block
+#pragma unroll
+            for (int q = 0; q < QB; ++q) {
+                wa[q] = ldsn32(recA + 16 + 16 * (b0 + q) + 4 * t);
+                wb[q] = ldsn32(recB + 16 + 16 * (b0 + q) + 4 * t);
+            }
+            float c[QB][NT][4];
+#pragma unroll
+            for (int s = 0; s < 2; ++s) {
+#pragma unroll
+                for (int q = 0; q < QB; ++q) {
+                    const int sb = b0 + q;
+                    const uint32_t ba = mxfp4_bytes(wa[q] >> (16 * s)), bb = mxfp4_bytes(wb[q] >> (16 * s));
+                    // (b0, b2) and (b1, b3) as bf16 pairs 128 + b
+                    const uint32_t a0 = __byte_perm(ba, 0x43434343u, 0x4240), a2 = __byte_perm(ba, 0x43434343u, 0x4341);
+                    const uint32_t a1 = __byte_perm(bb, 0x43434343u, 0x4240), a3 = __byte_perm(bb, 0x43434343u, 0x4341);
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt) {
+                        const int bi = ((nt * 8 + sb) * 2 + s) * 2;
+                        if (s == 0) mma_first(c[q][nt], a0, a1, a2, a3, B[bi], B[bi + 1]);
+                        else mma_more(c[q][nt], a0, a1, a2, a3, B[bi], B[bi + 1]);
+                    }
+                }
+            }
+#pragma unroll
+            for (int q = 0; q < QB; ++q) {
+                const int sb = b0 + q;
+                const float2 pa = ldsn_f2(sct + (sb * kSkRows + g) * 8), pb = ldsn_f2(sct + (sb * kSkRows + g + 8) * 8);
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) fold(acc[nt], c[q][nt], pa, pb, ldsn_f2(xst + ((sb * NT + nt) * 8 + 2 * t) * 4));
+            }
+        }
     }
 };
 
@@ -945,6 +997,8 @@ cudaError_t skinny_set_launch(const SkinnySet *set, cudaStream_t st) {
     switch (set->qt * 4 + set->NT) {
     case QT_Q4_K * 4 + 1: e = sk_launch_t<QT_Q4_K, 1>(set->p, set->grid, set->smem_limit, st); break;
     case QT_Q4_K * 4 + 2: e = sk_launch_t<QT_Q4_K, 2>(set->p, set->grid, set->smem_limit, st); break;
+    case QT_MXFP4 * 4 + 1: e = sk_launch_t<QT_MXFP4, 1>(set->p, set->grid, set->smem_limit, st); break;
+    case QT_MXFP4 * 4 + 2: e = sk_launch_t<QT_MXFP4, 2>(set->p, set->grid, set->smem_limit, st); break;
     case QT_Q4_0 * 4 + 1: e = sk_launch_t<QT_Q4_0, 1>(set->p, set->grid, set->smem_limit, st); break;
     case QT_Q4_0 * 4 + 2: e = sk_launch_t<QT_Q4_0, 2>(set->p, set->grid, set->smem_limit, st); break;
     case QT_Q5_K * 4 + 1: e = sk_launch_t<QT_Q5_K, 1>(set->p, set->grid, set->smem_limit, st); break;

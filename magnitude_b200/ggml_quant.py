@@ -11,8 +11,8 @@ from __future__ import annotations
 
 import numpy as np
 
-Q4_0, Q8_0, Q4_K, Q5_K, Q6_K = 2, 8, 12, 13, 14
-BLOCK = {Q4_0: (32, 18), Q8_0: (32, 34), Q4_K: (256, 144), Q5_K: (256, 176), Q6_K: (256, 210)}
+Q4_0, Q8_0, Q4_K, Q5_K, Q6_K, MXFP4 = 2, 8, 12, 13, 14, 39
+BLOCK = {MXFP4: (32, 17), Q4_0: (32, 18), Q8_0: (32, 34), Q4_K: (256, 144), Q5_K: (256, 176), Q6_K: (256, 210)}
 
 
 def _check(w: np.ndarray, blk: int) -> np.ndarray:

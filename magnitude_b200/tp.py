@@ -12,7 +12,7 @@ import numpy as np
 from . import _binding as B
 from .projection import shard_range
 
-BLOCK = {B.TYPE_Q4_0: (32, 18), B.TYPE_Q8_0: (32, 34), B.TYPE_Q4_K: (256, 144), B.TYPE_Q5_K: (256, 176), B.TYPE_Q6_K: (256, 210)}
+BLOCK = {B.TYPE_MXFP4: (32, 17), B.TYPE_Q4_0: (32, 18), B.TYPE_Q8_0: (32, 34), B.TYPE_Q4_K: (256, 144), B.TYPE_Q5_K: (256, 176), B.TYPE_Q6_K: (256, 210)}
 
 
 def shard_gguf(qtype: int, packed: np.ndarray, n: int, k: int, split: int, rank: int, world: int,

@@ -1,5 +1,5 @@
 /*
- * CPU oracle for the GGUF block-quantized projection matmul (Q4_0 / Q8_0 / Q4_K / Q5_K / Q6_K).
+ * CPU oracle for the GGUF block-quantized projection matmul (Q4_0 / Q8_0 / Q4_K / Q5_K / Q6_K / MXFP4).
  *
  * TEST INFRASTRUCTURE ONLY.  Nothing in the shipped library links, loads or calls this
  * file; it exists so the tests, the smoke check and the bench's CPU-baseline leg have an
@@ -25,6 +25,7 @@
  *   operation, no fused multiply-add (build with -ffp-contract=off):
  *     Q8_0:  w = d * q
  *     Q4_0:  w = (q - 8) * d
+ *     MXFP4: w = kvalue[q] * 2^(e - 128)
  *     Q4_K:  w = (d * sc) * q - (dmin * m)
  *     Q5_K:  w = (d * sc) * q - (dmin * m)   with q = nibble + 16 * high bit
  *     Q6_K:  w = (d * sc) * q         with q in [-32, 31]
@@ -45,11 +46,12 @@
 #define K_SCALE_SIZE 12
 #define GROUP_MAX_EPS 1e-15f
 
-enum { GGQ_TYPE_Q4_0 = 2, GGQ_TYPE_Q8_0 = 8, GGQ_TYPE_Q4_K = 12, GGQ_TYPE_Q5_K = 13, GGQ_TYPE_Q6_K = 14 };
+enum { GGQ_TYPE_Q4_0 = 2, GGQ_TYPE_Q8_0 = 8, GGQ_TYPE_Q4_K = 12, GGQ_TYPE_Q5_K = 13, GGQ_TYPE_Q6_K = 14, GGQ_TYPE_MXFP4 = 39 };
 
 #pragma pack(push, 1)
 typedef struct { uint16_t d; int8_t qs[QK8_0]; } blk_q8_0;                 /* 34 B  */
 typedef struct { uint16_t d; uint8_t qs[QK8_0 / 2]; } blk_q4_0;            /* 18 B  */
+typedef struct { uint8_t e; uint8_t qs[QK8_0 / 2]; } blk_mxfp4;            /* 17 B  */
 typedef struct { uint16_t d; uint16_t dmin; uint8_t scales[K_SCALE_SIZE];
                  uint8_t qs[QK_K / 2]; } blk_q4_K;                          /* 144 B */
 typedef struct { uint16_t d; uint16_t dmin; uint8_t scales[K_SCALE_SIZE];
@@ -61,6 +63,7 @@ typedef struct { float d; int8_t qs[QK_K]; int16_t bsums[QK_K / 16]; } blk_q8_K;
 
 _Static_assert(sizeof(blk_q8_0) == 34, "q8_0 size");
 _Static_assert(sizeof(blk_q4_0) == 18, "q4_0 size");
+_Static_assert(sizeof(blk_mxfp4) == 17, "mxfp4 size");
 _Static_assert(sizeof(blk_q4_K) == 144, "q4_K size");
 _Static_assert(sizeof(blk_q5_K) == 176, "q5_K size");
 _Static_assert(sizeof(blk_q6_K) == 210, "q6_K size");
@@ -154,12 +157,13 @@ void ggq_f16_to_f32(const uint16_t *src, float *dst, int64_t n) {
 /* ------------------------------------------------------------------ sizes */
 
 int64_t ggq_block_elems(int type) {
-    return (type == GGQ_TYPE_Q8_0 || type == GGQ_TYPE_Q4_0) ? QK8_0 : (type == GGQ_TYPE_Q4_K || type == GGQ_TYPE_Q5_K || type == GGQ_TYPE_Q6_K) ? QK_K : 0;
+    return (type == GGQ_TYPE_Q8_0 || type == GGQ_TYPE_Q4_0 || type == GGQ_TYPE_MXFP4) ? QK8_0 : (type == GGQ_TYPE_Q4_K || type == GGQ_TYPE_Q5_K || type == GGQ_TYPE_Q6_K) ? QK_K : 0;
 }
 int64_t ggq_block_bytes(int type) {
     switch (type) {
     case GGQ_TYPE_Q8_0: return sizeof(blk_q8_0);
     case GGQ_TYPE_Q4_0: return sizeof(blk_q4_0);
+    case GGQ_TYPE_MXFP4: return sizeof(blk_mxfp4);
     case GGQ_TYPE_Q4_K: return sizeof(blk_q4_K);
     case GGQ_TYPE_Q5_K: return sizeof(blk_q5_K);
     case GGQ_TYPE_Q6_K: return sizeof(blk_q6_K);
@@ -214,6 +218,26 @@ static void dequant_row_q4_0(const blk_q4_0 *x, float *y, int64_t k) {
             int x1 = (x[i].qs[j] >> 4) - 8;
             y[i * QK8_0 + j] = (float)x0 * d;
             y[i * QK8_0 + j + QK8_0 / 2] = (float)x1 * d;
+        }
+    }
+}
+
+/* MXFP4 (OCP microscaling): 32 e2m1 values share one e8m0 scale.  ggml keeps the e2m1 values doubled
+ * (kvalues_mxfp4) and halves the scale instead: d = 2^(e - 128) (GGML_E8M0_TO_FP32_HALF), w = kvalue[q] * d. */
+static const int8_t kvalues_mxfp4[16] = {0, 1, 2, 3, 4, 6, 8, 12, 0, -1, -2, -3, -4, -6, -8, -12};
+static float e8m0_to_f32_half(uint8_t e) {
+    uint32_t bits = e < 2 ? (0x00200000u << e) : ((uint32_t)(e - 1) << 23);
+    float f;
+    memcpy(&f, &bits, 4);
+    return f;
+}
+static void dequant_row_mxfp4(const blk_mxfp4 *x, float *y, int64_t k) {
+    int64_t nb = k / QK8_0;
+    for (int64_t i = 0; i < nb; ++i) {
+        float d = e8m0_to_f32_half(x[i].e);
+        for (int j = 0; j < QK8_0 / 2; ++j) {
+            y[i * QK8_0 + j] = (float)kvalues_mxfp4[x[i].qs[j] & 0x0F] * d;
+            y[i * QK8_0 + j + QK8_0 / 2] = (float)kvalues_mxfp4[x[i].qs[j] >> 4] * d;
         }
     }
 }
@@ -311,6 +335,7 @@ int ggq_dequantize(int type, const void *packed, float *out, int64_t n_rows, int
         float *y = out + r * k;
         if (type == GGQ_TYPE_Q8_0) dequant_row_q8_0((const blk_q8_0 *)row, y, k);
         else if (type == GGQ_TYPE_Q4_0) dequant_row_q4_0((const blk_q4_0 *)row, y, k);
+        else if (type == GGQ_TYPE_MXFP4) dequant_row_mxfp4((const blk_mxfp4 *)row, y, k);
         else if (type == GGQ_TYPE_Q4_K) dequant_row_q4_K((const blk_q4_K *)row, y, k);
         else if (type == GGQ_TYPE_Q5_K) dequant_row_q5_K((const blk_q5_K *)row, y, k);
         else dequant_row_q6_K((const blk_q6_K *)row, y, k);
@@ -358,6 +383,45 @@ static void quant_row_q4_0(const float *x, blk_q4_0 *y, int64_t k) {
             xi0 = xi0 > 15 ? 15 : xi0;
             xi1 = xi1 > 15 ? 15 : xi1;
             y[i].qs[j] = (uint8_t)(xi0 | (xi1 << 4));
+        }
+    }
+}
+
+/* ggml quantize_row_mxfp4_ref: e = floor(log2(max|x|)) - 2 + 127, each value to the nearest d * kvalue
+ * (the first of equally near ones).  floor(log2) is taken from the float's exponent here. */
+static void quant_row_mxfp4(const float *x, blk_mxfp4 *y, int64_t k) {
+    int64_t nb = k / QK8_0;
+    for (int64_t i = 0; i < nb; ++i) {
+        float amax = 0.0f;
+        for (int j = 0; j < QK8_0; ++j) {
+            float v = fabsf(x[i * QK8_0 + j]);
+            if (amax < v) amax = v;
+        }
+        int ex = 0;
+        uint8_t e = 0;
+        if (amax > 0.0f) {
+            frexpf(amax, &ex);                 /* amax = m * 2^ex, m in [0.5, 1): floor(log2 amax) = ex - 1 */
+            int ev = ex - 1 - 2 + 127;
+            e = (uint8_t)(ev < 0 ? 0 : ev > 255 ? 255 : ev);
+        }
+        float d = e8m0_to_f32_half(e);
+        y[i].e = e;
+        for (int j = 0; j < QK8_0 / 2; ++j) {
+            uint8_t q[2];
+            for (int h = 0; h < 2; ++h) {
+                float v = x[i * QK8_0 + h * (QK8_0 / 2) + j];
+                int best = 0;
+                float best_err = fabsf((float)kvalues_mxfp4[0] * d - v);
+                for (int c = 1; c < 16; ++c) {
+                    float err = fabsf((float)kvalues_mxfp4[c] * d - v);
+                    if (err < best_err) {
+                        best = c;
+                        best_err = err;
+                    }
+                }
+                q[h] = (uint8_t)best;
+            }
+            y[i].qs[j] = (uint8_t)(q[0] | (q[1] << 4));
         }
     }
 }
@@ -675,6 +739,7 @@ int ggq_quantize(int type, const float *src, void *packed, int64_t n_rows, int64
         const float *x = src + r * k;
         if (type == GGQ_TYPE_Q8_0) quant_row_q8_0(x, (blk_q8_0 *)row, k);
         else if (type == GGQ_TYPE_Q4_0) quant_row_q4_0(x, (blk_q4_0 *)row, k);
+        else if (type == GGQ_TYPE_MXFP4) quant_row_mxfp4(x, (blk_mxfp4 *)row, k);
         else if (type == GGQ_TYPE_Q4_K) quant_row_q4_K(x, (blk_q4_K *)row, k);
         else if (type == GGQ_TYPE_Q5_K) quant_row_q5_K(x, (blk_q5_K *)row, k);
         else quant_row_q6_K(x, (blk_q6_K *)row, k);
@@ -699,6 +764,7 @@ int ggq_matmul_exact(int type, const void *packed, int64_t n, int64_t k, const f
             const void *row = p + r * rb;
             if (type == GGQ_TYPE_Q8_0) dequant_row_q8_0((const blk_q8_0 *)row, wf, k);
             else if (type == GGQ_TYPE_Q4_0) dequant_row_q4_0((const blk_q4_0 *)row, wf, k);
+            else if (type == GGQ_TYPE_MXFP4) dequant_row_mxfp4((const blk_mxfp4 *)row, wf, k);
             else if (type == GGQ_TYPE_Q4_K) dequant_row_q4_K((const blk_q4_K *)row, wf, k);
             else if (type == GGQ_TYPE_Q5_K) dequant_row_q5_K((const blk_q5_K *)row, wf, k);
             else dequant_row_q6_K((const blk_q6_K *)row, wf, k);
@@ -782,6 +848,21 @@ static float vec_dot_q4_0_q8_0(int64_t k, const blk_q4_0 *x, const blk_q8_0 *y) 
             sumi1 += v1 * y[i].qs[j + QK8_0 / 2];
         }
         sumf += (float)(sumi0 + sumi1) * f16_to_f32(x[i].d) * f16_to_f32(y[i].d);
+    }
+    return sumf;
+}
+
+/* ggml_vec_dot_mxfp4_q8_0 (generic path) */
+static float vec_dot_mxfp4_q8_0(int64_t k, const blk_mxfp4 *x, const blk_q8_0 *y) {
+    int64_t nb = k / QK8_0;
+    float sumf = 0;
+    for (int64_t i = 0; i < nb; ++i) {
+        int sumi1 = 0, sumi2 = 0;
+        for (int j = 0; j < QK8_0 / 2; ++j) {
+            sumi1 += y[i].qs[j] * kvalues_mxfp4[x[i].qs[j] & 0xF];
+            sumi2 += y[i].qs[j + QK8_0 / 2] * kvalues_mxfp4[x[i].qs[j] >> 4];
+        }
+        sumf += f16_to_f32(y[i].d) * e8m0_to_f32_half(x[i].e) * (float)(sumi1 + sumi2);
     }
     return sumf;
 }
@@ -921,7 +1002,7 @@ int ggq_matmul_cpu(int type, const void *packed, int64_t n, int64_t k, const flo
     int64_t rb = ggq_row_bytes(type, k);
     if (rb < 0) return -1;
     const uint8_t *p = (const uint8_t *)packed;
-    const int act8_0 = type == GGQ_TYPE_Q8_0 || type == GGQ_TYPE_Q4_0;      /* these pair with Q8_0 activations */
+    const int act8_0 = type == GGQ_TYPE_Q8_0 || type == GGQ_TYPE_Q4_0 || type == GGQ_TYPE_MXFP4;      /* these pair with Q8_0 activations */
     size_t act_row = act8_0 ? (size_t)(k / QK8_0) * sizeof(blk_q8_0)
                                               : (size_t)(k / QK_K) * sizeof(blk_q8_K);
     uint8_t *act = (uint8_t *)malloc(act_row * (size_t)m);
@@ -945,6 +1026,7 @@ int ggq_matmul_cpu(int type, const void *packed, int64_t n, int64_t k, const flo
             float v;
             if (type == GGQ_TYPE_Q8_0) v = vec_dot_q8_0_q8_0(k, (const blk_q8_0 *)row, (const blk_q8_0 *)a);
             else if (type == GGQ_TYPE_Q4_0) v = vec_dot_q4_0_q8_0(k, (const blk_q4_0 *)row, (const blk_q8_0 *)a);
+            else if (type == GGQ_TYPE_MXFP4) v = vec_dot_mxfp4_q8_0(k, (const blk_mxfp4 *)row, (const blk_q8_0 *)a);
             else if (type == GGQ_TYPE_Q4_K) v = vec_dot_q4_K_q8_K(k, (const blk_q4_K *)row, (const blk_q8_K *)a);
             else if (type == GGQ_TYPE_Q5_K) v = vec_dot_q5_K_q8_K(k, (const blk_q5_K *)row, (const blk_q8_K *)a);
             else v = vec_dot_q6_K_q8_K(k, (const blk_q6_K *)row, (const blk_q8_K *)a);

@@ -15,8 +15,8 @@ from pathlib import Path
 
 import numpy as np
 
-Q4_0, Q8_0, Q4_K, Q5_K, Q6_K = 2, 8, 12, 13, 14
-TYPE_NAMES = {Q4_0: "Q4_0", Q8_0: "Q8_0", Q4_K: "Q4_K", Q5_K: "Q5_K", Q6_K: "Q6_K"}
+Q4_0, Q8_0, Q4_K, Q5_K, Q6_K, MXFP4 = 2, 8, 12, 13, 14, 39
+TYPE_NAMES = {Q4_0: "Q4_0", Q8_0: "Q8_0", Q4_K: "Q4_K", Q5_K: "Q5_K", Q6_K: "Q6_K", MXFP4: "MXFP4"}
 _HERE = Path(__file__).resolve().parent
 _LIB_PATH = _HERE / "libggq_oracle.so"
 _lib = None

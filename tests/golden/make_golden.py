@@ -13,10 +13,10 @@ from gguf import quants
 
 OUT = Path(__file__).resolve().parent / "ggml_blocks.npz"
 T = {2: gguf.GGMLQuantizationType.Q4_0, 8: gguf.GGMLQuantizationType.Q8_0, 12: gguf.GGMLQuantizationType.Q4_K, 13: gguf.GGMLQuantizationType.Q5_K,
-     14: gguf.GGMLQuantizationType.Q6_K}
-BLK = {2: (32, 18), 8: (32, 34), 12: (256, 144), 13: (256, 176), 14: (256, 210)}
+     14: gguf.GGMLQuantizationType.Q6_K, 39: gguf.GGMLQuantizationType.MXFP4}
+BLK = {39: (32, 17), 2: (32, 18), 8: (32, 34), 12: (256, 144), 13: (256, 176), 14: (256, 210)}
 # byte offsets of the fp16 fields inside a block (kept finite so decoded values are comparable)
-F16_AT = {2: [0], 8: [0], 12: [0, 2], 13: [0, 2], 14: [208]}
+F16_AT = {39: [], 2: [0], 8: [0], 12: [0, 2], 13: [0, 2], 14: [208]}
 
 
 def random_blocks(rng, qt, rows, k):
@@ -51,6 +51,8 @@ def main():
     case(13)      # drawn last: the cases above keep the bytes they had before Q5_K was added
     case(2)       # ... and before Q4_0 was
     out["q4_0_packed"] = quants.quantize(w, T[2])       # of the same source as the Q8_0 case
+    case(39)      # MXFP4: every byte random, the whole range of e8m0 scales included
+    out["mxfp4_packed"] = quants.quantize(w, T[39])
     np.savez_compressed(OUT, **out)
     print("wrote", OUT, OUT.stat().st_size, "bytes")
 

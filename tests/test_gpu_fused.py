@@ -24,7 +24,7 @@ def _bound(ref, rel):
     return rel * np.maximum(np.abs(ref), np.sqrt(np.mean(ref ** 2)))
 
 
-@pytest.mark.parametrize("qt", [mb.TYPE_Q4_K, mb.TYPE_Q6_K, mb.TYPE_Q8_0, mb.TYPE_Q5_K, mb.TYPE_Q4_0])
+@pytest.mark.parametrize("qt", [mb.TYPE_Q4_K, mb.TYPE_Q6_K, mb.TYPE_Q8_0, mb.TYPE_Q5_K, mb.TYPE_Q4_0, mb.TYPE_MXFP4])
 @pytest.mark.parametrize("m,n,k,out_dtype", [(1, 1024, 2048, torch.float32), (2, 771, 4096, torch.float32), (1, 5, 256, torch.bfloat16),
                                              (4, 130, 2304, torch.float32)])
 def test_swiglu_job(backend, orc, qt, m, n, k, out_dtype):

@@ -16,7 +16,7 @@ import magnitude_b200 as mb  # noqa: E402
 from magnitude_b200 import ggml_quant as gq  # noqa: E402
 
 GOLD = Path(__file__).resolve().parent / "golden" / "ggml_blocks.npz"
-TYPES = [mb.TYPE_Q4_K, mb.TYPE_Q6_K, mb.TYPE_Q8_0, mb.TYPE_Q5_K, mb.TYPE_Q4_0]
+TYPES = [mb.TYPE_Q4_K, mb.TYPE_Q6_K, mb.TYPE_Q8_0, mb.TYPE_Q5_K, mb.TYPE_Q4_0, mb.TYPE_MXFP4]
 REL_DECODE = 1e-3
 REL_BF16 = 5e-3
 

@@ -17,7 +17,7 @@ from magnitude_b200 import _binding as B  # noqa: E402
 
 REL_DECODE = 1e-3
 REL_BF16 = 5e-3
-TYPES = [mb.TYPE_Q4_K, mb.TYPE_Q6_K, mb.TYPE_Q8_0, mb.TYPE_Q5_K, mb.TYPE_Q4_0]
+TYPES = [mb.TYPE_Q4_K, mb.TYPE_Q6_K, mb.TYPE_Q8_0, mb.TYPE_Q5_K, mb.TYPE_Q4_0, mb.TYPE_MXFP4]
 
 
 def _acts(m, k, seed, dtype=None):

@@ -7,8 +7,8 @@ import pytest
 from magnitude_b200 import ggml_quant as gq
 
 GOLD = Path(__file__).resolve().parent / "golden" / "ggml_blocks.npz"
-TYPES = [2, 8, 12, 13, 14]
-SIZES = {2: (32, 18), 8: (32, 34), 12: (256, 144), 13: (256, 176), 14: (256, 210)}
+TYPES = [2, 8, 12, 13, 14, 39]
+SIZES = {39: (32, 17), 2: (32, 18), 8: (32, 34), 12: (256, 144), 13: (256, 176), 14: (256, 210)}
 
 
 @pytest.mark.parametrize("qt", TYPES)
@@ -53,7 +53,7 @@ def test_quantizer_edge_blocks(orc, qt):
     assert np.all(d[0] == 0)
     assert np.all(np.isfinite(d))
     assert np.max(np.abs(d[1] - w[1])) < 2e-4
-    assert np.max(np.abs(d[2] - w[2])) < 0.08
+    assert np.max(np.abs(d[2] - w[2])) < (0.13 if qt == 39 else 0.08)      # MXFP4's top levels are 8 and 12 scale units apart
 
 
 @pytest.mark.parametrize("qt", TYPES)
@@ -139,7 +139,7 @@ def test_library_quantizer_is_the_oracles_quantizer_byte_for_byte(orc):
     import magnitude_b200 as mb
 
     rng = np.random.default_rng(11)
-    for qt in (orc.Q4_0, orc.Q8_0, orc.Q4_K, orc.Q5_K, orc.Q6_K):
+    for qt in (orc.Q4_0, orc.Q8_0, orc.Q4_K, orc.Q5_K, orc.Q6_K, orc.MXFP4):
         for n, k, scale in ((33, 1024, 0.02), (5, 256, 1.0), (4, 512, 1e-9), (6, 768, 300.0)):
             w = (rng.standard_normal((n, k)) * scale).astype(np.float32)
             w[0] = 0.0
