@@ -337,7 +337,9 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1) stream_kernel(const S
                         const uint32_t bar = fbar + 8 * slot;
                         fence_proxy_async();   // the consumer's reads of this slot precede the engine's writes
                         mbar_expect_tx(bar, bytes);
-                        bulk_g2s(ring_s + slot * slot_bytes, J.seg[sg].w + tile_off(J.qt, lg, c, J.seg[sg].n, J.nsb),
+                        // tile (row group lg, chunk c): both strides were worked out when the job was made, so the
+                        // producer's per-item path has no type logic
+                        bulk_g2s(ring_s + slot * slot_bytes, J.seg[sg].w + (long long)lg * J.tile_group_stride + c * J.tile_chunk_stride,
                                  bytes, bar);
                         item += tcw;
                         c += tcw;
@@ -1020,6 +1022,8 @@ void stream_job_finish(StreamJob &J) {
     J.nchunks = (J.nsb + KC - 1) / KC;
     J.bytes_full = (unsigned)chunk_row_bytes(J.qt, 0, J.nsb);
     J.bytes_tail = (unsigned)chunk_row_bytes(J.qt, J.nchunks - 1, J.nsb);
+    J.tile_group_stride = tile_off(J.qt, 1, 0, 0, J.nsb);              // both offsets are linear in their index
+    J.tile_chunk_stride = (int)tile_off(J.qt, 0, 1, 0, J.nsb);
 }
 
 void stream_assign_teams(StreamJob *jobs, int n) {

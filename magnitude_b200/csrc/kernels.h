@@ -51,6 +51,8 @@ struct StreamJob {
     int nsb, nchunks;                  // filled by stream_job_finish
     long long row_bytes;
     unsigned bytes_full, bytes_tail;   // filled: bytes one row adds to a chunk, all but the last / the last
+    long long tile_group_stride;       // filled: bytes between the tiles of consecutive row groups (same chunk)
+    int tile_chunk_stride;             // filled: bytes between the tiles of consecutive chunks (same row group)
     const void *x;
     long long ldx;
     int x_is_bf16, x_vec_ok, y_is_bf16;
