@@ -128,6 +128,10 @@ __host__ __device__ __forceinline__ void cta_groups(const StreamJob &J, int b, i
         const long long pairs = J.total_groups >> 1;
         gb = 2 * (int)(pairs * b / grid);
         ge = 2 * (int)(pairs * (b + 1) / grid);
+    } else if (J.total_groups < (1 << 21)) {
+        // (32-bit division: this runs once per job in every warp, the producer's included)
+        gb = (int)((unsigned)J.total_groups * (unsigned)b / (unsigned)grid);
+        ge = (int)((unsigned)J.total_groups * (unsigned)(b + 1) / (unsigned)grid);
     } else {
         gb = (int)((long long)J.total_groups * b / grid);
         ge = (int)((long long)J.total_groups * (b + 1) / grid);
