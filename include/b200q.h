@@ -340,7 +340,7 @@ typedef struct b200q_job {
      * apply before QKV and before gate/up.  Streaming plans only (M <= 4). */
     const float *norm_weight;
     float norm_eps;
-    int32_t reserved;         /* 0 */
+    int32_t reserved;         /* 0: zero-initialise the struct; a non-zero value is refused (it catches uninitialised jobs) */
 } b200q_job;
 
 b200q_status b200q_plan_create(b200q_ctx *ctx, const b200q_job *jobs, int32_t n_jobs, int64_t M,

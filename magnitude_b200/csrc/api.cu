@@ -951,6 +951,8 @@ b200q_status b200q_plan_create(b200q_ctx *ctx, const b200q_job *jobs, int32_t n_
     *out = nullptr;
     if (!jobs || n_jobs < 1) return fail(ctx, B200Q_ERR_INVALID_CONFIG, "a plan needs at least one job");
     if (M < 1 || M > skinny_max_m()) return fail(ctx, B200Q_ERR_INVALID_CONFIG, "plans take 1..%d activation rows", skinny_max_m());
+    for (int i = 0; i < n_jobs; ++i)
+        if (jobs[i].reserved != 0) return fail(ctx, B200Q_ERR_INVALID_CONFIG, "job %d: the reserved field must be 0 (zero-initialise b200q_job)", i);
     b200q_plan *pl = new (std::nothrow) b200q_plan();
     if (!pl) return fail(ctx, B200Q_ERR_OVERLOADED, "out of host memory");
     pl->ctx = ctx;
