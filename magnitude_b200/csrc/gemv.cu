@@ -223,10 +223,63 @@ __device__ __forceinline__ void item_dot(int nsb, uint32_t sl, int stride, int s
 // single-type launch compiles only that type's unpacking, which keeps it free of register spills.
 constexpr int TY_Q4K = 1, TY_Q6K = 2, TY_Q80 = 4, TY_Q5K = 8, TY_Q40 = 16, TY_MX4 = 32;
 
-// FUSED: some job of the launch has a fused epilogue (SWIGLU, ACCUM); launches without any run the
-// instantiation that carries none of that code.
-template <int MT, int TYPES, bool FUSED>
+// Adds up, in rank order, what the same CTA of every rank posted for job Jc under exchange number e and
+// stores the sums.  A function of its own (not inlined): its registers do not weigh on the streaming loop.
+template <int MT, bool FUSED>
+__device__ __noinline__ void exchange_complete_rows(const StreamJob &Jc, const uint8_t *local_base, int world, int M, int team, int tid,
+                                                    int T, unsigned e, int *xfail, int *status) {
+    const unsigned long long *slots = reinterpret_cast<const unsigned long long *>(local_base + kPeerFusedSlotOff) +
+                                      (size_t)(team * 2 + (e & 1)) * kPeerMaxWorld * kPeerSlotFloats;
+    int gbc, gec;
+    cta_groups<FUSED>(Jc, blockIdx.x, gridDim.x, gbc, gec);
+    const int n = Jc.seg[0].n;
+    const bool accum = FUSED && (Jc.flags & STREAM_JOB_ACCUM) != 0;
+    const int cells = (gec - gbc) * R * MT;
+    for (int t = tid; t < cells; t += T) {
+        const int rl = t / MT, m = t - rl * MT;
+        const int row = gbc * R + rl;
+        if (row < n && m < M) {
+            const int si = m * n + row;
+            float acc = 0.f;
+            bool ok = !*reinterpret_cast<volatile int *>(xfail);
+            // all ranks' pairs are requested before the first is looked at: one trip to memory, not one per rank
+            unsigned long long w[kPeerMaxWorld];
+#pragma unroll
+            for (int r = 0; r < kPeerMaxWorld; ++r)
+                if (r < world) w[r] = ld_pair(slots + (size_t)r * kPeerSlotFloats + si);
+#pragma unroll
+            for (int r = 0; r < kPeerMaxWorld; ++r) {
+                if (r >= world || !ok) continue;
+                if ((unsigned)(w[r] >> 32) != e) {
+                    const unsigned long long *q = slots + (size_t)r * kPeerSlotFloats + si;
+                    const uint64_t t0 = globaltimer_ns();
+                    int spins = 0;
+                    while ((unsigned)((w[r] = ld_pair(q)) >> 32) != e) {
+                        if ((++spins & 63) == 0 && globaltimer_ns() - t0 > kWaitLimitNs) {
+                            ok = false;
+                            *reinterpret_cast<volatile int *>(xfail) = 1;
+                            atomicMax(status, DEV_ERR_PIPE_TIMEOUT);
+                            break;
+                        }
+                    }
+                }
+                acc = r == 0 ? __uint_as_float((unsigned)w[r]) : acc + __uint_as_float((unsigned)w[r]);
+            }
+            if (ok) {
+                float *yp = reinterpret_cast<float *>(Jc.seg[0].y) + (long long)m * Jc.seg[0].ldy + row;
+                *yp = accum ? *yp + acc : acc;
+            }
+        }
+    }
+}
+
+// VAR: which optional code the instantiation carries.  0: none; 1: the fused epilogues (SWIGLU, ACCUM, norm
+// on the load) for launches that hold such jobs; 2: those and the rank-sum exchange, for launches of
+// attached tensor-parallel ranks.  The plain form stays free of both (the kernel is sensitive to their
+// registers and code).
+template <int MT, int TYPES, int VAR>
 __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1) stream_kernel(const StreamParams p) {
+    constexpr bool FUSED = VAR >= 1, PEER = VAR == 2;
     extern __shared__ __align__(128) uint8_t smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int CW = (blockDim.x >> 5) - 1;     // consumer warps; warp CW is the producer
@@ -451,49 +504,12 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1) stream_kernel(const S
     // complete it at once.  Two slot sets alternate; a CTA posts exchange e + 1 only after it has
     // read exchange e, and can only read e + 1 after the peers posted it, i.e. after they read e:
     // no pair is overwritten before it has been read.  All ranks run the same plan on the same grid.
-    const bool xenabled = p.peer_world > 1;
+    const bool xenabled = PEER && p.peer_world > 1;
     unsigned xe = 0;
     bool xe_loaded = false;
     int xpending = -1;
     auto exchange_complete = [&](int job, unsigned e) {
-        const StreamJob &Jc = jobs_s[job];
-        const unsigned long long *slots = reinterpret_cast<const unsigned long long *>(p.peer_base[p.peer_rank] + kPeerFusedSlotOff) +
-                                          (size_t)(team * 2 + (e & 1)) * kPeerMaxWorld * kPeerSlotFloats;
-        int gbc, gec;
-        cta_groups<FUSED>(Jc, blockIdx.x, gridDim.x, gbc, gec);
-        const int n = Jc.seg[0].n;
-        const bool accum = FUSED && (Jc.flags & STREAM_JOB_ACCUM) != 0;
-        const int cells = (gec - gbc) * R * MT;
-        for (int t = tid; t < cells; t += T) {
-            const int rl = t / MT, m = t - rl * MT;
-            const int row = gbc * R + rl;
-            if (row < n && m < p.M) {
-                const int si = m * n + row;
-                float acc = 0.f;
-                bool ok = !*reinterpret_cast<volatile int *>(&head.xfail);
-                for (int r = 0; r < p.peer_world && ok; ++r) {
-                    const unsigned long long *q = slots + (size_t)r * kPeerSlotFloats + si;
-                    unsigned long long w = ld_pair(q);
-                    if ((unsigned)(w >> 32) != e && !GEMV_DBG(64)) {
-                        const uint64_t t0 = globaltimer_ns();
-                        int spins = 0;
-                        while ((unsigned)((w = ld_pair(q)) >> 32) != e) {
-                            if ((++spins & 63) == 0 && globaltimer_ns() - t0 > kWaitLimitNs) {
-                                ok = false;
-                                head.xfail = 1;
-                                atomicMax(p.status, DEV_ERR_PIPE_TIMEOUT);
-                                break;
-                            }
-                        }
-                    }
-                    acc = r == 0 ? __uint_as_float((unsigned)w) : acc + __uint_as_float((unsigned)w);
-                }
-                if (ok) {
-                    float *yp = reinterpret_cast<float *>(Jc.seg[0].y) + (long long)m * Jc.seg[0].ldy + row;
-                    *yp = accum ? *yp + acc : acc;
-                }
-            }
-        }
+        exchange_complete_rows<MT, FUSED>(jobs_s[job], p.peer_base[p.peer_rank], p.peer_world, p.M, team, tid, T, e, &head.xfail, p.status);
     };
 
     bool first_job = true;
@@ -874,7 +890,7 @@ cudaError_t stream_xprep_launch(const StreamJob *jobs_dev, int njobs, int M, cud
 
 namespace {
 
-template <int MT, int TYPES, bool FUSED = false>
+template <int MT, int TYPES, int VAR = 0>
 cudaError_t launch_t(const StreamLaunch &a, StreamParams &p, int grid, cudaStream_t st) {
     int warps = a.warps > 0 ? a.warps : kMaxWarps;
     if (warps > kMaxWarps) warps = kMaxWarps;
@@ -909,11 +925,16 @@ cudaError_t launch_t(const StreamLaunch &a, StreamParams &p, int grid, cudaStrea
     p.depth = depth;
     const size_t smem = fixed + (size_t)warps * depth * R * stride;
 
-    bool fused = false;
-    for (int i = 0; i < a.njobs; ++i)
-        fused = fused || (a.jobs_host[i].flags & (STREAM_JOB_SWIGLU | STREAM_JOB_ACCUM)) != 0 || a.jobs_host[i].gamma != nullptr;
-    if (fused != FUSED) return launch_t<MT, TYPES, !FUSED>(a, p, grid, st);
-    auto kern = stream_kernel<MT, TYPES, FUSED>;
+    if (VAR == 0) {      // pick the form once, from the plain entry
+        bool fused = false, sums = false;
+        for (int i = 0; i < a.njobs; ++i) {
+            fused = fused || (a.jobs_host[i].flags & (STREAM_JOB_SWIGLU | STREAM_JOB_ACCUM)) != 0 || a.jobs_host[i].gamma != nullptr;
+            sums = sums || (a.jobs_host[i].flags & STREAM_JOB_SUM_RANKS) != 0;
+        }
+        if (sums && p.peer_world > 1) return launch_t<MT, TYPES, (VAR == 0 ? 2 : VAR)>(a, p, grid, st);
+        if (fused) return launch_t<MT, TYPES, (VAR == 0 ? 1 : VAR)>(a, p, grid, st);
+    }
+    auto kern = stream_kernel<MT, TYPES, VAR>;
     static std::atomic<size_t> configured{0};   // per instantiation; a context on another device re-sets it
     static std::atomic<int> configured_dev{-1};  // (contexts on several threads may launch at once)
     int dev = 0;
