@@ -223,63 +223,13 @@ __device__ __forceinline__ void item_dot(int nsb, uint32_t sl, int stride, int s
 // single-type launch compiles only that type's unpacking, which keeps it free of register spills.
 constexpr int TY_Q4K = 1, TY_Q6K = 2, TY_Q80 = 4, TY_Q5K = 8, TY_Q40 = 16, TY_MX4 = 32;
 
-// Adds up, in rank order, what the same CTA of every rank posted for job Jc under exchange number e and
-// stores the sums.  A function of its own (not inlined): its registers do not weigh on the streaming loop.
-template <int MT, bool FUSED>
-__device__ __noinline__ void exchange_complete_rows(const StreamJob &Jc, const uint8_t *local_base, int world, int M, int team, int tid,
-                                                    int T, unsigned e, int *xfail, int *status) {
-    const unsigned long long *slots = reinterpret_cast<const unsigned long long *>(local_base + kPeerFusedSlotOff) +
-                                      (size_t)(team * 2 + (e & 1)) * kPeerMaxWorld * kPeerSlotFloats;
-    int gbc, gec;
-    cta_groups<FUSED>(Jc, blockIdx.x, gridDim.x, gbc, gec);
-    const int n = Jc.seg[0].n;
-    const bool accum = FUSED && (Jc.flags & STREAM_JOB_ACCUM) != 0;
-    const int cells = (gec - gbc) * R * MT;
-    for (int t = tid; t < cells; t += T) {
-        const int rl = t / MT, m = t - rl * MT;
-        const int row = gbc * R + rl;
-        if (row < n && m < M) {
-            const int si = m * n + row;
-            float acc = 0.f;
-            bool ok = !*reinterpret_cast<volatile int *>(xfail);
-            // all ranks' pairs are requested before the first is looked at: one trip to memory, not one per rank
-            unsigned long long w[kPeerMaxWorld];
-#pragma unroll
-            for (int r = 0; r < kPeerMaxWorld; ++r)
-                if (r < world) w[r] = ld_pair(slots + (size_t)r * kPeerSlotFloats + si);
-#pragma unroll
-            for (int r = 0; r < kPeerMaxWorld; ++r) {
-                if (r >= world || !ok) continue;
-                if ((unsigned)(w[r] >> 32) != e) {
-                    const unsigned long long *q = slots + (size_t)r * kPeerSlotFloats + si;
-                    const uint64_t t0 = globaltimer_ns();
-                    int spins = 0;
-                    while ((unsigned)((w[r] = ld_pair(q)) >> 32) != e) {
-                        if ((++spins & 63) == 0 && globaltimer_ns() - t0 > kWaitLimitNs) {
-                            ok = false;
-                            *reinterpret_cast<volatile int *>(xfail) = 1;
-                            atomicMax(status, DEV_ERR_PIPE_TIMEOUT);
-                            break;
-                        }
-                    }
-                }
-                acc = r == 0 ? __uint_as_float((unsigned)w[r]) : acc + __uint_as_float((unsigned)w[r]);
-            }
-            if (ok) {
-                float *yp = reinterpret_cast<float *>(Jc.seg[0].y) + (long long)m * Jc.seg[0].ldy + row;
-                *yp = accum ? *yp + acc : acc;
-            }
-        }
-    }
-}
-
-// VAR: which optional code the instantiation carries.  0: none; 1: the fused epilogues (SWIGLU, ACCUM, norm
-// on the load) for launches that hold such jobs; 2: those and the rank-sum exchange, for launches of
-// attached tensor-parallel ranks.  The plain form stays free of both (the kernel is sensitive to their
-// registers and code).
+// VAR: which optional code the instantiation carries.  Bit 0: the fused epilogues (SWIGLU, ACCUM, norm on
+// the load) for launches that hold such jobs; bit 1: the rank-sum exchange, for launches of attached
+// tensor-parallel ranks.  Every form carries only what it needs: the kernel is sensitive to the
+// registers and code of what it does not use.
 template <int MT, int TYPES, int VAR>
 __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1) stream_kernel(const StreamParams p) {
-    constexpr bool FUSED = VAR >= 1, PEER = VAR == 2;
+    constexpr bool FUSED = (VAR & 1) != 0, PEER = (VAR & 2) != 0;
     extern __shared__ __align__(128) uint8_t smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int CW = (blockDim.x >> 5) - 1;     // consumer warps; warp CW is the producer
@@ -509,7 +459,55 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1) stream_kernel(const S
     bool xe_loaded = false;
     int xpending = -1;
     auto exchange_complete = [&](int job, unsigned e) {
-        exchange_complete_rows<MT, FUSED>(jobs_s[job], p.peer_base[p.peer_rank], p.peer_world, p.M, team, tid, T, e, &head.xfail, p.status);
+        const StreamJob &Jc = jobs_s[job];
+        const unsigned long long *slots = reinterpret_cast<const unsigned long long *>(p.peer_base[p.peer_rank] + kPeerFusedSlotOff) +
+                                          (size_t)(team * 2 + (e & 1)) * kPeerMaxWorld * kPeerSlotFloats;
+        int gbc, gec;
+        cta_groups<FUSED>(Jc, blockIdx.x, gridDim.x, gbc, gec);
+        const int n = Jc.seg[0].n;
+        const bool accum = FUSED && (Jc.flags & STREAM_JOB_ACCUM) != 0;
+        const int cells = (gec - gbc) * R * MT;
+        // Eight lanes share one output: lane r of the group fetches rank r's pair (and waits for it, with the
+        // usual limit), so all ranks' pairs travel at the same time; lane 0 then adds them in rank order.
+        const bool dead = *reinterpret_cast<volatile int *>(&head.xfail) != 0;
+        for (int base = 0; base < cells; base += T / kPeerMaxWorld) {
+            const int t = base + (tid >> 3), r = lane & 7;
+            const int rl = t / MT, m = t - rl * MT;
+            const int row = gbc * R + rl;
+            const bool valid = t < cells && row < n && m < p.M;
+            const int si = m * n + row;
+            unsigned long long w = 0;
+            bool ok = !dead;
+            if (valid && r < p.peer_world && ok) {
+                const unsigned long long *q = slots + (size_t)r * kPeerSlotFloats + si;
+                w = ld_pair(q);
+                if ((unsigned)(w >> 32) != e && !GEMV_DBG(64)) {
+                    const uint64_t t0 = globaltimer_ns();
+                    int spins = 0;
+                    while ((unsigned)((w = ld_pair(q)) >> 32) != e) {
+                        if ((++spins & 63) == 0 && globaltimer_ns() - t0 > kWaitLimitNs) {
+                            ok = false;
+                            head.xfail = 1;
+                            atomicMax(p.status, DEV_ERR_PIPE_TIMEOUT);
+                            break;
+                        }
+                    }
+                }
+            }
+            const float v = __uint_as_float((unsigned)w);
+            const int lane0 = lane & ~7;
+            float acc = __shfl_sync(0xFFFFFFFFu, v, lane0);
+#pragma unroll
+            for (int rr = 1; rr < kPeerMaxWorld; ++rr) {
+                const float o = __shfl_sync(0xFFFFFFFFu, v, lane0 + rr);
+                if (rr < p.peer_world) acc += o;
+            }
+            const unsigned okmask = __ballot_sync(0xFFFFFFFFu, ok);
+            if (valid && r == 0 && ((okmask >> lane0) & 0xFFu) == 0xFFu) {
+                float *yp = reinterpret_cast<float *>(Jc.seg[0].y) + (long long)m * Jc.seg[0].ldy + row;
+                *yp = accum ? *yp + acc : acc;
+            }
+        }
     };
 
     bool first_job = true;
@@ -931,7 +929,9 @@ cudaError_t launch_t(const StreamLaunch &a, StreamParams &p, int grid, cudaStrea
             fused = fused || (a.jobs_host[i].flags & (STREAM_JOB_SWIGLU | STREAM_JOB_ACCUM)) != 0 || a.jobs_host[i].gamma != nullptr;
             sums = sums || (a.jobs_host[i].flags & STREAM_JOB_SUM_RANKS) != 0;
         }
-        if (sums && p.peer_world > 1) return launch_t<MT, TYPES, (VAR == 0 ? 2 : VAR)>(a, p, grid, st);
+        const bool peer = sums && p.peer_world > 1;
+        if (peer && fused) return launch_t<MT, TYPES, (VAR == 0 ? 3 : VAR)>(a, p, grid, st);
+        if (peer) return launch_t<MT, TYPES, (VAR == 0 ? 2 : VAR)>(a, p, grid, st);
         if (fused) return launch_t<MT, TYPES, (VAR == 0 ? 1 : VAR)>(a, p, grid, st);
     }
     auto kern = stream_kernel<MT, TYPES, VAR>;

@@ -70,20 +70,26 @@ __global__ void __launch_bounds__(kPeerThreads) peer_allreduce_kernel(const Peer
     for (int i = lo + threadIdx.x; i < hi; i += kPeerThreads) {
         float acc = 0.f;
         bool ok = true;
-        for (int r = 0; r < p.world && ok; ++r) {
-            const unsigned long long *q = slots + (size_t)r * kPeerSlotFloats + i;
-            unsigned long long w = ld_pair(q);
-            if ((unsigned)(w >> 32) != e) {
+        // all ranks' pairs are requested before the first is looked at: one trip to memory, not one per rank
+        unsigned long long w[kPeerMaxWorld];
+#pragma unroll
+        for (int r = 0; r < kPeerMaxWorld; ++r)
+            if (r < p.world) w[r] = ld_pair(slots + (size_t)r * kPeerSlotFloats + i);
+#pragma unroll
+        for (int r = 0; r < kPeerMaxWorld; ++r) {
+            if (r >= p.world || !ok) continue;
+            if ((unsigned)(w[r] >> 32) != e) {
+                const unsigned long long *q = slots + (size_t)r * kPeerSlotFloats + i;
                 const uint64_t t0 = globaltimer_ns();
                 int spins = 0;
-                while ((unsigned)((w = ld_pair(q)) >> 32) != e) {
+                while ((unsigned)((w[r] = ld_pair(q)) >> 32) != e) {
                     if ((++spins & 63) == 0 && globaltimer_ns() - t0 > kWaitLimitNs) {
                         ok = false;
                         break;
                     }
                 }
             }
-            acc = r == 0 ? __uint_as_float((unsigned)w) : acc + __uint_as_float((unsigned)w);
+            acc = r == 0 ? __uint_as_float((unsigned)w[r]) : acc + __uint_as_float((unsigned)w[r]);
         }
         if (ok) p.y[i] = acc;
         else s_fail = 1;
