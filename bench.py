@@ -11,7 +11,11 @@ addresses.
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
 
 For N > 1 launch under torchrun; weights are split tensor-parallel (gate/up by rows, down by K
-superblocks with one all-reduce per down projection).  Rank 0 prints one JSON line.
+superblocks with the rank sums taken inside the launch).  Rank 0 prints one JSON line.  Beside the
+headline figure the N = 1 line carries: the host check of the step's results, the step with its real
+dependencies (plain and as chained fused MLP blocks), a seconds-long replay, the prefill (TFLOP/s),
+skinny-batch and per-type calibration figures, a library arm (the vllm package's GGUF kernels) and the
+CPU baseline.  --workload prefill | skinny | calibration | layer32b | library print those lines alone.
 """
 from __future__ import annotations
 
