@@ -5,7 +5,9 @@
 //   * work item = 16 weight rows x one chunk (8 superblock records = 2048 weights) of the streaming
 //     layout.  A persistent CTA per SM owns a contiguous run of items (chunk-major, so most CTAs
 //     stay inside one chunk); its producer warp streams them into a shared-memory ring, one bulk
-//     copy per row (rows are padded in shared memory so that fragment loads spread over the banks).
+//     copy per four-row group of the layout (four per item).  The groups are padded apart in shared
+//     memory and MMA row f is row f >> 2 of group f & 3, so that the rows one fragment load touches
+//     lie in four different groups and spread over the banks.
 //   * 8 consumer warps; warp w owns record w of the chunk, i.e. a fixed 256-wide K range, for all
 //     16 rows.  Its activations for that range (every token, exact bf16) stay in REGISTERS as
 //     the B fragments of mma.sync.m16n8k16, loaded once per chunk straight from X (in the element
@@ -60,10 +62,13 @@ constexpr int kSkInline = 4;                      // products whose descriptions
 constexpr int kRedStride = 20;                    // floats between the tokens of a partial tile (bank spread)
 constexpr int kRedDepth = 4;                      // partial-tile sets in flight between consumers and reducer
 
-// shared-memory distance between the rows of a stage: the chunk's bytes per row, padded so that the
-// 8 rows a fragment load touches start 32 bytes apart modulo 128 (Q6_K reads 4-byte words and is
-// conflict-free at its natural 1680)
-__host__ __device__ constexpr int sk_row_stride(int qt) { return (qt == QT_Q4_K || qt == QT_Q4_0 || qt == QT_MXFP4) ? 1184 : qt == QT_Q5_K ? 1440 : qt == QT_Q8_0 ? 2208 : 1680; }
+// bytes one row adds to a full chunk
+__host__ __device__ constexpr int sk_chunk_row_bytes(int qt) { return qt == QT_Q6_K ? 1680 : rec_bytes(qt) * kChunkRecs; }
+// shared-memory distance between the four-row groups of a stage: four rows of a full chunk, padded to
+// 32 modulo 128.  The rows of a group lie as in device memory (one copy per group); the four rows a
+// fragment-load phase touches come from the four groups at the same offset, i.e. 32 bytes apart
+// modulo 128 (Q6_K reads 4-byte words: eight rows = four groups x two 16-byte steps).
+__host__ __device__ constexpr int sk_group_stride(int qt) { return ((kRowGroup * sk_chunk_row_bytes(qt) - 32 + 127) / 128) * 128 + 32; }
 __host__ __device__ constexpr int sk_subblocks(int qt) { return qt == QT_Q6_K ? 16 : 8; }   // scale blocks per record
 
 struct SkJob {
@@ -101,8 +106,9 @@ constexpr size_t kSkHeadBytes = (sizeof(SkHead) + 127) & ~size_t(127);
 
 template <int QT, int NT> struct SkLayout {
     static constexpr int SBK = sk_subblocks(QT);
-    static constexpr int S = sk_row_stride(QT);
-    static constexpr int kStageBytes = kSkRows * S;
+    static constexpr int GS = sk_group_stride(QT);
+    static constexpr int kStageBytes = (kSkRows / kRowGroup) * GS;
+    static_assert(GS >= kRowGroup * sk_chunk_row_bytes(QT) && GS % 128 == 32, "group stride");
     static constexpr int kRedFloats = 8 * NT * kRedStride;                    // one warp's partial tile
     static constexpr size_t kRedOff = kSkHeadBytes;
     static constexpr size_t kSctOff = kRedOff + size_t(kRedDepth) * kSkWarps * kRedFloats * 4;
@@ -176,23 +182,34 @@ __device__ __forceinline__ void fold(float (&acc)[4], const float (&c)[4], float
 // Sub-blocks are taken QB at a time with QB * NT = 8 independent accumulator chains in flight, so
 // the tensor-core latency of one chain hides behind the others.
 
+// The (p, -q) table entries of a Q4_K / Q5_K header: lane L prepares row L >> 1, sub-blocks
+// 4 (L & 1) .. + 3, with p = d sc and q = 128 p + dmin m.  The 6-bit fields are unpacked four at a
+// time in the bytes of a word, the same way in every lane; a byte becomes a float through the 2^23
+// form (one byte permute, one subtraction).
+__device__ __forceinline__ void k_scale_table(uint32_t rec_row, int lane, uint32_t sct) {
+    const int row = lane >> 1;
+    const bool upper = lane & 1;
+    const uint4 hdr = ldsn128(rec_row);       // d | dmin << 16, then the twelve scale bytes
+    const float d = half_bits_to_float(hdr.x), dmin = half_bits_to_float(hdr.x >> 16);
+    const uint32_t scw = upper ? ((hdr.w & 0x0F0F0F0Fu) | ((hdr.y >> 2) & 0x30303030u)) : (hdr.y & 0x3F3F3F3Fu);
+    const uint32_t mnw = upper ? (((hdr.w >> 4) & 0x0F0F0F0Fu) | ((hdr.z >> 2) & 0x30303030u)) : (hdr.z & 0x3F3F3F3Fu);
+    const uint32_t dst = sct + ((upper ? 4 : 0) * kSkRows + row) * 8;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float sc = __uint_as_float(__byte_perm(scw, 0x4B000000u, 0x7440 + i)) - 8388608.f;
+        const float mn = __uint_as_float(__byte_perm(mnw, 0x4B000000u, 0x7440 + i)) - 8388608.f;
+        const float p = d * sc;
+        sts_f2(dst + i * (kSkRows * 8), p, -fmaf(128.f, p, dmin * mn));
+    }
+}
+
 template <int QT, int NT> struct SkRecord;
 
 template <int NT> struct SkRecord<QT_Q4_K, NT> {
     static constexpr int QB = 8 / NT;
     // lane L prepares row L >> 1, sub-blocks 4 (L & 1) .. + 3: p = d sc, q = 128 p + dmin m
     static __device__ __forceinline__ void scales(uint32_t rec_row, uint32_t, int lane, uint32_t sct) {
-        const int row = lane >> 1, half = lane & 1;
-        const uint4 hdr = ldsn128(rec_row);
-        const float d = half_bits_to_float(hdr.x), dmin = half_bits_to_float(hdr.x >> 16);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const int sb = 4 * half + i;
-            int sc, mn;
-            q4k_scale_min(hdr.y, hdr.z, hdr.w, sb, sc, mn);
-            const float p = d * (float)sc;
-            sts_f2(sct + (sb * kSkRows + row) * 8, p, -fmaf(128.f, p, dmin * (float)mn));
-        }
+        k_scale_table(rec_row, lane, sct);
     }
     static __device__ __forceinline__ void run(uint32_t recA, uint32_t recB, int g, int t, const uint32_t (&B)[32 * NT],
                                                uint32_t sct, uint32_t xst, float (&acc)[NT][4]) {
@@ -238,17 +255,7 @@ template <int NT> struct SkRecord<QT_Q5_K, NT> {
     static constexpr int QB = 8 / NT;
     // lane L prepares row L >> 1, sub-blocks 4 (L & 1) .. + 3: p = d sc, q = 128 p + dmin m
     static __device__ __forceinline__ void scales(uint32_t rec_row, uint32_t, int lane, uint32_t sct) {
-        const int row = lane >> 1, half = lane & 1;
-        const uint4 hdr = ldsn128(rec_row);
-        const float d = half_bits_to_float(hdr.x), dmin = half_bits_to_float(hdr.x >> 16);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const int sb = 4 * half + i;
-            int sc, mn;
-            q4k_scale_min(hdr.y, hdr.z, hdr.w, sb, sc, mn);
-            const float p = d * (float)sc;
-            sts_f2(sct + (sb * kSkRows + row) * 8, p, -fmaf(128.f, p, dmin * (float)mn));
-        }
+        k_scale_table(rec_row, lane, sct);
     }
     static __device__ __forceinline__ void run(uint32_t recA, uint32_t recB, int g, int t, const uint32_t (&B)[32 * NT],
                                                uint32_t sct, uint32_t xst, float (&acc)[NT][4]) {
@@ -605,7 +612,7 @@ __device__ __forceinline__ bool sk_wait(uint32_t bar, uint32_t parity, volatile 
 template <int QT, int NT>
 __global__ void __launch_bounds__(kSkThreads, sk_ctas_per_sm(NT)) skinny_kernel(const __grid_constant__ SkParams p) {
     using L = SkLayout<QT, NT>;
-    constexpr int SBK = L::SBK, S = L::S;
+    constexpr int SBK = L::SBK, GS = L::GS;
     extern __shared__ __align__(128) uint8_t smem[];
     SkHead &head = *reinterpret_cast<SkHead *>(smem);
     const uint32_t full0 = smem_u32(head.full), empty0 = smem_u32(head.empty);
@@ -641,7 +648,7 @@ __global__ void __launch_bounds__(kSkThreads, sk_ctas_per_sm(NT)) skinny_kernel(
     const SkJob *jobs = head.jobs;
     volatile int *fail_flag = &head.fail;
 
-    // ===== producer: lane r copies row r of every item of this CTA into the ring =====================
+    // ===== producer: lane q copies row group q (four rows) of every item of this CTA into the ring ===
     if (warp == kSkWarps) {
         int n = 0, slot = 0;
         uint32_t phase = 0;        // parity of the ring pass in progress (no division in the loop)
@@ -657,16 +664,16 @@ __global__ void __launch_bounds__(kSkThreads, sk_ctas_per_sm(NT)) skinny_kernel(
             }
             if (!ok) break;
             const uint32_t crb = (c == J.nchunks - 1) ? (uint32_t)J.crb_tail : (uint32_t)J.crb_full;
-            const int rows = min(kSkRows, J.groups * kRowGroup - rb * kSkRows);     // rows present in device memory
+            const int ng = min(kSkRows / kRowGroup, J.groups - rb * (kSkRows / kRowGroup));     // groups present in device memory
             const uint32_t bar = full0 + 8 * slot;
             if (lane == 0) {
                 fence_proxy_async();     // the consumers' reads of this slot precede the copy engine's writes
-                mbar_expect_tx(bar, rows * crb);
+                mbar_expect_tx(bar, ng * kRowGroup * crb);
             }
             __syncwarp();
-            if (lane < rows) {
-                const uint8_t *src = J.w + tile_off(QT, rb * (kSkRows / kRowGroup) + (lane >> 2), c, 0, J.nsb) + (lane & 3) * (int64_t)crb;
-                bulk_g2s(ring0 + slot * L::kStageBytes + lane * S, src, crb, bar);
+            if (lane < ng) {
+                const uint8_t *src = J.w + tile_off(QT, rb * (kSkRows / kRowGroup) + lane, c, 0, J.nsb);
+                bulk_g2s(ring0 + slot * L::kStageBytes + lane * GS, src, kRowGroup * crb, bar);
             }
             if (lane == 0) SK_TRACE(10 + (n & 63));
             if (++slot == D) slot = 0, phase ^= 1u;
@@ -701,7 +708,8 @@ __global__ void __launch_bounds__(kSkThreads, sk_ctas_per_sm(NT)) skinny_kernel(
             }
             const float *rbase = red + (size_t)rs * kSkWarps * L::kRedFloats;
             const size_t npad = (size_t)J.n_rb * kSkRows;
-            const int row = lane & 15, grow = rb * kSkRows + row;
+            const int row = lane & 15;                                           // MMA row of the partial tiles
+            const int grow = rb * kSkRows + (row & 3) * kRowGroup + (row >> 2);    // = row (row >> 2) of group (row & 3)
 #pragma unroll
             for (int i = 0; i < 4 * NT; ++i) {
                 const int tok = 2 * i + (lane >> 4);      // element (tok, row): tok * 16 + row = lane + 32 i
@@ -773,12 +781,16 @@ __global__ void __launch_bounds__(kSkThreads, sk_ctas_per_sm(NT)) skinny_kernel(
             for (int i = 0; i < 4; ++i) acc[nt][i] = 0.f;
         if (active) {
             const uint32_t stage = hold_after_wait(ring0 + slot * L::kStageBytes);
+            const uint32_t crb = (c == J.nchunks - 1) ? (uint32_t)J.crb_tail : (uint32_t)J.crb_full;
             const uint32_t roff = QT == QT_Q6_K ? warp * 208 : warp * rec_bytes(QT);
             const uint32_t doff = nrec * 208 + 2 * warp;                      // Q6_K: the row's fp16 d of this record
-            SkRecord<QT, NT>::scales(stage + (lane >> 1) * S + roff, stage + (lane >> 1) * S + doff, lane, sct0);
+            // MMA row f lies in group f & 3 as its row f >> 2
+            const uint32_t srow = stage + ((lane >> 1) & 3) * GS + (lane >> 3) * crb;
+            SkRecord<QT, NT>::scales(srow + roff, srow + doff, lane, sct0);
             __syncwarp();
             const uint32_t sct = hold_after_wait(sct0);
-            SkRecord<QT, NT>::run(stage + g * S + roff, stage + (g + 8) * S + roff, g, t, B, sct, xst, acc);
+            const uint32_t recA = stage + (g & 3) * GS + (g >> 2) * crb + roff;
+            SkRecord<QT, NT>::run(recA, recA + 2 * crb, g, t, B, sct, xst, acc);
             keep_before<NT>(acc);
         }
         __syncwarp();
