@@ -44,7 +44,7 @@ FALLBACK_TFLOPS = 1400.0
 # dram__bytes_write.sum per launch; summaries under profiles/).  The decode figure was captured on a
 # 4-layer launch and is proportional to the layers a launch streams, so it is kept as a ratio to
 # the algorithmic bytes; a prefill launch is one whole product whatever the number of copies.
-NCU_DECODE_TRAFFIC_PER_ALGORITHMIC_BYTE = 1.012
+NCU_DECODE_TRAFFIC_PER_ALGORITHMIC_BYTE = 1.014
 NCU_PREFILL_TRAFFIC_BYTES_PER_LAUNCH = 73.9e6
 
 
