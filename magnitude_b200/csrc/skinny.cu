@@ -21,8 +21,9 @@
 //     Q8_0 splits its byte into two nibble planes (128 + low, 2048 + 16 high) sharing the B fragment.
 //     Nothing is rounded except in fp32, so results agree with the fp64 oracle to ~1e-6.
 //   * the 8 warps' partial tiles (different K ranges of the same rows) go through a small ring in
-//     shared memory to a ninth ("reducer") warp, which adds them in warp order and stores the
-//     item's sums; the consumers never meet at a barrier.  When K spans several chunks the sums
+//     shared memory to a "reducer" warp (two in the 16-token form, each taking half the token
+//     pairs), which adds them in warp order and stores the item's sums; the consumers never meet
+//     at a barrier.  When K spans several chunks the sums
 //     of a chunk go to a workspace and a second, small launch adds the chunks in order (bit-
 //     reproducible) and stores Y.
 // Every mbarrier wait is bounded; a wait that runs out raises the status word and a flag that every
@@ -48,7 +49,9 @@ __device__ unsigned long long g_sk_trace[4096];
 namespace {
 
 constexpr int kSkWarps = 8;                       // consumer warps = records per chunk
-constexpr int kSkThreads = (kSkWarps + 2) * 32;   // + the producer warp and the reducer warp
+// + the producer warp and one reducer warp per 8-token tile (a single reducer warp was the slowest
+// role of the 16-token form)
+__host__ __device__ constexpr int sk_threads(int nt) { return (kSkWarps + 1 + nt) * 32; }
 constexpr int kSkRows = 16;                       // weight rows per item (MMA M)
 constexpr int kSkMaxDepth = 12;
 constexpr int kSkMaxCtas = 320;     // two CTAs per SM for the 8-token tile
@@ -610,7 +613,7 @@ __device__ __forceinline__ bool sk_wait(uint32_t bar, uint32_t parity, volatile 
 }
 
 template <int QT, int NT>
-__global__ void __launch_bounds__(kSkThreads, sk_ctas_per_sm(NT)) skinny_kernel(const __grid_constant__ SkParams p) {
+__global__ void __launch_bounds__(sk_threads(NT), sk_ctas_per_sm(NT)) skinny_kernel(const __grid_constant__ SkParams p) {
     using L = SkLayout<QT, NT>;
     constexpr int SBK = L::SBK, GS = L::GS;
     extern __shared__ __align__(128) uint8_t smem[];
@@ -630,7 +633,7 @@ __global__ void __launch_bounds__(kSkThreads, sk_ctas_per_sm(NT)) skinny_kernel(
         }
         for (int i = 0; i < kRedDepth; ++i) {
             mbar_init(rfull0 + 8 * i, kSkWarps);
-            mbar_init(rempty0 + 8 * i, 1);
+            mbar_init(rempty0 + 8 * i, NT);
         }
         head.fail = 0;
         mbar_fence_init();
@@ -687,8 +690,10 @@ __global__ void __launch_bounds__(kSkThreads, sk_ctas_per_sm(NT)) skinny_kernel(
         return;
     }
 
-    // ===== reducer: adds the eight warps' partial tiles of every item and stores the item's sums ====
-    if (warp == kSkWarps + 1) {
+    // ===== reducers: add the eight warps' partial tiles of every item and store the item's sums; =====
+    // ===== reducer r takes the token pairs i = r, r + NT, ... of the tile                        =====
+    if (warp > kSkWarps) {
+        const int r = warp - (kSkWarps + 1);
         int n = 0;
         bool waited = false;
         SkCursor cur;
@@ -711,7 +716,8 @@ __global__ void __launch_bounds__(kSkThreads, sk_ctas_per_sm(NT)) skinny_kernel(
             const int row = lane & 15;                                           // MMA row of the partial tiles
             const int grow = rb * kSkRows + (row & 3) * kRowGroup + (row >> 2);    // = row (row >> 2) of group (row & 3)
 #pragma unroll
-            for (int i = 0; i < 4 * NT; ++i) {
+            for (int ii = 0; ii < 4; ++ii) {
+                const int i = ii * NT + r;
                 const int tok = 2 * i + (lane >> 4);      // element (tok, row): tok * 16 + row = lane + 32 i
                 if (tok >= J.M) continue;
                 const float *rsrc = rbase + tok * kRedStride + row;
@@ -827,18 +833,38 @@ __global__ void __launch_bounds__(kSkThreads, sk_ctas_per_sm(NT)) skinny_kernel(
 __global__ void __launch_bounds__(256) skinny_chunk_sum_kernel(const __grid_constant__ SkParams p) {
     pdl_launch_dependents();
     pdl_wait();
-    for (int ji = 0; ji < p.njobs; ++ji) {
+    // The products share the grid side by side (a share of the blocks each), and a thread reads the
+    // chunk sums of several outputs before it stores the first: taken one after another, every
+    // product and every output would cost a trip to L2.
+    constexpr int U = 4;
+    const int bpj = max(1, (int)gridDim.x / p.njobs);          // blocks per product
+    for (int slot = blockIdx.x; slot < p.njobs * bpj; slot += gridDim.x) {
+        const int ji = slot / bpj, lb = slot - ji * bpj;
         const SkJob &J = p.jobs ? p.jobs[ji] : p.inl[ji];
         if (J.nchunks <= 1) continue;
         const size_t npad = (size_t)J.n_rb * kSkRows;
-        const int total = J.M * J.N;
-        for (int e = blockIdx.x * blockDim.x + threadIdx.x; e < total; e += gridDim.x * blockDim.x) {
-            const int tok = e / J.N, row = e - tok * J.N;
-            float v = 0.f;
-            for (int cc = 0; cc < J.nchunks; ++cc) v += __ldcg(&J.part[((size_t)cc * J.M + tok) * npad + row]);
-            const long long idx = (long long)tok * J.ldy + row;
-            if (J.y_is_bf16) reinterpret_cast<__nv_bfloat16 *>(J.y)[idx] = __float2bfloat16_rn(v);
-            else reinterpret_cast<float *>(J.y)[idx] = v;
+        const int total = J.M * J.N, stride = bpj * blockDim.x;
+        for (int e0 = lb * blockDim.x + threadIdx.x; e0 < total; e0 += U * stride) {
+            float v[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int e = e0 + u * stride;
+                v[u] = 0.f;
+                if (e < total) {
+                    const int tok = e / J.N, row = e - tok * J.N;
+                    for (int cc = 0; cc < J.nchunks; ++cc) v[u] += __ldcg(&J.part[((size_t)cc * J.M + tok) * npad + row]);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int e = e0 + u * stride;
+                if (e < total) {
+                    const int tok = e / J.N, row = e - tok * J.N;
+                    const long long idx = (long long)tok * J.ldy + row;
+                    if (J.y_is_bf16) reinterpret_cast<__nv_bfloat16 *>(J.y)[idx] = __float2bfloat16_rn(v[u]);
+                    else reinterpret_cast<float *>(J.y)[idx] = v[u];
+                }
+            }
         }
     }
 }
@@ -866,7 +892,7 @@ cudaError_t sk_launch_t(const SkParams &p, int grid, size_t smem_limit, cudaStre
     }
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3((unsigned)grid);
-    cfg.blockDim = dim3(kSkThreads);
+    cfg.blockDim = dim3(sk_threads(NT));
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
     cudaLaunchAttribute attr[1];
@@ -993,7 +1019,7 @@ cudaError_t skinny_set_create(const SkinnyProduct *prods, int n, const SkinnyBuf
     set->qt = qt;
     set->NT = NT;
     set->grid = grid;
-    set->sum_grid = sum_elems > 0 ? (int)std::min<long long>((sum_elems + 255) / 256, 2LL * buf.sm_count) : 0;
+    set->sum_grid = sum_elems > 0 ? (int)std::min<long long>((sum_elems + 255) / 256, 8LL * buf.sm_count) : 0;
     set->smem_limit = buf.smem_limit;
     *out = set;
     return cudaSuccess;
