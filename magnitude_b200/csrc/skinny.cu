@@ -833,36 +833,54 @@ __global__ void __launch_bounds__(sk_threads(NT), sk_ctas_per_sm(NT)) skinny_ker
 __global__ void __launch_bounds__(256) skinny_chunk_sum_kernel(const __grid_constant__ SkParams p) {
     pdl_launch_dependents();
     pdl_wait();
-    // The products share the grid side by side (a share of the blocks each), and a thread reads the
-    // chunk sums of several outputs before it stores the first: taken one after another, every
-    // product and every output would cost a trip to L2.
+    if (p.njobs <= kSkInline) {        // a call's few products, one after another: one output per thread and pass
+        for (int ji = 0; ji < p.njobs; ++ji) {
+            const SkJob &J = p.jobs ? p.jobs[ji] : p.inl[ji];
+            if (J.nchunks <= 1) continue;
+            const size_t npad = (size_t)J.n_rb * kSkRows;
+            const int total = J.M * J.N;
+            for (int e = blockIdx.x * blockDim.x + threadIdx.x; e < total; e += gridDim.x * blockDim.x) {
+                const int tok = e / J.N, row = e - tok * J.N;
+                float v = 0.f;
+                for (int cc = 0; cc < J.nchunks; ++cc) v += __ldcg(&J.part[((size_t)cc * J.M + tok) * npad + row]);
+                const long long idx = (long long)tok * J.ldy + row;
+                if (J.y_is_bf16) reinterpret_cast<__nv_bfloat16 *>(J.y)[idx] = __float2bfloat16_rn(v);
+                else reinterpret_cast<float *>(J.y)[idx] = v;
+            }
+        }
+        return;
+    }
+    // A plan's many products share the grid side by side (a share of the blocks each), and a thread
+    // reads the chunk sums of several outputs before it stores the first: taken one after another,
+    // every product and every output would cost a trip to L2.
     constexpr int U = 4;
     const int bpj = max(1, (int)gridDim.x / p.njobs);          // blocks per product
     for (int slot = blockIdx.x; slot < p.njobs * bpj; slot += gridDim.x) {
         const int ji = slot / bpj, lb = slot - ji * bpj;
-        const SkJob &J = p.jobs ? p.jobs[ji] : p.inl[ji];
+        const SkJob &J = p.jobs[ji];
         if (J.nchunks <= 1) continue;
         const size_t npad = (size_t)J.n_rb * kSkRows;
         const int total = J.M * J.N, stride = bpj * blockDim.x;
         for (int e0 = lb * blockDim.x + threadIdx.x; e0 < total; e0 += U * stride) {
             float v[U];
+            long long idx[U];
 #pragma unroll
             for (int u = 0; u < U; ++u) {
                 const int e = e0 + u * stride;
                 v[u] = 0.f;
+                idx[u] = -1;
                 if (e < total) {
                     const int tok = e / J.N, row = e - tok * J.N;
+                    idx[u] = (long long)tok * J.ldy + row;
+#pragma unroll 2
                     for (int cc = 0; cc < J.nchunks; ++cc) v[u] += __ldcg(&J.part[((size_t)cc * J.M + tok) * npad + row]);
                 }
             }
 #pragma unroll
             for (int u = 0; u < U; ++u) {
-                const int e = e0 + u * stride;
-                if (e < total) {
-                    const int tok = e / J.N, row = e - tok * J.N;
-                    const long long idx = (long long)tok * J.ldy + row;
-                    if (J.y_is_bf16) reinterpret_cast<__nv_bfloat16 *>(J.y)[idx] = __float2bfloat16_rn(v[u]);
-                    else reinterpret_cast<float *>(J.y)[idx] = v[u];
+                if (idx[u] >= 0) {
+                    if (J.y_is_bf16) reinterpret_cast<__nv_bfloat16 *>(J.y)[idx[u]] = __float2bfloat16_rn(v[u]);
+                    else reinterpret_cast<float *>(J.y)[idx[u]] = v[u];
                 }
             }
         }
@@ -1019,7 +1037,7 @@ cudaError_t skinny_set_create(const SkinnyProduct *prods, int n, const SkinnyBuf
     set->qt = qt;
     set->NT = NT;
     set->grid = grid;
-    set->sum_grid = sum_elems > 0 ? (int)std::min<long long>((sum_elems + 255) / 256, 8LL * buf.sm_count) : 0;
+    set->sum_grid = sum_elems > 0 ? (int)std::min<long long>((sum_elems + 255) / 256, (n <= kSkInline ? 2LL : 8LL) * buf.sm_count) : 0;
     set->smem_limit = buf.smem_limit;
     *out = set;
     return cudaSuccess;
