@@ -940,7 +940,7 @@ def run_skinny(args, emit=True):
     line = {
         "metric": "skinny_gemm_weight_bandwidth", "value": value, "unit": UNIT, "n_gpus": 1, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": tot_s * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-        "dtype": "M <= 4: u8 x s16 dp4a; M >= 5: exact integer weights x bf16 in mma.sync, fp32 accumulate", "data": "synthetic",
+        "dtype": "M <= 2: u8 x s16 dp4a; M >= 3: exact integer weights x bf16 in mma.sync, fp32 accumulate", "data": "synthetic",
         "config": {"workload": "configs[2]: skinny verify batches, Q4_K 6144x4096 and Q6_K 4096x14336, M in {2,4,8,16}, bf16 tokens, fp32 out",
                    "l2": f"{copies} distinct weight copies per case", "parallelism": "single"},
         "roofline": {"bound": "hbm", "achieved": value, "peak": peak, "unit": UNIT, "frac": value / peak, "peak_source": f"of {src}",

@@ -296,10 +296,13 @@ b200q_status b200q_matmul_prefill_noalloc(b200q_ctx *ctx, const b200q_weight *w,
 
 /* -- decode plans ------------------------------------------------------------------------------ */
 
-/* A plan is a fixed list of projections (M <= 4 activation rows, the same M for all) that one
- * launch executes back to back on persistent CTAs: the weights of projection i+1 stream from HBM
- * while projection i is still being reduced and stored, so a decode step is not broken up by
- * launch gaps.  It plays the role of the per-token graph that context.decode(batch) runs for a
+/* A plan is a fixed list of projections (1..16 activation rows, the same M for all) prepared once
+ * and run many times.  With 1..2 rows (the route edge B200Q_OPT_SKINNY_MIN_M moves it up to 4 rows;
+ * plans with rank sums, SWIGLU, ACCUMULATE or fused-norm jobs always, and with at most 4 rows) one
+ * launch executes the jobs back to back on persistent CTAs: the weights of projection i+1 stream
+ * from HBM while projection i is still being reduced and stored, so a decode step is not broken up
+ * by launch gaps.  With more rows (a verify batch) consecutive jobs of one block type run as
+ * skinny-kernel launches of up to 32 products each.  It plays the role of the per-token graph that context.decode(batch) runs for a
  * batch of 1..4 tokens (inference/crates/icn-engine/src/lib.rs:2264).  Pointers are captured at
  * creation: run the plan again after rewriting the activation buffers in place. */
 typedef struct b200q_plan b200q_plan;

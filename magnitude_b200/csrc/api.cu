@@ -119,7 +119,7 @@ struct b200q_plan {
     uint8_t *xq_dev = nullptr;        // fixed-point activation images of the jobs (filled by the prep launch of every run)
     bool has_xq = false;
     int M = 0;
-    // plans of 5..16 rows: groups of products run by the skinny kernel, one launch pair per group
+    // plans on the skinny route (3..16 rows by default): groups of products run by the skinny kernel, one launch pair per group
     std::vector<SkinnySet *> sets;
     uint8_t *sk_ws = nullptr;
     uint8_t *sk_jobs = nullptr;
@@ -470,7 +470,7 @@ b200q_status ensure_host_path(b200q_ctx *ctx, size_t xb, size_t yb) {
     return B200Q_OK;
 }
 
-// A plan of 5..16 activation rows: consecutive products of one block type form a group that one
+// A plan on the skinny route (3..16 activation rows by default): consecutive products of one block type form a group that one
 // skinny launch runs (a job that reads what earlier jobs wrote starts a new group, so stream order
 // provides the dependency); the plan owns the groups' images, chunk sums, counters and job tables.
 b200q_status plan_create_skinny(b200q_ctx *ctx, b200q_plan *pl, const b200q_job *jobs, int n_jobs, int M) {
