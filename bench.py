@@ -14,7 +14,7 @@ For N > 1 launch under torchrun; weights are split tensor-parallel (gate/up by r
 superblocks with the rank sums taken inside the launch).  Rank 0 prints one JSON line.  Beside the
 headline figure the N = 1 line carries: the host check of the step's results, the step with its real
 dependencies (plain and as chained fused MLP blocks), a seconds-long replay, the prefill (TFLOP/s),
-skinny-batch and per-type calibration figures, a library arm (the vllm package's GGUF kernels) and the
+skinny-batch (one product per call, and as plans) and per-type calibration figures, a library arm (the vllm package's GGUF kernels) and the
 CPU baseline.  --workload prefill | skinny | calibration | layer32b | library print those lines alone.
 """
 from __future__ import annotations
@@ -694,6 +694,12 @@ def run_b200(args):
                 line["secondary"][name] = fn(sec_args, emit=False)
             except Exception as exc:  # pragma: no cover
                 line["secondary"][name] = {"unavailable": f"{type(exc).__name__}: {exc}"}
+        try:      # the same verify batches as the engine would issue them inside a step: one plan per case
+            plan_args = argparse.Namespace(**vars(sec_args))
+            plan_args.skinny_plan = True
+            line["secondary"]["skinny_plan"] = run_skinny(plan_args, emit=False)
+        except Exception as exc:  # pragma: no cover
+            line["secondary"]["skinny_plan"] = {"unavailable": f"{type(exc).__name__}: {exc}"}
         cal = line["secondary"].get("calibration")
         if isinstance(cal, dict) and "rows" in cal:
             line["calibration"] = cal["rows"]
@@ -942,7 +948,8 @@ def run_skinny(args, emit=True):
         "warmup": max(args.warmup, 3), "ms_per_step": tot_s * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "M <= 2: u8 x s16 dp4a; M >= 3: exact integer weights x bf16 in mma.sync, fp32 accumulate", "data": "synthetic",
         "config": {"workload": "configs[2]: skinny verify batches, Q4_K 6144x4096 and Q6_K 4096x14336, M in {2,4,8,16}, bf16 tokens, fp32 out",
-                   "l2": f"{copies} distinct weight copies per case", "parallelism": "single"},
+                   "l2": f"{copies} distinct weight copies per case", "parallelism": "single",
+                   "form": "the 16 products of a case as one decode plan" if args.skinny_plan else "one product per call"},
         "roofline": {"bound": "hbm", "achieved": value, "peak": peak, "unit": UNIT, "frac": value / peak, "peak_source": f"of {src}",
                      "traffic": None, "note": "algorithmic bytes of all eight cases / their device time"},
         "cases": cases, "cpu_baseline": None, "e2e": None, "gpu_launches": None, "clocks": clocks.summary(),

@@ -132,6 +132,31 @@ def test_skinny_repeated_calls_are_bit_identical(backend, orc):
     backend.sync()
 
 
+@pytest.mark.parametrize("qt", [mb.TYPE_Q4_K, mb.TYPE_Q6_K])
+@pytest.mark.parametrize("m", [3, 8, 16])
+def test_skinny_plan_of_many_products(backend, orc, qt, m):
+    # more products than travel in the kernel parameters: the job table lives in device memory and the
+    # chunk-sum launch shares its grid among the products.  One, two, three and seven chunks (a
+    # one-chunk product needs no chunk sum and is skipped there), rows that fill no 16-row block, a bf16 output.
+    shapes = [(301, 4096), (64, 2048), (19, 6144), (130, 2304), (40, 14336), (257, 4096), (16, 512)]
+    x = {k: _acts(m, k, seed=k + m) for k in {k for _, k in shapes}}
+    packed, ws, ys = [], [], []
+    for i, (n, k) in enumerate(shapes):
+        packed.append(_weights(orc, qt, n, k, seed=100 + i))
+        ws.append(backend.upload(qt, packed[-1], n, k))
+        ys.append(torch.full((m, n), 7.0, dtype=torch.bfloat16 if i == 2 else torch.float32, device="cuda"))
+    plan = backend.plan([([w], x[k], [y]) for w, (n, k), y in zip(ws, shapes, ys)])
+    for _ in range(2):
+        plan.run()
+        backend.sync()
+        assert backend.last_route()[0] == mb.ROUTE_SKINNY
+        for i, (n, k) in enumerate(shapes):
+            ref = orc.matmul_exact(qt, packed[i], n, k, x[k].float().cpu().numpy())
+            ok, worst = orc.within_tolerance(ys[i].float().cpu().numpy(), ref, REL_BF16 if i == 2 else REL_DECODE)
+            assert ok, f"product {i} ({n}x{k}): worst error {worst:.3f} x tolerance"
+            assert torch.equal(ys[i], backend.project(ws[i], x[k], out_dtype=ys[i].dtype)), f"product {i}: plan and single call differ"
+
+
 @pytest.mark.parametrize("m", [5, 16])
 def test_skinny_plan_with_dependent_job(backend, orc, m):
     # gate/up share x; down reads what they wrote (a new launch, so stream order is the dependency)
