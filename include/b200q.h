@@ -121,6 +121,8 @@ int64_t b200q_tensor_storage_bytes_shape(int32_t type, int32_t n_dims, const int
 /* One context per GPU / executor thread.  Replaces LlamaBackend::init + model.new_context
  * (icn-engine/src/lib.rs:141, 990) for this path. */
 b200q_status b200q_ctx_create(int32_t device, b200q_ctx **out);
+/* Weights and plans of the context are not destroyed with it and may be destroyed after it (they
+ * keep what they need for that); every other call on them needs the context alive. */
 void b200q_ctx_destroy(b200q_ctx *ctx);
 
 /* Changes a per-context setting (B200Q_OPT_*); B200Q_ERR_INVALID_CONFIG for an unknown option or a

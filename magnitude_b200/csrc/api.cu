@@ -114,6 +114,7 @@ struct b200q_ctx {
 
 struct b200q_plan {
     b200q_ctx *ctx = nullptr;
+    int device = 0;                   // the context's device, kept here: the plan may outlive the context
     std::vector<StreamJob> jobs;
     StreamJob *jobs_dev = nullptr;
     uint8_t *xq_dev = nullptr;        // fixed-point activation images of the jobs (filled by the prep launch of every run)
@@ -127,6 +128,7 @@ struct b200q_plan {
 
 struct b200q_weight {
     b200q_ctx *ctx = nullptr;
+    int device = 0;                   // the context's device, kept here: the weight may outlive the context
     int type = 0;
     int64_t N = 0, K = 0, Kpad = 0;
     int64_t row_bytes = 0;
@@ -174,6 +176,7 @@ b200q_status make_weight(b200q_ctx *ctx, int type, int64_t N, int64_t Kfull, con
     b200q_weight *w = new (std::nothrow) b200q_weight();
     if (!w) return fail(ctx, B200Q_ERR_OVERLOADED, "out of host memory");
     w->ctx = ctx;
+    w->device = ctx->device;
     w->type = type;
     w->N = n;
     w->K = k;
@@ -217,6 +220,9 @@ b200q_status check_ctx(b200q_ctx *ctx) {
     if (ctx->poisoned) return fail(ctx, B200Q_ERR_STOPPED, "context stopped after a device error");
     cudaError_t e = cudaSetDevice(ctx->device);
     if (e != cudaSuccess) return cuda_fail(ctx, e, "cudaSetDevice");
+    // a launch is checked with cudaGetLastError(): an error some earlier, unrelated runtime call of the
+    // process left behind (they are not sticky) must not be taken for this call's
+    (void)cudaGetLastError();
     return B200Q_OK;
 }
 
@@ -818,7 +824,7 @@ b200q_status b200q_weight_info(const b200q_weight *w, int32_t *type, int64_t *N,
 void b200q_weight_destroy(b200q_weight *w) {
     if (!w) return;
     if (w->dev) {
-        if (w->ctx) cudaSetDevice(w->ctx->device);
+        cudaSetDevice(w->device);     // not through w->ctx: the context may be gone already
         cudaFree(w->dev);
     }
     delete w;
@@ -956,6 +962,7 @@ b200q_status b200q_plan_create(b200q_ctx *ctx, const b200q_job *jobs, int32_t n_
     b200q_plan *pl = new (std::nothrow) b200q_plan();
     if (!pl) return fail(ctx, B200Q_ERR_OVERLOADED, "out of host memory");
     pl->ctx = ctx;
+    pl->device = ctx->device;
     pl->M = (int)M;
     bool rank_sums = false;      // ... or another epilogue only the streaming kernel has
     for (int i = 0; i < n_jobs; ++i)
@@ -1093,7 +1100,7 @@ b200q_status b200q_plan_run(b200q_ctx *ctx, b200q_plan *plan, void *stream) {
 
 void b200q_plan_destroy(b200q_plan *plan) {
     if (!plan) return;
-    if (plan->ctx) cudaSetDevice(plan->ctx->device);
+    cudaSetDevice(plan->device);      // not through plan->ctx: the context may be gone already
     if (plan->jobs_dev) cudaFree(plan->jobs_dev);
     if (plan->xq_dev) cudaFree(plan->xq_dev);
     for (SkinnySet *set : plan->sets) skinny_set_destroy(set);

@@ -8,6 +8,7 @@ PyTorch is used only to hold device memory and streams; every product runs in li
 from __future__ import annotations
 
 import ctypes
+import weakref
 from ctypes import byref, c_int32, c_int64, c_size_t, c_void_p
 from typing import Sequence
 
@@ -46,6 +47,7 @@ class ProjectionWeight:
     def __init__(self, backend: "Backend", handle: int):
         self.backend = backend
         self._h = c_void_p(handle)
+        backend._children.add(self)
         t, n, k, gb, db = c_int32(), c_int64(), c_int64(), c_size_t(), c_size_t()
         backend._check(B.lib().b200q_weight_info(self._h, byref(t), byref(n), byref(k), byref(gb), byref(db)))
         self.qtype, self.n, self.k = t.value, n.value, k.value
@@ -79,6 +81,7 @@ class Plan:
         self.backend = backend
         self._h = c_void_p(handle)
         self._keep = keep
+        backend._children.add(self)
 
     def run(self, stream=None) -> None:
         self.backend._check(B.lib().b200q_plan_run(self.backend._h, self._h, self.backend._stream_ptr(stream)))
@@ -105,6 +108,7 @@ class Backend:
             raise B.B200QError(st, f"cannot create a context on CUDA device {device} (no CPU fallback exists)")
         self._h = h
         self.device = device
+        self._children = weakref.WeakSet()      # live weights and plans: closed before the context
 
     # -- errors ------------------------------------------------------------------------------
     def last_error(self) -> str:
@@ -118,6 +122,8 @@ class Backend:
 
     def close(self) -> None:
         if self._h:
+            for child in list(self._children):      # weights and plans go first, whatever order the caller drops them in
+                child.close()
             B.lib().b200q_ctx_destroy(self._h)
             self._h = c_void_p()
 

@@ -324,3 +324,41 @@ def test_plan_argument_checks(backend, orc):
     w6 = backend.upload(mb.TYPE_Q6_K, _weights(orc, mb.TYPE_Q6_K, 8, k, 1), 8, k)
     with pytest.raises(mb.B200QError):
         backend.plan([([w, w6], x, [y, y.clone()])])   # mixed types inside one job
+
+
+def test_weights_and_plans_may_outlive_their_context(orc):
+    # A caller may drop the context first.  Destroying a weight or a plan afterwards must not read the
+    # freed context (it used to take the device number from it, and the failed cudaSetDevice it then made
+    # was reported by the next launch of another context as its own error).
+    import ctypes
+
+    from magnitude_b200 import _binding as B
+
+    n, k = 64, 1024
+    rng = np.random.default_rng(5)
+    packed = orc.quantize(mb.TYPE_Q4_K, rng.standard_normal((n, k), dtype=np.float32) * np.float32(0.02))
+    x = torch.from_numpy(rng.standard_normal((2, k), dtype=np.float32)).cuda().to(torch.bfloat16)
+    ref = orc.matmul_exact(mb.TYPE_Q4_K, packed, n, k, x.float().cpu().numpy())
+
+    def run_plan(be):
+        w = be.upload(mb.TYPE_Q4_K, packed, n, k)
+        y = torch.zeros((2, n), device="cuda")
+        plan = be.plan([([w], x, [y])])
+        plan.run()
+        be.sync()
+        assert orc.within_tolerance(y.cpu().numpy(), ref, REL_DECODE)[0]
+        return w, plan
+
+    be = mb.Backend(0)
+    w, plan = run_plan(be)
+    hw, hp, hc = w._h, plan._h, be._h
+    w._h, plan._h, be._h = ctypes.c_void_p(), ctypes.c_void_p(), ctypes.c_void_p()     # the wrappers let go: raw C order below
+    B.lib().b200q_ctx_destroy(hc)
+    junk = [np.full(4096, 0x7F, np.uint8) for _ in range(64)]      # reuse the freed host block with a bad device number
+    B.lib().b200q_plan_destroy(hp)
+    B.lib().b200q_weight_destroy(hw)
+    del junk
+    be2 = mb.Backend(0)
+    w2, plan2 = run_plan(be2)                                      # its activation prep launch checks the last error
+    be2.close()                                                    # closes w2 and plan2 first
+    assert not w2._h and not plan2._h
