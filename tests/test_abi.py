@@ -29,6 +29,13 @@ def test_header_and_library_agree():
     assert sorted(B.SIGNATURES) == names, "the ctypes table and the header list different entry points"
 
 
+def test_integration_notes_bind_every_entry_point():
+    # the reference-side binding shown to a maintainer (the Rust extern block) lists exactly the header's functions
+    notes = (ROOT / "INTEGRATION.md").read_text()
+    bound = sorted(set(re.findall(r"pub fn (b200q_[a-z0-9_]+)\s*\(", notes)))
+    assert bound == declared_symbols()
+
+
 def test_version_and_storage_bytes():
     assert re.fullmatch(r"\d+\.\d+\.\d+", mb.__version__)
     assert mb.tensor_storage_bytes(mb.TYPE_Q8_0, 4096 * 4096) == 17825792
